@@ -1,0 +1,111 @@
+"""The numpy oracle against fixtures produced by the reference's own code
+(tests/golden/make_golden.py).  CPU only."""
+import numpy as np
+import pytest
+
+from conftest import load_golden
+from oracle import sacq_oracle as O
+
+
+def test_bit_packing_known_answers():
+    kat = load_golden("pack_kat")
+    for bits in (1, 2, 3, 5, 7, 8, 9, 11, 12, 16):
+        idx = kat[f"idx_{bits}"]
+        want = kat[f"packed_{bits}"]
+        got = O.pack_indices(idx, bits)
+        assert got.dtype == np.uint8 and np.array_equal(got, want)
+        assert np.array_equal(O.unpack_indices(want, bits, idx.size), idx)
+
+
+def test_bit_packing_against_big_integer():
+    # the reference's own check (tests/test_core.py:142-151): an independent
+    # arbitrary-precision unpacker, including widths whose fields cross bytes
+    rng = np.random.default_rng(5)
+    for bits in (1, 2, 3, 7, 8, 9, 11, 16):
+        idx = rng.integers(0, 1 << bits, size=79)
+        payload = bytes(O.pack_indices(idx, bits).tolist())
+        integer = int.from_bytes(payload, "little")
+        recovered = [(integer >> (j * bits)) & ((1 << bits) - 1) for j in range(idx.size)]
+        assert recovered == idx.tolist()
+        assert len(payload) == (idx.size * bits + 7) // 8
+
+
+def test_pack_rejects_bad_arguments():
+    with pytest.raises(ValueError):
+        O.pack_indices(np.array([0, 1]), 0)
+    with pytest.raises(ValueError):
+        O.pack_indices(np.array([0, 1]), 57)
+    with pytest.raises(ValueError):
+        O.pack_indices(np.array([0, 8]), 3)
+
+
+def test_window_bytes():
+    assert [O.index_window_bytes(b) for b in (1, 8, 11, 12, 16)] == [1, 1, 3, 2, 2]
+    assert [O.index_bits_for(c) for c in (1, 2, 32, 256, 257, 4096, 65536)] == [1, 1, 5, 8, 9, 12, 16]
+
+
+def test_reconstruction_bit_exact(golden_layer):
+    g = golden_layer
+    shift = int(g["shift"][0])
+    w = O.dequantize_bf16_bits(g["codebook"], g["indices"], g["scales"], shift,
+                               int(g["N"]), int(g["K"]), int(g["G"]))
+    assert np.array_equal(w, g["w_ref"])
+    w2 = O.dequantize_packed_bf16_bits(g["packed"], int(g["index_bits"]), g["codebook"], g["scales"], shift,
+                                       int(g["N"]), int(g["K"]), int(g["G"]))
+    assert np.array_equal(w2, g["w_ref"])
+    assert np.array_equal(O.pack_indices(g["indices"], int(g["index_bits"])), g["packed"])
+
+
+def test_tiny_hand_written_payload():
+    # tests/test_cache.py:10-14 of the reference
+    want = load_golden("tiny_cache_payload")["w_ref"]
+    cb = O.f32_to_bf16_bits(np.array([[1., 2.], [3., 4.]], dtype=np.float32))
+    sc = O.f32_to_bf16_bits(np.ones((2, 1), dtype=np.float32))
+    got = O.dequantize_bf16_bits(cb, np.array([[[0, 1]], [[1, 0]]]), sc, 0, 2, 4, 4)
+    assert np.array_equal(got, want)
+    assert O.bf16_bits_to_f32(got).tolist() == [[1, 2, 3, 4], [3, 4, 1, 2]]
+
+
+def test_activation_quantizer_bit_exact(golden_layer):
+    g = golden_layer
+    q, s = O.quantize_rows_e4m3(g["x"])
+    assert np.array_equal(q, g["q"])
+    assert np.array_equal(s.view(np.uint32), g["act_scale"].view(np.uint32))
+
+
+def test_weight_row_quantizer_bit_exact(golden_layer):
+    g = golden_layer
+    wq, sw = O.quantize_weight_rows_e4m3(g["w_ref"])
+    assert np.array_equal(wq, g["wq"])
+    assert np.array_equal(sw.view(np.uint32), g["w_scale"].view(np.uint32))
+
+
+def test_linear_reference(golden_layer):
+    g = golden_layer
+    y = O.linear_a8_reference(g["q"], g["act_scale"], g["w_ref"], g.get("bias"))
+    # same composition evaluated by torch in fp32 when the fixture was made
+    assert O.rel_frobenius(y, g["y_ref"]) < 1e-5
+    # and the stock dense bf16 forward of the reference module stays close to it
+    # (activation quantization is the only difference)
+    dense = O.bf16_bits_to_f32(g["y_dense"])
+    assert O.rel_frobenius(y, dense) < 0.08
+
+
+def test_scalar_formats():
+    f = load_golden("formats")
+    allbf = O.bf16_bits_to_f32(np.arange(65536, dtype=np.uint16))
+    finite = ~np.isnan(allbf)
+    got = O.f32_to_e4m3_bits(np.clip(allbf, -448.0, 448.0))
+    assert np.array_equal(got[finite], f["e4m3_of_all_bf16"][finite])
+    # decode table round trip
+    vals = O.e4m3_bits_to_f32(np.arange(256, dtype=np.uint8))
+    ok = ~np.isnan(vals)
+    assert np.array_equal(O.f32_to_e4m3_bits(vals[ok]), np.arange(256, dtype=np.uint8)[ok])
+    q6, s6 = O.quantize_rows_e4m3(f["x6"])
+    assert np.array_equal(q6, f["q6"]) and np.array_equal(s6.view(np.uint32), f["s6"].view(np.uint32))
+    assert float(s6[1, 0]) == 1.0                     # all-zero row keeps scale 1
+    # bf16 multiply and add roundings
+    prod = O.f32_to_bf16_bits(O.bf16_bits_to_f32(f["mul_a"]) * O.bf16_bits_to_f32(f["mul_b"]))
+    assert np.array_equal(prod, f["mul_out"])
+    summed = O.f32_to_bf16_bits(O.bf16_bits_to_f32(prod) + O.bf16_bits_to_f32(f["add_c"])[0])
+    assert np.array_equal(summed, f["add_out"])
