@@ -1,0 +1,345 @@
+"""Benchmark of the W1.5A8 quantized-linear path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (`config.workload = "decode_sweep"`): the decode-shape sweep of Qwen3-1.7B-shaped
+decoder linears at W1.5A8 (dim-8 vectors, 4096-entry codebook, per-channel scales): shapes
+K x N = 2048x2048 (q), 2048x1024 (kv), 2048x2048 (o), 2048x6144 (gate/up), 6144x2048 (down),
+each at M in {1,2,4,8,16,32,64}.  One STEP = one pass over all 35 (shape, M) layer calls,
+every call on its own layer instance; consecutive steps rotate through enough replica sets
+that the touched weights exceed the 126 MB L2 before anything repeats.  Weights are
+N(0, 0.02) fitted with a seeded k-means, activations N(0,1) with 1 % outlier channels x20.
+
+Reported: metric = microseconds per layer call (whole job: elapsed / (35 * ranks * steps)),
+`value` with inputs resident in HBM (CUDA-graph replay of quantizer + GEMM kernels),
+`e2e` through the module's forward with host buffers (pinned H2D of the activations and
+D2H of the result inside the timed region), `roofline` for the dominant kernel (small-M
+GEMM; algorithmic bytes / its mean launch time measured with CUDA events on a graph that
+holds only that kernel), and `cpu_baseline` = the reference's CPU path (PyTorch ops, all
+host threads) on the same sweep.
+
+`--impl reference` times that CPU path alone (rank 0 only under torchrun).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from sacq_b200.synthetic import DECODE_MS, DECODE_SHAPES, algorithmic_bytes, make_activations, make_payload  # noqa: E402
+
+METRIC = "w1p5a8_codebook_gemm_us_per_layer"
+UNIT = "us/layer"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def sweep_calls():
+    return [(name, K, N, M) for (name, K, N) in DECODE_SHAPES for M in DECODE_MS]
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+
+def cpu_sweep_payloads():
+    """One payload per shape on the CPU (random indices: the CPU path's cost does not depend
+    on which codewords are hit, and fitting 6144-wide layers on the host would dominate)."""
+    out = {}
+    for i, (name, K, N) in enumerate(DECODE_SHAPES):
+        out[name] = make_payload(N, K, seed=i, fit=False)
+    return out
+
+
+def run_cpu_reference(steps: int, warmup: int):
+    from oracle import torch_port
+    payloads = cpu_sweep_payloads()
+    xs = {(name, M): make_activations(M, K, seed=M) for (name, K, N, M) in sweep_calls()}
+    threads = torch.get_num_threads()
+
+    def step():
+        for name, K, N, M in sweep_calls():
+            torch_port.forward(payloads[name], xs[(name, M)])
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    calls = len(sweep_calls())
+    return dt / steps, (dt / steps) / calls * 1e6, threads
+
+
+def reference_main(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = min(args.steps, 20)
+    warmup = min(args.warmup, 3)
+    sec_per_step, us_per_layer, threads = run_cpu_reference(steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": us_per_layer, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus, l2="n/a (CPU)"),
+        "cpu_baseline": {"value": us_per_layer, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"full 35-call sweep per step, {steps} steps, PyTorch CPU ops as the reference "
+                                   "runs them (unpack, bf16 gather/mul/add, fp32 matmul)"},
+        "e2e": {"value": us_per_layer, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "tokens_per_s": sum(M for *_, M in sweep_calls()) / sec_per_step,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus, l2):
+    return {"workload": "decode_sweep", "shapes_KxN": [f"{K}x{N}" for _, K, N in DECODE_SHAPES],
+            "M": list(DECODE_MS), "vector_dim": 8, "codebook_size": 4096, "index_bits": 12,
+            "scales": "per-output-channel bf16", "activations": "fp8 e4m3 per-token",
+            "calls_per_step": len(sweep_calls()), "parallelism": f"dp{n_gpus} (independent layer calls per rank)",
+            "l2": l2}
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def gpu_main(args):
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    calls = sweep_calls()
+
+    # ---- layers: one fitted payload per shape, one device instance per (call, replica set)
+    per_set_bytes = sum(N * (K // 8) * 12 // 8 + 4096 * 16 + N * 2 for _, K, N, _ in calls)
+    n_sets = max(2, -(-int(2.2 * L2_BYTES) // per_set_bytes))
+    payloads = {name: make_payload(N, K, seed=i, device=dev, iters=1) for i, (name, K, N) in enumerate(DECODE_SHAPES)}
+    sets = []
+    for _ in range(n_sets):
+        sets.append([PrecomputedPackedVectorCodebookLinear(payloads[name], None, str(dev)) for name, K, N, M in calls])
+    x_host = [make_activations(M, K, seed=M).pin_memory() for name, K, N, M in calls]
+    x_dev = [x.to(dev) for x in x_host]
+    y_dev = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for name, K, N, M in calls]
+    y_host = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for name, K, N, M in calls]
+    q_dev = [torch.empty(M, K, dtype=torch.uint8, device=dev) for name, K, N, M in calls]
+    s_dev = [torch.empty(M, dtype=torch.float32, device=dev) for name, K, N, M in calls]
+    ws_bytes = max(int(lib.sacq_workspace_bytes(m._handle, M)) for m, (_, _, _, M) in zip(sets[0], calls))
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+
+    def enqueue_full(layer_set, s):
+        for i, (mod, (name, K, N, M)) in enumerate(zip(layer_set, calls)):
+            _lib.check(lib.sacq_linear_bf16(mod._handle, x_dev[i].data_ptr(), K, M, q_dev[i].data_ptr(),
+                                            s_dev[i].data_ptr(), y_dev[i].data_ptr(), N, ws.data_ptr(), ws.numel(),
+                                            s.cuda_stream))
+
+    def enqueue_gemm_only(layer_set, s):
+        for i, (mod, (name, K, N, M)) in enumerate(zip(layer_set, calls)):
+            _lib.check(lib.sacq_linear_a8(mod._handle, q_dev[i].data_ptr(), s_dev[i].data_ptr(), M,
+                                          y_dev[i].data_ptr(), N, ws.data_ptr(), ws.numel(), s.cuda_stream))
+
+    def capture(fn):
+        graphs, launches = [], 0
+        for layer_set in sets:
+            g = torch.cuda.CUDAGraph()
+            before = lib.sacq_launch_count()
+            with torch.cuda.graph(g, stream=stream):
+                fn(layer_set, torch.cuda.current_stream())
+            launches = lib.sacq_launch_count() - before
+            graphs.append(g)
+        return graphs, launches
+
+    with torch.cuda.stream(stream):
+        enqueue_full(sets[0], stream)          # eager warm-up: module loading, attribute setting
+    stream.synchronize()
+    full_graphs, full_launches = capture(enqueue_full)
+    gemm_graphs, gemm_launches = capture(enqueue_gemm_only)
+
+    def timed_replay(graphs, steps, warmup):
+        with torch.cuda.stream(stream):
+            for i in range(warmup):
+                graphs[i % len(graphs)].replay()
+            stream.synchronize()
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(steps):
+                graphs[(warmup + i) % len(graphs)].replay()
+            e1.record(stream)
+            stream.synchronize()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        return e0.elapsed_time(e1) / 1e3
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    sec = timed_replay(full_graphs, args.steps, args.warmup)
+    sec_gemm = timed_replay(gemm_graphs, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the module's forward with host buffers
+    def e2e_step(layer_set):
+        outs = []
+        for i, mod in enumerate(layer_set):
+            x_dev[i].copy_(x_host[i], non_blocking=True)
+            outs.append(mod(x_dev[i]))
+        for i, y in enumerate(outs):
+            y_host[i].copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(max(3, args.warmup)):
+        e2e_step(sets[i % n_sets])
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(sets[i % n_sets])
+    torch.cuda.synchronize()
+    sec_e2e = time.perf_counter() - t0
+
+    if dist is not None:
+        t = torch.tensor([sec, sec_gemm, sec_e2e], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec, sec_gemm, sec_e2e = (float(v) for v in t.cpu())
+
+    if rank == 0:
+        n_calls = len(calls)
+        us_layer = sec / args.steps / (n_calls * world) * 1e6
+        us_layer_e2e = sec_e2e / args.steps / (n_calls * world) * 1e6
+        gemm_launch_s = sec_gemm / (args.steps * gemm_launches)
+        alg = sum(algorithmic_bytes(N, K, M) for _, K, N, M in calls) / n_calls
+        peak, peak_kind = load_peaks()
+        achieved = alg / gemm_launch_s / 1e9
+        tokens = sum(M for *_, M in calls)
+        line = {
+            "metric": METRIC, "value": us_layer, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x (fp16 codewords | fp8 hi+lo), fp32 accumulate",
+            "data": "synthetic",
+            "config": workload_config(world, l2=f"{n_sets} replica sets x {per_set_bytes / 1e6:.1f} MB of distinct "
+                                                "layer instances rotate, > 2x the 126 MB L2"),
+            "tokens_per_s": tokens * world / (sec / args.steps),
+            "e2e": {"value": us_layer_e2e, "unit": UNIT,
+                    "h2d_bytes_per_step": sum(M * K * 2 for _, K, N, M in calls),
+                    "d2h_bytes_per_step": sum(M * N * 2 for _, K, N, M in calls),
+                    "ms_per_step": sec_e2e / args.steps * 1e3},
+            "gpu_launches": int(full_launches * args.steps),
+            "roofline": {"bound": "hbm", "kernel": "small_m_kernel (packed-index GEMM, M<=64)",
+                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "algorithmic_bytes_per_launch": alg, "us_per_launch": gemm_launch_s * 1e6,
+                         "launches_timed": int(gemm_launches * args.steps)},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cpu_steps = 3
+            sec_per_step, us_cpu, threads = run_cpu_reference(cpu_steps, 1)
+            line["cpu_baseline"] = {
+                "value": us_cpu, "unit": UNIT, "cores": threads, "kind": "port",
+                "sample": f"the same 35-call sweep, {cpu_steps} passes after 1 warm-up, PyTorch CPU ops as the "
+                          "reference runs them (random-index layers of the same shapes)"}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        reference_main(args)
+    else:
+        gpu_main(args)
+
+
+if __name__ == "__main__":
+    main()

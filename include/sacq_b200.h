@@ -1,0 +1,154 @@
+/*
+ * sacq_b200 -- C ABI of the B200 (sm_100a) implementation of SACQ's packed
+ * vector-codebook quantized-linear forward ("W1.5A8" path).
+ *
+ * Plain C, no torch types: device pointers are `void*`, the CUDA stream is a
+ * `void*` holding a cudaStream_t, sizes are int64_t.  Every function returns
+ * an int status (0 = ok, negative = error, see SACQ_ERR_*) and never aborts
+ * or traps; `sacq_last_error()` returns a thread-local message for the last
+ * failure.  All launches go to the stream the caller passes and do not
+ * synchronise, allocate or free device memory (layer creation and destruction
+ * excepted), so a forward can sit inside a larger stream-ordered program.
+ *
+ * File/line citations name the interface of the reference (haesunglee116/SACQ)
+ * that each entry point stands in for.  `SHIM` abbreviates
+ * gr00t_libero/sources/libero_pro_eval/Isaac-GR00T-N1.7/gr00t/eval/cosmos_quant_shim.py,
+ * `REC` abbreviates gr00t_libero/acceleration/sources/libero_pro_eval/
+ * inference_acceleration_2026_10_11/a8_accuracy_recovery_2026_10_20_r1.
+ */
+#ifndef SACQ_B200_H_
+#define SACQ_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SACQ_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define SACQ_API __attribute__((visibility("default")))
+#else
+#define SACQ_API
+#endif
+
+#define SACQ_OK 0
+#define SACQ_ERR_INVALID_ARGUMENT (-1) /* null pointer, negative size, inconsistent geometry      */
+#define SACQ_ERR_UNSUPPORTED (-2)      /* geometry outside what the kernels implement              */
+#define SACQ_ERR_ALIGNMENT (-3)        /* a pointer or pitch misses its stated alignment           */
+#define SACQ_ERR_WORKSPACE (-4)        /* workspace missing or smaller than sacq_workspace_bytes() */
+#define SACQ_ERR_CUDA (-5)             /* a CUDA runtime/driver call failed (message has detail)   */
+#define SACQ_ERR_DEVICE_TIMEOUT (-6)   /* a bounded device-side wait expired (see sacq_layer_status) */
+
+/* Guard bytes that must be readable after the packed stream.  The reference
+ * keeps `index_window_bytes - 1` zero bytes (SHIM:348-360); the kernels here read
+ * aligned 32-bit and 128-bit words, so they ask for a little more. */
+#define SACQ_PACKED_GUARD_BYTES 16
+
+typedef struct sacq_layer sacq_layer_t; /* opaque; owns only small derived tables */
+
+/* One `packed_vector_codebook_v1` layer as produced by
+ * sacq/vector_quantization.py:369-382 and bit-packed by
+ * sacq/calibration_layers.py:44-74.  Every pointer is DEVICE memory that the
+ * caller keeps alive until sacq_layer_destroy(); the library borrows it. */
+typedef struct sacq_layer_desc {
+  uint32_t struct_size;     /* sizeof(sacq_layer_desc), for ABI checking                         */
+  int32_t device;           /* CUDA device ordinal that owns every pointer below                 */
+  int64_t out_features;     /* N                                                                 */
+  int64_t in_features;      /* K                                                                 */
+  int32_t group_size;       /* G, scales are [N, K/G]                                            */
+  int32_t vector_dim;       /* d, codebook is [C, d]                                             */
+  int32_t codebook_size;    /* C                                                                 */
+  int32_t index_bits;       /* b, index i occupies bits [i*b, i*b+b) of the little-endian stream */
+  const void* packed;       /* uint8, ceil(N*(K/d)*b/8) bytes + SACQ_PACKED_GUARD_BYTES readable,
+                               16-byte aligned                                                    */
+  int64_t packed_bytes;     /* bytes of the stream proper (without the guard)                    */
+  const void* codebook;     /* bf16 [C, d]                                                       */
+  const void* scales;       /* bf16 [N, K/G]                                                     */
+  const void* bias;         /* bf16 [N] or NULL                                                  */
+  uint16_t shift_bf16;      /* scalar shift as a bf16 bit pattern (0 in every fitted payload)    */
+  uint16_t reserved0;
+  uint32_t reserved1;
+} sacq_layer_desc;
+
+/* Replaces PrecomputedPackedVectorCodebookLinear.__init__ (SHIM:316-407): validates
+ * the geometry, and builds the layer's derived device tables (an fp16 copy of the
+ * codebook and an FP8 high/low split of it, a few times C*d bytes).  Allocates; call
+ * at load time, not inside a captured region. */
+SACQ_API int sacq_layer_create(const sacq_layer_desc* desc, sacq_layer_t** out_layer);
+SACQ_API int sacq_layer_destroy(sacq_layer_t* layer);
+
+/* Bytes of device memory the layer's derived tables hold (for residency accounting). */
+SACQ_API int64_t sacq_layer_resident_bytes(const sacq_layer_t* layer);
+
+/* Replaces .dequantize_weight() (SHIM:409-454) == decode_fixed
+ * (sacq/index_correction.py:98-108) == QuantLinear.weight_
+ * (sacq/calibration_layers.py:100-113):
+ *   W[n, g*G + v*d + j] = bf16( bf16(codebook[idx[n,g,v], j] * scales[n,g]) + shift )
+ * w_out: bf16 [N, K] row-major.  Bit-exact with the reference. */
+SACQ_API int sacq_dequant_bf16(const sacq_layer_t* layer, void* w_out, void* stream);
+
+/* Replaces quantize_rows(x, 'fp8_e4m3fn') (REC/perrow_a8_candidate_r3.py:17-25):
+ *   s[m] = max_k |x[m,k]| / 448 (1 when the row is all zero)
+ *   q[m,k] = e4m3_rne( clamp(x[m,k] / s[m], -448, 448) )
+ * x: bf16 [M, K] row-major with row pitch `x_pitch` elements; q: uint8 [M, K];
+ * scale: float [M].  Bit-exact with the reference for finite input. */
+SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, int64_t K, void* q_out, float* scale_out,
+                       void* stream);
+
+/* Replaces the per-output-row 8-bit weight producer of the reference's A8 recipe
+ * (REC/perrow_a8_candidate_r3.py:52-53 for the scale, :61-63 for the bytes):
+ * sacq_weight_row_scale writes sw[n] = max_k |W[n,k]| / 448 (1 for a zero row);
+ * sacq_decode_weight_fp8 writes wq[n,k] = e4m3_rne(clamp(W[n,k] / sw[n], +-448))
+ * from the packed stream without materialising the bf16 weight. */
+SACQ_API int sacq_weight_row_scale(const sacq_layer_t* layer, float* sw_out, void* stream);
+SACQ_API int sacq_decode_weight_fp8(const sacq_layer_t* layer, const float* sw, void* wq_out, void* stream);
+
+/* Scratch a forward with M activation rows needs (split-K partial sums and the
+ * arrival counters of the small-M kernel).  The counter region -- the FIRST
+ * sacq_workspace_counter_bytes() bytes -- must be zero before the first call
+ * that uses the buffer; every call leaves it zero again.  One workspace may be
+ * shared by calls that are ordered on one stream, never by concurrent ones. */
+SACQ_API int64_t sacq_workspace_bytes(const sacq_layer_t* layer, int64_t M);
+SACQ_API int64_t sacq_workspace_counter_bytes(void);
+
+/* Replaces the A8 forward of the reference overlay, i.e. decode + 8-bit GEMM +
+ * ordered epilogue (REC/perrow_a8_candidate_r3.py:56-69,
+ * REC/int8_ordered_epilogue_20261028_r1.py:11-22), with the weight side kept at the
+ * reconstruction's precision:
+ *   y[m,n] = bf16( s[m] * sum_k q[m,k] * W[n,k]  + bias[n] )
+ * q: e4m3 bytes [M, K]; scale: float [M]; y_out: bf16 [M, ldy] (ldy >= N elements).
+ * Chooses the small-M (CUDA-core, HBM-bound) or the large-M (TMA + tcgen05) kernel
+ * from M and the layer geometry alone. */
+SACQ_API int sacq_linear_a8(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M, void* y_out,
+                   int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Convenience: sacq_quant_act_fp8 + sacq_linear_a8 for a bf16 input (the module's
+ * forward(x), SHIM:456-541).  `q_scratch` (M*K bytes) and `scale_scratch` (M floats)
+ * are caller-provided device buffers. */
+SACQ_API int sacq_linear_bf16(const sacq_layer_t* layer, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
+                     float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
+                     void* stream);
+
+/* Forces one of the two GEMM kernels (for tests and benchmarks): 0 = automatic,
+ * 1 = small-M kernel, 2 = large-M kernel.  Returns SACQ_ERR_UNSUPPORTED from the
+ * next forward if the forced kernel cannot run the layer. */
+SACQ_API int sacq_layer_set_kernel(sacq_layer_t* layer, int which);
+/* Which kernel a forward with M rows would use (1 or 2), or a negative error. */
+SACQ_API int sacq_layer_kernel_for(const sacq_layer_t* layer, int64_t M);
+
+/* Reads the layer's device-side status word (synchronises the device): 0, or a
+ * nonzero code written by a kernel whose bounded wait gave up. */
+SACQ_API int sacq_layer_status(const sacq_layer_t* layer, int* status_out);
+
+/* Kernels launched by this library since it was loaded (all devices, all streams). */
+SACQ_API int64_t sacq_launch_count(void);
+
+SACQ_API const char* sacq_last_error(void);
+SACQ_API int sacq_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SACQ_B200_H_ */

@@ -1,0 +1,22 @@
+"""sacq_b200 -- B200 (sm_100a) implementation of SACQ's packed vector-codebook
+quantized-linear forward (W1.5A8): hand-written CUDA kernels behind a C ABI, with a
+PyTorch module that keeps the reference's payload format and module interface.
+
+Importing the package does not need a GPU; constructing a layer or calling a kernel
+does, and fails loudly when the CUDA library has not been built."""
+from .packing import index_bits_for, index_window_bytes, pack_indices, pack_payload, unpack_indices  # noqa: F401
+
+__all__ = [
+    "PrecomputedPackedVectorCodebookLinear", "quantize_rows", "pack_indices", "unpack_indices",
+    "pack_payload", "index_bits_for", "index_window_bytes",
+]
+
+
+def __getattr__(name):
+    if name == "PrecomputedPackedVectorCodebookLinear":
+        from .linear import PrecomputedPackedVectorCodebookLinear
+        return PrecomputedPackedVectorCodebookLinear
+    if name == "quantize_rows":
+        from .activation import quantize_rows
+        return quantize_rows
+    raise AttributeError(name)

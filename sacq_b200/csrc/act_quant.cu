@@ -1,0 +1,123 @@
+// Fused per-token FP8 activation quantizer.
+//
+// Restates quantize_rows(x, 'fp8_e4m3fn') of the reference
+// (inference_acceleration_2026_10_11/a8_accuracy_recovery_2026_10_20_r1/
+// perrow_a8_candidate_r3.py:17-25; zero-scale rule a8_rtn_r2.py:29-30):
+//   z = float(x); s = max|z| / 448 per row, 1 for an all-zero row;
+//   q = e4m3( clamp(z / s, -448, 448) )   with IEEE division and RNE conversion.
+// The reference spends five elementwise torch kernels on this; here one launch reads
+// the bf16 row once from HBM (second pass from registers), so the algorithmic traffic
+// is 2 bytes read + 1 byte written per element.
+#include "common.cuh"
+
+namespace sacq {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxChunksPerThread = 4;  // 16-byte chunks a thread keeps in registers: K <= 8192 stays on chip
+
+// One CTA per row.  VEC: rows are 16-byte aligned and K % 8 == 0.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, uint8_t* __restrict__ q,
+                     float* __restrict__ scale_out) {
+  __shared__ float red[kThreads / 32];
+  __shared__ float s_scale;
+  const int64_t m = blockIdx.x;
+  const uint16_t* row = x + m * pitch;
+  uint8_t* qrow = q + m * K;
+  const int tid = threadIdx.x;
+
+  float mx = 0.f;
+  uint4 keep[kMaxChunksPerThread];
+  const int64_t chunks = VEC ? (K >> 3) : 0;
+  if constexpr (VEC) {
+#pragma unroll
+    for (int c = 0; c < kMaxChunksPerThread; ++c) {
+      const int64_t ch = tid + (int64_t)c * kThreads;
+      keep[c] = make_uint4(0, 0, 0, 0);
+      if (ch < chunks) keep[c] = __ldg(reinterpret_cast<const uint4*>(row) + ch);
+      const uint32_t w[4] = {keep[c].x, keep[c].y, keep[c].z, keep[c].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] & 0xffff)));
+        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] >> 16)));
+      }
+    }
+    for (int64_t ch = tid + (int64_t)kMaxChunksPerThread * kThreads; ch < chunks; ch += kThreads) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(row) + ch);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] & 0xffff)));
+        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] >> 16)));
+      }
+    }
+  } else {
+    for (int64_t k = tid; k < K; k += kThreads) mx = fmaxf(mx, fabsf(bf16_bits_to_float(__ldg(row + k))));
+  }
+  mx = warp_max(mx);
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid < 32) {
+    float v = tid < kThreads / 32 ? red[tid] : 0.f;
+    v = warp_max(v);
+    if (tid == 0) {
+      const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
+      s_scale = s;
+      scale_out[m] = s;
+    }
+  }
+  __syncthreads();
+  const float s = s_scale;
+
+  if constexpr (VEC) {
+    auto emit = [&](const uint4& v, int64_t ch) {
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      uint32_t o[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t a = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] & 0xffff), s)),
+                                            clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] >> 16), s)));
+        const uint32_t b = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] & 0xffff), s)),
+                                            clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] >> 16), s)));
+        o[j] = a | (b << 16);
+      }
+      *(reinterpret_cast<uint2*>(qrow) + ch) = make_uint2(o[0], o[1]);
+    };
+#pragma unroll
+    for (int c = 0; c < kMaxChunksPerThread; ++c) {
+      const int64_t ch = tid + (int64_t)c * kThreads;
+      if (ch < chunks) emit(keep[c], ch);
+    }
+    for (int64_t ch = tid + (int64_t)kMaxChunksPerThread * kThreads; ch < chunks; ch += kThreads)
+      emit(__ldg(reinterpret_cast<const uint4*>(row) + ch), ch);
+  } else {
+    for (int64_t k = tid; k < K; k += kThreads) {
+      const float z = bf16_bits_to_float(__ldg(row + k));
+      qrow[k] = (uint8_t)(float2_to_e4m3x2(clamp448(__fdiv_rn(z, s)), 0.f) & 0xff);
+    }
+  }
+}
+
+}  // namespace
+
+int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale,
+                         cudaStream_t s) {
+  if (M == 0 || K == 0) return SACQ_OK;
+  const bool vec = (K % 8 == 0) && (pitch % 8 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(q) % 8 == 0);
+  if (M > 2147483647LL) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
+  if (vec)
+    quant_act_fp8_kernel<true><<<(unsigned)M, kThreads, 0, s>>>(static_cast<const uint16_t*>(x), pitch, K,
+                                                               static_cast<uint8_t*>(q), scale);
+  else
+    quant_act_fp8_kernel<false><<<(unsigned)M, kThreads, 0, s>>>(static_cast<const uint16_t*>(x), pitch, K,
+                                                                static_cast<uint8_t*>(q), scale);
+  count_launch();
+  SACQ_CUDA_TRY(cudaGetLastError());
+  return SACQ_OK;
+}
+
+}  // namespace sacq

@@ -1,0 +1,277 @@
+// C ABI of libsacq_b200: layer handles, argument checking, kernel selection.
+// The kernels live in dequant.cu, act_quant.cu, linear_small_m.cu, linear_large_m.cu.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+static_assert(sizeof(sacq_layer_desc) == 88, "sacq_layer_desc layout is part of the ABI");
+
+namespace sacq {
+
+namespace {
+thread_local char g_error[512] = "";
+std::atomic<long long> g_launches{0};
+constexpr int64_t kCounterBytes = 64 * 1024;  // 16384 row-block arrival counters
+}  // namespace
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return set_error(SACQ_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+
+// Runs `fn` with the layer's device current, restoring the caller's device afterwards.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+int check_layer(const sacq_layer_t* L) {
+  if (L == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "layer handle is null");
+  return SACQ_OK;
+}
+
+// Rows per launch of the small-M kernel so that its arrival counters fit their region.
+int64_t small_m_slab_rows(const sacq_layer* L) {
+  const int64_t row_blocks = (L->d.out_features + 31) / 32;
+  int64_t chunks = (kCounterBytes / (int64_t)sizeof(int)) / (row_blocks > 0 ? row_blocks : 1);
+  if (chunks < 1) chunks = 1;
+  return chunks * 16;
+}
+
+int pick_kernel(const sacq_layer* L, int64_t M) {
+  if (L->force_kernel == 1) return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
+  if (L->force_kernel == 2) return large_m_supported(L) ? 2 : SACQ_ERR_UNSUPPORTED;
+  // A shape rule, not a backend switch: the CUDA-core kernel wins while the grid of
+  // 128-row tensor-core tiles cannot fill the device.
+  if (large_m_supported(L) && M > 32) return 2;
+  return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+}  // namespace sacq
+
+using namespace sacq;
+
+extern "C" {
+
+SACQ_API int sacq_abi_version(void) { return SACQ_ABI_VERSION; }
+SACQ_API const char* sacq_last_error(void) { return g_error; }
+SACQ_API int64_t sacq_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
+SACQ_API int64_t sacq_workspace_counter_bytes(void) { return kCounterBytes; }
+
+SACQ_API int sacq_layer_create(const sacq_layer_desc* desc, sacq_layer_t** out_layer) {
+  if (desc == nullptr || out_layer == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  *out_layer = nullptr;
+  if (desc->struct_size != sizeof(sacq_layer_desc))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "sacq_layer_desc.struct_size is %u, this library expects %zu",
+                     desc->struct_size, sizeof(sacq_layer_desc));
+  const sacq_layer_desc& d = *desc;
+  if (d.out_features < 0 || d.in_features <= 0 || d.vector_dim <= 0 || d.group_size <= 0 || d.codebook_size <= 0)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "non-positive geometry (N=%lld K=%lld d=%d G=%d C=%d)",
+                     (long long)d.out_features, (long long)d.in_features, d.vector_dim, d.group_size,
+                     d.codebook_size);
+  if (d.in_features % d.group_size != 0)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "in_features=%lld is not a multiple of group_size=%d",
+                     (long long)d.in_features, d.group_size);
+  if (d.group_size % d.vector_dim != 0)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "group_size=%d is not a multiple of vector_dim=%d", d.group_size,
+                     d.vector_dim);
+  if (d.index_bits < 1 || d.index_bits > 24)
+    return set_error(SACQ_ERR_UNSUPPORTED, "index_bits=%d outside [1, 24]", d.index_bits);
+  if (d.index_bits < 31 && (int64_t)d.codebook_size > (1LL << d.index_bits))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "codebook_size=%d does not fit index_bits=%d", d.codebook_size,
+                     d.index_bits);
+  if (d.in_features > (1 << 24) || d.out_features > (1 << 24))
+    return set_error(SACQ_ERR_UNSUPPORTED, "features above 2^24 are not supported");
+  const int64_t vpr = d.in_features / d.vector_dim;
+  const int64_t expect = (d.out_features * vpr * d.index_bits + 7) / 8;
+  if (d.packed_bytes != expect)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "packed stream has %lld bytes, expected %lld",
+                     (long long)d.packed_bytes, (long long)expect);
+  if (d.codebook == nullptr || d.scales == nullptr || (d.packed == nullptr && expect > 0))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null device pointer in layer description");
+  if (reinterpret_cast<uintptr_t>(d.packed) % 16 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "packed stream must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(d.codebook) % 16 != 0 || reinterpret_cast<uintptr_t>(d.scales) % 2 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "codebook must be 16-byte aligned");
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0)
+    return set_error(SACQ_ERR_CUDA, "no CUDA device is available; this library has no CPU path");
+  if (d.device < 0 || d.device >= ndev)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "device %d out of range (%d devices)", d.device, ndev);
+
+  DeviceGuard guard(d.device);
+  if (!guard.ok) return set_error(SACQ_ERR_CUDA, "cannot make device %d current", d.device);
+  sacq_layer* L = new (std::nothrow) sacq_layer();
+  if (L == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "out of host memory");
+  memset(L, 0, sizeof(*L));
+  L->d = d;
+  L->vectors_per_row = vpr;
+  L->num_groups = d.in_features / d.group_size;
+  L->row_bits = vpr * d.index_bits;
+  L->rows_16b_aligned = (L->row_bits % 128) == 0;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, d.device) != cudaSuccess) {
+    delete L;
+    return set_error(SACQ_ERR_CUDA, "cudaGetDeviceProperties failed");
+  }
+  if (prop.major != 10) {
+    delete L;
+    return set_error(SACQ_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", d.device,
+                     prop.major, prop.minor);
+  }
+  L->num_sms = prop.multiProcessorCount;
+  const int64_t count = (int64_t)d.codebook_size * d.vector_dim;
+  cudaError_t e = cudaMalloc(&L->cb_f16, (size_t)count * sizeof(__half));
+  if (e == cudaSuccess) e = cudaMalloc(&L->cb_hilo, (size_t)count * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&L->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(L->d_status, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    sacq_layer_destroy(L);
+    return cuda_fail(e, "allocating derived codebook tables");
+  }
+  L->resident_bytes = count * 4 + (int64_t)sizeof(int);
+  const int rc = launch_build_tables(L, nullptr);
+  if (rc != SACQ_OK) {
+    sacq_layer_destroy(L);
+    return rc;
+  }
+  *out_layer = L;
+  return SACQ_OK;
+}
+
+SACQ_API int sacq_layer_destroy(sacq_layer_t* L) {
+  if (L == nullptr) return SACQ_OK;
+  DeviceGuard guard(L->d.device);
+  large_m_release(L);
+  if (L->cb_f16) cudaFree(L->cb_f16);
+  if (L->cb_hilo) cudaFree(L->cb_hilo);
+  if (L->d_status) cudaFree(L->d_status);
+  delete L;
+  return SACQ_OK;
+}
+
+SACQ_API int64_t sacq_layer_resident_bytes(const sacq_layer_t* L) { return L ? L->resident_bytes : 0; }
+
+SACQ_API int sacq_dequant_bf16(const sacq_layer_t* L, void* w_out, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (w_out == nullptr && L->d.out_features > 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "w_out is null");
+  DeviceGuard guard(L->d.device);
+  return launch_dequant_bf16(L, w_out, static_cast<cudaStream_t>(stream));
+}
+
+SACQ_API int sacq_weight_row_scale(const sacq_layer_t* L, float* sw_out, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (sw_out == nullptr && L->d.out_features > 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "sw_out is null");
+  DeviceGuard guard(L->d.device);
+  return launch_weight_row_scale(L, sw_out, static_cast<cudaStream_t>(stream));
+}
+
+SACQ_API int sacq_decode_weight_fp8(const sacq_layer_t* L, const float* sw, void* wq_out, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if ((sw == nullptr || wq_out == nullptr) && L->d.out_features > 0)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard guard(L->d.device);
+  return launch_decode_weight_fp8(L, sw, wq_out, static_cast<cudaStream_t>(stream));
+}
+
+SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, int64_t K, void* q_out, float* scale_out,
+                       void* stream) {
+  if (M < 0 || K < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "negative size (M=%lld K=%lld)", (long long)M,
+                                       (long long)K);
+  if (M == 0) return SACQ_OK;
+  if (x_pitch < K) return set_error(SACQ_ERR_INVALID_ARGUMENT, "row pitch %lld smaller than K=%lld",
+                                    (long long)x_pitch, (long long)K);
+  if (scale_out == nullptr || ((x_bf16 == nullptr || q_out == nullptr) && K > 0))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (K == 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "K must be positive");
+  return launch_quant_act_fp8(x_bf16, x_pitch, M, K, q_out, scale_out, static_cast<cudaStream_t>(stream));
+}
+
+SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
+  if (int rc = check_layer(L)) return rc;
+  if (which < 0 || which > 2) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in {0,1,2}", which);
+  L->force_kernel = which;
+  return SACQ_OK;
+}
+
+SACQ_API int sacq_layer_kernel_for(const sacq_layer_t* L, int64_t M) {
+  if (int rc = check_layer(L)) return rc;
+  const int k = pick_kernel(L, M);
+  if (k < 0) return set_error(k, "no kernel can run this layer geometry");
+  return k;
+}
+
+SACQ_API int64_t sacq_workspace_bytes(const sacq_layer_t* L, int64_t M) {
+  if (L == nullptr || M < 0) return 0;
+  const int64_t slab = small_m_slab_rows(L);
+  return small_m_workspace_bytes(L, M < slab ? M : slab);
+}
+
+SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,
+                   void* workspace, int64_t workspace_bytes, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
+  if (M == 0 || L->d.out_features == 0) return SACQ_OK;
+  if (q == nullptr || scale == nullptr || y_out == nullptr)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (ldy < L->d.out_features)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "ldy=%lld smaller than out_features=%lld", (long long)ldy,
+                     (long long)L->d.out_features);
+  DeviceGuard guard(L->d.device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int k = pick_kernel(L, M);
+  if (k < 0) return set_error(k, "no kernel can run this layer geometry");
+  if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s);
+  const int64_t slab = small_m_slab_rows(L);
+  for (int64_t m0 = 0; m0 < M; m0 += slab) {
+    const int64_t rows = (M - m0) < slab ? (M - m0) : slab;
+    const int rc = launch_small_m(L, static_cast<const uint8_t*>(q) + m0 * L->d.in_features, scale + m0, rows,
+                                  static_cast<uint16_t*>(y_out) + m0 * ldy, ldy, workspace, workspace_bytes, s);
+    if (rc != SACQ_OK) return rc;
+  }
+  return SACQ_OK;
+}
+
+SACQ_API int sacq_linear_bf16(const sacq_layer_t* L, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
+                     float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
+                     void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (M == 0) return SACQ_OK;
+  int rc = sacq_quant_act_fp8(x_bf16, x_pitch, M, L->d.in_features, q_scratch, scale_scratch, stream);
+  if (rc != SACQ_OK) return rc;
+  return sacq_linear_a8(L, q_scratch, scale_scratch, M, y_out, ldy, workspace, workspace_bytes, stream);
+}
+
+SACQ_API int sacq_layer_status(const sacq_layer_t* L, int* status_out) {
+  if (int rc = check_layer(L)) return rc;
+  if (status_out == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "status_out is null");
+  DeviceGuard guard(L->d.device);
+  SACQ_CUDA_TRY(cudaMemcpy(status_out, L->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  return SACQ_OK;
+}
+
+}  // extern "C"

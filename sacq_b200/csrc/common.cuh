@@ -1,0 +1,122 @@
+// Shared device/host helpers for the sacq_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/sacq_b200.h"
+
+namespace sacq {
+
+constexpr float kE4M3Max = 448.0f;
+constexpr int kNumSMsB200 = 148;
+
+// ----------------------------------------------------------------------------
+// host side: the layer handle and error plumbing
+// ----------------------------------------------------------------------------
+
+struct LargeMPlan;  // built lazily by the large-M kernel's host code
+
+}  // namespace sacq
+
+struct sacq_layer {
+  sacq_layer_desc d;
+  int64_t vectors_per_row;   // K / d
+  int64_t num_groups;        // K / G
+  int64_t row_bits;          // (K/d) * b
+  bool rows_16b_aligned;     // every row of the packed stream starts on a 16-byte boundary
+  int num_sms;
+  int force_kernel;          // 0 auto, 1 small-M, 2 large-M
+  // derived device tables (owned)
+  __half* cb_f16;            // [C, d] codebook * 2^cb_exp_shift as fp16 (small-M kernel)
+  uint8_t* cb_hilo;          // [C][2][d] e4m3 high/low split of codebook * 2^cb8_exp_shift (large-M kernel)
+  int cb_exp_shift;          // power-of-two normalisation folded back in the epilogue
+  int cb8_exp_shift;
+  int* d_status;             // device status word, 0 = ok
+  int64_t resident_bytes;
+  sacq::LargeMPlan* large_plan;
+};
+
+namespace sacq {
+
+int set_error(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+void count_launch(int n = 1);
+
+#define SACQ_CUDA_TRY(expr)                                  \
+  do {                                                       \
+    cudaError_t _e = (expr);                                 \
+    if (_e != cudaSuccess) return ::sacq::cuda_fail(_e, #expr); \
+  } while (0)
+
+// kernel entry points implemented in the other translation units
+int launch_dequant_bf16(const sacq_layer* L, void* w_out, cudaStream_t s);
+int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s);
+int launch_decode_weight_fp8(const sacq_layer* L, const float* sw, void* wq, cudaStream_t s);
+int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
+int launch_build_tables(sacq_layer* L, cudaStream_t s);
+
+bool small_m_supported(const sacq_layer* L);
+int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M);
+int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                   void* ws, int64_t ws_bytes, cudaStream_t s);
+
+bool large_m_supported(const sacq_layer* L);
+int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                   cudaStream_t s);
+void large_m_release(sacq_layer* L);
+
+// ----------------------------------------------------------------------------
+// device side
+// ----------------------------------------------------------------------------
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+// The reference reconstruction: bf16(bf16(c * s) + shift), two roundings
+// (sacq/index_correction.py:104-106).  c*s is exact in fp32 (8-bit x 8-bit
+// significands), so one RNE rounding gives torch's bf16 product.
+__device__ __forceinline__ uint16_t reconstruct_bf16(uint32_t c_bits, float s, float shift) {
+  float p = __bfloat162float(__float2bfloat16_rn(__fmul_rn(bf16_bits_to_float(c_bits), s)));
+  return float_to_bf16_bits(__fadd_rn(p, shift));
+}
+
+// One e4m3 byte from a float with RNE and saturation; callers clamp first so
+// saturation never changes a value.
+__device__ __forceinline__ uint32_t float2_to_e4m3x2(float lo, float hi) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ float clamp448(float v) { return fminf(fmaxf(v, -kE4M3Max), kE4M3Max); }
+
+// Index `i` of a little-endian bit stream of `bits`-wide fields, read through
+// aligned 32-bit words (bits <= 24).  `words` must be readable one word past
+// the word holding the field's last bit.
+__device__ __forceinline__ uint32_t extract_index(const uint32_t* __restrict__ words, int64_t i, int bits) {
+  const int64_t p = i * bits;
+  const int64_t w = p >> 5;
+  const uint32_t off = (uint32_t)(p & 31);
+  const uint32_t lo = __ldg(words + w);
+  const uint32_t hi = __ldg(words + w + 1);
+  return __funnelshift_r(lo, hi, off) & ((1u << bits) - 1u);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace sacq

@@ -1,0 +1,518 @@
+// Small-M ("decode") quantized linear: y = s[m] * sum_k q[m,k] * W[n,k] + bias[n] for a
+// handful of activation rows, reading the packed index stream exactly once.
+//
+// Stands in for the reference's small-M packed GEMMs (Triton
+// codebook_linear_triton_2026_08_23.py:499-705 incl. its split-K variant, and the A8
+// decode + small-M GEMM pair a8_accuracy_recovery_2026_10_20_r1/
+// int8_aligned_index_decoder_20261028_r1.py:26-112 + int8_small_m_gemm_20261028_r1.py:7-32)
+// without ever writing an expanded weight.
+//
+// Design (CUDA cores; tensor cores are left to the large-M kernel):
+//   * persistent grid, one CTA per SM; each CTA stages the fp16 codebook in shared
+//     memory once (64 KB for 4096 x 8);
+//   * work item = (token chunk, block of 32 output rows, span group); a WARP owns an item,
+//     lane = output row, and walks its row's slice of the index stream with 128-bit loads
+//     (32 indices = 48 bytes at 12 bits);
+//   * per index: one 128-bit shared-memory gather of the codeword, and per token one
+//     broadcast 128-bit read of the activations and four HFMA2; fp16 partial sums are
+//     flushed to fp32 every 32 products;
+//   * K is split across warps/CTAs; partial sums meet in a global scratch buffer and the
+//     last warp to arrive for a row block (arrival counter, no spinning) adds them in a
+//     fixed order and applies the epilogue, so results do not depend on scheduling.
+//
+// Roofline: bound by HBM on the packed indices in principle (1.5 bits per weight); in
+// practice the shared-memory gather rate (one 16-byte lookup per 8 weights) caps it.
+#include "common.cuh"
+
+#include <math.h>
+#include <string.h>
+
+#include <type_traits>
+
+namespace sacq {
+
+namespace {
+
+constexpr int kSpanIdx = 32;   // indices a lane consumes per span
+constexpr int kMaxWarps = 8;
+
+struct SmallMParams {
+  const uint8_t* packed;
+  const __half* cb_f16;        // [C, D] scaled by 2^cb_exp_shift
+  const uint16_t* cb_bf16;     // [C, d] original (generic kernel)
+  const uint16_t* scales;      // bf16 [N, num_groups]
+  const uint16_t* bias;        // bf16 [N] or null
+  const uint8_t* q;            // e4m3 [M, K]
+  const float* act_scale;      // [M]
+  uint16_t* y;                 // bf16 [M, ldy]
+  float* partial;              // [num_sg][M][N] (only when num_sg > 1)
+  int* counters;               // [chunks * row_blocks]
+  int64_t ldy;
+  int64_t row_bytes;           // bytes per packed row (fast kernel)
+  int N, K, M;
+  int vpr;                     // vectors per row
+  int d, bits;
+  int num_groups, group_size;
+  int C;
+  int span_idx;                // generic kernel: vectors per span
+  int spans_per_row;           // vpr / span
+  int spans_per_item;          // consecutive spans one item covers
+  int num_sg;                  // span groups per row = ceil(spans_per_row / spans_per_item)
+  int row_blocks;              // ceil(N / 32)
+  int chunks;                  // ceil(M / MT)
+  int64_t num_items;
+  float out_mul;               // 2^-cb_exp_shift (fast) or 1 (generic)
+  float shift;
+};
+
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// e4m3 x4 (one 32-bit word) -> 2 x half2, exact.
+__device__ __forceinline__ void e4m3x4_to_h2(uint32_t v, uint32_t& lo, uint32_t& hi) {
+  const __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xffff), __NV_E4M3);
+  const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v >> 16), __NV_E4M3);
+  lo = (uint32_t)a.x | ((uint32_t)a.y << 16);
+  hi = (uint32_t)b.x | ((uint32_t)b.y << 16);
+}
+
+template <int BITS>
+__device__ __forceinline__ uint32_t field(const uint32_t (&w)[BITS], int i) {
+  const int bit = i * BITS;
+  const int word = bit >> 5;
+  const int off = bit & 31;
+  if (off + BITS <= 32) return (w[word] >> off) & ((1u << BITS) - 1u);
+  return __funnelshift_r(w[word], w[word + 1 < BITS ? word + 1 : word], off) & ((1u << BITS) - 1u);
+}
+
+// Adds the partial sums of one row block in span-group order and writes y.  Called by
+// the last warp to arrive (or directly when K is not split).  `val` holds this warp's
+// own MT partial sums for row n (already in true units).
+template <int MT>
+__device__ __forceinline__ void finish_rows(const SmallMParams& p, int chunk, int rb, int sg, float (&val)[MT],
+                                            int n, bool row_ok) {
+  const int m0 = chunk * MT;
+  if (p.num_sg > 1) {
+    // publish, then count arrivals
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+      if (row_ok && m0 + m < p.M) p.partial[((int64_t)sg * p.M + (m0 + m)) * p.N + n] = val[m];
+    __threadfence();
+    __syncwarp();
+    int old = 0;
+    int* ctr = p.counters + (int64_t)chunk * p.row_blocks + rb;
+    if ((threadIdx.x & 31) == 0) old = atomicAdd(ctr, 1);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old != p.num_sg - 1) return;
+    __threadfence();
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float t = 0.f;
+      if (row_ok && m0 + m < p.M)
+        for (int g = 0; g < p.num_sg; ++g) t += __ldcg(p.partial + ((int64_t)g * p.M + (m0 + m)) * p.N + n);
+      val[m] = t;
+    }
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) *ctr = 0;  // leave the counter region zero for the next call
+  }
+  if (!row_ok) return;
+  const float b = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    if (m0 + m < p.M) {
+      const float sa = __ldg(p.act_scale + m0 + m);
+      p.y[(int64_t)(m0 + m) * p.ldy + n] = float_to_bf16_bits(fmaf(sa, val[m], b));
+    }
+  }
+}
+
+// Fast path: D in {4, 8}, BITS in {8, 12, 16}, rows of the packed stream 16-byte aligned,
+// group_size a multiple of kSpanIdx * D.
+template <int D, int BITS, int MT, bool CB_SMEM>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_kernel(const SmallMParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;   // D halfs
+  CwVec* cbs = reinterpret_cast<CwVec*>(smem);
+  const int cb_bytes = CB_SMEM ? p.C * D * 2 : 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+  // per-warp activation staging: [MT][kSpanIdx] vectors of D halfs
+  CwVec* xs = reinterpret_cast<CwVec*>(smem + cb_bytes) + (size_t)warp * MT * kSpanIdx;
+
+  if (CB_SMEM) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.cb_f16);
+    uint4* dst = reinterpret_cast<uint4*>(smem);
+    const int n16 = cb_bytes >> 4;
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldg(src + i);
+  }
+  __syncthreads();
+
+  const int64_t total_warps = (int64_t)gridDim.x * nwarps;
+  for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; item < p.num_items; item += total_warps) {
+    // item -> (chunk, rb, sg), sg fastest so neighbouring warps share index sectors
+    const int sg = (int)(item % p.num_sg);
+    const int64_t t1 = item / p.num_sg;
+    const int rb = (int)(t1 % p.row_blocks);
+    const int chunk = (int)(t1 / p.row_blocks);
+    const int m0 = chunk * MT;
+    const int n = rb * 32 + lane;
+    const bool row_ok = n < p.N;
+    const int nr = row_ok ? n : p.N - 1;
+    const int sp_begin = sg * p.spans_per_item;
+    const int sp_end = min(sp_begin + p.spans_per_item, p.spans_per_row);
+
+    float acc[MT];
+    float xsum[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) { acc[m] = 0.f; xsum[m] = 0.f; }
+
+    for (int sp = sp_begin; sp < sp_end; ++sp) {
+      // ---- stage this span's activations as fp16: xs[m][i] = q[m0+m, (sp*32+i)*D .. +D)
+      __syncwarp();
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        CwVec o;
+        const int64_t kbyte = ((int64_t)sp * kSpanIdx + lane) * D;
+        if (m0 + m < p.M) {
+          const uint8_t* src = p.q + (int64_t)(m0 + m) * p.K + kbyte;
+          if constexpr (D == 8) {
+            const uint2 v = __ldg(reinterpret_cast<const uint2*>(src));
+            e4m3x4_to_h2(v.x, o.x, o.y);
+            e4m3x4_to_h2(v.y, o.z, o.w);
+          } else {
+            const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(src));
+            e4m3x4_to_h2(v, o.x, o.y);
+          }
+        } else {
+          if constexpr (D == 8) o = make_uint4(0, 0, 0, 0); else o = make_uint2(0, 0);
+        }
+        xs[m * kSpanIdx + lane] = o;
+        if (p.shift != 0.f) {
+          float t = __low2float(as_h2(o.x)) + __high2float(as_h2(o.x)) + __low2float(as_h2(o.y)) +
+                    __high2float(as_h2(o.y));
+          if constexpr (D == 8)
+            t += __low2float(as_h2(o.z)) + __high2float(as_h2(o.z)) + __low2float(as_h2(o.w)) +
+                 __high2float(as_h2(o.w));
+          xsum[m] += warp_sum(t);
+        }
+      }
+      // ---- this lane's 32 indices of row n
+      uint32_t w[BITS];
+      {
+        const uint4* src = reinterpret_cast<const uint4*>(p.packed + (int64_t)nr * p.row_bytes + (int64_t)sp * (4 * BITS));
+#pragma unroll
+        for (int j = 0; j < BITS / 4; ++j) {
+          const uint4 v = __ldg(src + j);
+          w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        }
+      }
+      __syncwarp();
+
+      float sacc[MT];
+      __half2 hacc[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) { sacc[m] = 0.f; hacc[m] = __float2half2_rn(0.f); }
+
+      constexpr int kFlush = 32 / D;  // indices between fp16 -> fp32 flushes (32 products)
+#pragma unroll
+      for (int i = 0; i < kSpanIdx; ++i) {
+        const uint32_t idx = field<BITS>(w, i);
+        CwVec c;
+        if constexpr (CB_SMEM) c = cbs[idx];
+        else c = __ldg(reinterpret_cast<const CwVec*>(p.cb_f16) + idx);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const CwVec xv = xs[m * kSpanIdx + i];
+          hacc[m] = __hfma2(as_h2(c.x), as_h2(xv.x), hacc[m]);
+          hacc[m] = __hfma2(as_h2(c.y), as_h2(xv.y), hacc[m]);
+          if constexpr (D == 8) {
+            hacc[m] = __hfma2(as_h2(c.z), as_h2(xv.z), hacc[m]);
+            hacc[m] = __hfma2(as_h2(c.w), as_h2(xv.w), hacc[m]);
+          }
+        }
+        if ((i % kFlush) == kFlush - 1) {
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            sacc[m] += __low2float(hacc[m]) + __high2float(hacc[m]);
+            hacc[m] = __float2half2_rn(0.f);
+          }
+        }
+      }
+      const int g = (sp * kSpanIdx * D) / p.group_size;
+      const float s = bf16_bits_to_float(__ldg(p.scales + (int64_t)nr * p.num_groups + g));
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[m] = fmaf(s, sacc[m], acc[m]);
+    }
+
+    float val[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) val[m] = fmaf(acc[m], p.out_mul, p.shift * xsum[m]);
+    finish_rows<MT>(p, chunk, rb, sg, val, n, row_ok);
+  }
+}
+
+// Generic path: any vector_dim, index width <= 24 bits, any group size, rows at any bit
+// offset.  Same item structure, scalar fp32 math, codewords fetched from global memory.
+template <int MT>
+__global__ void __launch_bounds__(kMaxWarps * 32) small_m_generic_kernel(const SmallMParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+  const int span_k = p.span_idx * p.d;
+  float* xs = reinterpret_cast<float*>(smem) + (size_t)warp * MT * span_k;  // [MT][span_k]
+  const uint32_t* words = reinterpret_cast<const uint32_t*>(p.packed);
+
+  const int64_t total_warps = (int64_t)gridDim.x * nwarps;
+  for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; item < p.num_items; item += total_warps) {
+    const int sg = (int)(item % p.num_sg);
+    const int64_t t1 = item / p.num_sg;
+    const int rb = (int)(t1 % p.row_blocks);
+    const int chunk = (int)(t1 / p.row_blocks);
+    const int m0 = chunk * MT;
+    const int n = rb * 32 + lane;
+    const bool row_ok = n < p.N;
+    const int nr = row_ok ? n : p.N - 1;
+    const int sp_begin = sg * p.spans_per_item;
+    const int sp_end = min(sp_begin + p.spans_per_item, p.spans_per_row);
+
+    float acc[MT], xsum[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) { acc[m] = 0.f; xsum[m] = 0.f; }
+
+    for (int sp = sp_begin; sp < sp_end; ++sp) {
+      __syncwarp();
+      const int kbase = sp * span_k;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        float t = 0.f;
+        for (int k = lane; k < span_k; k += 32) {
+          float v = 0.f;
+          if (m0 + m < p.M) {
+            const uint8_t b = __ldg(p.q + (int64_t)(m0 + m) * p.K + kbase + k);
+            v = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3)));
+          }
+          xs[m * span_k + k] = v;
+          t += v;
+        }
+        if (p.shift != 0.f) xsum[m] += warp_sum(t);
+      }
+      __syncwarp();
+      float sacc[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) sacc[m] = 0.f;
+      const int64_t i0 = (int64_t)nr * p.vpr + (int64_t)sp * p.span_idx;
+      for (int i = 0; i < p.span_idx; ++i) {
+        const uint32_t idx = extract_index(words, i0 + i, p.bits);
+        for (int j = 0; j < p.d; ++j) {
+          const float c = bf16_bits_to_float(__ldg(p.cb_bf16 + (int64_t)idx * p.d + j));
+#pragma unroll
+          for (int m = 0; m < MT; ++m) sacc[m] = fmaf(c, xs[m * span_k + i * p.d + j], sacc[m]);
+        }
+      }
+      const int g = kbase / p.group_size;
+      const float s = bf16_bits_to_float(__ldg(p.scales + (int64_t)nr * p.num_groups + g));
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[m] = fmaf(s, sacc[m], acc[m]);
+    }
+    float val[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) val[m] = fmaf(acc[m], p.out_mul, p.shift * xsum[m]);
+    finish_rows<MT>(p, chunk, rb, sg, val, n, row_ok);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+
+struct Plan {
+  bool fast;
+  int D, BITS;
+  bool cb_smem;
+  int MT;
+  int span_idx, spans_per_row, spans_per_item, num_sg, row_blocks, chunks;
+  int64_t num_items;
+  int warps, grid;
+  size_t smem;
+};
+
+inline int pick_mt(int64_t M) {
+  if (M <= 1) return 1;
+  if (M <= 2) return 2;
+  if (M <= 4) return 4;
+  if (M <= 8) return 8;
+  return 16;
+}
+
+bool fast_eligible(const sacq_layer* L) {
+  const sacq_layer_desc& d = L->d;
+  if (d.vector_dim != 8 && d.vector_dim != 4) return false;
+  if (d.index_bits != 8 && d.index_bits != 12 && d.index_bits != 16) return false;
+  if (!L->rows_16b_aligned) return false;
+  const int span_k = kSpanIdx * d.vector_dim;
+  if (d.in_features % span_k != 0) return false;
+  if (d.group_size % span_k != 0) return false;
+  return true;
+}
+
+constexpr size_t kSmemBudget = 200 * 1024;
+
+Plan make_plan(const sacq_layer* L, int64_t M) {
+  const sacq_layer_desc& d = L->d;
+  Plan pl{};
+  pl.fast = fast_eligible(L);
+  pl.MT = pick_mt(M);
+  pl.chunks = (int)((M + pl.MT - 1) / pl.MT);
+  pl.row_blocks = (int)((d.out_features + 31) / 32);
+  pl.D = d.vector_dim;
+  pl.BITS = d.index_bits;
+  if (pl.fast) {
+    pl.span_idx = kSpanIdx;
+    const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
+    pl.cb_smem = cb_bytes <= 64 * 1024;
+  } else {
+    // largest span (<= 32 vectors) that stays inside one scale group and divides the row
+    int s = 32;
+    const int vpg = d.group_size / d.vector_dim;
+    while (s > 1 && (vpg % s != 0 || L->vectors_per_row % s != 0 || (size_t)s * d.vector_dim > 512)) s >>= 1;
+    if (vpg % s != 0 || L->vectors_per_row % s != 0) s = 1;
+    pl.span_idx = s;
+    pl.cb_smem = false;
+  }
+  pl.spans_per_row = (int)(L->vectors_per_row / pl.span_idx);
+  // Spread the row's spans over enough items to occupy every warp of the device once,
+  // but no finer than one span per item.
+  const int64_t base = (int64_t)pl.row_blocks * pl.chunks;
+  const int64_t want = (int64_t)L->num_sms * 4;
+  int per_item = pl.spans_per_row;
+  while (per_item > 1 && base * ((pl.spans_per_row + per_item - 1) / per_item) < want) per_item = (per_item + 1) / 2;
+  pl.spans_per_item = per_item;
+  pl.num_sg = (pl.spans_per_row + per_item - 1) / per_item;
+  pl.num_items = base * pl.num_sg;
+  // one CTA per SM; warps per CTA: enough for the items, at most 8
+  pl.grid = (int)(pl.num_items < L->num_sms ? pl.num_items : L->num_sms);
+  if (pl.grid < 1) pl.grid = 1;
+  int64_t warps_needed = (pl.num_items + pl.grid - 1) / pl.grid;
+  pl.warps = (int)(warps_needed < 1 ? 1 : (warps_needed > kMaxWarps ? kMaxWarps : warps_needed));
+  if (pl.fast) {
+    const size_t cb_bytes = pl.cb_smem ? (size_t)d.codebook_size * d.vector_dim * 2 : 0;
+    pl.smem = cb_bytes + (size_t)pl.warps * pl.MT * kSpanIdx * d.vector_dim * 2;
+  } else {
+    const size_t per_warp = (size_t)pl.MT * pl.span_idx * d.vector_dim * 4;
+    while (pl.warps > 1 && per_warp * pl.warps > kSmemBudget) --pl.warps;
+    pl.smem = per_warp * pl.warps;
+  }
+  return pl;
+}
+
+template <int D, int BITS, bool CB_SMEM>
+cudaError_t launch_fast_mt(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  auto go = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+    if (e != cudaSuccess) return e;
+    kern<<<pl.grid, pl.warps * 32, pl.smem, s>>>(p);
+    return cudaGetLastError();
+  };
+  switch (pl.MT) {
+    case 1: return go(small_m_kernel<D, BITS, 1, CB_SMEM>);
+    case 2: return go(small_m_kernel<D, BITS, 2, CB_SMEM>);
+    case 4: return go(small_m_kernel<D, BITS, 4, CB_SMEM>);
+    case 8: return go(small_m_kernel<D, BITS, 8, CB_SMEM>);
+    default: return go(small_m_kernel<D, BITS, 16, CB_SMEM>);
+  }
+}
+
+template <int D, int BITS>
+cudaError_t launch_fast_cb(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  return pl.cb_smem ? launch_fast_mt<D, BITS, true>(pl, p, s) : launch_fast_mt<D, BITS, false>(pl, p, s);
+}
+
+cudaError_t launch_generic(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  auto go = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+    if (e != cudaSuccess) return e;
+    kern<<<pl.grid, pl.warps * 32, pl.smem, s>>>(p);
+    return cudaGetLastError();
+  };
+  switch (pl.MT) {
+    case 1: return go(small_m_generic_kernel<1>);
+    case 2: return go(small_m_generic_kernel<2>);
+    case 4: return go(small_m_generic_kernel<4>);
+    case 8: return go(small_m_generic_kernel<8>);
+    default: return go(small_m_generic_kernel<16>);
+  }
+}
+
+}  // namespace
+
+bool small_m_supported(const sacq_layer* L) {
+  return L->d.index_bits <= 24 && L->d.vector_dim <= 64;
+}
+
+int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M) {
+  if (M <= 0) return sacq_workspace_counter_bytes();
+  const Plan pl = make_plan(L, M);
+  int64_t bytes = sacq_workspace_counter_bytes();
+  if (pl.num_sg > 1) bytes += (int64_t)pl.num_sg * M * L->d.out_features * (int64_t)sizeof(float);
+  return bytes;
+}
+
+int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                   void* ws, int64_t ws_bytes, cudaStream_t s) {
+  const sacq_layer_desc& d = L->d;
+  if (M == 0 || d.out_features == 0) return SACQ_OK;
+  if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
+  const Plan pl = make_plan(L, M);
+  if (pl.smem > kSmemBudget)
+    return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel needs %zu bytes of shared memory", pl.smem);
+  const int64_t need = small_m_workspace_bytes(L, M);
+  if ((int64_t)pl.chunks * pl.row_blocks * (int64_t)sizeof(int) > sacq_workspace_counter_bytes())
+    return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: %d x %d row-block counters exceed the counter region",
+                     pl.chunks, pl.row_blocks);
+  if (pl.num_sg > 1 && (ws == nullptr || ws_bytes < need))
+    return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given", (long long)need,
+                     (long long)ws_bytes);
+  if (pl.num_sg > 1 && reinterpret_cast<uintptr_t>(ws) % 16 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
+
+  SmallMParams p{};
+  p.packed = static_cast<const uint8_t*>(d.packed);
+  p.cb_f16 = L->cb_f16;
+  p.cb_bf16 = static_cast<const uint16_t*>(d.codebook);
+  p.scales = static_cast<const uint16_t*>(d.scales);
+  p.bias = static_cast<const uint16_t*>(d.bias);
+  p.q = static_cast<const uint8_t*>(q);
+  p.act_scale = scale;
+  p.y = static_cast<uint16_t*>(y);
+  p.counters = static_cast<int*>(ws);
+  p.partial = ws ? reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + sacq_workspace_counter_bytes()) : nullptr;
+  p.ldy = ldy;
+  p.row_bytes = L->row_bits / 8;
+  p.N = (int)d.out_features; p.K = (int)d.in_features; p.M = (int)M;
+  p.vpr = (int)L->vectors_per_row;
+  p.d = d.vector_dim; p.bits = d.index_bits;
+  p.num_groups = (int)L->num_groups; p.group_size = d.group_size;
+  p.C = d.codebook_size;
+  p.span_idx = pl.span_idx; p.spans_per_row = pl.spans_per_row; p.spans_per_item = pl.spans_per_item;
+  p.num_sg = pl.num_sg; p.row_blocks = pl.row_blocks; p.chunks = pl.chunks; p.num_items = pl.num_items;
+  uint32_t sb = (uint32_t)d.shift_bf16 << 16;
+  memcpy(&p.shift, &sb, sizeof(float));
+
+  cudaError_t e;
+  if (pl.fast) {
+    if (reinterpret_cast<uintptr_t>(q) % 8 != 0 || d.in_features % 8 != 0)
+      return set_error(SACQ_ERR_ALIGNMENT, "quantized activations must be 8-byte aligned with K %% 8 == 0");
+    p.out_mul = ldexpf(1.f, -L->cb_exp_shift);
+    if (pl.D == 8 && pl.BITS == 12) e = launch_fast_cb<8, 12>(pl, p, s);
+    else if (pl.D == 8 && pl.BITS == 8) e = launch_fast_cb<8, 8>(pl, p, s);
+    else if (pl.D == 8 && pl.BITS == 16) e = launch_fast_cb<8, 16>(pl, p, s);
+    else if (pl.D == 4 && pl.BITS == 12) e = launch_fast_cb<4, 12>(pl, p, s);
+    else if (pl.D == 4 && pl.BITS == 8) e = launch_fast_cb<4, 8>(pl, p, s);
+    else e = launch_fast_cb<4, 16>(pl, p, s);
+  } else {
+    p.out_mul = 1.f;
+    e = launch_generic(pl, p, s);
+  }
+  count_launch();
+  if (e != cudaSuccess) return cuda_fail(e, "small-M launch");
+  return SACQ_OK;
+}
+
+}  // namespace sacq

@@ -1,0 +1,298 @@
+"""Drop-in quantized linear module backed by the sm_100a kernels.
+
+Mirrors ``PrecomputedPackedVectorCodebookLinear`` of the reference
+(gr00t_libero/sources/libero_pro_eval/Isaac-GR00T-N1.7/gr00t/eval/cosmos_quant_shim.py:313-541):
+same constructor ``(payload, bias, device)``, same registered buffers and attributes
+(``codebook``, ``packed_indices``, ``scales``, ``shift``, ``bias``, ``in_features``,
+``out_features``, ``group_size``, ``vector_dim``, ``index_bits``, ``index_shape``,
+``index_window_bytes``, ``runtime_backend``, ``runtime_scope``,
+``runtime_kernel_eligible``), same ``dequantize_weight()`` result bit for bit, and a
+``forward(x)`` that takes any ``[..., K]`` tensor and returns ``[..., N]`` in ``x.dtype``.
+
+What differs is how ``forward`` computes: instead of materialising the bf16 weight and
+calling a dense GEMM, it quantizes the activations per token to FP8 e4m3 and runs the
+packed-index GEMM kernels (W1.5A8).  There is one backend and no CPU path: constructing
+the module on a non-CUDA device raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from .packing import index_bits_for, index_window_bytes, pack_indices
+
+_REQUIRED = ("codebook", "scales", "in_features", "out_features", "group_size", "vector_dim")
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class _Workspace:
+    """Per-device scratch shared by the layers of a process: split-K partial sums and the
+    zero-initialised arrival counters of the small-M kernel, plus the FP8 activation
+    staging buffers.  Grown on demand outside captured regions."""
+
+    _by_device: dict[int, "_Workspace"] = {}
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.ws = None
+        self.q = None
+        self.scale = None
+
+    @classmethod
+    def get(cls, device: torch.device) -> "_Workspace":
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        w = cls._by_device.get(idx)
+        if w is None:
+            w = cls(torch.device("cuda", idx))
+            cls._by_device[idx] = w
+        return w
+
+    def scratch(self, nbytes: int) -> torch.Tensor:
+        if self.ws is None or self.ws.numel() < nbytes:
+            self.ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=self.device)
+        return self.ws
+
+    def act(self, m: int, k: int):
+        if self.q is None or self.q.numel() < m * k:
+            self.q = torch.empty(max(m * k, 1 << 16), dtype=torch.uint8, device=self.device)
+        if self.scale is None or self.scale.numel() < m:
+            self.scale = torch.empty(max(m, 1024), dtype=torch.float32, device=self.device)
+        return self.q, self.scale
+
+
+class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
+    """``packed_vector_codebook_v1`` layer executed by libsacq_b200."""
+
+    def __init__(self, payload: dict, bias: torch.Tensor | None, device: str):
+        super().__init__()
+        missing = set(_REQUIRED).difference(payload)
+        if missing:
+            raise ValueError(f"Packed codebook payload is missing: {sorted(missing)}")
+        if "indices" not in payload and "packed_indices" not in payload:
+            raise ValueError("Packed codebook payload requires indices or packed_indices")
+        device_obj = torch.device(device)
+        if device_obj.type != "cuda":
+            raise ValueError("sacq_b200 runs on CUDA devices only; there is no CPU path")
+        if device_obj.index is None:
+            device_obj = torch.device("cuda", torch.cuda.current_device())
+        self._lib = _lib.load()                       # raises if the CUDA library is missing
+        self.in_features = int(payload["in_features"])
+        self.out_features = int(payload["out_features"])
+        self.group_size = int(payload["group_size"])
+        self.vector_dim = int(payload["vector_dim"])
+        codebook = torch.as_tensor(payload["codebook"]).to(device=device_obj, dtype=torch.bfloat16).contiguous()
+        self.register_buffer("codebook", codebook)
+
+        if "packed_indices" in payload:
+            self.index_bits = int(payload["index_bits"])
+            self.index_shape = tuple(int(x) for x in payload["index_shape"])
+            packed_source = torch.as_tensor(payload["packed_indices"])
+            if packed_source.dtype != torch.uint8:
+                packed_source = packed_source.to(torch.uint8)
+            if packed_source.ndim != 1:
+                raise ValueError(f"packed_indices must be flat, got shape={tuple(packed_source.shape)}")
+            if self.index_bits < 1 or self.index_bits > 56:
+                raise ValueError(f"index_bits must be in [1, 56], got {self.index_bits}")
+        else:
+            # an unpacked payload (uint8 or int32 indices) is serialised once at load time;
+            # the kernels only ever see the bit stream
+            source = torch.as_tensor(payload["indices"])
+            self.index_shape = tuple(int(x) for x in source.shape)
+            self.index_bits = index_bits_for(codebook.shape[0])
+            packed_source = pack_indices(source, self.index_bits)
+        expected_bytes = (math.prod(self.index_shape) * self.index_bits + 7) // 8
+        if packed_source.numel() != expected_bytes:
+            raise ValueError(
+                f"packed_indices has {packed_source.numel()} bytes, expected {expected_bytes} "
+                f"for shape={self.index_shape}, index_bits={self.index_bits}")
+        self.index_window_bytes = index_window_bytes(self.index_bits)
+        guard_bytes = self.index_window_bytes - 1
+        # the buffer the attribute exposes has the reference's length (stream + window guard);
+        # its storage is longer so the kernels' 128-bit reads stay inside the allocation
+        storage = torch.zeros(expected_bytes + guard_bytes + _lib.SACQ_PACKED_GUARD_BYTES + 16,
+                              dtype=torch.uint8, device=device_obj)
+        storage[:expected_bytes].copy_(packed_source.to(device_obj))
+        self._packed_storage = storage
+        self.register_buffer("packed_indices", storage[: expected_bytes + guard_bytes])
+        self.indices = None
+        self._packed_bytes = expected_bytes
+
+        self.register_buffer("scales", torch.as_tensor(payload["scales"]).to(device=device_obj, dtype=torch.bfloat16)
+                             .contiguous())
+        self.register_buffer("shift", torch.as_tensor(payload.get("shift", 0.0)).to(device=device_obj,
+                                                                                     dtype=torch.bfloat16))
+        if bias is None:
+            self.bias = None
+        else:
+            self.register_buffer("bias", bias.detach().to(device=device_obj, dtype=torch.bfloat16).contiguous())
+
+        self.runtime_backend = "sacq_b200"
+        self.runtime_scope = "unknown"
+        expected_index_shape = None
+        if (self.vector_dim > 0 and self.group_size % self.vector_dim == 0
+                and self.in_features % self.group_size == 0):
+            expected_index_shape = (self.out_features, self.in_features // self.group_size,
+                                    self.group_size // self.vector_dim)
+        if self.index_shape != expected_index_shape:
+            raise ValueError(f"index_shape {self.index_shape} does not match geometry {expected_index_shape}")
+        if self.shift.numel() != 1:
+            raise ValueError("shift must be a scalar")
+        if tuple(self.scales.shape) != (self.out_features, self.in_features // self.group_size):
+            raise ValueError(f"scales shape {tuple(self.scales.shape)} does not match geometry")
+        if self.codebook.ndim != 2 or self.codebook.shape[1] != self.vector_dim:
+            raise ValueError(f"codebook shape {tuple(self.codebook.shape)} does not match vector_dim")
+        self.runtime_kernel_eligible = True
+        self._handle = None
+        self._create_handle()
+
+    # ------------------------------------------------------------------ handle
+    def _create_handle(self):
+        dev = self.codebook.device
+        torch.cuda.synchronize(dev)          # uploads above must have landed before the tables are built
+        desc = _lib.LayerDesc()
+        desc.struct_size = ctypes.sizeof(_lib.LayerDesc)
+        desc.device = dev.index
+        desc.out_features = self.out_features
+        desc.in_features = self.in_features
+        desc.group_size = self.group_size
+        desc.vector_dim = self.vector_dim
+        desc.codebook_size = int(self.codebook.shape[0])
+        desc.index_bits = self.index_bits
+        desc.packed = self._packed_storage.data_ptr()
+        desc.packed_bytes = self._packed_bytes
+        desc.codebook = self.codebook.data_ptr()
+        desc.scales = self.scales.data_ptr()
+        desc.bias = self.bias.data_ptr() if self.bias is not None else None
+        desc.shift_bf16 = int(self.shift.reshape(1).view(torch.int16).item()) & 0xFFFF
+        handle = ctypes.c_void_p()
+        _lib.check(self._lib.sacq_layer_create(ctypes.byref(desc), ctypes.byref(handle)))
+        self._handle = handle
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h is not None and getattr(self, "_lib", None) is not None:
+            try:
+                self._lib.sacq_layer_destroy(h)
+            except Exception:
+                pass
+            self._handle = None
+
+    def _apply(self, fn, recurse=True):
+        # .to()/.cuda() would move the borrowed buffers out from under the handle
+        old = self.codebook.data_ptr()
+        out = super()._apply(fn, recurse)
+        if self.codebook.data_ptr() != old:
+            raise RuntimeError("a sacq_b200 layer is bound to the device it was created on; "
+                               "construct a new module instead of moving it")
+        return out
+
+    # ------------------------------------------------------------------ reference API
+    def dequantize_weight(self) -> torch.Tensor:
+        """[N, K] bf16 reconstruction, bit-identical to the reference's."""
+        w = torch.empty((self.out_features, self.in_features), dtype=torch.bfloat16, device=self.codebook.device)
+        with torch.cuda.device(w.device):
+            _lib.check(self._lib.sacq_dequant_bf16(self._handle, w.data_ptr(), _stream_ptr()))
+        return w
+
+    def quantize_activations(self, x: torch.Tensor):
+        """Per-token FP8 quantization of a ``[M, K]`` bf16 tensor -> (e4m3 [M,K], fp32 [M,1])."""
+        from .activation import quantize_rows
+        return quantize_rows(x, "fp8_e4m3fn")
+
+    def weight_row_scale(self) -> torch.Tensor:
+        """fp32 [N, 1]: max|W[n,:]| / 448 (the A8 recipe's per-output-row weight scale)."""
+        sw = torch.empty((self.out_features, 1), dtype=torch.float32, device=self.codebook.device)
+        with torch.cuda.device(sw.device):
+            _lib.check(self._lib.sacq_weight_row_scale(self._handle, sw.data_ptr(), _stream_ptr()))
+        return sw
+
+    def decode_weight_fp8(self, weight_row_scale: torch.Tensor) -> torch.Tensor:
+        """e4m3 [N, K] = e4m3(clamp(W / row_scale)) decoded straight from the packed stream."""
+        sw = weight_row_scale.to(device=self.codebook.device, dtype=torch.float32).contiguous()
+        if sw.numel() != self.out_features:
+            raise ValueError("weight_row_scale must have out_features entries")
+        wq = torch.empty((self.out_features, self.in_features), dtype=torch.uint8, device=self.codebook.device)
+        with torch.cuda.device(wq.device):
+            _lib.check(self._lib.sacq_decode_weight_fp8(self._handle, sw.data_ptr(), wq.data_ptr(), _stream_ptr()))
+        return wq.view(torch.float8_e4m3fn)
+
+    def linear_a8(self, q: torch.Tensor, scale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """GEMM on already-quantized activations: q e4m3 ``[M, K]``, scale fp32 ``[M]`` -> bf16 ``[M, N]``."""
+        if q.dim() != 2 or q.shape[1] != self.in_features:
+            raise ValueError("q must be [M, in_features]")
+        if not q.is_cuda or q.device != self.codebook.device:
+            raise ValueError("Matching CUDA operands required")
+        if q.element_size() != 1:
+            raise TypeError("q must hold e4m3 bytes")
+        q = q.contiguous()
+        scale = scale.reshape(-1).to(torch.float32).contiguous()
+        m = q.shape[0]
+        if scale.numel() != m:
+            raise ValueError("scale must have one entry per row of q")
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=q.device)
+        ws = _Workspace.get(q.device)
+        need = int(self._lib.sacq_workspace_bytes(self._handle, m))
+        buf = ws.scratch(need)
+        with torch.cuda.device(q.device):
+            _lib.check(self._lib.sacq_linear_a8(self._handle, q.data_ptr(), scale.data_ptr(), m, out.data_ptr(),
+                                                out.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
+        return out
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Linear shape mismatch")
+        if not x.is_cuda or x.device != self.codebook.device:
+            raise ValueError("Matching CUDA operands required")
+        a = x.reshape(-1, self.in_features)
+        if a.dtype != torch.bfloat16:
+            a = a.to(torch.bfloat16)
+        if a.stride(-1) != 1:
+            a = a.contiguous()
+        m = a.shape[0]
+        y = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=x.device)
+        if m > 0 and self.out_features > 0:
+            ws = _Workspace.get(x.device)
+            need = int(self._lib.sacq_workspace_bytes(self._handle, m))
+            buf = ws.scratch(need)
+            q, s = ws.act(m, self.in_features)
+            with torch.cuda.device(x.device):
+                _lib.check(self._lib.sacq_linear_bf16(
+                    self._handle, a.data_ptr(), a.stride(0), m, q.data_ptr(), s.data_ptr(), y.data_ptr(),
+                    y.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
+        y = y.reshape(*x.shape[:-1], self.out_features)
+        return y if x.dtype == torch.bfloat16 else y.to(x.dtype)
+
+    # ------------------------------------------------------------------ extras
+    def set_kernel(self, which: str | int) -> None:
+        """Force a GEMM kernel: 'auto' (0), 'small' (1) or 'large' (2)."""
+        code = {"auto": 0, "small": 1, "large": 2}.get(which, which)
+        _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
+
+    def kernel_for(self, m: int) -> str:
+        k = self._lib.sacq_layer_kernel_for(self._handle, m)
+        if k < 0:
+            _lib.check(k)
+        return {1: "small", 2: "large"}[k]
+
+    def device_status(self) -> int:
+        st = ctypes.c_int(0)
+        _lib.check(self._lib.sacq_layer_status(self._handle, ctypes.byref(st)))
+        return st.value
+
+    def resident_bytes(self) -> int:
+        """Device bytes held for this layer: payload buffers plus derived tables."""
+        own = sum(t.numel() * t.element_size() for t in (self._packed_storage, self.codebook, self.scales, self.shift))
+        if self.bias is not None:
+            own += self.bias.numel() * 2
+        return own + int(self._lib.sacq_layer_resident_bytes(self._handle))
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, vector_dim={self.vector_dim}, "
+                f"codebook={tuple(self.codebook.shape)}, index_bits={self.index_bits}, group_size={self.group_size}")

@@ -1,0 +1,330 @@
+"""GPU parity tests: every kernel, called through the C ABI (via the ctypes-backed
+module), against the CPU oracle and the reference-generated fixtures.
+
+Bars: bit-exact for the weight reconstruction, the activation quantizer and the FP8
+weight producer; relative Frobenius error <= 1e-2 for the quantized linear against
+reconstruct-then-matmul on identical quantized activations."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_layer_names, load_golden
+from oracle import sacq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+GEMM_TOL = 1e-2          # relative Frobenius norm, the tolerance the task states
+
+
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+def bf16_bits(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def from_bf16_bits(a, device="cuda"):
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(torch.bfloat16).to(device)
+
+
+def payload_from_golden(g, packed=True):
+    p = dict(codebook=from_bf16_bits(g["codebook"], "cpu"), scales=from_bf16_bits(g["scales"], "cpu"),
+             shift=from_bf16_bits(g["shift"], "cpu").reshape(()), in_features=int(g["K"]),
+             out_features=int(g["N"]), group_size=int(g["G"]), vector_dim=int(g["d"]))
+    if packed:
+        p.update(packed_indices=torch.from_numpy(g["packed"]), index_bits=int(g["index_bits"]),
+                 index_shape=tuple(g["indices"].shape))
+    else:
+        dt = torch.uint8 if str(g["indices_dtype"]) == "torch.uint8" else torch.int32
+        p["indices"] = torch.from_numpy(g["indices"]).to(dt)
+    return p
+
+
+def module_from_golden(g, packed=True):
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    bias = from_bf16_bits(g["bias"], "cpu") if "bias" in g else None
+    return PrecomputedPackedVectorCodebookLinear(payload_from_golden(g, packed), bias, "cuda")
+
+
+def oracle_weight(payload):
+    """bf16 bits [N, K] from a payload dict via the numpy oracle."""
+    cb = bf16_bits(payload["codebook"])
+    sc = bf16_bits(payload["scales"])
+    sh = int(bf16_bits(payload["shift"].reshape(1))[0])
+    return O.dequantize_packed_bf16_bits(payload["packed_indices"].numpy(), payload["index_bits"], cb, sc, sh,
+                                         payload["out_features"], payload["in_features"], payload["group_size"])
+
+
+# --------------------------------------------------------------------------- reconstruction
+
+@pytest.mark.parametrize("name", golden_layer_names())
+@pytest.mark.parametrize("packed", [True, False])
+def test_dequant_matches_reference_fixture(name, packed):
+    _need_gpu()
+    g = load_golden("layer_" + name)
+    mod = module_from_golden(g, packed)
+    w = mod.dequantize_weight()
+    assert w.dtype == torch.bfloat16 and tuple(w.shape) == (int(g["N"]), int(g["K"]))
+    assert np.array_equal(bf16_bits(w), g["w_ref"])
+    assert mod.index_bits == int(g["index_bits"])
+    assert mod.packed_indices.numel() == g["packed"].size + mod.index_window_bytes - 1
+    assert mod.device_status() == 0
+
+
+@pytest.mark.parametrize("d,C,N,K", [(8, 4096, 2048, 2048), (8, 256, 512, 2048), (8, 65536, 256, 2048),
+                                     (4, 4096, 512, 2048), (2, 16, 64, 96), (16, 64, 32, 128), (3, 8, 10, 12)])
+def test_dequant_full_size_against_oracle(d, C, N, K):
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, seed=11, iters=1, device="cuda",
+                     sample_size=max(65536, C))
+    mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
+    w = mod.dequantize_weight()
+    assert np.array_equal(bf16_bits(w), oracle_weight(p))
+    # idempotent and leaves the payload untouched
+    assert torch.equal(mod.dequantize_weight(), w)
+    assert np.array_equal(mod.packed_indices[: p["packed_indices"].numel()].cpu().numpy(), p["packed_indices"].numpy())
+
+
+# --------------------------------------------------------------------------- activation quantizer
+
+@pytest.mark.parametrize("name", golden_layer_names())
+def test_act_quant_matches_reference_fixture(name):
+    _need_gpu()
+    from sacq_b200 import quantize_rows
+    g = load_golden("layer_" + name)
+    q, s = quantize_rows(from_bf16_bits(g["x"]), "fp8_e4m3fn")
+    assert q.dtype == torch.float8_e4m3fn and tuple(s.shape) == (g["x"].shape[0], 1)
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), g["q"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), g["act_scale"].view(np.uint32))
+
+
+@pytest.mark.parametrize("M,K", [(1, 2048), (4, 2048), (16, 2048), (64, 6144), (3, 100), (5, 8200), (2, 7), (300, 1536)])
+def test_act_quant_against_oracle(M, K):
+    _need_gpu()
+    from sacq_b200 import quantize_rows
+    from sacq_b200.synthetic import make_activations
+    x = make_activations(M, K, seed=M * 7 + K)
+    if M > 2:
+        x[1].zero_()
+        x[2] *= 1e-4
+    xq, xs = O.quantize_rows_e4m3(bf16_bits(x))
+    q, s = quantize_rows(x.cuda())
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), xq)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), xs.view(np.uint32))
+    # a row-strided view gives the same bytes
+    wide = torch.zeros(M, K + 24, dtype=torch.bfloat16, device="cuda")
+    wide[:, :K] = x.cuda()
+    q2, s2 = quantize_rows(wide[:, :K])
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s2, s)
+
+
+def test_act_quant_every_bf16_value():
+    _need_gpu()
+    from sacq_b200 import quantize_rows
+    bits = np.arange(65536, dtype=np.uint16)
+    vals = O.bf16_bits_to_f32(bits)
+    keep = np.isfinite(vals)
+    rows = bits[keep].reshape(-1, 1)                      # one value per row: scale = |v|/448, q = +-448
+    rows = np.concatenate([rows, np.zeros_like(rows)], axis=1)
+    xq, xs = O.quantize_rows_e4m3(rows)
+    q, s = quantize_rows(from_bf16_bits(rows))
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), xq)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), xs.view(np.uint32))
+    # all values in one row against a fixed scale: every rounding boundary of e4m3
+    f = load_golden("formats")
+    row = bits[keep & (np.abs(vals) <= 448.0)]
+    row = np.concatenate([row, O.f32_to_bf16_bits(np.array([448.0], dtype=np.float32))]).reshape(1, -1)
+    q1, s1 = quantize_rows(from_bf16_bits(row))
+    assert float(s1[0, 0]) == 1.0
+    assert np.array_equal(q1.view(torch.uint8).cpu().numpy()[0, :-1], f["e4m3_of_all_bf16"][row[0, :-1]])
+
+
+# --------------------------------------------------------------------------- FP8 weight producer
+
+@pytest.mark.parametrize("name", golden_layer_names())
+def test_weight_fp8_producer_matches_reference_fixture(name):
+    _need_gpu()
+    g = load_golden("layer_" + name)
+    mod = module_from_golden(g)
+    sw = mod.weight_row_scale()
+    assert np.array_equal(sw.cpu().numpy().view(np.uint32), g["w_scale"].view(np.uint32))
+    wq = mod.decode_weight_fp8(sw)
+    assert np.array_equal(wq.view(torch.uint8).cpu().numpy(), g["wq"])
+
+
+# --------------------------------------------------------------------------- quantized linear
+
+def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=("auto",)):
+    ref = O.linear_a8_reference(q_bits, s, w_bits, bias_bits)
+    q = torch.from_numpy(q_bits).cuda().view(torch.float8_e4m3fn)
+    sc = torch.from_numpy(s).cuda()
+    outs = {}
+    for k in kernels:
+        mod.set_kernel(k)
+        y = mod.linear_a8(q, sc)
+        torch.cuda.synchronize()
+        assert y.dtype == torch.bfloat16
+        err = O.rel_frobenius(y.float().cpu().numpy(), ref)
+        assert err <= GEMM_TOL, (k, err)
+        y2 = mod.linear_a8(q, sc)
+        assert torch.equal(y, y2), "forward must be deterministic"
+        outs[k] = (y, err)
+    mod.set_kernel("auto")
+    assert mod.device_status() == 0
+    return outs
+
+
+@pytest.mark.parametrize("name", golden_layer_names())
+def test_linear_matches_reference_fixture(name):
+    _need_gpu()
+    g = load_golden("layer_" + name)
+    mod = module_from_golden(g)
+    outs = _check_linear(mod, g["q"], g["act_scale"], g["w_ref"], g.get("bias"))
+    y, _ = outs["auto"]
+    assert O.rel_frobenius(y.float().cpu().numpy(), g["y_ref"]) <= GEMM_TOL
+    # module forward on the bf16 input = fused quantizer + GEMM, same bytes
+    yf = mod(from_bf16_bits(g["x"]))
+    assert torch.equal(yf, y)
+    # a [B, T, K] input keeps its leading shape
+    x3 = from_bf16_bits(g["x"]).reshape(1, g["x"].shape[0], -1)
+    assert tuple(mod(x3).shape) == (1, g["x"].shape[0], int(g["N"]))
+    assert mod(x3.float()).dtype == torch.float32
+
+
+CONFIG0 = [(2048, 2048, 8, 4096)]
+DECODE = [(2048, 2048), (2048, 1024), (2048, 6144), (6144, 2048)]      # (K, N)
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_linear_config0(M):
+    """K = N = 2048, d = 8, 4096 codewords, M in {1, 4, 16}."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(2048, 2048, seed=0, device="cuda")
+    mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
+    w_bits = oracle_weight(p)
+    assert np.array_equal(bf16_bits(mod.dequantize_weight()), w_bits)
+    q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, 2048)))
+    _check_linear(mod, q_bits, s, w_bits, None)
+
+
+@pytest.mark.parametrize("K,N", DECODE)
+def test_linear_decode_shapes(K, N):
+    """The decoder-linear sweep: every M of the sweep on one layer per shape."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, seed=K + N, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(5)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    for M in (1, 2, 4, 8, 16, 32, 64):
+        q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M)))
+        _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias))
+
+
+@pytest.mark.parametrize("d,C", [(8, 256), (8, 4096), (8, 65536), (4, 4096)])
+@pytest.mark.parametrize("M", [1, 16, 256])
+def test_linear_mixed_bits(d, C, M):
+    """1 / 1.5 / 2 / 3 bits per weight on a 2048 x 6144 layer."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    N, K = 6144, 2048
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, seed=C + d, device="cuda", iters=1,
+                     sample_size=max(65536, 2 * C), fit=(C < 65536))
+    mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
+    w_bits = oracle_weight(p)
+    q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 1)))
+    _check_linear(mod, q_bits, s, w_bits, None)
+
+
+@pytest.mark.parametrize("N,K,d,C,G", [(40, 128, 4, 32, 64), (100, 256, 4, 2048, 64), (33, 512, 8, 4096, 256),
+                                       (7, 24, 4, 8, 24), (64, 1536, 4, 128, 64)])
+def test_linear_grouped_and_ragged_geometries(N, K, d, C, G):
+    """Group-64 scales, odd index widths, rows that are not byte aligned, N % 32 != 0."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N, device="cuda", iters=1)
+    p["shift"] = torch.tensor(0.0078125, dtype=torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
+    w_bits = oracle_weight(p)
+    assert np.array_equal(bf16_bits(mod.dequantize_weight()), w_bits)
+    for M in (1, 3, 17):
+        q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M)))
+        _check_linear(mod, q_bits, s, w_bits, None)
+
+
+def test_linear_properties_and_edges():
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
+    from sacq_b200.synthetic import make_activations, make_payload
+    N, K = 2048, 6144
+    p = make_payload(N, K, seed=4, device="cuda", iters=1)
+    mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
+    x = make_activations(8, K, seed=9).cuda()
+    q, s = quantize_rows(x)
+    y = mod.linear_a8(q, s)
+    # against the dense product of the library's own (bit-exact) reconstruction, at full size
+    dense = (q.float() @ mod.dequantize_weight().float().t()) * s
+    assert O.rel_frobenius(y.float().cpu().numpy(), dense.cpu().numpy()) <= GEMM_TOL
+    # scaling the activation scales scales the output (up to the bf16 output rounding)
+    y2 = mod.linear_a8(q, s * 2.0)
+    assert O.rel_frobenius(y2.float().cpu().numpy(), 2.0 * y.float().cpu().numpy()) < 1e-6
+    # zero activations give the bias (zero here); empty batch gives an empty result
+    z = mod.linear_a8(torch.zeros_like(q), s)
+    assert float(z.float().abs().max()) == 0.0
+    e = mod(torch.zeros(0, K, dtype=torch.bfloat16, device="cuda"))
+    assert tuple(e.shape) == (0, N)
+    # output into a wider row pitch leaves the padding untouched
+    out = torch.full((8, N + 64), 7.0, dtype=torch.bfloat16, device="cuda")
+    mod.linear_a8(q, s, out=out[:, :N])
+    assert torch.equal(out[:, :N], y) and float(out[:, N:].float().min()) == 7.0
+    # the arrival counters are back to zero after every call
+    from sacq_b200.linear import _Workspace
+    ws = _Workspace.get(q.device).ws
+    assert int(ws[: mod._lib.sacq_workspace_counter_bytes()].sum()) == 0
+    with pytest.raises(ValueError):
+        mod(torch.zeros(2, K - 8, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        mod(torch.zeros(2, K, dtype=torch.bfloat16))
+
+
+def test_c_abi_error_codes_on_device():
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, _lib
+    from sacq_b200.synthetic import make_payload
+    p = make_payload(64, 256, seed=1, device="cuda", iters=1)
+    mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
+    lib = mod._lib
+    y = torch.empty(4, 64, dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros(4, 256, dtype=torch.uint8, device="cuda")
+    s = torch.ones(4, device="cuda")
+    assert lib.sacq_linear_a8(mod._handle, q.data_ptr(), s.data_ptr(), 4, y.data_ptr(), 32, None, 0, None) == -1
+    assert "ldy" in _lib.last_error()
+    assert lib.sacq_linear_a8(mod._handle, q.data_ptr(), s.data_ptr(), -1, y.data_ptr(), 64, None, 0, None) == -1
+    assert lib.sacq_linear_a8(mod._handle, None, s.data_ptr(), 4, y.data_ptr(), 64, None, 0, None) == -1
+    need = lib.sacq_workspace_bytes(mod._handle, 4)
+    if need > lib.sacq_workspace_counter_bytes():
+        assert lib.sacq_linear_a8(mod._handle, q.data_ptr(), s.data_ptr(), 4, y.data_ptr(), 64, None, 0, None) == -4
+    assert lib.sacq_layer_set_kernel(mod._handle, 9) == -1
+    assert lib.sacq_launch_count() > 0
+    # misaligned packed pointer is refused at creation
+    d = _lib.LayerDesc()
+    d.struct_size = ctypes.sizeof(d)
+    d.device = 0
+    d.out_features, d.in_features, d.group_size, d.vector_dim, d.codebook_size, d.index_bits = 64, 256, 256, 8, 4096, 12
+    d.packed = mod._packed_storage.data_ptr() + 4
+    d.packed_bytes = 64 * 32 * 12 // 8
+    d.codebook = mod.codebook.data_ptr()
+    d.scales = mod.scales.data_ptr()
+    h = ctypes.c_void_p()
+    assert lib.sacq_layer_create(ctypes.byref(d), ctypes.byref(h)) == -3
