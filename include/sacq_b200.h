@@ -131,9 +131,10 @@ SACQ_API int sacq_linear_bf16(const sacq_layer_t* layer, const void* x_bf16, int
                      float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
                      void* stream);
 
-/* Forces one of the two GEMM kernels (for tests and benchmarks): 0 = automatic,
- * 1 = small-M kernel, 2 = large-M kernel.  Returns SACQ_ERR_UNSUPPORTED from the
- * next forward if the forced kernel cannot run the layer. */
+/* Forces a GEMM kernel (for tests and benchmarks): 0 = automatic, 1 = small-M kernel
+ * (its own choice of variant), 2 = large-M kernel, 3 = small-M CUDA-core variant,
+ * 4 = small-M warp-MMA variant.  Returns SACQ_ERR_UNSUPPORTED from the next forward if
+ * the forced kernel cannot run the layer. */
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* layer, int which);
 /* Which kernel a forward with M rows would use (1 or 2), or a negative error. */
 SACQ_API int sacq_layer_kernel_for(const sacq_layer_t* layer, int64_t M);

@@ -62,7 +62,8 @@ int64_t small_m_slab_rows(const sacq_layer* L) {
 }
 
 int pick_kernel(const sacq_layer* L, int64_t M) {
-  if (L->force_kernel == 1) return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
+  if (L->force_kernel == 1 || L->force_kernel == 3 || L->force_kernel == 4)
+    return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 2) return large_m_supported(L) ? 2 : SACQ_ERR_UNSUPPORTED;
   // A shape rule, not a backend switch: the CUDA-core kernel wins while the grid of
   // 128-row tensor-core tiles cannot fill the device.
@@ -213,7 +214,7 @@ SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, 
 
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
-  if (which < 0 || which > 2) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in {0,1,2}", which);
+  if (which < 0 || which > 4) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..4", which);
   L->force_kernel = which;
   return SACQ_OK;
 }

@@ -22,67 +22,13 @@
 //
 // Roofline: bound by HBM on the packed indices in principle (1.5 bits per weight); in
 // practice the shared-memory gather rate (one 16-byte lookup per 8 weights) caps it.
-#include "common.cuh"
-
-#include <math.h>
-#include <string.h>
-
-#include <type_traits>
+#include "small_m.cuh"
 
 namespace sacq {
 
+using namespace smallm;
+
 namespace {
-
-constexpr int kSpanIdx = 32;   // indices a lane consumes per span
-constexpr int kMaxWarps = 8;
-
-struct SmallMParams {
-  const uint8_t* packed;
-  const __half* cb_f16;        // [C, D] scaled by 2^cb_exp_shift
-  const uint16_t* cb_bf16;     // [C, d] original (generic kernel)
-  const uint16_t* scales;      // bf16 [N, num_groups]
-  const uint16_t* bias;        // bf16 [N] or null
-  const uint8_t* q;            // e4m3 [M, K]
-  const float* act_scale;      // [M]
-  uint16_t* y;                 // bf16 [M, ldy]
-  float* partial;              // [num_sg][M][N] (only when num_sg > 1)
-  int* counters;               // [chunks * row_blocks]
-  int64_t ldy;
-  int64_t row_bytes;           // bytes per packed row (fast kernel)
-  int N, K, M;
-  int vpr;                     // vectors per row
-  int d, bits;
-  int num_groups, group_size;
-  int C;
-  int span_idx;                // generic kernel: vectors per span
-  int spans_per_row;           // vpr / span
-  int spans_per_item;          // consecutive spans one item covers
-  int num_sg;                  // span groups per row = ceil(spans_per_row / spans_per_item)
-  int row_blocks;              // ceil(N / 32)
-  int chunks;                  // ceil(M / MT)
-  int64_t num_items;
-  float out_mul;               // 2^-cb_exp_shift (fast) or 1 (generic)
-  float shift;
-};
-
-__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
-
-// e4m3 x4 (one 32-bit word) -> 2 x half2, exact.
-__device__ __forceinline__ void e4m3x4_to_h2(uint32_t v, uint32_t& lo, uint32_t& hi) {
-  const __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xffff), __NV_E4M3);
-  const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v >> 16), __NV_E4M3);
-  lo = (uint32_t)a.x | ((uint32_t)a.y << 16);
-  hi = (uint32_t)b.x | ((uint32_t)b.y << 16);
-}
-
-template <int BITS>
-__device__ __forceinline__ uint32_t field(const uint32_t (&w)[BITS], int i) {
-  const int bit = i * BITS;
-  const int word = bit >> 5;
-  const int off = bit & 31;
-  if (off + BITS <= 32) return (w[word] >> off) & ((1u << BITS) - 1u);
-  return __funnelshift_r(w[word], w[word + 1 < BITS ? word + 1 : word], off) & ((1u << BITS) - 1u);
-}
 
 // Adds the partial sums of one row block in span-group order and writes y.  Called by
 // the last warp to arrive (or directly when K is not split).  `val` holds this warp's
@@ -127,10 +73,16 @@ __device__ __forceinline__ void finish_rows(const SmallMParams& p, int chunk, in
 
 // Fast path: D in {4, 8}, BITS in {8, 12, 16}, rows of the packed stream 16-byte aligned,
 // group_size a multiple of kSpanIdx * D.
+//
+// The inner loop is deliberately NOT unrolled over the whole span: a warp runs an item
+// once, so straight-line code would be fetched from the instruction cache exactly once
+// per warp; the body handles 8 indices (BITS/4 words) and is reused 4 times per span.
 template <int D, int BITS, int MT, bool CB_SMEM>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_kernel(const SmallMParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;   // D halfs
+  constexpr int WPG = BITS / 4;                                          // words per group of 8 indices
+  constexpr int kFlush = 32 / D;        // indices between fp16 -> fp32 flushes (32 products)
   CwVec* cbs = reinterpret_cast<CwVec*>(smem);
   const int cb_bytes = CB_SMEM ? p.C * D * 2 : 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,114 +91,148 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_kernel(const SmallM
   CwVec* xs = reinterpret_cast<CwVec*>(smem + cb_bytes) + (size_t)warp * MT * kSpanIdx;
 
   if (CB_SMEM) {
+    // asynchronous copies: every thread issues all of its 16-byte chunks before anyone waits
     const uint4* src = reinterpret_cast<const uint4*>(p.cb_f16);
     uint4* dst = reinterpret_cast<uint4*>(smem);
     const int n16 = cb_bytes >> 4;
-    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldg(src + i);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) cp_async_16(dst + i, src + i);
   }
-  __syncthreads();
+
+  // state of the current item
+  int sg = 0, rb = 0, chunk = 0, m0 = 0, n = 0, nr = 0, sp_begin = 0, sp_end = 0;
+  bool row_ok = false;
+  const uint32_t* wsrc = nullptr;
+  uint32_t wg[WPG];
+  float xsum[MT];
+
+  auto decode_item = [&](int64_t item) {
+    sg = (int)(item % p.num_sg);
+    const int64_t t1 = item / p.num_sg;
+    rb = (int)(t1 % p.row_blocks);
+    chunk = (int)(t1 / p.row_blocks);
+    m0 = chunk * MT;
+    n = rb * 32 + lane;
+    row_ok = n < p.N;
+    nr = row_ok ? n : p.N - 1;
+    sp_begin = sg * p.spans_per_item;
+    sp_end = min(sp_begin + p.spans_per_item, p.spans_per_row);
+  };
+
+  // Loads the lane's first 8 indices of span `sp` and stages the span's activations as
+  // fp16 in the warp's shared-memory slice: xs[m][i] = q[m0+m, (sp*32+i)*D .. +D).
+  auto load_span = [&](int sp) {
+    wsrc = reinterpret_cast<const uint32_t*>(p.packed + (int64_t)nr * p.row_bytes + (int64_t)sp * (4 * BITS));
+#pragma unroll
+    for (int j = 0; j < WPG; ++j) wg[j] = __ldg(wsrc + j);
+    __syncwarp();                       // previous span's readers are done with xs
+    uint2 o[MT];
+    const int64_t kbyte = ((int64_t)sp * kSpanIdx + lane) * D;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      o[m] = make_uint2(0, 0);
+      if (m0 + m < p.M) {
+        const uint8_t* src = p.q + (int64_t)(m0 + m) * p.K + kbyte;
+        if constexpr (D == 8) o[m] = __ldg(reinterpret_cast<const uint2*>(src));
+        else o[m].x = __ldg(reinterpret_cast<const uint32_t*>(src));
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      CwVec h;
+      e4m3x4_to_h2(o[m].x, h.x, h.y);
+      if constexpr (D == 8) e4m3x4_to_h2(o[m].y, h.z, h.w);
+      xs[m * kSpanIdx + lane] = h;
+      if (p.shift != 0.f) {
+        float t = __low2float(as_h2(h.x)) + __high2float(as_h2(h.x)) + __low2float(as_h2(h.y)) +
+                  __high2float(as_h2(h.y));
+        if constexpr (D == 8)
+          t += __low2float(as_h2(h.z)) + __high2float(as_h2(h.z)) + __low2float(as_h2(h.w)) +
+               __high2float(as_h2(h.w));
+        xsum[m] += warp_sum(t);
+      }
+    }
+    __syncwarp();
+  };
 
   const int64_t total_warps = (int64_t)gridDim.x * nwarps;
-  for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; item < p.num_items; item += total_warps) {
-    // item -> (chunk, rb, sg), sg fastest so neighbouring warps share index sectors
-    const int sg = (int)(item % p.num_sg);
-    const int64_t t1 = item / p.num_sg;
-    const int rb = (int)(t1 % p.row_blocks);
-    const int chunk = (int)(t1 / p.row_blocks);
-    const int m0 = chunk * MT;
-    const int n = rb * 32 + lane;
-    const bool row_ok = n < p.N;
-    const int nr = row_ok ? n : p.N - 1;
-    const int sp_begin = sg * p.spans_per_item;
-    const int sp_end = min(sp_begin + p.spans_per_item, p.spans_per_row);
-
-    float acc[MT];
-    float xsum[MT];
+  int64_t item = (int64_t)warp * gridDim.x + blockIdx.x;
+  bool have = item < p.num_items;
 #pragma unroll
-    for (int m = 0; m < MT; ++m) { acc[m] = 0.f; xsum[m] = 0.f; }
+  for (int m = 0; m < MT; ++m) xsum[m] = 0.f;
+  if (have) {
+    decode_item(item);
+    load_span(sp_begin);                // overlaps the codebook copy
+  }
+  if (CB_SMEM) {
+    cp_async_wait_all();
+    __syncthreads();                    // reached by every warp, with or without an item
+  }
+
+  while (have) {
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
 
     for (int sp = sp_begin; sp < sp_end; ++sp) {
-      // ---- stage this span's activations as fp16: xs[m][i] = q[m0+m, (sp*32+i)*D .. +D)
-      __syncwarp();
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        CwVec o;
-        const int64_t kbyte = ((int64_t)sp * kSpanIdx + lane) * D;
-        if (m0 + m < p.M) {
-          const uint8_t* src = p.q + (int64_t)(m0 + m) * p.K + kbyte;
-          if constexpr (D == 8) {
-            const uint2 v = __ldg(reinterpret_cast<const uint2*>(src));
-            e4m3x4_to_h2(v.x, o.x, o.y);
-            e4m3x4_to_h2(v.y, o.z, o.w);
-          } else {
-            const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(src));
-            e4m3x4_to_h2(v, o.x, o.y);
-          }
-        } else {
-          if constexpr (D == 8) o = make_uint4(0, 0, 0, 0); else o = make_uint2(0, 0);
-        }
-        xs[m * kSpanIdx + lane] = o;
-        if (p.shift != 0.f) {
-          float t = __low2float(as_h2(o.x)) + __high2float(as_h2(o.x)) + __low2float(as_h2(o.y)) +
-                    __high2float(as_h2(o.y));
-          if constexpr (D == 8)
-            t += __low2float(as_h2(o.z)) + __high2float(as_h2(o.z)) + __low2float(as_h2(o.w)) +
-                 __high2float(as_h2(o.w));
-          xsum[m] += warp_sum(t);
-        }
-      }
-      // ---- this lane's 32 indices of row n
-      uint32_t w[BITS];
-      {
-        const uint4* src = reinterpret_cast<const uint4*>(p.packed + (int64_t)nr * p.row_bytes + (int64_t)sp * (4 * BITS));
-#pragma unroll
-        for (int j = 0; j < BITS / 4; ++j) {
-          const uint4 v = __ldg(src + j);
-          w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-        }
-      }
-      __syncwarp();
-
       float sacc[MT];
       __half2 hacc[MT];
 #pragma unroll
       for (int m = 0; m < MT; ++m) { sacc[m] = 0.f; hacc[m] = __float2half2_rn(0.f); }
 
-      constexpr int kFlush = 32 / D;  // indices between fp16 -> fp32 flushes (32 products)
+#pragma unroll 1
+      for (int g = 0; g < kSpanIdx / 8; ++g) {
+        uint32_t wn[WPG];
 #pragma unroll
-      for (int i = 0; i < kSpanIdx; ++i) {
-        const uint32_t idx = field<BITS>(w, i);
-        CwVec c;
-        if constexpr (CB_SMEM) c = cbs[idx];
-        else c = __ldg(reinterpret_cast<const CwVec*>(p.cb_f16) + idx);
+        for (int j = 0; j < WPG; ++j) wn[j] = (g + 1 < kSpanIdx / 8) ? __ldg(wsrc + (g + 1) * WPG + j) : 0u;
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          const CwVec xv = xs[m * kSpanIdx + i];
-          hacc[m] = __hfma2(as_h2(c.x), as_h2(xv.x), hacc[m]);
-          hacc[m] = __hfma2(as_h2(c.y), as_h2(xv.y), hacc[m]);
-          if constexpr (D == 8) {
-            hacc[m] = __hfma2(as_h2(c.z), as_h2(xv.z), hacc[m]);
-            hacc[m] = __hfma2(as_h2(c.w), as_h2(xv.w), hacc[m]);
-          }
-        }
-        if ((i % kFlush) == kFlush - 1) {
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t idx = field8<BITS>(wg, j);
+          CwVec c;
+          if constexpr (CB_SMEM) c = cbs[idx];
+          else c = __ldg(reinterpret_cast<const CwVec*>(p.cb_f16) + idx);
+          const CwVec* xrow = xs + g * 8 + j;
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
-            sacc[m] += __low2float(hacc[m]) + __high2float(hacc[m]);
-            hacc[m] = __float2half2_rn(0.f);
+            const CwVec xv = xrow[m * kSpanIdx];
+            hacc[m] = __hfma2(as_h2(c.x), as_h2(xv.x), hacc[m]);
+            hacc[m] = __hfma2(as_h2(c.y), as_h2(xv.y), hacc[m]);
+            if constexpr (D == 8) {
+              hacc[m] = __hfma2(as_h2(c.z), as_h2(xv.z), hacc[m]);
+              hacc[m] = __hfma2(as_h2(c.w), as_h2(xv.w), hacc[m]);
+            }
+          }
+          if ((j % kFlush) == kFlush - 1) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              sacc[m] += __low2float(hacc[m]) + __high2float(hacc[m]);
+              hacc[m] = __float2half2_rn(0.f);
+            }
           }
         }
+#pragma unroll
+        for (int j = 0; j < WPG; ++j) wg[j] = wn[j];
       }
       const int g = (sp * kSpanIdx * D) / p.group_size;
       const float s = bf16_bits_to_float(__ldg(p.scales + (int64_t)nr * p.num_groups + g));
 #pragma unroll
       for (int m = 0; m < MT; ++m) acc[m] = fmaf(s, sacc[m], acc[m]);
+      if (sp + 1 < sp_end) load_span(sp + 1);
     }
 
     float val[MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) val[m] = fmaf(acc[m], p.out_mul, p.shift * xsum[m]);
+    for (int m = 0; m < MT; ++m) {
+      val[m] = fmaf(acc[m], p.out_mul, p.shift * xsum[m]);
+      xsum[m] = 0.f;
+    }
     finish_rows<MT>(p, chunk, rb, sg, val, n, row_ok);
+
+    item += total_warps;
+    have = item < p.num_items;
+    if (have) {
+      decode_item(item);
+      load_span(sp_begin);
+    }
   }
 }
 
@@ -322,17 +308,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32) small_m_generic_kernel(const S
 
 // ---- host side ---------------------------------------------------------------
 
-struct Plan {
-  bool fast;
-  int D, BITS;
-  bool cb_smem;
-  int MT;
-  int span_idx, spans_per_row, spans_per_item, num_sg, row_blocks, chunks;
-  int64_t num_items;
-  int warps, grid;
-  size_t smem;
-};
-
 inline int pick_mt(int64_t M) {
   if (M <= 1) return 1;
   if (M <= 2) return 2;
@@ -352,13 +327,16 @@ bool fast_eligible(const sacq_layer* L) {
   return true;
 }
 
-constexpr size_t kSmemBudget = 200 * 1024;
+
+// M from which the warp-MMA variant is preferred over the CUDA-core one.
+constexpr int64_t kMmaMinM = 5;
 
 Plan make_plan(const sacq_layer* L, int64_t M) {
   const sacq_layer_desc& d = L->d;
   Plan pl{};
   pl.fast = fast_eligible(L);
-  pl.MT = pick_mt(M);
+  pl.mma = pl.fast && (L->force_kernel == 4 || (L->force_kernel != 3 && M >= kMmaMinM));
+  pl.MT = pl.mma ? 16 : pick_mt(M);
   pl.chunks = (int)((M + pl.MT - 1) / pl.MT);
   pl.row_blocks = (int)((d.out_features + 31) / 32);
   pl.D = d.vector_dim;
@@ -377,6 +355,30 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
     pl.cb_smem = false;
   }
   pl.spans_per_row = (int)(L->vectors_per_row / pl.span_idx);
+  if (pl.mma) {
+    // tile = 16 tokens x 8*r8 rows, one CTA per tile at a time, warps split the spans.
+    // Time ~ waves * (fixed tile latency + r8); on a tie prefer the larger tile (fewer CTAs).
+    const int64_t sub = (d.out_features + 7) / 8;
+    int best = 1;
+    int64_t best_cost = -1;
+    for (int r8 = 1; r8 <= 4; r8 *= 2) {
+      const int64_t tiles = ((sub + r8 - 1) / r8) * pl.chunks;
+      const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
+      const int64_t cost = waves * (3 + r8);     // 3 ~ the per-tile latency that does not shrink with r8
+      if (best_cost < 0 || cost <= best_cost) { best_cost = cost; best = r8; }
+    }
+    pl.r8 = best;
+    pl.row_blocks = (int)((sub + best - 1) / best);
+    pl.spans_per_item = pl.spans_per_row;
+    pl.num_sg = 1;
+    pl.num_items = (int64_t)pl.row_blocks * pl.chunks;
+    pl.grid = (int)(pl.num_items < L->num_sms ? pl.num_items : L->num_sms);
+    if (pl.grid < 1) pl.grid = 1;
+    pl.warps = pl.spans_per_row < kMaxWarps ? pl.spans_per_row : kMaxWarps;
+    const size_t cb_bytes = pl.cb_smem ? (size_t)d.codebook_size * d.vector_dim * 2 : 0;
+    pl.smem = cb_bytes + (size_t)pl.warps * pl.r8 * 4 * 32 * sizeof(float);
+    return pl;
+  }
   // Spread the row's spans over enough items to occupy every warp of the device once,
   // but no finer than one span per item.
   const int64_t base = (int64_t)pl.row_blocks * pl.chunks;
@@ -393,7 +395,7 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
   pl.warps = (int)(warps_needed < 1 ? 1 : (warps_needed > kMaxWarps ? kMaxWarps : warps_needed));
   if (pl.fast) {
     const size_t cb_bytes = pl.cb_smem ? (size_t)d.codebook_size * d.vector_dim * 2 : 0;
-    pl.smem = cb_bytes + (size_t)pl.warps * pl.MT * kSpanIdx * d.vector_dim * 2;
+    pl.smem = cb_bytes + (pl.mma ? 0 : (size_t)pl.warps * pl.MT * kSpanIdx * d.vector_dim * 2);
   } else {
     const size_t per_warp = (size_t)pl.MT * pl.span_idx * d.vector_dim * 4;
     while (pl.warps > 1 && per_warp * pl.warps > kSmemBudget) --pl.warps;
@@ -404,18 +406,12 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
 
 template <int D, int BITS, bool CB_SMEM>
 cudaError_t launch_fast_mt(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
-  auto go = [&](auto kern) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
-    if (e != cudaSuccess) return e;
-    kern<<<pl.grid, pl.warps * 32, pl.smem, s>>>(p);
-    return cudaGetLastError();
-  };
   switch (pl.MT) {
-    case 1: return go(small_m_kernel<D, BITS, 1, CB_SMEM>);
-    case 2: return go(small_m_kernel<D, BITS, 2, CB_SMEM>);
-    case 4: return go(small_m_kernel<D, BITS, 4, CB_SMEM>);
-    case 8: return go(small_m_kernel<D, BITS, 8, CB_SMEM>);
-    default: return go(small_m_kernel<D, BITS, 16, CB_SMEM>);
+    case 1: return launch_kernel<small_m_kernel<D, BITS, 1, CB_SMEM>>(pl, p, s);
+    case 2: return launch_kernel<small_m_kernel<D, BITS, 2, CB_SMEM>>(pl, p, s);
+    case 4: return launch_kernel<small_m_kernel<D, BITS, 4, CB_SMEM>>(pl, p, s);
+    case 8: return launch_kernel<small_m_kernel<D, BITS, 8, CB_SMEM>>(pl, p, s);
+    default: return launch_kernel<small_m_kernel<D, BITS, 16, CB_SMEM>>(pl, p, s);
   }
 }
 
@@ -425,18 +421,12 @@ cudaError_t launch_fast_cb(const Plan& pl, const SmallMParams& p, cudaStream_t s
 }
 
 cudaError_t launch_generic(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
-  auto go = [&](auto kern) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
-    if (e != cudaSuccess) return e;
-    kern<<<pl.grid, pl.warps * 32, pl.smem, s>>>(p);
-    return cudaGetLastError();
-  };
   switch (pl.MT) {
-    case 1: return go(small_m_generic_kernel<1>);
-    case 2: return go(small_m_generic_kernel<2>);
-    case 4: return go(small_m_generic_kernel<4>);
-    case 8: return go(small_m_generic_kernel<8>);
-    default: return go(small_m_generic_kernel<16>);
+    case 1: return launch_kernel<small_m_generic_kernel<1>>(pl, p, s);
+    case 2: return launch_kernel<small_m_generic_kernel<2>>(pl, p, s);
+    case 4: return launch_kernel<small_m_generic_kernel<4>>(pl, p, s);
+    case 8: return launch_kernel<small_m_generic_kernel<8>>(pl, p, s);
+    default: return launch_kernel<small_m_generic_kernel<16>>(pl, p, s);
   }
 }
 
@@ -500,7 +490,11 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
     if (reinterpret_cast<uintptr_t>(q) % 8 != 0 || d.in_features % 8 != 0)
       return set_error(SACQ_ERR_ALIGNMENT, "quantized activations must be 8-byte aligned with K %% 8 == 0");
     p.out_mul = ldexpf(1.f, -L->cb_exp_shift);
-    if (pl.D == 8 && pl.BITS == 12) e = launch_fast_cb<8, 12>(pl, p, s);
+    if (pl.mma) {
+      if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
+        return set_error(SACQ_ERR_ALIGNMENT, "small-M MMA kernel: q must be 16-byte aligned");
+      e = launch_small_m_mma(pl, p, s);
+    } else if (pl.D == 8 && pl.BITS == 12) e = launch_fast_cb<8, 12>(pl, p, s);
     else if (pl.D == 8 && pl.BITS == 8) e = launch_fast_cb<8, 8>(pl, p, s);
     else if (pl.D == 8 && pl.BITS == 16) e = launch_fast_cb<8, 16>(pl, p, s);
     else if (pl.D == 4 && pl.BITS == 12) e = launch_fast_cb<4, 12>(pl, p, s);

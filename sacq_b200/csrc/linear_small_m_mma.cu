@@ -1,0 +1,257 @@
+// Small-M quantized linear, warp-MMA variant: the same packed-index walk as the CUDA-core
+// kernel (linear_small_m.cu), but the 16-token x 8-row x 32-k products of one step are
+// two m16n8k16 fp16 MMAs whose B fragments ARE the gathered codewords -- a lane fetches one
+// 16-byte codeword from shared memory and feeds its four registers to the tensor pipe
+// without ever writing an expanded weight tile.  Per index this costs one shared-memory
+// gather and two MMAs instead of 16 activation reads and 64 half2 FMAs, which is what the
+// instruction-issue-bound CUDA-core loop could not afford beyond a few tokens.
+//
+// Fragment bookkeeping (lane = 4*g + t): the lane owns the 8 consecutive indices
+// 8t..8t+7 of row (block + g) in the current 32-index span.  In step s the warp multiplies
+// vectors {8t+s}: MMA k-slots (2t, 2t+1) carry halfs (0,1) of vector 8t+s and k-slots
+// (2t+8, 2t+9) carry halfs (2,3); the second MMA of the step carries halfs (4..7).  The A
+// fragments use the same slot order, so the activations a lane needs are the 64
+// contiguous e4m3 bytes q[token, (span*32 + 8t)*8 ...) of tokens g and g+8, read straight
+// from global memory and widened to fp16 in registers (exactly).
+//
+// Stands in for the reference's small-M packed GEMMs: codebook_cutlass_kernel.cu:234-583
+// (mma.sync m16n8k16 with a reconstructed B tile in shared memory) and
+// codebook_linear_triton_2026_08_23.py:499-705.
+#include "small_m.cuh"
+
+namespace sacq {
+namespace smallm {
+
+namespace {
+
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D in {4, 8}; BITS in {8, 12, 16}; R8 = 8-row sub-blocks per tile.
+//
+// Work decomposition: a CTA owns a tile of 16 tokens x (8*R8) output rows and loops over
+// tiles; its warps split the row's 32-index spans among themselves (warp w takes spans w,
+// w + nwarps, ...), so the K reduction ends in shared memory behind one __syncthreads and
+// needs neither global scratch nor arrival counters.
+template <int D, int BITS, bool CB_SMEM, int R8>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const SmallMParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;   // D halfs
+  constexpr int WPG = BITS / 4;            // 32-bit words holding a lane's 8 indices
+  constexpr int AREG = D / 2;              // half2 registers per activation vector
+  constexpr int QV = D / 4;                // uint4 pairs covering a lane's 8 vectors (8*D bytes)
+  constexpr int kFrag = R8 * 4;            // accumulator registers per lane
+  const CwVec* cbs = reinterpret_cast<const CwVec*>(smem);
+  const int cb_bytes = CB_SMEM ? p.C * D * 2 : 0;
+  float* red = reinterpret_cast<float*>(smem + cb_bytes);               // [nwarps][kFrag][32]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  if (CB_SMEM) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.cb_f16);
+    uint4* dst = reinterpret_cast<uint4*>(smem);
+    const int n16 = cb_bytes >> 4;
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) cp_async_16(dst + i, src + i);
+  }
+
+  int64_t row_off[R8];                       // byte offset of rows (8r + g) of the tile in the packed stream
+  uint4 qa[2 * QV], qb[2 * QV];              // raw e4m3 bytes of tokens g / g+8 for the lane's 8 vectors
+  uint32_t wd[R8][WPG];                      // the lane's 8 indices for each row sub-block
+  bool ok_a = false, ok_b = false;
+  const uint8_t* qrow_a = nullptr;
+  const uint8_t* qrow_b = nullptr;
+
+  // Issues the global loads of one span: 8*D activation bytes per token and BITS bytes of
+  // indices per row sub-block.
+  auto load_span = [&](int sp) {
+    const int64_t kb = ((int64_t)sp * kSpanIdx + 8 * t) * D;
+#pragma unroll
+    for (int j = 0; j < 2 * QV; ++j) {
+      qa[j] = ok_a ? __ldg(reinterpret_cast<const uint4*>(qrow_a + kb) + j) : make_uint4(0, 0, 0, 0);
+      qb[j] = ok_b ? __ldg(reinterpret_cast<const uint4*>(qrow_b + kb) + j) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int r = 0; r < R8; ++r) {
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(p.packed + row_off[r] + (int64_t)sp * (4 * BITS) + t * BITS);
+#pragma unroll
+      for (int j = 0; j < WPG; ++j) wd[r][j] = __ldg(src + j);
+    }
+  };
+
+  int chunk = 0, n_base = 0;
+  // Sets the per-tile state the loads depend on.
+  auto setup_tile = [&](int64_t tile) {
+    const int rt = (int)(tile % p.row_blocks);
+    chunk = (int)(tile / p.row_blocks);
+    n_base = rt * 8 * R8;
+    const int ma = chunk * 16 + g, mb = ma + 8;
+    ok_a = ma < p.M;
+    ok_b = mb < p.M;
+    qrow_a = p.q + (int64_t)(ok_a ? ma : 0) * p.K;
+    qrow_b = p.q + (int64_t)(ok_b ? mb : 0) * p.K;
+#pragma unroll
+    for (int r = 0; r < R8; ++r) {
+      int n = n_base + r * 8 + g;
+      if (n >= p.N) n = p.N - 1;
+      row_off[r] = (int64_t)n * p.row_bytes;
+    }
+  };
+
+  int64_t tile = blockIdx.x;
+  if (tile < p.num_items) {
+    setup_tile(tile);
+    if (warp < p.spans_per_row) load_span(warp);   // overlaps the codebook copy
+  }
+  if (CB_SMEM) {
+    cp_async_wait_all();
+    __syncthreads();                               // every warp of the CTA, with or without a span
+  }
+
+  for (; tile < p.num_items; tile += gridDim.x) {
+    const int cur_chunk = chunk, cur_n_base = n_base;
+    float acc[R8][4];
+#pragma unroll
+    for (int r = 0; r < R8; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[r][j] = 0.f;
+    float xs_a = 0.f, xs_b = 0.f;
+
+    int sp = warp;
+    for (; sp < p.spans_per_row; sp += nwarps) {
+      // ---- A fragments: widen the e4m3 bytes to fp16 (exact)
+      uint32_t fa[8][AREG], fb[8][AREG];
+      {
+        const uint32_t* wa = reinterpret_cast<const uint32_t*>(qa);
+        const uint32_t* wb = reinterpret_cast<const uint32_t*>(qb);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          if constexpr (D == 8) {
+            e4m3x4_to_h2(wa[2 * s], fa[s][0], fa[s][1]);
+            e4m3x4_to_h2(wa[2 * s + 1], fa[s][2], fa[s][3]);
+            e4m3x4_to_h2(wb[2 * s], fb[s][0], fb[s][1]);
+            e4m3x4_to_h2(wb[2 * s + 1], fb[s][2], fb[s][3]);
+          } else {
+            e4m3x4_to_h2(wa[s], fa[s][0], fa[s][1]);
+            e4m3x4_to_h2(wb[s], fb[s][0], fb[s][1]);
+          }
+        }
+      }
+      if (p.shift != 0.f) {
+        float ta = 0.f, tb = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+#pragma unroll
+          for (int j = 0; j < AREG; ++j) {
+            ta += __low2float(as_h2(fa[s][j])) + __high2float(as_h2(fa[s][j]));
+            tb += __low2float(as_h2(fb[s][j])) + __high2float(as_h2(fb[s][j]));
+          }
+        ta += __shfl_xor_sync(0xffffffffu, ta, 1);
+        ta += __shfl_xor_sync(0xffffffffu, ta, 2);
+        tb += __shfl_xor_sync(0xffffffffu, tb, 1);
+        tb += __shfl_xor_sync(0xffffffffu, tb, 2);
+        xs_a += ta;
+        xs_b += tb;
+      }
+      uint32_t wcur[R8][WPG];
+#pragma unroll
+      for (int r = 0; r < R8; ++r)
+#pragma unroll
+        for (int j = 0; j < WPG; ++j) wcur[r][j] = wd[r][j];
+      if (sp + nwarps < p.spans_per_row) load_span(sp + nwarps);   // next span's loads fly during the MMAs
+
+      float cs[R8][4];
+#pragma unroll
+      for (int r = 0; r < R8; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cs[r][j] = 0.f;
+      // step-major so the R8 accumulator chains interleave
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+#pragma unroll
+        for (int r = 0; r < R8; ++r) {
+          const uint32_t idx = field8<BITS>(wcur[r], s);
+          CwVec c;
+          if constexpr (CB_SMEM) c = cbs[idx];
+          else c = __ldg(reinterpret_cast<const CwVec*>(p.cb_f16) + idx);
+          mma_m16n8k16(cs[r], fa[s][0], fb[s][0], fa[s][1], fb[s][1], c.x, c.y);
+          if constexpr (D == 8) mma_m16n8k16(cs[r], fa[s][2], fb[s][2], fa[s][3], fb[s][3], c.z, c.w);
+        }
+      }
+      // ---- fold in the group scale of the two output rows this lane holds per sub-block
+      const int grp = (sp * kSpanIdx * D) / p.group_size;
+#pragma unroll
+      for (int r = 0; r < R8; ++r) {
+        const int n0 = min(cur_n_base + r * 8 + 2 * t, p.N - 1);
+        const int n1 = min(cur_n_base + r * 8 + 2 * t + 1, p.N - 1);
+        const float s0 = bf16_bits_to_float(__ldg(p.scales + (int64_t)n0 * p.num_groups + grp));
+        const float s1 = bf16_bits_to_float(__ldg(p.scales + (int64_t)n1 * p.num_groups + grp));
+        acc[r][0] = fmaf(s0, cs[r][0], acc[r][0]);
+        acc[r][1] = fmaf(s1, cs[r][1], acc[r][1]);
+        acc[r][2] = fmaf(s0, cs[r][2], acc[r][2]);
+        acc[r][3] = fmaf(s1, cs[r][3], acc[r][3]);
+      }
+    }
+
+    // ---- the next tile's first loads fly during this tile's reduction and epilogue
+    if (tile + gridDim.x < p.num_items) {
+      setup_tile(tile + gridDim.x);
+      if (warp < p.spans_per_row) load_span(warp);
+    }
+    // ---- K reduction across the CTA's warps, then the epilogue
+#pragma unroll
+    for (int r = 0; r < R8; ++r) {
+      red[(warp * kFrag + r * 4 + 0) * 32 + lane] = fmaf(acc[r][0], p.out_mul, p.shift * xs_a);
+      red[(warp * kFrag + r * 4 + 1) * 32 + lane] = fmaf(acc[r][1], p.out_mul, p.shift * xs_a);
+      red[(warp * kFrag + r * 4 + 2) * 32 + lane] = fmaf(acc[r][2], p.out_mul, p.shift * xs_b);
+      red[(warp * kFrag + r * 4 + 3) * 32 + lane] = fmaf(acc[r][3], p.out_mul, p.shift * xs_b);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kFrag * 32; e += blockDim.x) {
+      float v = 0.f;
+      for (int w = 0; w < nwarps; ++w) v += red[w * kFrag * 32 + e];     // fixed order: deterministic
+      const int ln = e & 31, j = (e >> 5) & 3, r = e >> 7;
+      const int m = cur_chunk * 16 + (ln >> 2) + ((j & 2) ? 8 : 0);
+      const int n = cur_n_base + r * 8 + 2 * (ln & 3) + (j & 1);
+      if (m < p.M && n < p.N) {
+        const float b = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
+        p.y[(int64_t)m * p.ldy + n] = float_to_bf16_bits(fmaf(__ldg(p.act_scale + m), v, b));
+      }
+    }
+    __syncthreads();                           // red is reused by the next tile
+  }
+}
+
+template <int D, int BITS, bool CB>
+cudaError_t launch_r8(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  switch (pl.r8) {
+    case 1: return launch_kernel<small_m_mma_kernel<D, BITS, CB, 1>>(pl, p, s);
+    case 2: return launch_kernel<small_m_mma_kernel<D, BITS, CB, 2>>(pl, p, s);
+    default: return launch_kernel<small_m_mma_kernel<D, BITS, CB, 4>>(pl, p, s);
+  }
+}
+
+template <int D, int BITS>
+cudaError_t launch_cb(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  return pl.cb_smem ? launch_r8<D, BITS, true>(pl, p, s) : launch_r8<D, BITS, false>(pl, p, s);
+}
+
+}  // namespace
+
+cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  if (pl.D == 8 && pl.BITS == 12) return launch_cb<8, 12>(pl, p, s);
+  if (pl.D == 8 && pl.BITS == 8) return launch_cb<8, 8>(pl, p, s);
+  if (pl.D == 8 && pl.BITS == 16) return launch_cb<8, 16>(pl, p, s);
+  if (pl.D == 4 && pl.BITS == 12) return launch_cb<4, 12>(pl, p, s);
+  if (pl.D == 4 && pl.BITS == 8) return launch_cb<4, 8>(pl, p, s);
+  if (pl.D == 4 && pl.BITS == 16) return launch_cb<4, 16>(pl, p, s);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace smallm
+}  // namespace sacq

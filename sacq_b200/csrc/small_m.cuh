@@ -1,0 +1,111 @@
+// Shared declarations of the small-M quantized-linear kernels (CUDA-core and mma variants).
+#pragma once
+
+#include <math.h>
+#include <string.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace sacq {
+namespace smallm {
+
+constexpr int kSpanIdx = 32;   // indices a lane consumes per span
+constexpr int kMaxWarps = 8;
+
+struct SmallMParams {
+  const uint8_t* packed;
+  const __half* cb_f16;        // [C, D] scaled by 2^cb_exp_shift
+  const uint16_t* cb_bf16;     // [C, d] original (generic kernel)
+  const uint16_t* scales;      // bf16 [N, num_groups]
+  const uint16_t* bias;        // bf16 [N] or null
+  const uint8_t* q;            // e4m3 [M, K]
+  const float* act_scale;      // [M]
+  uint16_t* y;                 // bf16 [M, ldy]
+  float* partial;              // [num_sg][M][N] (only when num_sg > 1)
+  int* counters;               // [chunks * row_blocks]
+  int64_t ldy;
+  int64_t row_bytes;           // bytes per packed row (fast kernel)
+  int N, K, M;
+  int vpr;                     // vectors per row
+  int d, bits;
+  int num_groups, group_size;
+  int C;
+  int span_idx;                // generic kernel: vectors per span
+  int spans_per_row;           // vpr / span
+  int spans_per_item;          // consecutive spans one item covers
+  int num_sg;                  // span groups per row = ceil(spans_per_row / spans_per_item)
+  int row_blocks;              // ceil(N / 32)
+  int chunks;                  // ceil(M / MT)
+  int64_t num_items;
+  float out_mul;               // 2^-cb_exp_shift (fast) or 1 (generic)
+  float shift;
+};
+
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// e4m3 x4 (one 32-bit word) -> 2 x half2, exact.
+__device__ __forceinline__ void e4m3x4_to_h2(uint32_t v, uint32_t& lo, uint32_t& hi) {
+  const __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xffff), __NV_E4M3);
+  const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v >> 16), __NV_E4M3);
+  lo = (uint32_t)a.x | ((uint32_t)a.y << 16);
+  hi = (uint32_t)b.x | ((uint32_t)b.y << 16);
+}
+
+// 8 consecutive fields of BITS bits held in BITS/4 words.
+template <int BITS>
+__device__ __forceinline__ uint32_t field8(const uint32_t (&w)[BITS / 4], int j) {
+  const int bit = j * BITS;
+  const int word = bit >> 5;
+  const int off = bit & 31;
+  if (off + BITS <= 32) return (w[word] >> off) & ((1u << BITS) - 1u);
+  return __funnelshift_r(w[word], w[word + 1 < BITS / 4 ? word + 1 : word], off) & ((1u << BITS) - 1u);
+}
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
+// Host-side launch plan shared by the variants.
+struct Plan {
+  bool fast;
+  bool mma;                  // warp-MMA variant (16 tokens per item) instead of the CUDA-core one
+  int D, BITS;
+  bool cb_smem;
+  int MT;
+  int span_idx, spans_per_row, spans_per_item, num_sg, row_blocks, chunks;
+  int64_t num_items;
+  int warps, grid;
+  int r8;                    // warp-MMA variant: 8-row sub-blocks per tile (1, 2 or 4)
+  size_t smem;
+};
+
+
+constexpr size_t kSmemBudget = 200 * 1024;
+
+// Launches one instantiation; the opt-in to large dynamic shared memory is per function
+// and device, so it is set on first use and remembered.
+template <auto Kern>
+cudaError_t launch_kernel(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  Kern<<<pl.grid, pl.warps * 32, pl.smem, s>>>(p);
+  return cudaGetLastError();
+}
+
+// linear_small_m_mma.cu
+cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s);
+
+}  // namespace smallm
+}  // namespace sacq

@@ -160,7 +160,10 @@ def test_weight_fp8_producer_matches_reference_fixture(name):
 
 # --------------------------------------------------------------------------- quantized linear
 
-def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=("auto",)):
+ALL_SMALL = ("auto", "small_simt", "small_mma")
+
+
+def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=ALL_SMALL):
     ref = O.linear_a8_reference(q_bits, s, w_bits, bias_bits)
     q = torch.from_numpy(q_bits).cuda().view(torch.float8_e4m3fn)
     sc = torch.from_numpy(s).cuda()
