@@ -175,13 +175,15 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         self._handle = handle
 
     def __del__(self):
-        h = getattr(self, "_handle", None)
-        if h is not None and getattr(self, "_lib", None) is not None:
+        # runs during interpreter shutdown too: touch nothing but plain attributes
+        d = self.__dict__
+        h, lib = d.get("_handle"), d.get("_lib")
+        d["_handle"] = None
+        if h is not None and lib is not None:
             try:
-                self._lib.sacq_layer_destroy(h)
+                lib.sacq_layer_destroy(h)
             except Exception:
                 pass
-            self._handle = None
 
     def _apply(self, fn, recurse=True):
         # .to()/.cuda() would move the borrowed buffers out from under the handle

@@ -161,6 +161,7 @@ def test_weight_fp8_producer_matches_reference_fixture(name):
 # --------------------------------------------------------------------------- quantized linear
 
 ALL_SMALL = ("auto", "small_simt", "small_mma")
+ALL_KERNELS = ALL_SMALL + ("large",)
 
 
 def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=ALL_SMALL):
@@ -170,6 +171,8 @@ def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=ALL_SMALL):
     outs = {}
     for k in kernels:
         mod.set_kernel(k)
+        if k == "large" and mod._lib.sacq_layer_kernel_for(mod._handle, q.shape[0]) < 0:
+            continue                                   # geometry outside the tensor-core kernel
         y = mod.linear_a8(q, sc)
         torch.cuda.synchronize()
         assert y.dtype == torch.bfloat16
@@ -246,7 +249,50 @@ def test_linear_mixed_bits(d, C, M):
     mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
     w_bits = oracle_weight(p)
     q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 1)))
-    _check_linear(mod, q_bits, s, w_bits, None)
+    _check_linear(mod, q_bits, s, w_bits, None, kernels=ALL_KERNELS)
+
+
+@pytest.mark.parametrize("K,N", [(2048, 6144), (6144, 2048)])
+@pytest.mark.parametrize("M", [256, 1024])
+def test_linear_large_m_batched_shapes(K, N, M):
+    """The batched-throughput layers on the TMA + tcgen05 kernel."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, seed=K // 7 + N, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(6)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    assert mod.kernel_for(M) == "large"
+    w_bits = oracle_weight(p)
+    q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 3)))
+    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=("large", "small_mma"))
+    # both kernels see the same operands; they may differ only by summation order and the
+    # fp16 vs FP8 hi+lo codeword encodings
+    a, b = outs["large"][0].float().cpu().numpy(), outs["small_mma"][0].float().cpu().numpy()
+    assert O.rel_frobenius(a, b) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K,d,C", [(77, 200, 512, 8, 4096), (300, 1000, 256, 8, 256), (129, 136, 768, 4, 4096),
+                                       (1, 128, 256, 8, 4096), (128, 128, 1024, 4, 256)])
+def test_linear_large_m_ragged(M, N, K, d, C):
+    """Partial tiles in M and N, both vector widths, 8- and 12-bit indices."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, seed=M, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(8)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 5)))
+    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=("large",))
+    assert "large" in outs
+    # rows of a wider output buffer beyond N stay untouched
+    q = torch.from_numpy(q_bits).cuda().view(torch.float8_e4m3fn)
+    out = torch.full((M, N + 40), 3.0, dtype=torch.bfloat16, device="cuda")
+    mod.set_kernel("large")
+    mod.linear_a8(q, torch.from_numpy(s).cuda(), out=out[:, :N])
+    mod.set_kernel("auto")
+    assert torch.equal(out[:, :N], outs["large"][0]) and float(out[:, N:].float().min()) == 3.0
 
 
 @pytest.mark.parametrize("N,K,d,C,G", [(40, 128, 4, 32, 64), (100, 256, 4, 2048, 64), (33, 512, 8, 4096, 256),
