@@ -131,6 +131,26 @@ SACQ_API int sacq_linear_bf16(const sacq_layer_t* layer, const void* x_bf16, int
                      float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
                      void* stream);
 
+/* The same forward as sacq_linear_a8's split-K small-M kernel, for callers that cannot
+ * allocate device memory (a control loop with a frozen memory budget, a server whose
+ * arena already owns the GPU, a plugin that is handed nothing but its inputs and
+ * outputs).  It has no counterpart in the reference.  The split-K partial sums and
+ * arrival counters live in an array built into the library: sacq_static_scratch_bytes()
+ * bytes (8 MiB) of device memory on every GPU that loads it, held until the process
+ * exits.  The call allocates and frees nothing.  Limits and rules:
+ *   - a call whose partial sums (M * N * 4 bytes per K split) or arrival counters
+ *     (ceil(M/16) * ceil(N/32), at most 16384) do not fit the array returns
+ *     SACQ_ERR_WORKSPACE and launches nothing; the decode shapes (M <= 64, N <= 6144)
+ *     need at most about 2 MiB;
+ *   - the first call on a device looks up the array's device address; make that call
+ *     before starting any stream capture;
+ *   - every call uses the same array: calls that may overlap on the GPU (different
+ *     streams) race, calls ordered on one stream do not.  The counters are cleared at
+ *     the start of each call, the partial sums are overwritten before they are read. */
+SACQ_API int sacq_linear_a8_static_scratch(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M,
+                                           void* y_out, int64_t ldy, void* stream);
+SACQ_API int64_t sacq_static_scratch_bytes(void);
+
 /* Forces a GEMM kernel (for tests and benchmarks): 0 = automatic, 1 = small-M kernel
  * (its own choice of variant), 2 = large-M kernel, 3 = small-M CUDA-core variant,
  * 4 = small-M warp-MMA variant.  Returns SACQ_ERR_UNSUPPORTED from the next forward if
