@@ -307,7 +307,7 @@ def gpu_main(args):
                     "d2h_bytes_per_step": sum(M * N * 2 for _, K, N, M in calls),
                     "ms_per_step": sec_e2e / args.steps * 1e3},
             "gpu_launches": int(full_launches * args.steps),
-            "roofline": {"bound": "hbm", "kernel": "small_m_kernel (packed-index GEMM, M<=64)",
+            "roofline": {"bound": "hbm", "kernel": "small_m_mma_kernel (packed-index GEMM, M<=64)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None,
                          "algorithmic_bytes_per_launch": alg, "us_per_launch": gemm_launch_s * 1e6,

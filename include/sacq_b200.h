@@ -126,7 +126,9 @@ SACQ_API int sacq_linear_a8(const sacq_layer_t* layer, const void* q, const floa
 
 /* Convenience: sacq_quant_act_fp8 + sacq_linear_a8 for a bf16 input (the module's
  * forward(x), SHIM:456-541).  `q_scratch` (M*K bytes) and `scale_scratch` (M floats)
- * are caller-provided device buffers. */
+ * are caller-provided device buffers.  For small M the quantizer is fused into the GEMM
+ * kernel: the result is the same, `scale_scratch` still receives the per-token scales,
+ * but `q_scratch` is then left untouched. */
 SACQ_API int sacq_linear_bf16(const sacq_layer_t* layer, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
                      float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
                      void* stream);
@@ -153,7 +155,7 @@ SACQ_API int64_t sacq_static_scratch_bytes(void);
 
 /* Forces a GEMM kernel (for tests and benchmarks): 0 = automatic, 1 = small-M kernel
  * (its own choice of variant), 2 = large-M kernel, 3 = small-M CUDA-core variant,
- * 4 = small-M warp-MMA variant.  Returns SACQ_ERR_UNSUPPORTED from the next forward if
+ * 4 = small-M warp-MMA variant, 5 = warp-MMA variant without shared-memory staging.  Returns SACQ_ERR_UNSUPPORTED from the next forward if
  * the forced kernel cannot run the layer. */
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* layer, int which);
 /* Which kernel a forward with M rows would use (1 or 2), or a negative error. */

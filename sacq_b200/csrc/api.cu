@@ -62,12 +62,12 @@ int64_t small_m_slab_rows(const sacq_layer* L) {
 }
 
 int pick_kernel(const sacq_layer* L, int64_t M) {
-  if (L->force_kernel == 1 || L->force_kernel == 3 || L->force_kernel == 4)
+  if (L->force_kernel == 1 || L->force_kernel >= 3)
     return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 2) return large_m_supported(L) ? 2 : SACQ_ERR_UNSUPPORTED;
   // A shape rule, not a backend switch: the CUDA-core kernel wins while the grid of
   // 128-row tensor-core tiles cannot fill the device.
-  if (large_m_supported(L) && M > 32) return 2;
+  if (large_m_supported(L) && M > 64) return 2;
   return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
 }
 
@@ -214,7 +214,7 @@ SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, 
 
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
-  if (which < 0 || which > 4) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..4", which);
+  if (which < 0 || which > 5) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..5", which);
   L->force_kernel = which;
   return SACQ_OK;
 }
@@ -262,6 +262,12 @@ SACQ_API int sacq_linear_bf16(const sacq_layer_t* L, const void* x_bf16, int64_t
                      void* stream) {
   if (int rc = check_layer(L)) return rc;
   if (M == 0) return SACQ_OK;
+  // Small batches run as one kernel: the GEMM's CTAs quantize their own token rows.
+  if (x_bf16 != nullptr && y_out != nullptr && ldy >= L->d.out_features && L->d.out_features > 0 &&
+      pick_kernel(L, M) == 1 && small_m_fused_available(L, M, x_bf16, x_pitch)) {
+    DeviceGuard guard(L->d.device);
+    return launch_small_m_fused(L, x_bf16, x_pitch, scale_scratch, M, y_out, ldy, static_cast<cudaStream_t>(stream));
+  }
   int rc = sacq_quant_act_fp8(x_bf16, x_pitch, M, L->d.in_features, q_scratch, scale_scratch, stream);
   if (rc != SACQ_OK) return rc;
   return sacq_linear_a8(L, q_scratch, scale_scratch, M, y_out, ldy, workspace, workspace_bytes, stream);

@@ -227,6 +227,324 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const Sm
   }
 }
 
+// ---- staged variant -------------------------------------------------------------------
+//
+// Same fragment arithmetic, different data movement: everything a tile touches is brought
+// into shared memory by a handful of bulk asynchronous copies (cp.async.bulk, one elected
+// thread, completion on an mbarrier) before the warps start: the codebook once per CTA,
+// then per tile the 8*R8 packed index rows (one contiguous block of the stream) and the 16
+// activation rows.  The inner loop then has no global loads at all, and the memory latency
+// is paid once per tile instead of once per span.  With FUSED the activation rows are not
+// copied but produced in place: the CTA quantizes its 16 bf16 token rows itself (row
+// abs-max / 448, IEEE division, e4m3 RNE -- the quantizer kernel's arithmetic), which
+// removes the separate quantizer launch from a small-M forward.
+
+constexpr int kActPad = 16;                       // bytes of padding per staged activation row
+
+__device__ __forceinline__ uint32_t sm_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(sm_addr(dst)), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded: gives up after about two seconds and reports through the layer's status word.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255) == 255) {
+      uint64_t t1;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 2000000000ull) {
+        atomicExch(status, 2);
+        return false;
+      }
+    }
+  }
+}
+
+struct StagedLayout {
+  uint32_t cb_off, idx_off, act_off, red_off, sa_off, bar_off, total;
+};
+__host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64_t row_bytes, int r8, int warps) {
+  StagedLayout L;
+  L.cb_off = 0;
+  L.idx_off = (uint32_t)((C * D * 2 + 127) & ~127);
+  L.act_off = L.idx_off + (uint32_t)((8 * r8 * row_bytes + 127) & ~127);
+  L.red_off = L.act_off + (uint32_t)((16 * (K + kActPad) + 127) & ~127);
+  L.sa_off = L.red_off + (uint32_t)(warps * r8 * 4 * 32 * 4);
+  L.bar_off = L.sa_off + 64;
+  L.total = L.bar_off + 32;
+  return L;
+}
+
+template <int D, int BITS, int R8, bool FUSED>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(const SmallMParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;
+  constexpr int WPG = BITS / 4;
+  constexpr int AREG = D / 2;
+  constexpr int QV = D / 4;
+  constexpr int kFrag = R8 * 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const StagedLayout L = staged_layout(p.C, D, p.K, p.row_bytes, R8, nwarps);
+  const CwVec* cbs = reinterpret_cast<const CwVec*>(smem + L.cb_off);
+  const uint8_t* idx_s = smem + L.idx_off;
+  uint8_t* act_s = smem + L.act_off;
+  float* red = reinterpret_cast<float*>(smem + L.red_off);
+  float* sa_s = reinterpret_cast<float*>(smem + L.sa_off);
+  const uint32_t bar_cb = sm_addr(smem + L.bar_off), bar_tile = bar_cb + 8;
+  const int act_pitch = p.K + kActPad;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_cb, 1);
+    mbar_init(bar_tile, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t cb_bytes = (uint32_t)(p.C * D * 2);
+    mbar_expect_tx(bar_cb, cb_bytes);
+    bulk_copy_g2s(smem + L.cb_off, p.cb_f16, cb_bytes, bar_cb);
+  }
+
+  bool ok = true;
+  uint32_t tile_parity = 0;
+  bool cb_waited = false;
+  for (int64_t tile = blockIdx.x; tile < p.num_items; tile += gridDim.x) {
+    const int rt = (int)(tile % p.row_blocks);
+    const int chunk = (int)(tile / p.row_blocks);
+    const int n_base = rt * 8 * R8;
+    const int m_base = chunk * 16;
+    const int rows_here = min(8 * R8, p.N - n_base);
+    const int toks_here = min(16, p.M - m_base);
+
+    // ---- bring the tile in
+    if (threadIdx.x == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic reads of these buffers
+      const uint32_t idx_bytes = (uint32_t)(rows_here * p.row_bytes);
+      const uint32_t act_bytes = FUSED ? 0u : (uint32_t)(toks_here * p.K);
+      mbar_expect_tx(bar_tile, idx_bytes + act_bytes);
+      bulk_copy_g2s(smem + L.idx_off, p.packed + (int64_t)n_base * p.row_bytes, idx_bytes, bar_tile);
+      if (!FUSED)
+        for (int m = 0; m < toks_here; ++m)
+          bulk_copy_g2s(act_s + m * act_pitch, p.q + (int64_t)(m_base + m) * p.K, (uint32_t)p.K, bar_tile);
+    }
+    if constexpr (FUSED) {
+      // quantize this tile's token rows in place: warp w takes rows w, w + nwarps, ...
+      for (int m = warp; m < toks_here; m += nwarps) {
+        const uint4* xrow = reinterpret_cast<const uint4*>(p.x_bf16 + (int64_t)(m_base + m) * p.x_pitch);
+        const int chunks = p.K >> 3;
+        float mx = 0.f;
+        for (int c = lane; c < chunks; c += 32) {
+          const uint4 v = __ldg(xrow + c);
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            mx = fmaxf(mx, fabsf(bf16_bits_to_float(w4[j] & 0xffff)));
+            mx = fmaxf(mx, fabsf(bf16_bits_to_float(w4[j] >> 16)));
+          }
+        }
+        mx = warp_max(mx);
+        const float sc = mx > 0.f ? __fdiv_rn(mx, kE4M3Max) : 1.0f;
+        if (lane == 0) {
+          sa_s[m] = sc;
+          if (p.act_scale_out != nullptr && rt == 0) p.act_scale_out[m_base + m] = sc;
+        }
+        for (int c = lane; c < chunks; c += 32) {
+          const uint4 v = __ldg(xrow + c);                      // second pass hits L1/L2
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+          uint32_t o[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint32_t a = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j] & 0xffff), sc)),
+                                                clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j] >> 16), sc)));
+            const uint32_t b = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j + 1] & 0xffff), sc)),
+                                                clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j + 1] >> 16), sc)));
+            o[j] = a | (b << 16);
+          }
+          *reinterpret_cast<uint2*>(act_s + m * act_pitch + c * 8) = make_uint2(o[0], o[1]);
+        }
+      }
+    } else {
+      if (threadIdx.x < 16) sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
+    }
+    if (!cb_waited) {
+      ok = mbar_wait_bounded(bar_cb, 0, p.status) && ok;
+      cb_waited = true;
+    }
+    ok = mbar_wait_bounded(bar_tile, tile_parity, p.status) && ok;
+    tile_parity ^= 1;
+    ok = __syncthreads_and(ok);
+    if (!ok) break;                                    // a bounded wait expired: status word is set
+
+    // per-row scales of the two output rows this lane holds in each sub-block
+    float s0[R8], s1[R8];
+    int sn0[R8], sn1[R8];
+#pragma unroll
+    for (int r = 0; r < R8; ++r) {
+      sn0[r] = min(n_base + r * 8 + 2 * t, p.N - 1);
+      sn1[r] = min(n_base + r * 8 + 2 * t + 1, p.N - 1);
+      s0[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn0[r] * p.num_groups));
+      s1[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn1[r] * p.num_groups));
+    }
+    float acc[R8][4];
+#pragma unroll
+    for (int r = 0; r < R8; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[r][j] = 0.f;
+    float xs_a = 0.f, xs_b = 0.f;
+
+    for (int sp = warp; sp < p.spans_per_row; sp += nwarps) {
+      uint32_t fa[8][AREG], fb[8][AREG];
+      {
+        const uint4* pa = reinterpret_cast<const uint4*>(act_s + g * act_pitch + (sp * kSpanIdx + 8 * t) * D);
+        const uint4* pb = reinterpret_cast<const uint4*>(act_s + (g + 8) * act_pitch + (sp * kSpanIdx + 8 * t) * D);
+        uint4 qa[2 * QV], qb[2 * QV];
+#pragma unroll
+        for (int j = 0; j < 2 * QV; ++j) { qa[j] = pa[j]; qb[j] = pb[j]; }
+        const uint32_t* wa = reinterpret_cast<const uint32_t*>(qa);
+        const uint32_t* wb = reinterpret_cast<const uint32_t*>(qb);
+#pragma unroll
+        for (int s8 = 0; s8 < 8; ++s8) {
+          if constexpr (D == 8) {
+            e4m3x4_to_h2(wa[2 * s8], fa[s8][0], fa[s8][1]);
+            e4m3x4_to_h2(wa[2 * s8 + 1], fa[s8][2], fa[s8][3]);
+            e4m3x4_to_h2(wb[2 * s8], fb[s8][0], fb[s8][1]);
+            e4m3x4_to_h2(wb[2 * s8 + 1], fb[s8][2], fb[s8][3]);
+          } else {
+            e4m3x4_to_h2(wa[s8], fa[s8][0], fa[s8][1]);
+            e4m3x4_to_h2(wb[s8], fb[s8][0], fb[s8][1]);
+          }
+        }
+      }
+      if (g >= toks_here) {
+#pragma unroll
+        for (int s8 = 0; s8 < 8; ++s8)
+#pragma unroll
+          for (int j = 0; j < AREG; ++j) fa[s8][j] = 0u;
+      }
+      if (g + 8 >= toks_here) {
+#pragma unroll
+        for (int s8 = 0; s8 < 8; ++s8)
+#pragma unroll
+          for (int j = 0; j < AREG; ++j) fb[s8][j] = 0u;
+      }
+      if (p.shift != 0.f) {
+        float ta = 0.f, tb = 0.f;
+#pragma unroll
+        for (int s8 = 0; s8 < 8; ++s8)
+#pragma unroll
+          for (int j = 0; j < AREG; ++j) {
+            ta += __low2float(as_h2(fa[s8][j])) + __high2float(as_h2(fa[s8][j]));
+            tb += __low2float(as_h2(fb[s8][j])) + __high2float(as_h2(fb[s8][j]));
+          }
+        ta += __shfl_xor_sync(0xffffffffu, ta, 1);
+        ta += __shfl_xor_sync(0xffffffffu, ta, 2);
+        tb += __shfl_xor_sync(0xffffffffu, tb, 1);
+        tb += __shfl_xor_sync(0xffffffffu, tb, 2);
+        xs_a += ta;
+        xs_b += tb;
+      }
+      uint32_t wcur[R8][WPG];
+#pragma unroll
+      for (int r = 0; r < R8; ++r) {
+        const int rr = min(r * 8 + g, rows_here - 1);
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(idx_s + (int64_t)rr * p.row_bytes + sp * (4 * BITS) + t * BITS);
+#pragma unroll
+        for (int j = 0; j < WPG; ++j) wcur[r][j] = src[j];
+      }
+      float cs[R8][4];
+#pragma unroll
+      for (int r = 0; r < R8; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cs[r][j] = 0.f;
+#pragma unroll
+      for (int s8 = 0; s8 < 8; ++s8) {
+#pragma unroll
+        for (int r = 0; r < R8; ++r) {
+          const CwVec c = cbs[field8<BITS>(wcur[r], s8)];
+          mma_m16n8k16(cs[r], fa[s8][0], fb[s8][0], fa[s8][1], fb[s8][1], c.x, c.y);
+          if constexpr (D == 8) mma_m16n8k16(cs[r], fa[s8][2], fb[s8][2], fa[s8][3], fb[s8][3], c.z, c.w);
+        }
+      }
+      if (p.num_groups > 1) {
+        const int grp = (sp * kSpanIdx * D) / p.group_size;
+#pragma unroll
+        for (int r = 0; r < R8; ++r) {
+          s0[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn0[r] * p.num_groups + grp));
+          s1[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn1[r] * p.num_groups + grp));
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R8; ++r) {
+        acc[r][0] = fmaf(s0[r], cs[r][0], acc[r][0]);
+        acc[r][1] = fmaf(s1[r], cs[r][1], acc[r][1]);
+        acc[r][2] = fmaf(s0[r], cs[r][2], acc[r][2]);
+        acc[r][3] = fmaf(s1[r], cs[r][3], acc[r][3]);
+      }
+    }
+
+#pragma unroll
+    for (int r = 0; r < R8; ++r) {
+      red[(warp * kFrag + r * 4 + 0) * 32 + lane] = fmaf(acc[r][0], p.out_mul, p.shift * xs_a);
+      red[(warp * kFrag + r * 4 + 1) * 32 + lane] = fmaf(acc[r][1], p.out_mul, p.shift * xs_a);
+      red[(warp * kFrag + r * 4 + 2) * 32 + lane] = fmaf(acc[r][2], p.out_mul, p.shift * xs_b);
+      red[(warp * kFrag + r * 4 + 3) * 32 + lane] = fmaf(acc[r][3], p.out_mul, p.shift * xs_b);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kFrag * 32; e += blockDim.x) {
+      float v = 0.f;
+      for (int w = 0; w < nwarps; ++w) v += red[w * kFrag * 32 + e];
+      const int ln = e & 31, j = (e >> 5) & 3, r = e >> 7;
+      const int ml = (ln >> 2) + ((j & 2) ? 8 : 0);
+      const int n = n_base + r * 8 + 2 * (ln & 3) + (j & 1);
+      if (ml < toks_here && n < p.N) {
+        const float b = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
+        p.y[(int64_t)(m_base + ml) * p.ldy + n] = float_to_bf16_bits(fmaf(sa_s[ml], v, b));
+      }
+    }
+    __syncthreads();                                   // buffers are reused by the next tile
+  }
+  if (!cb_waited) mbar_wait_bounded(bar_cb, 0, p.status);   // never exit with the codebook copy in flight
+}
+
+template <int D, int BITS, bool FUSED>
+cudaError_t launch_staged_r8(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  switch (pl.r8) {
+    case 1: return launch_kernel<small_m_mma_staged_kernel<D, BITS, 1, FUSED>>(pl, p, s);
+    case 2: return launch_kernel<small_m_mma_staged_kernel<D, BITS, 2, FUSED>>(pl, p, s);
+    default: return launch_kernel<small_m_mma_staged_kernel<D, BITS, 4, FUSED>>(pl, p, s);
+  }
+}
+
+template <int D, int BITS>
+cudaError_t launch_staged(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  return p.x_bf16 != nullptr ? launch_staged_r8<D, BITS, true>(pl, p, s) : launch_staged_r8<D, BITS, false>(pl, p, s);
+}
+
 template <int D, int BITS, bool CB>
 cudaError_t launch_r8(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
   switch (pl.r8) {
@@ -243,7 +561,20 @@ cudaError_t launch_cb(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
 
 }  // namespace
 
+size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps) {
+  return staged_layout(C, D, K, row_bytes, r8, warps).total;
+}
+
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  if (pl.staged) {
+    if (pl.D == 8 && pl.BITS == 12) return launch_staged<8, 12>(pl, p, s);
+    if (pl.D == 8 && pl.BITS == 8) return launch_staged<8, 8>(pl, p, s);
+    if (pl.D == 8 && pl.BITS == 16) return launch_staged<8, 16>(pl, p, s);
+    if (pl.D == 4 && pl.BITS == 12) return launch_staged<4, 12>(pl, p, s);
+    if (pl.D == 4 && pl.BITS == 8) return launch_staged<4, 8>(pl, p, s);
+    if (pl.D == 4 && pl.BITS == 16) return launch_staged<4, 16>(pl, p, s);
+    return cudaErrorInvalidValue;
+  }
   if (pl.D == 8 && pl.BITS == 12) return launch_cb<8, 12>(pl, p, s);
   if (pl.D == 8 && pl.BITS == 8) return launch_cb<8, 8>(pl, p, s);
   if (pl.D == 8 && pl.BITS == 16) return launch_cb<8, 16>(pl, p, s);

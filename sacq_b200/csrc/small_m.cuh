@@ -20,7 +20,11 @@ struct SmallMParams {
   const uint16_t* cb_bf16;     // [C, d] original (generic kernel)
   const uint16_t* scales;      // bf16 [N, num_groups]
   const uint16_t* bias;        // bf16 [N] or null
-  const uint8_t* q;            // e4m3 [M, K]
+  const uint8_t* q;            // e4m3 [M, K] (null when the quantizer is fused in)
+  const uint16_t* x_bf16;      // bf16 [M, x_pitch]: raw activations for the fused quantizer, or null
+  int* status;                 // layer status word (bounded waits report here)
+  float* act_scale_out;        // fused quantizer: per-token scales written here (may be null)
+  int64_t x_pitch;
   const float* act_scale;      // [M]
   uint16_t* y;                 // bf16 [M, ldy]
   float* partial;              // [num_sg][M][N] (only when num_sg > 1)
@@ -82,11 +86,12 @@ struct Plan {
   int64_t num_items;
   int warps, grid;
   int r8;                    // warp-MMA variant: 8-row sub-blocks per tile (1, 2 or 4)
+  bool staged;               // warp-MMA variant with bulk-copied tiles in shared memory
   size_t smem;
 };
 
 
-constexpr size_t kSmemBudget = 200 * 1024;
+constexpr size_t kSmemBudget = 227 * 1024;
 
 // Launches one instantiation; the opt-in to large dynamic shared memory is per function
 // and device, so it is set on first use and remembered.
@@ -106,6 +111,8 @@ cudaError_t launch_kernel(const Plan& pl, const SmallMParams& p, cudaStream_t s)
 
 // linear_small_m_mma.cu
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s);
+// Shared memory the staged warp-MMA kernel needs for (layer, r8); 0 if it cannot run it.
+size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps);
 
 }  // namespace smallm
 }  // namespace sacq

@@ -160,7 +160,7 @@ def test_weight_fp8_producer_matches_reference_fixture(name):
 
 # --------------------------------------------------------------------------- quantized linear
 
-ALL_SMALL = ("auto", "small_simt", "small_mma")
+ALL_SMALL = ("auto", "small_simt", "small_mma", "small_mma_direct")
 ALL_KERNELS = ALL_SMALL + ("large",)
 
 
@@ -232,8 +232,14 @@ def test_linear_decode_shapes(K, N):
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
     w_bits = oracle_weight(p)
     for M in (1, 2, 4, 8, 16, 32, 64):
-        q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M)))
-        _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias))
+        x = make_activations(M, K, seed=M)
+        q_bits, s = O.quantize_rows_e4m3(bf16_bits(x))
+        outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias))
+        # the bf16 forward fuses the quantizer into the GEMM kernel: same bytes as the two-step path
+        assert torch.equal(mod(x.cuda()), outs["auto"][0])
+        wide = torch.zeros(M, K + 8, dtype=torch.bfloat16, device="cuda")
+        wide[:, :K] = x.cuda()
+        assert torch.equal(mod(wide[:, :K]), outs["auto"][0])
 
 
 @pytest.mark.parametrize("d,C", [(8, 256), (8, 4096), (8, 65536), (4, 4096)])
