@@ -1,0 +1,74 @@
+"""Batched-throughput sweep of the column-split quantized linear (run under torchrun):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \
+        --master-port 29511 -m sacq_b200.bench_column_parallel [--ms 256,1024,4096,8192]
+
+Layers 2048x6144 and 6144x2048 (K x N) at W1.5A8, output rows split over the G ranks,
+result all-gathered over NVLink.  Prints one JSON line per (shape, M): GEMM-only time,
+GEMM + all-gather time (max over ranks, CUDA events), tokens/s and algorithmic TFLOP/s.
+With G = 1 it measures the single-GPU kernels.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .column_parallel import ColumnParallelCodebookLinear
+from .synthetic import make_activations, make_payload
+
+
+def _time(fn, reps, dev):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+    if dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()) * 1e3       # microseconds
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ms", default="256,1024,4096,8192")
+    ap.add_argument("--chunks", type=int, default=4)
+    ap.add_argument("--reps", type=int, default=10)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    for k, n in ((2048, 6144), (6144, 2048)):
+        payload = make_payload(n, k, seed=1, iters=1, device=dev)
+        for chunks in sorted({1, args.chunks}):
+            layer = ColumnParallelCodebookLinear(payload, None, str(dev), chunks=chunks)
+            for m in [int(v) for v in args.ms.split(",")]:
+                x = make_activations(m, k, seed=m).to(dev)
+                q, s = layer.local.quantize_activations(x)
+                t_gemm = _time(lambda: layer.local.linear_a8(q, s), args.reps, dev)
+                t_full = _time(lambda: layer(x), args.reps, dev)
+                if rank == 0:
+                    print(json.dumps({
+                        "shape_KxN": f"{k}x{n}", "M": m, "gpus": world, "chunks": chunks,
+                        "gemm_only_us": round(t_gemm, 2), "forward_with_gather_us": round(t_full, 2),
+                        "tokens_per_s": m / (t_full * 1e-6),
+                        "algorithmic_tflops_gemm_only": 2.0 * m * n * k / (t_gemm * 1e-6) / 1e12,
+                        "gather_bytes_per_rank": 2 * m * n // world}), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
