@@ -1,0 +1,166 @@
+"""Synthetic GR00T-N1.5-shaped policy forward with every linear at W1.5A8.
+
+A shape-equivalent stand-in, not the GR00T model: the reference's model sources
+(``gr00t.model.modules.dit``, the Qwen3 backbone) are not part of its tree and no
+checkpoint is available, so weights are random and no action parity is claimed.  What it
+reproduces is the *workload* a policy query puts on the quantized-linear path:
+
+  * vision tower: 24 pre-norm transformer blocks, hidden 1024, MLP 4096, 256 patch tokens;
+  * language model: 12 blocks, hidden 2048, 16 query / 8 key-value heads of 128, gated MLP
+    6144, 300 prefill tokens (the first 256 are the projected patch tokens);
+  * action head: 16 DiT blocks, hidden 1536, self-attention over the 16-step action
+    horizon, cross-attention to the language tokens, MLP 6144, AdaLN timestep modulation,
+    4 Euler flow-matching steps (the loop structure of gr00t_n1d7.py:396-434).
+
+Attention, norms and activations use stock PyTorch; every projection is a
+``PrecomputedPackedVectorCodebookLinear`` (dim-8 vectors, 4096-entry codebook,
+per-output-channel scales).  The cross-attention keys/values depend only on the language
+tokens and are computed once per query, not once per denoising step.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .linear import PrecomputedPackedVectorCodebookLinear
+from .synthetic import make_payload
+
+
+class _Factory:
+    """Creates quantized linears with seeded random payloads (one fitted payload per shape;
+    layers of the same shape get their own device buffers)."""
+
+    def __init__(self, device: torch.device, seed: int):
+        self.device = device
+        self.seed = seed
+        self._payloads = {}
+        self.count = 0
+
+    def linear(self, k: int, n: int) -> PrecomputedPackedVectorCodebookLinear:
+        key = (k, n)
+        if key not in self._payloads:
+            self._payloads[key] = make_payload(n, k, seed=self.seed + len(self._payloads), device=self.device,
+                                               fit=False)
+        self.count += 1
+        return PrecomputedPackedVectorCodebookLinear(self._payloads[key], None, str(self.device))
+
+
+class _Block(torch.nn.Module):
+    """Pre-norm transformer block: self-attention (+ optional cross-attention) + MLP."""
+
+    def __init__(self, f: _Factory, hidden: int, heads: int, kv_heads: int, mlp: int, gated: bool,
+                 cross_dim: int | None = None, adaln: bool = False):
+        super().__init__()
+        self.hidden, self.heads, self.kv_heads = hidden, heads, kv_heads
+        self.head_dim = hidden // heads
+        kv = kv_heads * self.head_dim
+        self.q, self.k, self.v, self.o = f.linear(hidden, hidden), f.linear(hidden, kv), f.linear(hidden, kv), \
+            f.linear(hidden, hidden)
+        self.gated = gated
+        if gated:
+            self.gate, self.up = f.linear(hidden, mlp), f.linear(hidden, mlp)
+        else:
+            self.up = f.linear(hidden, mlp)
+        self.down = f.linear(mlp, hidden)
+        self.cross = cross_dim is not None
+        if self.cross:
+            self.cq, self.ck, self.cv, self.co = f.linear(hidden, hidden), f.linear(cross_dim, hidden), \
+                f.linear(cross_dim, hidden), f.linear(hidden, hidden)
+        self.adaln = adaln
+        if adaln:
+            self.mod = f.linear(hidden, 4 * hidden)          # shift and scale for the two modulated norms
+        self.n1 = torch.nn.LayerNorm(hidden, elementwise_affine=not adaln, device=f.device, dtype=torch.bfloat16)
+        self.n2 = torch.nn.LayerNorm(hidden, elementwise_affine=not adaln, device=f.device, dtype=torch.bfloat16)
+        if self.cross:
+            self.n3 = torch.nn.LayerNorm(hidden, device=f.device, dtype=torch.bfloat16)
+
+    def _attend(self, q, k, v):
+        t, s = q.shape[0], k.shape[0]
+        q = q.view(t, self.heads, self.head_dim).transpose(0, 1)
+        k = k.view(s, -1, self.head_dim).transpose(0, 1)
+        v = v.view(s, -1, self.head_dim).transpose(0, 1)
+        if k.shape[0] != self.heads:
+            rep = self.heads // k.shape[0]
+            k, v = k.repeat_interleave(rep, 0), v.repeat_interleave(rep, 0)
+        return F.scaled_dot_product_attention(q, k, v).transpose(0, 1).reshape(t, self.hidden)
+
+    def cross_kv(self, ctx):
+        return self.ck(ctx), self.cv(ctx)
+
+    def forward(self, x, cond=None, cross_kv=None):
+        if self.adaln:
+            m = self.mod(cond).view(4, self.hidden)
+            h = self.n1(x) * (1 + m[1]) + m[0]
+        else:
+            h = self.n1(x)
+        x = x + self.o(self._attend(self.q(h), self.k(h), self.v(h)))
+        if self.cross:
+            h = self.n3(x)
+            x = x + self.co(self._attend(self.cq(h), cross_kv[0], cross_kv[1]))
+        h = self.n2(x) * (1 + m[3]) + m[2] if self.adaln else self.n2(x)
+        if self.gated:
+            h = F.silu(self.gate(h)) * self.up(h)
+        else:
+            h = F.gelu(self.up(h))
+        return x + self.down(h)
+
+
+class SyntheticGr00tPolicy(torch.nn.Module):
+    VIT_LAYERS, VIT_HIDDEN, VIT_MLP, PATCHES = 24, 1024, 4096, 256
+    LLM_LAYERS, LLM_HIDDEN, LLM_MLP, LLM_TOKENS = 12, 2048, 6144, 300
+    DIT_LAYERS, DIT_HIDDEN, DIT_MLP, HORIZON, STEPS = 16, 1536, 6144, 16, 4
+    ACTION_DIM = 32
+
+    def __init__(self, device: str = "cuda", seed: int = 0):
+        super().__init__()
+        dev = torch.device(device)
+        f = _Factory(dev, seed)
+        g = torch.Generator().manual_seed(seed)
+        bf = dict(device=dev, dtype=torch.bfloat16)
+        self.patch_embed = (torch.randn(3 * 14 * 14, self.VIT_HIDDEN, generator=g) * 0.02).to(**bf)
+        self.vit = torch.nn.ModuleList(_Block(f, self.VIT_HIDDEN, 16, 16, self.VIT_MLP, gated=False)
+                                       for _ in range(self.VIT_LAYERS))
+        self.vis_proj = f.linear(self.VIT_HIDDEN, self.LLM_HIDDEN)
+        self.text_embed = (torch.randn(self.LLM_TOKENS - self.PATCHES, self.LLM_HIDDEN, generator=g) * 0.02).to(**bf)
+        self.llm = torch.nn.ModuleList(_Block(f, self.LLM_HIDDEN, 16, 8, self.LLM_MLP, gated=True)
+                                       for _ in range(self.LLM_LAYERS))
+        self.dit = torch.nn.ModuleList(_Block(f, self.DIT_HIDDEN, 12, 12, self.DIT_MLP, gated=False,
+                                              cross_dim=self.LLM_HIDDEN, adaln=True) for _ in range(self.DIT_LAYERS))
+        self.time_embed = (torch.randn(self.STEPS, self.DIT_HIDDEN, generator=g) * 0.02).to(**bf)
+        self.action_in = (torch.randn(self.ACTION_DIM, self.DIT_HIDDEN, generator=g) * 0.02).to(**bf)
+        self.action_out = (torch.randn(self.DIT_HIDDEN, self.ACTION_DIM, generator=g) * 0.02).to(**bf)
+        self.num_quantized_linears = f.count
+        self.device = dev
+
+    def quantized_linear_calls_per_query(self) -> int:
+        vit = self.VIT_LAYERS * 6
+        llm = self.LLM_LAYERS * 7
+        dit = self.DIT_LAYERS * (2 + self.STEPS * 9)       # cross K/V once, 9 projections per step
+        return vit + 1 + llm + dit
+
+    @torch.no_grad()
+    def forward(self, image: torch.Tensor, noise: torch.Tensor) -> torch.Tensor:
+        """image: [3, 224, 224] bf16; noise: [HORIZON, ACTION_DIM] bf16 -> actions [HORIZON, ACTION_DIM]."""
+        patches = image.unfold(1, 14, 14).unfold(2, 14, 14).permute(1, 2, 0, 3, 4).reshape(self.PATCHES, -1)
+        x = patches @ self.patch_embed
+        for blk in self.vit:
+            x = blk(x)
+        tokens = torch.cat([self.vis_proj(x), self.text_embed], dim=0)
+        for blk in self.llm:
+            tokens = blk(tokens)
+        kv = [blk.cross_kv(tokens) for blk in self.dit]
+        actions = noise
+        dt = 1.0 / self.STEPS
+        for step in range(self.STEPS):
+            h = actions @ self.action_in
+            cond = self.time_embed[step: step + 1]
+            for blk, ckv in zip(self.dit, kv):
+                h = blk(h, cond=cond, cross_kv=ckv)
+            actions = actions + dt * (h @ self.action_out)
+        return actions
+
+    def example_inputs(self, seed: int = 42):
+        g = torch.Generator().manual_seed(seed)
+        image = torch.rand(3, 224, 224, generator=g).to(device=self.device, dtype=torch.bfloat16)
+        noise = torch.randn(self.HORIZON, self.ACTION_DIM, generator=g).to(device=self.device, dtype=torch.bfloat16)
+        return image, noise
