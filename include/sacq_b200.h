@@ -126,9 +126,7 @@ SACQ_API int sacq_linear_a8(const sacq_layer_t* layer, const void* q, const floa
 
 /* Convenience: sacq_quant_act_fp8 + sacq_linear_a8 for a bf16 input (the module's
  * forward(x), SHIM:456-541).  `q_scratch` (M*K bytes) and `scale_scratch` (M floats)
- * are caller-provided device buffers.  For small M the quantizer is fused into the GEMM
- * kernel: the result is the same, `scale_scratch` still receives the per-token scales,
- * but `q_scratch` is then left untouched. */
+ * are caller-provided device buffers. */
 SACQ_API int sacq_linear_bf16(const sacq_layer_t* layer, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
                      float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
                      void* stream);

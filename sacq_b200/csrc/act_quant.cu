@@ -24,6 +24,9 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
                      float* __restrict__ scale_out) {
   __shared__ float red[kThreads / 32];
   __shared__ float s_scale;
+  // A GEMM launched with programmatic stream serialization may start its prologue now; it
+  // waits for this grid to finish before it reads q or the scales.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t m = blockIdx.x;
   const uint16_t* row = x + m * pitch;
   uint8_t* qrow = q + m * K;

@@ -262,12 +262,6 @@ SACQ_API int sacq_linear_bf16(const sacq_layer_t* L, const void* x_bf16, int64_t
                      void* stream) {
   if (int rc = check_layer(L)) return rc;
   if (M == 0) return SACQ_OK;
-  // Small batches run as one kernel: the GEMM's CTAs quantize their own token rows.
-  if (x_bf16 != nullptr && y_out != nullptr && ldy >= L->d.out_features && L->d.out_features > 0 &&
-      pick_kernel(L, M) == 1 && small_m_fused_available(L, M, x_bf16, x_pitch)) {
-    DeviceGuard guard(L->d.device);
-    return launch_small_m_fused(L, x_bf16, x_pitch, scale_scratch, M, y_out, ldy, static_cast<cudaStream_t>(stream));
-  }
   int rc = sacq_quant_act_fp8(x_bf16, x_pitch, M, L->d.in_features, q_scratch, scale_scratch, stream);
   if (rc != SACQ_OK) return rc;
   return sacq_linear_a8(L, q_scratch, scale_scratch, M, y_out, ldy, workspace, workspace_bytes, stream);

@@ -64,10 +64,6 @@ int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M);
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    void* ws, int64_t ws_bytes, cudaStream_t s);
 
-bool small_m_fused_available(const sacq_layer* L, int64_t M, const void* x_bf16, int64_t x_pitch);
-int launch_small_m_fused(const sacq_layer* L, const void* x_bf16, int64_t x_pitch, float* scale_out, int64_t M,
-                         void* y, int64_t ldy, cudaStream_t s);
-
 bool large_m_supported(const sacq_layer* L);
 int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    cudaStream_t s);

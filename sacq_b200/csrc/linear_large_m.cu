@@ -40,13 +40,12 @@ namespace sacq {
 namespace {
 
 constexpr int kBM = 128;          // tokens per tile (TMEM lanes)
-constexpr int kBN = 128;          // weight rows per tile (accumulator columns)
+constexpr int kMaxBN = 128;       // weight rows per tile (accumulator columns): BN in {32, 64, 128}
 constexpr int kBK = 128;          // e4m3 elements (= bytes) per K block: one 128B swizzle row
 constexpr int kStages = 3;
 constexpr int kExpanderThreads = 256;
 constexpr int kThreads = 64 + kExpanderThreads;
 constexpr int kTileBytes = kBM * kBK;            // 16 KB: one operand tile
-constexpr uint32_t kTmemCols = 128;
 
 constexpr int kErrTimeout = 1;
 
@@ -162,8 +161,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 }
 
 // kind::f8f6f4 instruction descriptor: fp32 accumulate, A = B = e4m3, both K-major, N, M.
-constexpr uint32_t kIdesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) |
-                            ((uint32_t)(kBM >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
@@ -184,6 +184,34 @@ __device__ __forceinline__ uint32_t field8(const uint32_t (&w)[BITS / 4], int j)
   return __funnelshift_r(w[word], w[word + 1 < BITS / 4 ? word + 1 : word], off) & ((1u << BITS) - 1u);
 }
 
+// NIDX consecutive BITS-wide fields starting at field `first` of a little-endian stream
+// that begins at the 4-byte aligned address `base`; `first` is a multiple of NIDX.
+template <int BITS, int NIDX>
+__device__ __forceinline__ void load_fields(const uint8_t* base, int first, uint32_t (&out)[NIDX]) {
+  constexpr int kBits = BITS * NIDX;
+  constexpr uint32_t kMask = (1u << BITS) - 1u;
+  const uint32_t* w32 = reinterpret_cast<const uint32_t*>(base);
+  if constexpr (kBits % 32 == 0) {
+    constexpr int NW = kBits / 32;
+    uint32_t w[NW];
+    const int w0 = first * BITS / 32;
+#pragma unroll
+    for (int j = 0; j < NW; ++j) w[j] = w32[w0 + j];
+#pragma unroll
+    for (int j = 0; j < NIDX; ++j) {
+      const int bit = j * BITS, word = bit >> 5, off = bit & 31;
+      out[j] = (off + BITS <= 32) ? ((w[word] >> off) & kMask)
+                                  : (__funnelshift_r(w[word], w[word + 1 < NW ? word + 1 : word], off) & kMask);
+    }
+  } else {
+    static_assert(kBits <= 48, "unaligned field windows must fit 64 bits after a 16-bit offset");
+    const int start = first * BITS;
+    const uint64_t v = (((uint64_t)w32[(start >> 5) + 1] << 32) | w32[start >> 5]) >> (start & 31);
+#pragma unroll
+    for (int j = 0; j < NIDX; ++j) out[j] = (uint32_t)(v >> (j * BITS)) & kMask;
+  }
+}
+
 struct LargeMParams {
   const uint8_t* cb_hilo;       // [C][2][D] e4m3
   const uint16_t* scales;       // bf16 [N]
@@ -198,7 +226,8 @@ struct LargeMParams {
 
 // Shared-memory carve-up (offsets from a 1024-byte aligned base).
 struct SmemLayout {
-  uint32_t stage_off;      // kStages x {A, B_hi, B_lo} tiles of 16 KB
+  uint32_t stage_off;      // kStages x {A 16 KB, B_hi, B_lo of BN x 128 bytes}
+  uint32_t stage_bytes;
   uint32_t idx_off;        // 2 x [128 rows][sb_bytes]
   uint32_t cb_off;         // [C][2][D]
   uint32_t sw_off;         // float[128] scale[n] * out_mul
@@ -208,37 +237,42 @@ struct SmemLayout {
   uint32_t total;
 };
 
-__host__ __device__ inline SmemLayout make_layout(int sb_bytes, int cb_bytes) {
+__host__ __device__ inline SmemLayout make_layout(int bn, int sb_bytes, int cb_bytes) {
   SmemLayout L;
   L.stage_off = 0;
-  L.idx_off = kStages * 3 * kTileBytes;
-  L.cb_off = L.idx_off + 2 * kBN * sb_bytes;
+  L.stage_bytes = kTileBytes + 2 * bn * kBK;
+  L.idx_off = kStages * L.stage_bytes;
+  L.cb_off = L.idx_off + 2 * bn * sb_bytes;
   L.cb_off = (L.cb_off + 127) & ~127u;
   L.sw_off = L.cb_off + ((cb_bytes + 127) & ~127);
-  L.bias_off = L.sw_off + kBN * 4;
-  L.bar_off = L.bias_off + kBN * 4;
+  L.bias_off = L.sw_off + kMaxBN * 4;
+  L.bar_off = L.bias_off + kMaxBN * 4;
   L.misc_off = L.bar_off + 16 * 8;
   L.total = L.misc_off + 64;
   return L;
 }
 
-// D in {4, 8}, BITS in {8, 12, 16}.  grid = (ceil(N/128), ceil(M/128)).
-template <int D, int BITS>
+// D in {4, 8}, BITS in {8, 12, 16}, BN in {32, 64, 128}.  grid = (ceil(N/BN), ceil(M/128)).
+// Smaller BN trades tensor-core efficiency for more CTAs when M is only a few tiles.
+template <int D, int BITS, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
                const LargeMParams p) {
   constexpr int IDX_PER_KB = kBK / D;                 // indices per row per K block
   constexpr int KB_BYTES = IDX_PER_KB * BITS / 8;     // index bytes per row per K block
   constexpr int SB_BYTES = 2 * KB_BYTES;              // ... per super block (two K blocks): multiple of 16
-  constexpr int WPG = BITS / 4;                       // words holding 8 indices
-  constexpr int GROUPS = IDX_PER_KB / 16;             // groups of 8 indices per expander thread per K block
   constexpr int CW_BYTES = 2 * D;                     // hi + lo bytes per codeword
+  constexpr int PARTS = kExpanderThreads / BN;        // expander threads per weight row
+  constexpr int CPT = 8 / PARTS;                      // 16-byte chunks each of them writes per K block
+  constexpr int IPC = 16 / D;                         // indices per chunk
+  constexpr uint32_t kIdesc = make_idesc(BN);
+  constexpr int B_TILE = BN * kBK;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
-  const SmemLayout L = make_layout(SB_BYTES, p.C * CW_BYTES);
+  const SmemLayout L = make_layout(BN, SB_BYTES, p.C * CW_BYTES);
 
   // barrier indices
   constexpr int A_FULL = 0, B_FULL = kStages, EMPTY = 2 * kStages, IDX_FULL = 3 * kStages,
@@ -249,19 +283,19 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + L.misc_off + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kBN;
+  const int n0 = blockIdx.x * BN;
   const int m0 = blockIdx.y * kBM;
   const int num_kb = p.K / kBK;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(bar(A_FULL + i), 1);
-      mbar_init(bar(B_FULL + i), kExpanderThreads);
+      mbar_init(bar(B_FULL + i), kExpanderThreads / 32);
       mbar_init(bar(EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(IDX_FULL + i), 1);
-      mbar_init(bar(IDX_EMPTY + i), kExpanderThreads);
+      mbar_init(bar(IDX_EMPTY + i), kExpanderThreads / 32);
     }
     mbar_init(bar(ACC_FULL), 1);
     *abort_flag = 0;
@@ -269,7 +303,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_idx);
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), (uint32_t)BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -282,13 +316,13 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if ((kb & 1) == 0) {
           const int sb = kb >> 1, slot = sb & 1;
           if (!mbar_wait(bar(IDX_EMPTY + slot), ((sb >> 1) & 1) ^ 1, abort_flag, p.status)) break;
-          mbar_arrive_expect_tx(bar(IDX_FULL + slot), kBN * SB_BYTES);
-          tma_load_2d(base + L.idx_off + slot * kBN * SB_BYTES, &tmap_idx, sb * SB_BYTES, n0, bar(IDX_FULL + slot));
+          mbar_arrive_expect_tx(bar(IDX_FULL + slot), BN * SB_BYTES);
+          tma_load_2d(base + L.idx_off + slot * BN * SB_BYTES, &tmap_idx, sb * SB_BYTES, n0, bar(IDX_FULL + slot));
         }
         const int st = kb % kStages;
         if (!mbar_wait(bar(EMPTY + st), ((kb / kStages) & 1) ^ 1, abort_flag, p.status)) break;
         mbar_arrive_expect_tx(bar(A_FULL + st), kTileBytes);
-        tma_load_2d(base + L.stage_off + st * 3 * kTileBytes, &tmap_a, kb * kBK, m0, bar(A_FULL + st));
+        tma_load_2d(base + L.stage_off + st * L.stage_bytes, &tmap_a, kb * kBK, m0, bar(A_FULL + st));
       }
     }
     __syncwarp();
@@ -303,10 +337,10 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
              mbar_wait(bar(B_FULL + st), ph, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = base + L.stage_off + st * 3 * kTileBytes;
+        const uint32_t a_addr = base + L.stage_off + st * L.stage_bytes;
         const uint64_t a_desc = make_smem_desc(a_addr);
         const uint64_t bh_desc = make_smem_desc(a_addr + kTileBytes);
-        const uint64_t bl_desc = make_smem_desc(a_addr + 2 * kTileBytes);
+        const uint64_t bl_desc = make_smem_desc(a_addr + kTileBytes + B_TILE);
 #pragma unroll
         for (int ks = 0; ks < kBK / 32; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32) >> 4);
@@ -321,15 +355,15 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else {
     // ------------------------------------------------------------------ expanders, then epilogue
     const int et = threadIdx.x - 64;                 // 0..255
-    const int row = et & (kBN - 1);
-    const int half = et >> 7;
+    const int row = et % BN;
+    const int part = et / BN;                        // which CPT chunks of the row's 8 this thread writes
     {
       // codebook (hi/lo) and the per-column epilogue constants
       const uint4* src = reinterpret_cast<const uint4*>(p.cb_hilo);
       uint4* dst = reinterpret_cast<uint4*>(sm + L.cb_off);
       const int n16 = (p.C * CW_BYTES) >> 4;
       for (int i = et; i < n16; i += kExpanderThreads) cp_async_16(dst + i, src + i);
-      if (et < kBN) {
+      if (et < BN) {
         const int n = min(n0 + et, p.N - 1);
         reinterpret_cast<float*>(sm + L.sw_off)[et] = bf16_bits_to_float(__ldg(p.scales + n)) * p.out_mul;
         reinterpret_cast<float*>(sm + L.bias_off)[et] = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
@@ -345,43 +379,38 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       ok = mbar_wait(bar(IDX_FULL + slot), (sb >> 1) & 1, abort_flag, p.status) &&
            mbar_wait(bar(EMPTY + st), ((kb / kStages) & 1) ^ 1, abort_flag, p.status);
       if (!ok) break;
-      const uint8_t* irow = sm + L.idx_off + slot * kBN * SB_BYTES + row * SB_BYTES + (kb & 1) * KB_BYTES +
-                            half * (KB_BYTES / 2);
-      uint8_t* bhi = sm + L.stage_off + st * 3 * kTileBytes + kTileBytes + row * 128;
-      uint8_t* blo = bhi + kTileBytes;
+      // this thread's CPT * IPC indices of the row's K block
+      uint32_t idx[CPT * IPC];
+      load_fields<BITS, CPT * IPC>(sm + L.idx_off + slot * BN * SB_BYTES + row * SB_BYTES + (kb & 1) * KB_BYTES,
+                                   part * CPT * IPC, idx);
+      uint8_t* bhi = sm + L.stage_off + st * L.stage_bytes + kTileBytes + row * 128;
+      uint8_t* blo = bhi + B_TILE;
       const int sw = row & 7;
 #pragma unroll
-      for (int gI = 0; gI < GROUPS; ++gI) {
-        uint32_t w[WPG];
-#pragma unroll
-        for (int j = 0; j < WPG; ++j) w[j] = *reinterpret_cast<const uint32_t*>(irow + gI * BITS + 4 * j);
+      for (int c = 0; c < CPT; ++c) {
+        const int chunk = part * CPT + c;              // logical 16-byte chunk of the 128-byte row
+        uint4 hi4, lo4;
         if constexpr (D == 8) {
-          // 8 indices -> 4 chunks of 16 bytes (2 codewords each)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 c0 = *reinterpret_cast<const uint4*>(cbs + (size_t)field8<BITS>(w, 2 * c) * 16);
-            const uint4 c1 = *reinterpret_cast<const uint4*>(cbs + (size_t)field8<BITS>(w, 2 * c + 1) * 16);
-            const int chunk = (half * 4 + c) ^ sw;
-            *reinterpret_cast<uint4*>(bhi + chunk * 16) = make_uint4(c0.x, c0.y, c1.x, c1.y);
-            *reinterpret_cast<uint4*>(blo + chunk * 16) = make_uint4(c0.z, c0.w, c1.z, c1.w);
-          }
+          const uint4 c0 = *reinterpret_cast<const uint4*>(cbs + (size_t)idx[c * IPC] * 16);
+          const uint4 c1 = *reinterpret_cast<const uint4*>(cbs + (size_t)idx[c * IPC + 1] * 16);
+          hi4 = make_uint4(c0.x, c0.y, c1.x, c1.y);
+          lo4 = make_uint4(c0.z, c0.w, c1.z, c1.w);
         } else {
-          // D == 4: 8 indices -> 2 chunks of 16 bytes (4 codewords each); two groups per thread
+          uint2 cw[4];
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint2 cw[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              cw[j] = *reinterpret_cast<const uint2*>(cbs + (size_t)field8<BITS>(w, 4 * c + j) * 8);
-            const int chunk = (half * 4 + gI * 2 + c) ^ sw;
-            *reinterpret_cast<uint4*>(bhi + chunk * 16) = make_uint4(cw[0].x, cw[1].x, cw[2].x, cw[3].x);
-            *reinterpret_cast<uint4*>(blo + chunk * 16) = make_uint4(cw[0].y, cw[1].y, cw[2].y, cw[3].y);
-          }
+          for (int j = 0; j < 4; ++j) cw[j] = *reinterpret_cast<const uint2*>(cbs + (size_t)idx[c * IPC + j] * 8);
+          hi4 = make_uint4(cw[0].x, cw[1].x, cw[2].x, cw[3].x);
+          lo4 = make_uint4(cw[0].y, cw[1].y, cw[2].y, cw[3].y);
         }
+        *reinterpret_cast<uint4*>(bhi + ((chunk ^ sw) * 16)) = hi4;
+        *reinterpret_cast<uint4*>(blo + ((chunk ^ sw) * 16)) = lo4;
       }
       fence_proxy_async();                            // generic-proxy writes -> visible to the tensor core
-      mbar_arrive(bar(B_FULL + st));
-      if ((kb & 1) == 1 || kb == num_kb - 1) mbar_arrive(bar(IDX_EMPTY + slot));
+      __syncwarp();
+      if (lane == 0) {                                // one arrival per warp keeps the barrier off the critical path
+        mbar_arrive(bar(B_FULL + st));
+        if ((kb & 1) == 1 || kb == num_kb - 1) mbar_arrive(bar(IDX_EMPTY + slot));
+      }
     }
 
     // ---- epilogue: this warp's TMEM lane quarter, half of the 128 columns
@@ -390,14 +419,14 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (ok) {
       tc_fence_after();
       const int quarter = warp & 3;                   // TMEM lanes 32*quarter .. +31
-      const int col_half = (warp - 2) >> 2;           // warps 2-5: columns 0-63, warps 6-9: 64-127
+      const int col_half = (warp - 2) >> 2;           // two warps share a quarter: they split the 32-column groups
       const int m = m0 + quarter * 32 + lane;
       const float* swp = reinterpret_cast<const float*>(sm + L.sw_off);
       const float* bp = reinterpret_cast<const float*>(sm + L.bias_off);
       const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c0 = col_half * 64 + cc * 32;
+      for (int cc = col_half; cc < BN / 32; cc += 2) {
+        const int c0 = cc * 32;
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         if (m < p.M) {
@@ -430,16 +459,16 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // ---- common exit: every thread arrives here, also after an aborted wait
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)BN);
 }
 
 
 }  // namespace
 
 struct LargeMPlan {
-  CUtensorMap tmap_idx;
+  CUtensorMap tmap_idx[3];      // index-tile maps for BN = 32, 64, 128
+  bool have[3];
   int sb_bytes;
-  size_t smem;
 };
 
 namespace {
@@ -482,20 +511,28 @@ int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint
 
 int sb_bytes_for(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
 
-template <int D, int BITS>
-cudaError_t launch_one(const CUtensorMap& ta, const LargeMPlan* plan, const LargeMParams& p, dim3 grid,
-                       cudaStream_t s) {
+template <int D, int BITS, int BN>
+cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, dim3 grid, cudaStream_t s) {
+  const size_t smem = make_layout(BN, 2 * (kBK / D) * BITS / 8, p.C * 2 * D).total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)plan->smem);
+    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  large_m_kernel<D, BITS><<<grid, kThreads, plan->smem, s>>>(ta, plan->tmap_idx, p);
+  large_m_kernel<D, BITS, BN><<<grid, kThreads, smem, s>>>(ta, ti, p);
   return cudaGetLastError();
+}
+
+template <int D, int BITS>
+cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, int bn, dim3 grid,
+                       cudaStream_t s) {
+  if (bn == 32) return launch_bn<D, BITS, 32>(ta, ti, p, grid, s);
+  if (bn == 64) return launch_bn<D, BITS, 64>(ta, ti, p, grid, s);
+  return launch_bn<D, BITS, 128>(ta, ti, p, grid, s);
 }
 
 }  // namespace
@@ -508,7 +545,7 @@ bool large_m_supported(const sacq_layer* L) {
   if (d.in_features % (2 * kBK) != 0) return false;
   if (L->num_groups != 1 || d.shift_bf16 != 0) return false;
   const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
-  if (make_layout(sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) return false;
+  if (make_layout(kMaxBN, sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) return false;
   return true;
 }
 
@@ -529,15 +566,29 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
   if (Lm->large_plan == nullptr) {
     LargeMPlan* plan = new LargeMPlan();
     plan->sb_bytes = sb_bytes_for(L);
-    plan->smem = make_layout(plan->sb_bytes, d.codebook_size * d.vector_dim * 2).total + 1024;
-    const uint64_t row_bytes = (uint64_t)(L->row_bits / 8);
-    const int rc = encode_bytes_2d(&plan->tmap_idx, d.packed, row_bytes, (uint64_t)d.out_features, row_bytes,
-                                   (uint32_t)plan->sb_bytes, kBN, CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc != SACQ_OK) {
-      delete plan;
-      return rc;
-    }
+    plan->have[0] = plan->have[1] = plan->have[2] = false;
     Lm->large_plan = plan;
+  }
+  // Tile width.  A CTA's time per K block is roughly a fixed pipeline latency plus the
+  // expansion of BN rows (measured: about 0.3 us + 0.9 us * BN/128), and the grid runs in
+  // ceil(tiles / SMs) waves; take the BN with the smallest product.
+  const int64_t m_tiles = (M + kBM - 1) / kBM;
+  int bn = 128;
+  double best = 1e30;
+  for (int cand = 128; cand >= 32; cand >>= 1) {
+    const int64_t tiles = ((d.out_features + cand - 1) / cand) * m_tiles;
+    const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
+    const double cost = (double)waves * (0.3 + 0.9 * cand / 128.0);
+    if (cost < best - 1e-9) { best = cost; bn = cand; }
+  }
+  const int bi = bn == 32 ? 0 : (bn == 64 ? 1 : 2);
+  if (!Lm->large_plan->have[bi]) {
+    const uint64_t row_bytes = (uint64_t)(L->row_bits / 8);
+    const int rc = encode_bytes_2d(&Lm->large_plan->tmap_idx[bi], d.packed, row_bytes, (uint64_t)d.out_features,
+                                   row_bytes, (uint32_t)Lm->large_plan->sb_bytes, (uint32_t)bn,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != SACQ_OK) return rc;
+    Lm->large_plan->have[bi] = true;
   }
   CUtensorMap ta;
   {
@@ -555,16 +606,16 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
   p.ldy = ldy;
   p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features; p.C = d.codebook_size;
   p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
-  const dim3 grid((unsigned)((d.out_features + kBN - 1) / kBN), (unsigned)((M + kBM - 1) / kBM));
+  const dim3 grid((unsigned)((d.out_features + bn - 1) / bn), (unsigned)m_tiles);
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   cudaError_t e;
   const int D = d.vector_dim, B = d.index_bits;
-  if (D == 8 && B == 12) e = launch_one<8, 12>(ta, Lm->large_plan, p, grid, s);
-  else if (D == 8 && B == 8) e = launch_one<8, 8>(ta, Lm->large_plan, p, grid, s);
-  else if (D == 8 && B == 16) e = launch_one<8, 16>(ta, Lm->large_plan, p, grid, s);
-  else if (D == 4 && B == 12) e = launch_one<4, 12>(ta, Lm->large_plan, p, grid, s);
-  else if (D == 4 && B == 8) e = launch_one<4, 8>(ta, Lm->large_plan, p, grid, s);
-  else e = launch_one<4, 16>(ta, Lm->large_plan, p, grid, s);
+  if (D == 8 && B == 12) e = launch_one<8, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
+  else if (D == 8 && B == 8) e = launch_one<8, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
+  else if (D == 8 && B == 16) e = launch_one<8, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
+  else if (D == 4 && B == 12) e = launch_one<4, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
+  else if (D == 4 && B == 8) e = launch_one<4, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
+  else e = launch_one<4, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
   count_launch();
   if (e != cudaSuccess) return cuda_fail(e, "large-M launch");
   return SACQ_OK;

@@ -329,7 +329,7 @@ bool fast_eligible(const sacq_layer* L) {
 
 
 // M from which the warp-MMA variant is preferred over the CUDA-core one.
-constexpr int64_t kMmaMinM = 5;
+constexpr int64_t kMmaMinM = 1;
 
 Plan make_plan(const sacq_layer* L, int64_t M) {
   const sacq_layer_desc& d = L->d;
@@ -450,10 +450,8 @@ int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M) {
   return bytes;
 }
 
-namespace {
-int launch_small_m_impl(const sacq_layer* L, const void* q, const float* scale, const void* x_bf16, int64_t x_pitch,
-                        float* scale_out, int64_t M, void* y, int64_t ldy, void* ws, int64_t ws_bytes,
-                        cudaStream_t s) {
+int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                   void* ws, int64_t ws_bytes, cudaStream_t s) {
   const sacq_layer_desc& d = L->d;
   if (M == 0 || d.out_features == 0) return SACQ_OK;
   if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
@@ -478,12 +476,7 @@ int launch_small_m_impl(const sacq_layer* L, const void* q, const float* scale, 
   p.bias = static_cast<const uint16_t*>(d.bias);
   p.q = static_cast<const uint8_t*>(q);
   p.act_scale = scale;
-  p.x_bf16 = static_cast<const uint16_t*>(x_bf16);
-  p.x_pitch = x_pitch;
-  p.act_scale_out = scale_out;
   p.status = L->d_status;
-  if (x_bf16 != nullptr && !(pl.mma && pl.staged))
-    return set_error(SACQ_ERR_UNSUPPORTED, "the fused quantizer needs the staged small-M kernel");
   p.y = static_cast<uint16_t*>(y);
   p.counters = static_cast<int*>(ws);
   p.partial = ws ? reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + sacq_workspace_counter_bytes()) : nullptr;
@@ -501,11 +494,11 @@ int launch_small_m_impl(const sacq_layer* L, const void* q, const float* scale, 
 
   cudaError_t e;
   if (pl.fast) {
-    if (x_bf16 == nullptr && (reinterpret_cast<uintptr_t>(q) % 8 != 0 || d.in_features % 8 != 0))
+    if (reinterpret_cast<uintptr_t>(q) % 8 != 0 || d.in_features % 8 != 0)
       return set_error(SACQ_ERR_ALIGNMENT, "quantized activations must be 8-byte aligned with K %% 8 == 0");
     p.out_mul = ldexpf(1.f, -L->cb_exp_shift);
     if (pl.mma) {
-      if (x_bf16 == nullptr && reinterpret_cast<uintptr_t>(q) % 16 != 0)
+      if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
         return set_error(SACQ_ERR_ALIGNMENT, "small-M MMA kernel: q must be 16-byte aligned");
       e = launch_small_m_mma(pl, p, s);
     } else if (pl.D == 8 && pl.BITS == 12) e = launch_fast_cb<8, 12>(pl, p, s);
@@ -522,24 +515,4 @@ int launch_small_m_impl(const sacq_layer* L, const void* q, const float* scale, 
   if (e != cudaSuccess) return cuda_fail(e, "small-M launch");
   return SACQ_OK;
 }
-}  // namespace
-
-int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                   void* ws, int64_t ws_bytes, cudaStream_t s) {
-  return launch_small_m_impl(L, q, scale, nullptr, 0, nullptr, M, y, ldy, ws, ws_bytes, s);
-}
-
-// True when a bf16 forward of M rows can run as ONE kernel (quantizer fused into the GEMM).
-bool small_m_fused_available(const sacq_layer* L, int64_t M, const void* x_bf16, int64_t x_pitch) {
-  if (M <= 0 || M > 64) return false;
-  if (reinterpret_cast<uintptr_t>(x_bf16) % 16 != 0 || x_pitch % 8 != 0) return false;
-  const Plan pl = make_plan(L, M);
-  return pl.mma && pl.staged;
-}
-
-int launch_small_m_fused(const sacq_layer* L, const void* x_bf16, int64_t x_pitch, float* scale_out, int64_t M,
-                         void* y, int64_t ldy, cudaStream_t s) {
-  return launch_small_m_impl(L, nullptr, nullptr, x_bf16, x_pitch, scale_out, M, y, ldy, nullptr, 0, s);
-}
-
 }  // namespace sacq

@@ -234,10 +234,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const Sm
 // thread, completion on an mbarrier) before the warps start: the codebook once per CTA,
 // then per tile the 8*R8 packed index rows (one contiguous block of the stream) and the 16
 // activation rows.  The inner loop then has no global loads at all, and the memory latency
-// is paid once per tile instead of once per span.  With FUSED the activation rows are not
-// copied but produced in place: the CTA quantizes its 16 bf16 token rows itself (row
-// abs-max / 448, IEEE division, e4m3 RNE -- the quantizer kernel's arithmetic), which
-// removes the separate quantizer launch from a small-M forward.
+// is paid once per tile instead of once per span.
 
 constexpr int kActPad = 16;                       // bytes of padding per staged activation row
 
@@ -298,7 +295,7 @@ __host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64
   return L;
 }
 
-template <int D, int BITS, int R8, bool FUSED>
+template <int D, int BITS, int R8>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(const SmallMParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;
@@ -341,56 +338,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
     const int rows_here = min(8 * R8, p.N - n_base);
     const int toks_here = min(16, p.M - m_base);
 
-    // ---- bring the tile in
+    // ---- bring the tile in.  The packed indices (like the codebook) are layer constants;
+    // the activations and their scales come from the kernel before this one, so on the
+    // first tile everything issued before the dependency wait overlaps that kernel.
+    const uint32_t idx_bytes = (uint32_t)(rows_here * p.row_bytes);
+    const uint32_t act_bytes = (uint32_t)(toks_here * p.K);
     if (threadIdx.x == 0) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic reads of these buffers
-      const uint32_t idx_bytes = (uint32_t)(rows_here * p.row_bytes);
-      const uint32_t act_bytes = FUSED ? 0u : (uint32_t)(toks_here * p.K);
       mbar_expect_tx(bar_tile, idx_bytes + act_bytes);
       bulk_copy_g2s(smem + L.idx_off, p.packed + (int64_t)n_base * p.row_bytes, idx_bytes, bar_tile);
-      if (!FUSED)
-        for (int m = 0; m < toks_here; ++m)
-          bulk_copy_g2s(act_s + m * act_pitch, p.q + (int64_t)(m_base + m) * p.K, (uint32_t)p.K, bar_tile);
     }
-    if constexpr (FUSED) {
-      // quantize this tile's token rows in place: warp w takes rows w, w + nwarps, ...
-      for (int m = warp; m < toks_here; m += nwarps) {
-        const uint4* xrow = reinterpret_cast<const uint4*>(p.x_bf16 + (int64_t)(m_base + m) * p.x_pitch);
-        const int chunks = p.K >> 3;
-        float mx = 0.f;
-        for (int c = lane; c < chunks; c += 32) {
-          const uint4 v = __ldg(xrow + c);
-          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            mx = fmaxf(mx, fabsf(bf16_bits_to_float(w4[j] & 0xffff)));
-            mx = fmaxf(mx, fabsf(bf16_bits_to_float(w4[j] >> 16)));
-          }
-        }
-        mx = warp_max(mx);
-        const float sc = mx > 0.f ? __fdiv_rn(mx, kE4M3Max) : 1.0f;
-        if (lane == 0) {
-          sa_s[m] = sc;
-          if (p.act_scale_out != nullptr && rt == 0) p.act_scale_out[m_base + m] = sc;
-        }
-        for (int c = lane; c < chunks; c += 32) {
-          const uint4 v = __ldg(xrow + c);                      // second pass hits L1/L2
-          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-          uint32_t o[2];
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const uint32_t a = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j] & 0xffff), sc)),
-                                                clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j] >> 16), sc)));
-            const uint32_t b = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j + 1] & 0xffff), sc)),
-                                                clamp448(__fdiv_rn(bf16_bits_to_float(w4[2 * j + 1] >> 16), sc)));
-            o[j] = a | (b << 16);
-          }
-          *reinterpret_cast<uint2*>(act_s + m * act_pitch + c * 8) = make_uint2(o[0], o[1]);
-        }
-      }
-    } else {
-      if (threadIdx.x < 16) sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
+    if (!cb_waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) {
+      for (int m = 0; m < toks_here; ++m)
+        bulk_copy_g2s(act_s + m * act_pitch, p.q + (int64_t)(m_base + m) * p.K, (uint32_t)p.K, bar_tile);
     }
+    if (threadIdx.x < 16) sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
     if (!cb_waited) {
       ok = mbar_wait_bounded(bar_cb, 0, p.status) && ok;
       cb_waited = true;
@@ -531,18 +494,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
   if (!cb_waited) mbar_wait_bounded(bar_cb, 0, p.status);   // never exit with the codebook copy in flight
 }
 
-template <int D, int BITS, bool FUSED>
-cudaError_t launch_staged_r8(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
-  switch (pl.r8) {
-    case 1: return launch_kernel<small_m_mma_staged_kernel<D, BITS, 1, FUSED>>(pl, p, s);
-    case 2: return launch_kernel<small_m_mma_staged_kernel<D, BITS, 2, FUSED>>(pl, p, s);
-    default: return launch_kernel<small_m_mma_staged_kernel<D, BITS, 4, FUSED>>(pl, p, s);
-  }
-}
-
 template <int D, int BITS>
 cudaError_t launch_staged(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
-  return p.x_bf16 != nullptr ? launch_staged_r8<D, BITS, true>(pl, p, s) : launch_staged_r8<D, BITS, false>(pl, p, s);
+  switch (pl.r8) {
+    case 1: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 1>>(pl, p, s);
+    case 2: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 2>>(pl, p, s);
+    default: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 4>>(pl, p, s);
+  }
 }
 
 template <int D, int BITS, bool CB>

@@ -20,11 +20,8 @@ struct SmallMParams {
   const uint16_t* cb_bf16;     // [C, d] original (generic kernel)
   const uint16_t* scales;      // bf16 [N, num_groups]
   const uint16_t* bias;        // bf16 [N] or null
-  const uint8_t* q;            // e4m3 [M, K] (null when the quantizer is fused in)
-  const uint16_t* x_bf16;      // bf16 [M, x_pitch]: raw activations for the fused quantizer, or null
+  const uint8_t* q;            // e4m3 [M, K]
   int* status;                 // layer status word (bounded waits report here)
-  float* act_scale_out;        // fused quantizer: per-token scales written here (may be null)
-  int64_t x_pitch;
   const float* act_scale;      // [M]
   uint16_t* y;                 // bf16 [M, ldy]
   float* partial;              // [num_sg][M][N] (only when num_sg > 1)
@@ -107,6 +104,32 @@ cudaError_t launch_kernel(const Plan& pl, const SmallMParams& p, cudaStream_t s)
   }
   Kern<<<pl.grid, pl.warps * 32, pl.smem, s>>>(p);
   return cudaGetLastError();
+}
+
+// Same, with programmatic dependent launch: the grid may start while the previous kernel
+// of the stream is still running; the kernel must execute griddepcontrol.wait before it
+// touches anything that kernel produces.
+template <auto Kern>
+cudaError_t launch_kernel_pdl(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)pl.grid);
+  cfg.blockDim = dim3((unsigned)(pl.warps * 32));
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, Kern, p);
 }
 
 // linear_small_m_mma.cu

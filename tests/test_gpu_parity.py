@@ -235,7 +235,7 @@ def test_linear_decode_shapes(K, N):
         x = make_activations(M, K, seed=M)
         q_bits, s = O.quantize_rows_e4m3(bf16_bits(x))
         outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias))
-        # the bf16 forward fuses the quantizer into the GEMM kernel: same bytes as the two-step path
+        # the bf16 forward = quantizer + GEMM: same bytes as the two-step path
         assert torch.equal(mod(x.cuda()), outs["auto"][0])
         wide = torch.zeros(M, K + 8, dtype=torch.bfloat16, device="cuda")
         wide[:, :K] = x.cuda()
