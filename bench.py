@@ -42,6 +42,7 @@ from sacq_b200.synthetic import DECODE_MS, DECODE_SHAPES, algorithmic_bytes, mak
 METRIC = "w1p5a8_codebook_gemm_us_per_layer"
 UNIT = "us/layer"
 L2_BYTES = 126 * 1024 * 1024
+DRAM_TRAFFIC_RATIO = 2.500096 / 2.470948      # ncu dram bytes / algorithmic bytes, small-M GEMM
 
 
 def sweep_calls():
@@ -72,7 +73,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except OSError:
@@ -254,10 +255,9 @@ def gpu_main(args):
 
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.start()                      # samples through all three timed regions below
     sec = timed_replay(full_graphs, args.steps, args.warmup)
     sec_gemm = timed_replay(gemm_graphs, args.steps, args.warmup)
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the module's forward with host buffers
     def e2e_step(layer_set):
@@ -279,6 +279,7 @@ def gpu_main(args):
         e2e_step(sets[i % n_sets])
     torch.cuda.synchronize()
     sec_e2e = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
 
     if dist is not None:
         t = torch.tensor([sec, sec_gemm, sec_e2e], dtype=torch.float64, device=dev)
@@ -307,9 +308,12 @@ def gpu_main(args):
                     "d2h_bytes_per_step": sum(M * N * 2 for _, K, N, M in calls),
                     "ms_per_step": sec_e2e / args.steps * 1e3},
             "gpu_launches": int(full_launches * args.steps),
-            "roofline": {"bound": "hbm", "kernel": "small_m_mma_kernel (packed-index GEMM, M<=64)",
+            "roofline": {"bound": "hbm", "kernel": "small_m_mma_staged_kernel (packed-index GEMM, M<=64)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak, "traffic": alg * DRAM_TRAFFIC_RATIO,
+                         "traffic_note": "dram bytes read+written per launch = algorithmic bytes x 1.012, the ratio "
+                                         "ncu measured on the K=2048 N=6144 M=16 launch "
+                                         "(profiles/small_m_mma_staged_2048x6144_m16.md)",
                          "algorithmic_bytes_per_launch": alg, "us_per_launch": gemm_launch_s * 1e6,
                          "launches_timed": int(gemm_launches * args.steps)},
             "clocks": clocks,
@@ -329,8 +333,8 @@ def gpu_main(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
