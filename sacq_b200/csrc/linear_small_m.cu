@@ -356,33 +356,54 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
   }
   pl.spans_per_row = (int)(L->vectors_per_row / pl.span_idx);
   if (pl.mma) {
-    // tile = 16 tokens x 8*r8 rows, one CTA per tile at a time, warps split the spans.
-    // Time ~ waves * (fixed tile latency + r8); on a tie prefer the larger tile (fewer CTAs).
+    // tile = 16 tokens x 8*r8 rows; the CTA's warps split the K spans.
     const int64_t sub = (d.out_features + 7) / 8;
+    pl.warps = pl.spans_per_row < kMaxWarps ? pl.spans_per_row : kMaxWarps;
+    const size_t cb_bytes = pl.cb_smem ? (size_t)d.codebook_size * d.vector_dim * 2 : 0;
+    const bool staged_ok = pl.cb_smem && L->force_kernel != 5 && d.in_features % 16 == 0 && cb_bytes % 16 == 0;
     int best = 1;
-    int64_t best_cost = -1;
+    bool best_staged = false;
+    double best_cost = -1.0;
     for (int r8 = 1; r8 <= 4; r8 *= 2) {
-      const int64_t tiles = ((sub + r8 - 1) / r8) * pl.chunks;
-      const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
-      const int64_t cost = waves * (3 + r8);     // 3 ~ the per-tile latency that does not shrink with r8
-      if (best_cost < 0 || cost <= best_cost) { best_cost = cost; best = r8; }
+      const int64_t row_tiles = (sub + r8 - 1) / r8;
+      // staged kernel: a CTA walks row tiles and, inside each, all token chunks; the fixed
+      // start-up (launch, codebook copy) is paid once.  Unit = one sub-block of one span set.
+      const size_t need = small_m_mma_staged_smem(d.codebook_size, d.vector_dim, (int)d.in_features,
+                                                  L->row_bits / 8, r8, pl.warps, 1);
+      if (staged_ok && need <= kSmemBudget) {
+        // CTAs are grouped per token chunk: a group walks the row tiles with this stride
+        int64_t stride = L->num_sms / pl.chunks;
+        if (stride < 1) stride = 1;
+        const int64_t waves = (row_tiles + stride - 1) / stride;
+        const double cost = 3.0 + (double)waves * (0.2 + 0.6 * r8);
+        if (best_cost < 0 || cost < best_cost - 1e-9 || !best_staged) { best_cost = cost; best = r8; best_staged = true; }
+      } else if (!best_staged) {
+        const int64_t tiles = row_tiles * pl.chunks;
+        const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
+        const double cost = (double)waves * (3 + r8);
+        if (best_cost < 0 || cost <= best_cost) { best_cost = cost; best = r8; }
+      }
     }
     pl.r8 = best;
+    pl.staged = best_staged;
     pl.row_blocks = (int)((sub + best - 1) / best);
     pl.spans_per_item = pl.spans_per_row;
     pl.num_sg = 1;
     pl.num_items = (int64_t)pl.row_blocks * pl.chunks;
-    pl.grid = (int)(pl.num_items < L->num_sms ? pl.num_items : L->num_sms);
+    if (pl.staged) {
+      // grid = chunks x (row-tile lanes per chunk), a multiple of the chunk count
+      int64_t stride = L->num_sms / pl.chunks;
+      if (stride < 1) stride = 1;
+      if (stride > pl.row_blocks) stride = pl.row_blocks;
+      pl.grid = (int)(stride * pl.chunks);
+    } else {
+      pl.grid = (int)(pl.num_items < L->num_sms ? pl.num_items : L->num_sms);
+    }
     if (pl.grid < 1) pl.grid = 1;
-    pl.warps = pl.spans_per_row < kMaxWarps ? pl.spans_per_row : kMaxWarps;
-    const size_t cb_bytes = pl.cb_smem ? (size_t)d.codebook_size * d.vector_dim * 2 : 0;
-    pl.smem = cb_bytes + (size_t)pl.warps * pl.r8 * 4 * 32 * sizeof(float);
-    // staged variant: the tile's index rows and activation rows live in shared memory too
-    const size_t staged = small_m_mma_staged_smem(d.codebook_size, d.vector_dim, (int)d.in_features,
-                                                  L->row_bits / 8, pl.r8, pl.warps);
-    pl.staged = pl.cb_smem && L->force_kernel != 5 && staged <= kSmemBudget && d.in_features % 16 == 0 &&
-                (cb_bytes % 16 == 0);
-    if (pl.staged) pl.smem = staged;
+    pl.act_bufs = 1;
+    pl.smem = pl.staged ? small_m_mma_staged_smem(d.codebook_size, d.vector_dim, (int)d.in_features, L->row_bits / 8,
+                                                  pl.r8, pl.warps, pl.act_bufs)
+                        : cb_bytes + (size_t)pl.warps * pl.r8 * 4 * 32 * sizeof(float);
     return pl;
   }
   // Spread the row's spans over enough items to occupy every warp of the device once,
@@ -459,7 +480,7 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   if (pl.smem > kSmemBudget)
     return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel needs %zu bytes of shared memory", pl.smem);
   const int64_t need = small_m_workspace_bytes(L, M);
-  if ((int64_t)pl.chunks * pl.row_blocks * (int64_t)sizeof(int) > sacq_workspace_counter_bytes())
+  if (pl.num_sg > 1 && (int64_t)pl.chunks * pl.row_blocks * (int64_t)sizeof(int) > sacq_workspace_counter_bytes())
     return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: %d x %d row-block counters exceed the counter region",
                      pl.chunks, pl.row_blocks);
   if (pl.num_sg > 1 && (ws == nullptr || ws_bytes < need))
@@ -489,6 +510,7 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   p.C = d.codebook_size;
   p.span_idx = pl.span_idx; p.spans_per_row = pl.spans_per_row; p.spans_per_item = pl.spans_per_item;
   p.num_sg = pl.num_sg; p.row_blocks = pl.row_blocks; p.chunks = pl.chunks; p.num_items = pl.num_items;
+  p.act_bufs = pl.act_bufs > 0 ? pl.act_bufs : 1;
   uint32_t sb = (uint32_t)d.shift_bf16 << 16;
   memcpy(&p.shift, &sb, sizeof(float));
 

@@ -281,17 +281,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 struct StagedLayout {
-  uint32_t cb_off, idx_off, act_off, red_off, sa_off, bar_off, total;
+  uint32_t cb_off, idx_off, act_off, red_off, sa_off, bar_off, total;   // idx region holds two buffers
 };
-__host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64_t row_bytes, int r8, int warps) {
+__host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64_t row_bytes, int r8, int warps,
+                                                      int act_bufs = 1) {
   StagedLayout L;
   L.cb_off = 0;
   L.idx_off = (uint32_t)((C * D * 2 + 127) & ~127);
-  L.act_off = L.idx_off + (uint32_t)((8 * r8 * row_bytes + 127) & ~127);
-  L.red_off = L.act_off + (uint32_t)((16 * (K + kActPad) + 127) & ~127);
+  L.act_off = L.idx_off + 2 * (uint32_t)((8 * r8 * row_bytes + 127) & ~127);
+  L.red_off = L.act_off + (uint32_t)act_bufs * (uint32_t)((16 * (K + kActPad) + 127) & ~127);
   L.sa_off = L.red_off + (uint32_t)(warps * r8 * 4 * 32 * 4);
-  L.bar_off = L.sa_off + 64;
-  L.total = L.bar_off + 32;
+  L.bar_off = L.sa_off + 384;             // 16 token scales + 32 row scales + 32 row biases
+  L.total = L.bar_off + 64;
   return L;
 }
 
@@ -308,58 +309,98 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
   const int g = lane >> 2, t = lane & 3;
   const StagedLayout L = staged_layout(p.C, D, p.K, p.row_bytes, R8, nwarps);
   const CwVec* cbs = reinterpret_cast<const CwVec*>(smem + L.cb_off);
-  const uint8_t* idx_s = smem + L.idx_off;
-  uint8_t* act_s = smem + L.act_off;
+  uint8_t* act_base = smem + L.act_off;
   float* red = reinterpret_cast<float*>(smem + L.red_off);
-  float* sa_s = reinterpret_cast<float*>(smem + L.sa_off);
-  const uint32_t bar_cb = sm_addr(smem + L.bar_off), bar_tile = bar_cb + 8;
+  float* sa_s = reinterpret_cast<float*>(smem + L.sa_off);          // [16] token scales of the current chunk
+  float* rowsc_s = sa_s + 16;                                         // [8*R8] scale of the tile's rows (group 0)
+  float* rowb_s = rowsc_s + 32;                                       // [8*R8] bias of the tile's rows
+  const uint32_t bar_cb = sm_addr(smem + L.bar_off), bar_act0 = bar_cb + 8, bar_idx0 = bar_cb + 24;
   const int act_pitch = p.K + kActPad;
+  const uint32_t idx_buf_bytes = (L.act_off - L.idx_off) / 2;
+  const uint32_t act_buf_bytes = 0;                  // a single activation tile
 
   if (threadIdx.x == 0) {
     mbar_init(bar_cb, 1);
-    mbar_init(bar_tile, 1);
+    mbar_init(bar_act0, 1);
+    mbar_init(bar_act0 + 8, 1);
+    mbar_init(bar_idx0, 1);
+    mbar_init(bar_idx0 + 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+
+  // Work of this CTA: row tiles rt = blockIdx.x, + gridDim.x, ...; every row tile is
+  // multiplied with all token chunks before the next one, so its packed indices are read
+  // from HBM once.  Index tiles are double buffered (the next tile's copy flies during this
+  // tile's compute); the 16-token activation tile is copied once when there is a single
+  // chunk and once per (row tile, chunk) otherwise.
+  auto issue_idx = [&](int rt, int buf) {
+    const int n_base = rt * 8 * R8;
+    const uint32_t bytes = (uint32_t)(min(8 * R8, p.N - n_base) * p.row_bytes);
+    mbar_expect_tx(bar_idx0 + 8 * buf, bytes);
+    bulk_copy_g2s(smem + L.idx_off + buf * idx_buf_bytes, p.packed + (int64_t)n_base * p.row_bytes, bytes,
+                  bar_idx0 + 8 * buf);
+  };
+  // Called by threads 0..15: thread 0 posts the expected byte count (its arrival is the one
+  // the barrier waits for), every thread copies one token row.
+  auto issue_act = [&](int chunk, int buf) {
+    const int m_base = chunk * 16;
+    const int toks = min(16, p.M - m_base);
+    uint8_t* dst = act_base + buf * act_buf_bytes;
+    const int m = threadIdx.x;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // earlier generic reads of the buffer
+    if (m < toks)
+      bulk_copy_g2s(dst + m * act_pitch, p.q + (int64_t)(m_base + m) * p.K, (uint32_t)p.K, bar_act0 + 8 * buf);
+    if (m == 0) mbar_expect_tx(bar_act0 + 8 * buf, (uint32_t)(toks * p.K));
+  };
+
+  // This CTA's share: one token chunk (fixed for the CTA's lifetime, so its activation
+  // tile is copied once) and the row tiles rt_first, rt_first + rt_stride, ...  The host
+  // makes gridDim.x a multiple of the chunk count.
+  const int chunk = blockIdx.x % p.chunks;
+  const int first_rt = blockIdx.x / p.chunks;
+  const int rt_stride = gridDim.x / p.chunks;
+  const int m_base = chunk * 16;
+  const int toks_here = min(16, p.M - m_base);
+  uint8_t* act_s = act_base;
   if (threadIdx.x == 0) {
     const uint32_t cb_bytes = (uint32_t)(p.C * D * 2);
     mbar_expect_tx(bar_cb, cb_bytes);
-    bulk_copy_g2s(smem + L.cb_off, p.cb_f16, cb_bytes, bar_cb);
+    bulk_copy_g2s(smem + L.cb_off, p.cb_f16, cb_bytes, bar_cb);     // layer constants: may overlap
+    if (first_rt < p.row_blocks) issue_idx(first_rt, 0);            // the previous kernel of the stream
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");                // activations come from that kernel
+  if (threadIdx.x < 16 && first_rt < p.row_blocks) {
+    issue_act(chunk, 0);
+    sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
   }
 
   bool ok = true;
-  uint32_t tile_parity = 0;
-  bool cb_waited = false;
-  for (int64_t tile = blockIdx.x; tile < p.num_items; tile += gridDim.x) {
-    const int rt = (int)(tile % p.row_blocks);
-    const int chunk = (int)(tile / p.row_blocks);
+  uint32_t idx_parity[2] = {0, 0};
+  bool first = true;
+  int it = 0;
+  for (int rt = first_rt; rt < p.row_blocks; rt += rt_stride, ++it) {
+    const int buf = it & 1;
     const int n_base = rt * 8 * R8;
-    const int m_base = chunk * 16;
     const int rows_here = min(8 * R8, p.N - n_base);
-    const int toks_here = min(16, p.M - m_base);
-
-    // ---- bring the tile in.  The packed indices (like the codebook) are layer constants;
-    // the activations and their scales come from the kernel before this one, so on the
-    // first tile everything issued before the dependency wait overlaps that kernel.
-    const uint32_t idx_bytes = (uint32_t)(rows_here * p.row_bytes);
-    const uint32_t act_bytes = (uint32_t)(toks_here * p.K);
-    if (threadIdx.x == 0) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic reads of these buffers
-      mbar_expect_tx(bar_tile, idx_bytes + act_bytes);
-      bulk_copy_g2s(smem + L.idx_off, p.packed + (int64_t)n_base * p.row_bytes, idx_bytes, bar_tile);
+    const uint8_t* idx_s = smem + L.idx_off + buf * idx_buf_bytes;
+    if (threadIdx.x < 8 * R8) {
+      // row constants of this tile, fetched while the index copy is in flight
+      const int n = min(n_base + (int)threadIdx.x, p.N - 1);
+      rowsc_s[threadIdx.x] = bf16_bits_to_float(__ldg(p.scales + (int64_t)n * p.num_groups));
+      rowb_s[threadIdx.x] = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
     }
-    if (!cb_waited) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (threadIdx.x == 0) {
-      for (int m = 0; m < toks_here; ++m)
-        bulk_copy_g2s(act_s + m * act_pitch, p.q + (int64_t)(m_base + m) * p.K, (uint32_t)p.K, bar_tile);
+    if (threadIdx.x == 0 && rt + rt_stride < p.row_blocks) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the other buffer's readers are done
+      issue_idx(rt + rt_stride, buf ^ 1);
     }
-    if (threadIdx.x < 16) sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
-    if (!cb_waited) {
+    if (first) {
       ok = mbar_wait_bounded(bar_cb, 0, p.status) && ok;
-      cb_waited = true;
+      ok = mbar_wait_bounded(bar_act0, 0, p.status) && ok;
+      first = false;
     }
-    ok = mbar_wait_bounded(bar_tile, tile_parity, p.status) && ok;
-    tile_parity ^= 1;
+    ok = mbar_wait_bounded(bar_idx0 + 8 * buf, idx_parity[buf], p.status) && ok;
+    idx_parity[buf] ^= 1;
     ok = __syncthreads_and(ok);
     if (!ok) break;                                    // a bounded wait expired: status word is set
 
@@ -370,8 +411,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
     for (int r = 0; r < R8; ++r) {
       sn0[r] = min(n_base + r * 8 + 2 * t, p.N - 1);
       sn1[r] = min(n_base + r * 8 + 2 * t + 1, p.N - 1);
-      s0[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn0[r] * p.num_groups));
-      s1[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn1[r] * p.num_groups));
+      s0[r] = rowsc_s[r * 8 + 2 * t];
+      s1[r] = rowsc_s[r * 8 + 2 * t + 1];
     }
     float acc[R8][4];
 #pragma unroll
@@ -439,20 +480,30 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
 #pragma unroll
         for (int j = 0; j < WPG; ++j) wcur[r][j] = src[j];
       }
-      float cs[R8][4];
+      // two accumulators per sub-block (even / odd steps) halve the dependent MMA chain
+      float cs[R8][4], ct[R8][4];
 #pragma unroll
       for (int r = 0; r < R8; ++r)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cs[r][j] = 0.f;
+        for (int j = 0; j < 4; ++j) { cs[r][j] = 0.f; ct[r][j] = 0.f; }
 #pragma unroll
       for (int s8 = 0; s8 < 8; ++s8) {
 #pragma unroll
         for (int r = 0; r < R8; ++r) {
           const CwVec c = cbs[field8<BITS>(wcur[r], s8)];
-          mma_m16n8k16(cs[r], fa[s8][0], fb[s8][0], fa[s8][1], fb[s8][1], c.x, c.y);
-          if constexpr (D == 8) mma_m16n8k16(cs[r], fa[s8][2], fb[s8][2], fa[s8][3], fb[s8][3], c.z, c.w);
+          if (s8 & 1) {
+            mma_m16n8k16(ct[r], fa[s8][0], fb[s8][0], fa[s8][1], fb[s8][1], c.x, c.y);
+            if constexpr (D == 8) mma_m16n8k16(ct[r], fa[s8][2], fb[s8][2], fa[s8][3], fb[s8][3], c.z, c.w);
+          } else {
+            mma_m16n8k16(cs[r], fa[s8][0], fb[s8][0], fa[s8][1], fb[s8][1], c.x, c.y);
+            if constexpr (D == 8) mma_m16n8k16(cs[r], fa[s8][2], fb[s8][2], fa[s8][3], fb[s8][3], c.z, c.w);
+          }
         }
       }
+#pragma unroll
+      for (int r = 0; r < R8; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cs[r][j] += ct[r][j];
       if (p.num_groups > 1) {
         const int grp = (sp * kSpanIdx * D) / p.group_size;
 #pragma unroll
@@ -485,13 +536,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
       const int ml = (ln >> 2) + ((j & 2) ? 8 : 0);
       const int n = n_base + r * 8 + 2 * (ln & 3) + (j & 1);
       if (ml < toks_here && n < p.N) {
-        const float b = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
-        p.y[(int64_t)(m_base + ml) * p.ldy + n] = float_to_bf16_bits(fmaf(sa_s[ml], v, b));
+        p.y[(int64_t)(m_base + ml) * p.ldy + n] = float_to_bf16_bits(fmaf(sa_s[ml], v, rowb_s[n - n_base]));
       }
     }
-    __syncthreads();                                   // buffers are reused by the next tile
+    __syncthreads();                                   // red and the row constants are reused next
   }
-  if (!cb_waited) mbar_wait_bounded(bar_cb, 0, p.status);   // never exit with the codebook copy in flight
+  if (first) {                                         // a CTA without a row tile still owns its copies
+    mbar_wait_bounded(bar_cb, 0, p.status);
+  }
 }
 
 template <int D, int BITS>
@@ -519,8 +571,8 @@ cudaError_t launch_cb(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
 
 }  // namespace
 
-size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps) {
-  return staged_layout(C, D, K, row_bytes, r8, warps).total;
+size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps, int act_bufs) {
+  return staged_layout(C, D, K, row_bytes, r8, warps, act_bufs).total;
 }
 
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s) {

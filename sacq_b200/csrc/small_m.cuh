@@ -39,6 +39,7 @@ struct SmallMParams {
   int num_sg;                  // span groups per row = ceil(spans_per_row / spans_per_item)
   int row_blocks;              // ceil(N / 32)
   int chunks;                  // ceil(M / MT)
+  int act_bufs;                // staged warp-MMA kernel: activation tile buffers (1 or 2)
   int64_t num_items;
   float out_mul;               // 2^-cb_exp_shift (fast) or 1 (generic)
   float shift;
@@ -84,6 +85,7 @@ struct Plan {
   int warps, grid;
   int r8;                    // warp-MMA variant: 8-row sub-blocks per tile (1, 2 or 4)
   bool staged;               // warp-MMA variant with bulk-copied tiles in shared memory
+  int act_bufs;              // ... and how many activation tile buffers fit (1 or 2)
   size_t smem;
 };
 
@@ -135,7 +137,7 @@ cudaError_t launch_kernel_pdl(const Plan& pl, const SmallMParams& p, cudaStream_
 // linear_small_m_mma.cu
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s);
 // Shared memory the staged warp-MMA kernel needs for (layer, r8); 0 if it cannot run it.
-size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps);
+size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps, int act_bufs);
 
 }  // namespace smallm
 }  // namespace sacq
