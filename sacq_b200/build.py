@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         return LIB_PATH
     nvcc = _nvcc()
     os.makedirs(OBJ_DIR, exist_ok=True)
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else []) + os.environ.get("SACQ_NVCC_EXTRA", "").split()
 
     def compile_one(src):
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")

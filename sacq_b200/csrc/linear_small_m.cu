@@ -368,8 +368,12 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
       const int64_t row_tiles = (sub + r8 - 1) / r8;
       // staged kernel: a CTA walks row tiles and, inside each, all token chunks; the fixed
       // start-up (launch, codebook copy) is paid once.  Unit = one sub-block of one span set.
+      // tiles of at most 16 rows run two warps per span (up to 16 warps per CTA)
+      const int halves = r8 <= 2 ? 2 : 1;
+      const int st_warps = pl.spans_per_row * halves < kMaxWarps * halves ? pl.spans_per_row * halves
+                                                                          : kMaxWarps * halves;
       const size_t need = small_m_mma_staged_smem(d.codebook_size, d.vector_dim, (int)d.in_features,
-                                                  L->row_bits / 8, r8, pl.warps, 1);
+                                                  L->row_bits / 8, r8, st_warps, 1);
       if (staged_ok && need <= kSmemBudget) {
         // CTAs are grouped per token chunk: a group walks the row tiles with this stride
         int64_t stride = L->num_sms / pl.chunks;
@@ -401,6 +405,10 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
     }
     if (pl.grid < 1) pl.grid = 1;
     pl.act_bufs = 1;
+    if (pl.staged) {
+      const int halves = pl.r8 <= 2 ? 2 : 1;
+      pl.warps = pl.spans_per_row * halves < kMaxWarps * halves ? pl.spans_per_row * halves : kMaxWarps * halves;
+    }
     pl.smem = pl.staged ? small_m_mma_staged_smem(d.codebook_size, d.vector_dim, (int)d.in_features, L->row_bits / 8,
                                                   pl.r8, pl.warps, pl.act_bufs)
                         : cb_bytes + (size_t)pl.warps * pl.r8 * 4 * 32 * sizeof(float);
@@ -492,6 +500,7 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   SmallMParams p{};
   p.packed = static_cast<const uint8_t*>(d.packed);
   p.cb_f16 = L->cb_f16;
+  p.cb_hilo = L->cb_hilo;
   p.cb_bf16 = static_cast<const uint16_t*>(d.codebook);
   p.scales = static_cast<const uint16_t*>(d.scales);
   p.bias = static_cast<const uint16_t*>(d.bias);
@@ -518,7 +527,7 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   if (pl.fast) {
     if (reinterpret_cast<uintptr_t>(q) % 8 != 0 || d.in_features % 8 != 0)
       return set_error(SACQ_ERR_ALIGNMENT, "quantized activations must be 8-byte aligned with K %% 8 == 0");
-    p.out_mul = ldexpf(1.f, -L->cb_exp_shift);
+    p.out_mul = ldexpf(1.f, (pl.mma && pl.staged) ? -L->cb8_exp_shift : -L->cb_exp_shift);
     if (pl.mma) {
       if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
         return set_error(SACQ_ERR_ALIGNMENT, "small-M MMA kernel: q must be 16-byte aligned");

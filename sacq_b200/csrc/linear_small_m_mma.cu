@@ -296,8 +296,20 @@ __host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64
   return L;
 }
 
-template <int D, int BITS, int R8>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(const SmallMParams p) {
+__device__ __forceinline__ void mma_m16n8k32_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                  uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// HALVES = warps sharing one 32-index span (each takes 8/HALVES of its MMA steps): with
+// two, a CTA runs up to 16 lighter warps, which hides more of the gather -> MMA latency.
+template <int D, int BITS, int R8, int HALVES>
+__global__ void __launch_bounds__(kMaxWarps * 32 * HALVES, 1) small_m_mma_staged_kernel(const SmallMParams p) {
+  constexpr int NS = 8 / HALVES;           // MMA steps (vectors per lane) of one work item
+  constexpr int NQ = NS * D / 16;          // uint4 loads covering them per token row
   extern __shared__ __align__(128) uint8_t smem[];
   using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;
   constexpr int WPG = BITS / 4;
@@ -366,13 +378,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
   if (threadIdx.x == 0) {
     const uint32_t cb_bytes = (uint32_t)(p.C * D * 2);
     mbar_expect_tx(bar_cb, cb_bytes);
-    bulk_copy_g2s(smem + L.cb_off, p.cb_f16, cb_bytes, bar_cb);     // layer constants: may overlap
+    bulk_copy_g2s(smem + L.cb_off, p.cb_hilo, cb_bytes, bar_cb);    // layer constants: may overlap
     if (first_rt < p.row_blocks) issue_idx(first_rt, 0);            // the previous kernel of the stream
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");                // activations come from that kernel
   if (threadIdx.x < 16 && first_rt < p.row_blocks) {
     issue_act(chunk, 0);
     sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
+  }
+  if (threadIdx.x < 8 * R8 && first_rt < p.row_blocks) {
+    const int n = min(first_rt * 8 * R8 + (int)threadIdx.x, p.N - 1);
+    rowsc_s[threadIdx.x] = bf16_bits_to_float(__ldg(p.scales + (int64_t)n * p.num_groups));
+    rowb_s[threadIdx.x] = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
   }
 
   bool ok = true;
@@ -384,11 +401,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
     const int n_base = rt * 8 * R8;
     const int rows_here = min(8 * R8, p.N - n_base);
     const uint8_t* idx_s = smem + L.idx_off + buf * idx_buf_bytes;
-    if (threadIdx.x < 8 * R8) {
-      // row constants of this tile, fetched while the index copy is in flight
-      const int n = min(n_base + (int)threadIdx.x, p.N - 1);
-      rowsc_s[threadIdx.x] = bf16_bits_to_float(__ldg(p.scales + (int64_t)n * p.num_groups));
-      rowb_s[threadIdx.x] = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
+    // row constants (group-0 scale, bias): the NEXT tile's are fetched now into registers
+    // and stored after this tile is done, so their global-memory latency hides behind a
+    // whole tile; the first tile's were fetched before the loop
+    float next_sc = 0.f, next_b = 0.f;
+    if (threadIdx.x < 8 * R8 && rt + rt_stride < p.row_blocks) {
+      const int n = min((rt + rt_stride) * 8 * R8 + (int)threadIdx.x, p.N - 1);
+      next_sc = bf16_bits_to_float(__ldg(p.scales + (int64_t)n * p.num_groups));
+      next_b = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
     }
     if (threadIdx.x == 0 && rt + rt_stride < p.row_blocks) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the other buffer's readers are done
@@ -421,50 +441,42 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
       for (int j = 0; j < 4; ++j) acc[r][j] = 0.f;
     float xs_a = 0.f, xs_b = 0.f;
 
-    for (int sp = warp; sp < p.spans_per_row; sp += nwarps) {
-      uint32_t fa[8][AREG], fb[8][AREG];
+    for (int item = warp; item < p.spans_per_row * HALVES; item += nwarps) {
+      const int sp = item / HALVES, hf = item % HALVES;
+      // A fragments are the raw e4m3 bytes: vector (8t + first + s) of token rows g and g+8.
+      // FP8 MMAs need no widening; slots {4t..4t+3} carry bytes 0-3 and slots {16+4t..}
+      // bytes 4-7 of the lane's vector (for d = 4: of its two vectors).
+      constexpr int AW = NS * D / 4;             // 32-bit words per token row
+      uint32_t fa[AW], fb[AW];
       {
-        const uint4* pa = reinterpret_cast<const uint4*>(act_s + g * act_pitch + (sp * kSpanIdx + 8 * t) * D);
-        const uint4* pb = reinterpret_cast<const uint4*>(act_s + (g + 8) * act_pitch + (sp * kSpanIdx + 8 * t) * D);
-        uint4 qa[2 * QV], qb[2 * QV];
+        const int voff = (sp * kSpanIdx + 8 * t + hf * NS) * D;
+        const uint4* pa = reinterpret_cast<const uint4*>(act_s + g * act_pitch + voff);
+        const uint4* pb = reinterpret_cast<const uint4*>(act_s + (g + 8) * act_pitch + voff);
 #pragma unroll
-        for (int j = 0; j < 2 * QV; ++j) { qa[j] = pa[j]; qb[j] = pb[j]; }
-        const uint32_t* wa = reinterpret_cast<const uint32_t*>(qa);
-        const uint32_t* wb = reinterpret_cast<const uint32_t*>(qb);
-#pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8) {
-          if constexpr (D == 8) {
-            e4m3x4_to_h2(wa[2 * s8], fa[s8][0], fa[s8][1]);
-            e4m3x4_to_h2(wa[2 * s8 + 1], fa[s8][2], fa[s8][3]);
-            e4m3x4_to_h2(wb[2 * s8], fb[s8][0], fb[s8][1]);
-            e4m3x4_to_h2(wb[2 * s8 + 1], fb[s8][2], fb[s8][3]);
-          } else {
-            e4m3x4_to_h2(wa[s8], fa[s8][0], fa[s8][1]);
-            e4m3x4_to_h2(wb[s8], fb[s8][0], fb[s8][1]);
-          }
+        for (int j = 0; j < NQ; ++j) {
+          const uint4 va = pa[j], vb = pb[j];
+          fa[4 * j] = va.x; fa[4 * j + 1] = va.y; fa[4 * j + 2] = va.z; fa[4 * j + 3] = va.w;
+          fb[4 * j] = vb.x; fb[4 * j + 1] = vb.y; fb[4 * j + 2] = vb.z; fb[4 * j + 3] = vb.w;
         }
       }
       if (g >= toks_here) {
 #pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8)
-#pragma unroll
-          for (int j = 0; j < AREG; ++j) fa[s8][j] = 0u;
+        for (int j = 0; j < AW; ++j) fa[j] = 0u;
       }
       if (g + 8 >= toks_here) {
 #pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8)
-#pragma unroll
-          for (int j = 0; j < AREG; ++j) fb[s8][j] = 0u;
+        for (int j = 0; j < AW; ++j) fb[j] = 0u;
       }
       if (p.shift != 0.f) {
         float ta = 0.f, tb = 0.f;
 #pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8)
-#pragma unroll
-          for (int j = 0; j < AREG; ++j) {
-            ta += __low2float(as_h2(fa[s8][j])) + __high2float(as_h2(fa[s8][j]));
-            tb += __low2float(as_h2(fb[s8][j])) + __high2float(as_h2(fb[s8][j]));
-          }
+        for (int j = 0; j < AW; ++j) {
+          uint32_t lo, hi;
+          e4m3x4_to_h2(fa[j], lo, hi);
+          ta += __low2float(as_h2(lo)) + __high2float(as_h2(lo)) + __low2float(as_h2(hi)) + __high2float(as_h2(hi));
+          e4m3x4_to_h2(fb[j], lo, hi);
+          tb += __low2float(as_h2(lo)) + __high2float(as_h2(lo)) + __low2float(as_h2(hi)) + __high2float(as_h2(hi));
+        }
         ta += __shfl_xor_sync(0xffffffffu, ta, 1);
         ta += __shfl_xor_sync(0xffffffffu, ta, 2);
         tb += __shfl_xor_sync(0xffffffffu, tb, 1);
@@ -486,19 +498,41 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
       for (int r = 0; r < R8; ++r)
 #pragma unroll
         for (int j = 0; j < 4; ++j) { cs[r][j] = 0.f; ct[r][j] = 0.f; }
+      // the half index selects compile-time field positions, so dispatch on it once
+      auto mma_steps = [&](auto HF) {
+        constexpr int kFirst = decltype(HF)::value * NS;
+        if constexpr (D == 8) {
+          // one codeword per step: 16 bytes = e4m3 high half | low half
 #pragma unroll
-      for (int s8 = 0; s8 < 8; ++s8) {
+          for (int s8 = 0; s8 < NS; ++s8) {
 #pragma unroll
-        for (int r = 0; r < R8; ++r) {
-          const CwVec c = cbs[field8<BITS>(wcur[r], s8)];
-          if (s8 & 1) {
-            mma_m16n8k16(ct[r], fa[s8][0], fb[s8][0], fa[s8][1], fb[s8][1], c.x, c.y);
-            if constexpr (D == 8) mma_m16n8k16(ct[r], fa[s8][2], fb[s8][2], fa[s8][3], fb[s8][3], c.z, c.w);
-          } else {
-            mma_m16n8k16(cs[r], fa[s8][0], fb[s8][0], fa[s8][1], fb[s8][1], c.x, c.y);
-            if constexpr (D == 8) mma_m16n8k16(cs[r], fa[s8][2], fb[s8][2], fa[s8][3], fb[s8][3], c.z, c.w);
+            for (int r = 0; r < R8; ++r) {
+              const uint4 c = cbs[field8<BITS>(wcur[r], kFirst + s8)];
+              float (&acc2)[4] = (s8 & 1) ? ct[r] : cs[r];
+              mma_m16n8k32_e4m3(acc2, fa[2 * s8], fb[2 * s8], fa[2 * s8 + 1], fb[2 * s8 + 1], c.x, c.y);
+              mma_m16n8k32_e4m3(acc2, fa[2 * s8], fb[2 * s8], fa[2 * s8 + 1], fb[2 * s8 + 1], c.z, c.w);
+            }
+          }
+        } else {
+          // two 4-byte codewords per step (8 bytes each = high | low)
+#pragma unroll
+          for (int s2 = 0; s2 < NS / 2; ++s2) {
+#pragma unroll
+            for (int r = 0; r < R8; ++r) {
+              const uint2 ca = cbs[field8<BITS>(wcur[r], kFirst + 2 * s2)];
+              const uint2 cb2 = cbs[field8<BITS>(wcur[r], kFirst + 2 * s2 + 1)];
+              float (&acc2)[4] = (s2 & 1) ? ct[r] : cs[r];
+              mma_m16n8k32_e4m3(acc2, fa[2 * s2], fb[2 * s2], fa[2 * s2 + 1], fb[2 * s2 + 1], ca.x, cb2.x);
+              mma_m16n8k32_e4m3(acc2, fa[2 * s2], fb[2 * s2], fa[2 * s2 + 1], fb[2 * s2 + 1], ca.y, cb2.y);
+            }
           }
         }
+      };
+      if constexpr (HALVES == 1) {
+        mma_steps(std::integral_constant<int, 0>{});
+      } else {
+        if (hf == 0) mma_steps(std::integral_constant<int, 0>{});
+        else mma_steps(std::integral_constant<int, 1>{});
       }
 #pragma unroll
       for (int r = 0; r < R8; ++r)
@@ -520,7 +554,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
         acc[r][3] = fmaf(s1[r], cs[r][3], acc[r][3]);
       }
     }
-
 #pragma unroll
     for (int r = 0; r < R8; ++r) {
       red[(warp * kFrag + r * 4 + 0) * 32 + lane] = fmaf(acc[r][0], p.out_mul, p.shift * xs_a);
@@ -540,6 +573,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
       }
     }
     __syncthreads();                                   // red and the row constants are reused next
+    if (threadIdx.x < 8 * R8) {
+      rowsc_s[threadIdx.x] = next_sc;
+      rowb_s[threadIdx.x] = next_b;
+    }
   }
   if (first) {                                         // a CTA without a row tile still owns its copies
     mbar_wait_bounded(bar_cb, 0, p.status);
@@ -549,9 +586,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_staged_kernel(c
 template <int D, int BITS>
 cudaError_t launch_staged(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
   switch (pl.r8) {
-    case 1: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 1>>(pl, p, s);
-    case 2: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 2>>(pl, p, s);
-    default: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 4>>(pl, p, s);
+    case 1: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 1, 2>>(pl, p, s);
+    case 2: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 2, 2>>(pl, p, s);
+    default: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 4, 1>>(pl, p, s);
   }
 }
 

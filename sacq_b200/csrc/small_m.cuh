@@ -17,6 +17,7 @@ constexpr int kMaxWarps = 8;
 struct SmallMParams {
   const uint8_t* packed;
   const __half* cb_f16;        // [C, D] scaled by 2^cb_exp_shift
+  const uint8_t* cb_hilo;      // [C][2][D] e4m3 high/low halves scaled by 2^cb8_exp_shift (staged warp-MMA kernel)
   const uint16_t* cb_bf16;     // [C, d] original (generic kernel)
   const uint16_t* scales;      // bf16 [N, num_groups]
   const uint16_t* bias;        // bf16 [N] or null
