@@ -148,6 +148,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         if self.codebook.ndim != 2 or self.codebook.shape[1] != self.vector_dim:
             raise ValueError(f"codebook shape {tuple(self.codebook.shape)} does not match vector_dim")
         self.runtime_kernel_eligible = True
+        self._ws_bytes = {}
         self._handle = None
         self._create_handle()
 
@@ -250,25 +251,36 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape[-1] != self.in_features:
             raise ValueError("Linear shape mismatch")
-        if not x.is_cuda or x.device != self.codebook.device:
+        dev = self.codebook.device
+        if not x.is_cuda or x.device != dev:
             raise ValueError("Matching CUDA operands required")
-        a = x.reshape(-1, self.in_features)
+        a = x if x.dim() == 2 else x.reshape(-1, self.in_features)
         if a.dtype != torch.bfloat16:
             a = a.to(torch.bfloat16)
         if a.stride(-1) != 1:
             a = a.contiguous()
         m = a.shape[0]
-        y = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=x.device)
+        y = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=dev)
         if m > 0 and self.out_features > 0:
-            ws = _Workspace.get(x.device)
-            need = int(self._lib.sacq_workspace_bytes(self._handle, m))
+            ws = _Workspace.get(dev)
+            need = self._ws_bytes.get(m)
+            if need is None:
+                need = self._ws_bytes[m] = int(self._lib.sacq_workspace_bytes(self._handle, m))
             buf = ws.scratch(need)
             q, s = ws.act(m, self.in_features)
-            with torch.cuda.device(x.device):
-                _lib.check(self._lib.sacq_linear_bf16(
+            if torch.cuda.current_device() == dev.index:
+                rc = self._lib.sacq_linear_bf16(
                     self._handle, a.data_ptr(), a.stride(0), m, q.data_ptr(), s.data_ptr(), y.data_ptr(),
-                    y.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
-        y = y.reshape(*x.shape[:-1], self.out_features)
+                    y.stride(0), buf.data_ptr(), buf.numel(), torch.cuda.current_stream().cuda_stream)
+            else:
+                with torch.cuda.device(dev):
+                    rc = self._lib.sacq_linear_bf16(
+                        self._handle, a.data_ptr(), a.stride(0), m, q.data_ptr(), s.data_ptr(), y.data_ptr(),
+                        y.stride(0), buf.data_ptr(), buf.numel(), torch.cuda.current_stream().cuda_stream)
+            if rc != 0:
+                _lib.check(rc)
+        if x.dim() != 2:
+            y = y.reshape(*x.shape[:-1], self.out_features)
         return y if x.dtype == torch.bfloat16 else y.to(x.dtype)
 
     # ------------------------------------------------------------------ extras
@@ -276,6 +288,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         """Force a GEMM kernel: 'auto' (0), 'small' (1), 'large' (2), 'small_simt' (3), 'small_mma' (4)."""
         code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5}.get(which, which)
         _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
+        self._ws_bytes.clear()
 
     def kernel_for(self, m: int) -> str:
         k = self._lib.sacq_layer_kernel_for(self._handle, m)
