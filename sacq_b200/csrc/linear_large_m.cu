@@ -42,7 +42,7 @@ namespace {
 constexpr int kBM = 128;          // tokens per tile (TMEM lanes)
 constexpr int kMaxBN = 128;       // weight rows per tile (accumulator columns): BN in {32, 64, 128}
 constexpr int kBK = 128;          // e4m3 elements (= bytes) per K block: one 128B swizzle row
-constexpr int kStages = 3;
+constexpr int kMaxStages = 3;     // 3 stages with one 128-row M sub-tile, 2 with two
 constexpr int kExpanderThreads = 256;
 constexpr int kThreads = 64 + kExpanderThreads;
 constexpr int kTileBytes = kBM * kBK;            // 16 KB: one operand tile
@@ -226,7 +226,7 @@ struct LargeMParams {
 
 // Shared-memory carve-up (offsets from a 1024-byte aligned base).
 struct SmemLayout {
-  uint32_t stage_off;      // kStages x {A 16 KB, B_hi, B_lo of BN x 128 bytes}
+  uint32_t stage_off;      // stages x {MT x A 16 KB, B_hi, B_lo of BN x 128 bytes}
   uint32_t stage_bytes;
   uint32_t idx_off;        // 2 x [128 rows][sb_bytes]
   uint32_t cb_off;         // [C][2][D]
@@ -237,11 +237,13 @@ struct SmemLayout {
   uint32_t total;
 };
 
-__host__ __device__ inline SmemLayout make_layout(int bn, int sb_bytes, int cb_bytes) {
+__host__ __device__ constexpr int stages_for(int mt) { return mt == 2 ? 2 : kMaxStages; }
+
+__host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, int cb_bytes) {
   SmemLayout L;
   L.stage_off = 0;
-  L.stage_bytes = kTileBytes + 2 * bn * kBK;
-  L.idx_off = kStages * L.stage_bytes;
+  L.stage_bytes = mt * kTileBytes + 2 * bn * kBK;
+  L.idx_off = stages_for(mt) * L.stage_bytes;
   L.cb_off = L.idx_off + 2 * bn * sb_bytes;
   L.cb_off = (L.cb_off + 127) & ~127u;
   L.sw_off = L.cb_off + ((cb_bytes + 127) & ~127);
@@ -253,8 +255,10 @@ __host__ __device__ inline SmemLayout make_layout(int bn, int sb_bytes, int cb_b
 }
 
 // D in {4, 8}, BITS in {8, 12, 16}, BN in {32, 64, 128}.  grid = (ceil(N/BN), ceil(M/128)).
-// Smaller BN trades tensor-core efficiency for more CTAs when M is only a few tiles.
-template <int D, int BITS, int BN>
+// Smaller BN trades tensor-core efficiency for more CTAs when M is only a few tiles.  MT = 2
+// gives the CTA two 128-token sub-tiles (two TMEM accumulators) that share every expanded
+// B tile: the shared-memory gathers, not the MMAs, are what limits this kernel.
+template <int D, int BITS, int BN, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
                const LargeMParams p) {
@@ -267,16 +271,18 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr int IPC = 16 / D;                         // indices per chunk
   constexpr uint32_t kIdesc = make_idesc(BN);
   constexpr int B_TILE = BN * kBK;
+  constexpr int kStages = stages_for(MT);
+  constexpr int A_BYTES = MT * kTileBytes;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
-  const SmemLayout L = make_layout(BN, SB_BYTES, p.C * CW_BYTES);
+  const SmemLayout L = make_layout(BN, MT, SB_BYTES, p.C * CW_BYTES);
 
   // barrier indices
-  constexpr int A_FULL = 0, B_FULL = kStages, EMPTY = 2 * kStages, IDX_FULL = 3 * kStages,
-                IDX_EMPTY = 3 * kStages + 2, ACC_FULL = 3 * kStages + 4;
+  constexpr int A_FULL = 0, B_FULL = kMaxStages, EMPTY = 2 * kMaxStages, IDX_FULL = 3 * kMaxStages,
+                IDX_EMPTY = 3 * kMaxStages + 2, ACC_FULL = 3 * kMaxStages + 4;
   const uint32_t bars = base + L.bar_off;
   auto bar = [&](int i) { return bars + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + L.misc_off);
@@ -284,7 +290,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * kBM;
+  const int m0 = blockIdx.y * (kBM * MT);
   const int num_kb = p.K / kBK;
 
   if (threadIdx.x == 0) {
@@ -303,7 +309,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_idx);
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), (uint32_t)BN);
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), (uint32_t)(BN * MT));
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -321,8 +327,11 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         const int st = kb % kStages;
         if (!mbar_wait(bar(EMPTY + st), ((kb / kStages) & 1) ^ 1, abort_flag, p.status)) break;
-        mbar_arrive_expect_tx(bar(A_FULL + st), kTileBytes);
-        tma_load_2d(base + L.stage_off + st * L.stage_bytes, &tmap_a, kb * kBK, m0, bar(A_FULL + st));
+        mbar_arrive_expect_tx(bar(A_FULL + st), A_BYTES);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          tma_load_2d(base + L.stage_off + st * L.stage_bytes + mt * kTileBytes, &tmap_a, kb * kBK, m0 + mt * kBM,
+                      bar(A_FULL + st));
       }
     }
     __syncwarp();
@@ -338,14 +347,17 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = base + L.stage_off + st * L.stage_bytes;
-        const uint64_t a_desc = make_smem_desc(a_addr);
-        const uint64_t bh_desc = make_smem_desc(a_addr + kTileBytes);
-        const uint64_t bl_desc = make_smem_desc(a_addr + kTileBytes + B_TILE);
+        const uint64_t bh_desc = make_smem_desc(a_addr + A_BYTES);
+        const uint64_t bl_desc = make_smem_desc(a_addr + A_BYTES + B_TILE);
 #pragma unroll
         for (int ks = 0; ks < kBK / 32; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32) >> 4);
-          umma_f8(tmem_base, a_desc + adv, bh_desc + adv, kIdesc, (kb | ks) != 0);
-          umma_f8(tmem_base, a_desc + adv, bl_desc + adv, kIdesc, 1);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint64_t a_desc = make_smem_desc(a_addr + mt * kTileBytes);
+            umma_f8(tmem_base + (uint32_t)(mt * BN), a_desc + adv, bh_desc + adv, kIdesc, (kb | ks) != 0);
+            umma_f8(tmem_base + (uint32_t)(mt * BN), a_desc + adv, bl_desc + adv, kIdesc, 1);
+          }
         }
         umma_commit(bar(EMPTY + st));
       }
@@ -383,7 +395,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t idx[CPT * IPC];
       load_fields<BITS, CPT * IPC>(sm + L.idx_off + slot * BN * SB_BYTES + row * SB_BYTES + (kb & 1) * KB_BYTES,
                                    part * CPT * IPC, idx);
-      uint8_t* bhi = sm + L.stage_off + st * L.stage_bytes + kTileBytes + row * 128;
+      uint8_t* bhi = sm + L.stage_off + st * L.stage_bytes + A_BYTES + row * 128;
       uint8_t* blo = bhi + B_TILE;
       const int sw = row & 7;
 #pragma unroll
@@ -420,36 +432,39 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_after();
       const int quarter = warp & 3;                   // TMEM lanes 32*quarter .. +31
       const int col_half = (warp - 2) >> 2;           // two warps share a quarter: they split the 32-column groups
-      const int m = m0 + quarter * 32 + lane;
       const float* swp = reinterpret_cast<const float*>(sm + L.sw_off);
       const float* bp = reinterpret_cast<const float*>(sm + L.bias_off);
-      const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
 #pragma unroll
-      for (int cc = col_half; cc < BN / 32; cc += 2) {
-        const int c0 = cc * 32;
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
-        if (m < p.M) {
-          uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
-          const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
-          if (vec) {
+      for (int mt = 0; mt < MT; ++mt) {
+        const int m = m0 + mt * kBM + quarter * 32 + lane;
+        const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t o[4];
+        for (int cc = col_half; cc < BN / 32; cc += 2) {
+          const int c0 = cc * 32;
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + c0), r);
+          if (m < p.M) {
+            uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
+            const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
+            if (vec) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int c = v * 8 + 2 * j;
-                const float y0 = fmaf(sa, __uint_as_float(r[c]) * swp[c0 + c], bp[c0 + c]);
-                const float y1 = fmaf(sa, __uint_as_float(r[c + 1]) * swp[c0 + c + 1], bp[c0 + c + 1]);
-                o[j] = (uint32_t)float_to_bf16_bits(y0) | ((uint32_t)float_to_bf16_bits(y1) << 16);
+              for (int v = 0; v < 4; ++v) {
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int c = v * 8 + 2 * j;
+                  const float y0 = fmaf(sa, __uint_as_float(r[c]) * swp[c0 + c], bp[c0 + c]);
+                  const float y1 = fmaf(sa, __uint_as_float(r[c + 1]) * swp[c0 + c + 1], bp[c0 + c + 1]);
+                  o[j] = (uint32_t)float_to_bf16_bits(y0) | ((uint32_t)float_to_bf16_bits(y1) << 16);
+                }
+                *reinterpret_cast<uint4*>(yrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
               }
-              *reinterpret_cast<uint4*>(yrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          } else {
+            } else {
 #pragma unroll
-            for (int c = 0; c < 32; ++c)
-              if (n0 + c0 + c < p.N)
-                yrow[c] = float_to_bf16_bits(fmaf(sa, __uint_as_float(r[c]) * swp[c0 + c], bp[c0 + c]));
+              for (int c = 0; c < 32; ++c)
+                if (n0 + c0 + c < p.N)
+                  yrow[c] = float_to_bf16_bits(fmaf(sa, __uint_as_float(r[c]) * swp[c0 + c], bp[c0 + c]));
+            }
           }
         }
       }
@@ -459,7 +474,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // ---- common exit: every thread arrives here, also after an aborted wait
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)BN);
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(BN * MT));
 }
 
 
@@ -511,28 +526,29 @@ int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint
 
 int sb_bytes_for(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
 
-template <int D, int BITS, int BN>
+template <int D, int BITS, int BN, int MT>
 cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, dim3 grid, cudaStream_t s) {
-  const size_t smem = make_layout(BN, 2 * (kBK / D) * BITS / 8, p.C * 2 * D).total + 1024;
+  const size_t smem = make_layout(BN, MT, 2 * (kBK / D) * BITS / 8, p.C * 2 * D).total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  large_m_kernel<D, BITS, BN><<<grid, kThreads, smem, s>>>(ta, ti, p);
+  large_m_kernel<D, BITS, BN, MT><<<grid, kThreads, smem, s>>>(ta, ti, p);
   return cudaGetLastError();
 }
 
 template <int D, int BITS>
-cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, int bn, dim3 grid,
+cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, int bn, int mt, dim3 grid,
                        cudaStream_t s) {
-  if (bn == 32) return launch_bn<D, BITS, 32>(ta, ti, p, grid, s);
-  if (bn == 64) return launch_bn<D, BITS, 64>(ta, ti, p, grid, s);
-  return launch_bn<D, BITS, 128>(ta, ti, p, grid, s);
+  if (bn == 32) return launch_bn<D, BITS, 32, 1>(ta, ti, p, grid, s);
+  if (bn == 64) return launch_bn<D, BITS, 64, 1>(ta, ti, p, grid, s);
+  if (mt == 2) return launch_bn<D, BITS, 128, 2>(ta, ti, p, grid, s);
+  return launch_bn<D, BITS, 128, 1>(ta, ti, p, grid, s);
 }
 
 }  // namespace
@@ -545,7 +561,7 @@ bool large_m_supported(const sacq_layer* L) {
   if (d.in_features % (2 * kBK) != 0) return false;
   if (L->num_groups != 1 || d.shift_bf16 != 0) return false;
   const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
-  if (make_layout(kMaxBN, sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) return false;
+  if (make_layout(kMaxBN, 1, sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) return false;
   return true;
 }
 
@@ -606,16 +622,21 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
   p.ldy = ldy;
   p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features; p.C = d.codebook_size;
   p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
-  const dim3 grid((unsigned)((d.out_features + bn - 1) / bn), (unsigned)m_tiles);
+  // Two M sub-tiles per CTA as soon as the halved grid still covers every SM.
+  int mt = 1;
+  if (bn == 128 && ((d.out_features + 127) / 128) * ((M + 2 * kBM - 1) / (2 * kBM)) >= (int64_t)L->num_sms &&
+      make_layout(128, 2, sb_bytes_for(L), d.codebook_size * d.vector_dim * 2).total + 1024 <= 227 * 1024)
+    mt = 2;
+  const dim3 grid((unsigned)((d.out_features + bn - 1) / bn), (unsigned)((M + kBM * mt - 1) / (kBM * mt)));
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   cudaError_t e;
   const int D = d.vector_dim, B = d.index_bits;
-  if (D == 8 && B == 12) e = launch_one<8, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
-  else if (D == 8 && B == 8) e = launch_one<8, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
-  else if (D == 8 && B == 16) e = launch_one<8, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
-  else if (D == 4 && B == 12) e = launch_one<4, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
-  else if (D == 4 && B == 8) e = launch_one<4, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
-  else e = launch_one<4, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, grid, s);
+  if (D == 8 && B == 12) e = launch_one<8, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
+  else if (D == 8 && B == 8) e = launch_one<8, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
+  else if (D == 8 && B == 16) e = launch_one<8, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
+  else if (D == 4 && B == 12) e = launch_one<4, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
+  else if (D == 4 && B == 8) e = launch_one<4, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
+  else e = launch_one<4, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
   count_launch();
   if (e != cudaSuccess) return cuda_fail(e, "large-M launch");
   return SACQ_OK;

@@ -278,6 +278,31 @@ def test_linear_large_m_batched_shapes(K, N, M):
     assert O.rel_frobenius(a, b) < 5e-3
 
 
+def test_linear_large_m_two_subtiles():
+    """Enough tiles that a CTA takes two 128-token sub-tiles (two TMEM accumulators); the
+    last CTA's second sub-tile is partial.  Checked against the dense product of the
+    library's own bit-exact reconstruction."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
+    from sacq_b200.synthetic import make_activations, make_payload
+    N, K, M = 2048, 2048, 4800
+    p = make_payload(N, K, seed=9, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(4)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    q, s = quantize_rows(make_activations(M, K, seed=12).cuda())
+    assert mod.kernel_for(M) == "large"
+    y = mod.linear_a8(q, s)
+    dense = (q.float() @ mod.dequantize_weight().float().t()) * s + bias.cuda().float()
+    assert O.rel_frobenius(y.float().cpu().numpy(), dense.cpu().numpy()) <= GEMM_TOL
+    assert torch.equal(y, mod.linear_a8(q, s))
+    # rows of the partial sub-tile against the small-M kernel on the same operands
+    mod.set_kernel("small_mma")
+    tail = mod.linear_a8(q[4736:], s[4736:])
+    mod.set_kernel("auto")
+    assert O.rel_frobenius(y[4736:].float().cpu().numpy(), tail.float().cpu().numpy()) < 5e-3
+    assert mod.device_status() == 0
+
+
 @pytest.mark.parametrize("M,N,K,d,C", [(77, 200, 512, 8, 4096), (300, 1000, 256, 8, 256), (129, 136, 768, 4, 4096),
                                        (1, 128, 256, 8, 4096), (128, 128, 1024, 4, 256)])
 def test_linear_large_m_ragged(M, N, K, d, C):
