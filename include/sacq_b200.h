@@ -131,6 +131,17 @@ SACQ_API int sacq_linear_bf16(const sacq_layer_t* layer, const void* x_bf16, int
                      float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
                      void* stream);
 
+/* The module's forward for a caller whose activations and results live in HOST memory
+ * (the reference's CPU-side callers hand the module host tensors and read host tensors
+ * back, SHIM:456-541): copies x (bf16 [M, K], contiguous; pinned memory makes the copies
+ * asynchronous) to the device, runs sacq_linear_bf16 and copies y (bf16 [M, N]) back, all
+ * on `stream`, without synchronising.  `dev_scratch` is caller-owned device memory of
+ * sacq_host_forward_scratch_bytes(layer, M) bytes, 256-byte aligned, zero-filled once
+ * before its first use; it may be reused by later calls on the same stream. */
+SACQ_API int sacq_linear_bf16_host(const sacq_layer_t* layer, const void* x_host, int64_t M, void* y_host,
+                                   void* dev_scratch, int64_t dev_scratch_bytes, void* stream);
+SACQ_API int64_t sacq_host_forward_scratch_bytes(const sacq_layer_t* layer, int64_t M);
+
 /* The same forward as sacq_linear_a8's split-K small-M kernel, for callers that cannot
  * allocate device memory (a control loop with a frozen memory budget, a server whose
  * arena already owns the GPU, a plugin that is handed nothing but its inputs and

@@ -7,7 +7,7 @@ does, and fails loudly when the CUDA library has not been built."""
 from .packing import index_bits_for, index_window_bytes, pack_indices, pack_payload, unpack_indices  # noqa: F401
 
 __all__ = [
-    "PrecomputedPackedVectorCodebookLinear", "quantize_rows", "pack_indices", "unpack_indices",
+    "PrecomputedPackedVectorCodebookLinear", "forward_shared", "quantize_rows", "pack_indices", "unpack_indices",
     "pack_payload", "index_bits_for", "index_window_bytes",
 ]
 
@@ -16,6 +16,9 @@ def __getattr__(name):
     if name == "PrecomputedPackedVectorCodebookLinear":
         from .linear import PrecomputedPackedVectorCodebookLinear
         return PrecomputedPackedVectorCodebookLinear
+    if name == "forward_shared":
+        from .linear import forward_shared
+        return forward_shared
     if name == "quantize_rows":
         from .activation import quantize_rows
         return quantize_rows

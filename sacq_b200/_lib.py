@@ -64,6 +64,8 @@ SIGNATURES = {
     "sacq_workspace_counter_bytes": (_i64, []),
     "sacq_linear_a8": (_int, [_vp, _vp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "sacq_linear_bf16": (_int, [_vp, _vp, _i64, _i64, _vp, _fp, _vp, _i64, _vp, _i64, _vp]),
+    "sacq_linear_bf16_host": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _vp]),
+    "sacq_host_forward_scratch_bytes": (_i64, [_vp, _i64]),
     "sacq_linear_a8_static_scratch": (_int, [_vp, _vp, _fp, _i64, _vp, _i64, _vp]),
     "sacq_static_scratch_bytes": (_i64, []),
     "sacq_layer_set_kernel": (_int, [_vp, _int]),

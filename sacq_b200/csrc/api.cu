@@ -267,6 +267,55 @@ SACQ_API int sacq_linear_bf16(const sacq_layer_t* L, const void* x_bf16, int64_t
   return sacq_linear_a8(L, q_scratch, scale_scratch, M, y_out, ldy, workspace, workspace_bytes, stream);
 }
 
+// Layout of the device scratch of sacq_linear_bf16_host: workspace first (its counter
+// region leads), then scale, x, q, y, each 256-byte aligned.
+namespace {
+struct HostForwardLayout {
+  int64_t ws, scale, x, q, y, total;
+};
+HostForwardLayout host_forward_layout(const sacq_layer* L, int64_t M) {
+  auto up = [](int64_t v) { return (v + 255) & ~(int64_t)255; };
+  HostForwardLayout h;
+  h.ws = 0;
+  h.scale = up(sacq_workspace_bytes(L, M));
+  h.x = h.scale + up(M * 4);
+  h.q = h.x + up(M * L->d.in_features * 2);
+  h.y = h.q + up(M * L->d.in_features);
+  h.total = h.y + up(M * L->d.out_features * 2);
+  return h;
+}
+}  // namespace
+
+SACQ_API int64_t sacq_host_forward_scratch_bytes(const sacq_layer_t* L, int64_t M) {
+  if (L == nullptr || M < 0) return 0;
+  return host_forward_layout(L, M).total;
+}
+
+SACQ_API int sacq_linear_bf16_host(const sacq_layer_t* L, const void* x_host, int64_t M, void* y_host,
+                                   void* dev_scratch, int64_t dev_scratch_bytes, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
+  if (M == 0 || L->d.out_features == 0) return SACQ_OK;
+  if (x_host == nullptr || y_host == nullptr || dev_scratch == nullptr)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  const HostForwardLayout h = host_forward_layout(L, M);
+  if (dev_scratch_bytes < h.total)
+    return set_error(SACQ_ERR_WORKSPACE, "device scratch of %lld bytes needed, %lld given", (long long)h.total,
+                     (long long)dev_scratch_bytes);
+  if (reinterpret_cast<uintptr_t>(dev_scratch) % 256 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "device scratch must be 256-byte aligned");
+  DeviceGuard guard(L->d.device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(dev_scratch);
+  const int64_t K = L->d.in_features, N = L->d.out_features;
+  SACQ_CUDA_TRY(cudaMemcpyAsync(base + h.x, x_host, (size_t)(M * K * 2), cudaMemcpyHostToDevice, s));
+  const int rc = sacq_linear_bf16(L, base + h.x, K, M, base + h.q, reinterpret_cast<float*>(base + h.scale),
+                                  base + h.y, N, base + h.ws, h.scale, stream);
+  if (rc != SACQ_OK) return rc;
+  SACQ_CUDA_TRY(cudaMemcpyAsync(y_host, base + h.y, (size_t)(M * N * 2), cudaMemcpyDeviceToHost, s));
+  return SACQ_OK;
+}
+
 SACQ_API int sacq_layer_status(const sacq_layer_t* L, int* status_out) {
   if (int rc = check_layer(L)) return rc;
   if (status_out == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "status_out is null");

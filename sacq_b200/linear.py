@@ -43,6 +43,7 @@ class _Workspace:
         self.ws = None
         self.q = None
         self.scale = None
+        self.host_scratch = None
 
     @classmethod
     def get(cls, device: torch.device) -> "_Workspace":
@@ -149,6 +150,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
             raise ValueError(f"codebook shape {tuple(self.codebook.shape)} does not match vector_dim")
         self.runtime_kernel_eligible = True
         self._ws_bytes = {}
+        self._host_bytes = {}
         self._handle = None
         self._create_handle()
 
@@ -283,12 +285,42 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
             y = y.reshape(*x.shape[:-1], self.out_features)
         return y if x.dtype == torch.bfloat16 else y.to(x.dtype)
 
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor | None = None) -> torch.Tensor:
+        """Forward for host-resident activations: ``x_host`` is a CPU bf16 ``[M, K]`` tensor
+        (pinned for asynchronous copies), the result is a CPU bf16 ``[M, N]`` tensor.  The
+        copies and kernels are enqueued on the current stream of the layer's device; the
+        caller synchronises that stream before reading ``out_host``."""
+        if x_host.is_cuda or x_host.dtype != torch.bfloat16 or x_host.dim() != 2 or not x_host.is_contiguous():
+            raise TypeError("forward_host expects a contiguous 2-D bfloat16 CPU tensor")
+        if x_host.shape[1] != self.in_features:
+            raise ValueError("Linear shape mismatch")
+        m = x_host.shape[0]
+        if out_host is None:
+            out_host = torch.empty((m, self.out_features), dtype=torch.bfloat16, pin_memory=x_host.is_pinned())
+        dev = self.codebook.device
+        need = self._host_bytes.get(m)
+        if need is None:
+            need = self._host_bytes[m] = int(self._lib.sacq_host_forward_scratch_bytes(self._handle, m))
+        ws = _Workspace.get(dev)
+        if ws.host_scratch is None or ws.host_scratch.numel() < need:
+            ws.host_scratch = torch.zeros(max(need, 1 << 22), dtype=torch.uint8, device=dev)
+        buf = ws.host_scratch
+        if m > 0 and self.out_features > 0:
+            with torch.cuda.device(dev):
+                rc = self._lib.sacq_linear_bf16_host(self._handle, x_host.data_ptr(), m, out_host.data_ptr(),
+                                                     buf.data_ptr(), buf.numel(),
+                                                     torch.cuda.current_stream().cuda_stream)
+            if rc != 0:
+                _lib.check(rc)
+        return out_host
+
     # ------------------------------------------------------------------ extras
     def set_kernel(self, which: str | int) -> None:
         """Force a GEMM kernel: 'auto' (0), 'small' (1), 'large' (2), 'small_simt' (3), 'small_mma' (4)."""
         code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5}.get(which, which)
         _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
         self._ws_bytes.clear()
+        self._host_bytes.clear()
 
     def kernel_for(self, m: int) -> str:
         k = self._lib.sacq_layer_kernel_for(self._handle, m)
@@ -311,3 +343,24 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, vector_dim={self.vector_dim}, "
                 f"codebook={tuple(self.codebook.shape)}, index_bits={self.index_bits}, group_size={self.group_size}")
+
+
+def forward_shared(layers, x: torch.Tensor):
+    """Sibling projections that read the same input (q/k/v, gate/up): quantize ``x`` once and
+    run every layer's GEMM on the shared FP8 activations, as the reference's overlay does
+    (int8_shared_padded_activation_20261028_r1.py:44-63).  Returns one output per layer, each
+    identical to ``layer(x)``."""
+    from .activation import quantize_rows
+    layers = list(layers)
+    k = layers[0].in_features
+    if any(l.in_features != k for l in layers):
+        raise ValueError("layers that share an input must have the same in_features")
+    a = x.reshape(-1, k)
+    if a.dtype != torch.bfloat16:
+        a = a.to(torch.bfloat16)
+    q, s = quantize_rows(a.contiguous() if a.stride(-1) != 1 else a)
+    outs = []
+    for layer in layers:
+        y = layer.linear_a8(q, s).reshape(*x.shape[:-1], layer.out_features)
+        outs.append(y if x.dtype == torch.bfloat16 else y.to(x.dtype))
+    return outs

@@ -22,7 +22,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .linear import PrecomputedPackedVectorCodebookLinear
+from .linear import PrecomputedPackedVectorCodebookLinear, forward_shared
 from .synthetic import make_payload
 
 
@@ -85,7 +85,7 @@ class _Block(torch.nn.Module):
         return F.scaled_dot_product_attention(q, k, v).transpose(0, 1).reshape(t, self.hidden)
 
     def cross_kv(self, ctx):
-        return self.ck(ctx), self.cv(ctx)
+        return tuple(forward_shared((self.ck, self.cv), ctx))
 
     def forward(self, x, cond=None, cross_kv=None):
         if self.adaln:
@@ -93,13 +93,15 @@ class _Block(torch.nn.Module):
             h = self.n1(x) * (1 + m[1]) + m[0]
         else:
             h = self.n1(x)
-        x = x + self.o(self._attend(self.q(h), self.k(h), self.v(h)))
+        q, k, v = forward_shared((self.q, self.k, self.v), h)      # one activation quantization for q/k/v
+        x = x + self.o(self._attend(q, k, v))
         if self.cross:
             h = self.n3(x)
             x = x + self.co(self._attend(self.cq(h), cross_kv[0], cross_kv[1]))
         h = self.n2(x) * (1 + m[3]) + m[2] if self.adaln else self.n2(x)
         if self.gated:
-            h = F.silu(self.gate(h)) * self.up(h)
+            gate, up = forward_shared((self.gate, self.up), h)
+            h = F.silu(gate) * up
         else:
             h = F.gelu(self.up(h))
         return x + self.down(h)

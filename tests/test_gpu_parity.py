@@ -372,6 +372,13 @@ def test_linear_properties_and_edges():
     from sacq_b200.linear import _Workspace
     ws = _Workspace.get(q.device).ws
     assert int(ws[: mod._lib.sacq_workspace_counter_bytes()].sum()) == 0
+    # host-buffer forward: pinned host activations in, host result out, same bytes
+    xh = x.cpu().pin_memory()
+    yh = mod.forward_host(xh)
+    torch.cuda.synchronize()
+    assert not yh.is_cuda and torch.equal(yh, mod(x).cpu())
+    with pytest.raises(TypeError):
+        mod.forward_host(x)
     with pytest.raises(ValueError):
         mod(torch.zeros(2, K - 8, dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(ValueError):
