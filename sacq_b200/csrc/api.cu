@@ -65,9 +65,15 @@ int pick_kernel(const sacq_layer* L, int64_t M) {
   if (L->force_kernel == 1 || L->force_kernel >= 3)
     return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 2) return large_m_supported(L) ? 2 : SACQ_ERR_UNSUPPORTED;
-  // A shape rule, not a backend switch: the CUDA-core kernel wins while the grid of
-  // 128-row tensor-core tiles cannot fill the device.
-  if (large_m_supported(L) && M > 64) return 2;
+  // A shape rule, not a backend switch.  Above 64 rows the tcgen05 kernel always wins.
+  // Between 33 and 64 rows the small-M kernel walks its row tiles once per 16-token chunk
+  // while one tensor-core M tile covers them all; that pays off once the layer has enough
+  // output rows to give the tensor-core grid a CTA for most SMs (measured: N = 6144 yes,
+  // N <= 2048 no).
+  if (large_m_supported(L)) {
+    if (M > 64) return 2;
+    if (M > 32 && L->d.out_features >= 32 * (int64_t)L->num_sms) return 2;
+  }
   return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
 }
 

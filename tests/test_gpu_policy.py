@@ -32,3 +32,30 @@ def test_policy_forward_runs_and_is_deterministic():
         ref = (q.float() @ layer.dequantize_weight().float().t()) * s
         err = ((layer(x).float() - ref).norm() / ref.norm()).item()
         assert err <= 1e-2, err
+
+
+def test_overlay_installs_real_layers():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, overlay
+    from sacq_b200.synthetic import make_payload
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = torch.nn.Linear(256, 128, bias=True, device="cuda", dtype=torch.bfloat16)
+            self.up_proj = torch.nn.Linear(256, 512, bias=False, device="cuda", dtype=torch.bfloat16)
+
+    model = torch.nn.ModuleDict({"blk": Block()})
+    ov = {"weights": {"blk.q_proj": make_payload(128, 256, seed=1, iters=1),
+                      "blk.up_proj": make_payload(512, 256, seed=2, iters=1)}, "expected_applied": 2}
+    bias = model["blk"].q_proj.bias.detach().clone()
+    assert overlay.apply_overlay(model, ov, "cuda:0", scope="vlm",
+                                 allowed_suffixes=(".q_proj", ".up_proj")) == 2
+    q = model["blk"].q_proj
+    assert isinstance(q, PrecomputedPackedVectorCodebookLinear) and q.runtime_scope == "vlm"
+    assert torch.equal(q.bias, bias)
+    x = torch.randn(4, 256, device="cuda", dtype=torch.bfloat16)
+    aq, s = q.quantize_activations(x)
+    ref = (aq.float() @ q.dequantize_weight().float().t()) * s + bias.float()
+    assert ((q(x).float() - ref).norm() / ref.norm()).item() <= 1e-2
