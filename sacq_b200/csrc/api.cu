@@ -220,7 +220,7 @@ SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, 
 
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
-  if (which < 0 || which > 5) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..5", which);
+  if (which < 0 || which > 6) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..6", which);
   L->force_kernel = which;
   return SACQ_OK;
 }

@@ -327,6 +327,57 @@ bool fast_eligible(const sacq_layer* L) {
   return true;
 }
 
+// The index-unpacking warp-MMA variant: any index width up to 16 bits, scale groups of any
+// multiple of 32 weights.
+bool unpacked_eligible(const sacq_layer* L) {
+  const sacq_layer_desc& d = L->d;
+  if (d.vector_dim != 8 && d.vector_dim != 4) return false;
+  if (d.index_bits < 1 || d.index_bits > 16) return false;
+  if (!L->rows_16b_aligned) return false;
+  if (d.in_features % (8 * d.vector_dim) != 0 || d.in_features % 32 != 0) return false;
+  if (d.group_size % 32 != 0) return false;
+  const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
+  if (cb_bytes > 64 * 1024 || cb_bytes % 16 != 0) return false;
+  return true;
+}
+
+// Fills the plan for that variant; false if no tile height fits shared memory.
+bool plan_unpacked(const sacq_layer* L, Plan& pl) {
+  const sacq_layer_desc& d = L->d;
+  const int64_t sub = (d.out_features + 7) / 8;
+  const int steps = (int)(d.in_features / 32);
+  const int warps = steps < 16 ? steps : 16;
+  int64_t stride = L->num_sms / pl.chunks;
+  if (stride < 1) stride = 1;
+  double best_cost = -1.0;
+  int best = 0;
+  for (int r8 = 1; r8 <= 4; r8 *= 2) {
+    const size_t need = small_m_mma_unpacked_smem(d.codebook_size, d.vector_dim, (int)d.in_features, L->row_bits / 8,
+                                                  (int)L->num_groups, r8, warps);
+    if (need > kSmemBudget) continue;
+    const int64_t row_tiles = (sub + r8 - 1) / r8;
+    const int64_t waves = (row_tiles + stride - 1) / stride;
+    const double cost = 3.0 + (double)waves * (0.3 + 0.6 * r8);
+    if (best_cost < 0 || cost < best_cost - 1e-9) { best_cost = cost; best = r8; }
+  }
+  if (best == 0) return false;
+  pl.unpacked = true;
+  pl.mma = true;
+  pl.staged = true;
+  pl.r8 = best;
+  pl.warps = warps;
+  pl.row_blocks = (int)((sub + best - 1) / best);
+  pl.num_sg = 1;
+  pl.spans_per_item = pl.spans_per_row;
+  pl.num_items = (int64_t)pl.row_blocks * pl.chunks;
+  if (stride > pl.row_blocks) stride = pl.row_blocks;
+  pl.grid = (int)(stride * pl.chunks);
+  if (pl.grid < 1) pl.grid = 1;
+  pl.act_bufs = 1;
+  pl.smem = small_m_mma_unpacked_smem(d.codebook_size, d.vector_dim, (int)d.in_features, L->row_bits / 8,
+                                      (int)L->num_groups, best, warps);
+  return true;
+}
 
 // M from which the warp-MMA variant is preferred over the CUDA-core one.
 constexpr int64_t kMmaMinM = 1;
@@ -355,6 +406,16 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
     pl.cb_smem = false;
   }
   pl.spans_per_row = (int)(L->vectors_per_row / pl.span_idx);
+  // Layers the span-based fast kernels cannot take (odd index widths, narrow scale groups)
+  // go to the index-unpacking warp-MMA variant; selector 6 forces it for any eligible layer.
+  if (unpacked_eligible(L) && (L->force_kernel == 6 || (!pl.fast && L->force_kernel != 3))) {
+    const int mt = pl.MT, chunks = pl.chunks;
+    pl.MT = 16;
+    pl.chunks = (int)((M + 15) / 16);
+    if (plan_unpacked(L, pl)) return pl;
+    pl.MT = mt;
+    pl.chunks = chunks;
+  }
   if (pl.mma) {
     // tile = 16 tokens x 8*r8 rows; the CTA's warps split the K spans.
     const int64_t sub = (d.out_features + 7) / 8;
@@ -485,6 +546,8 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   if (M == 0 || d.out_features == 0) return SACQ_OK;
   if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
   const Plan pl = make_plan(L, M);
+  if (L->force_kernel == 6 && !pl.unpacked)
+    return set_error(SACQ_ERR_UNSUPPORTED, "index-unpacking warp-MMA variant cannot run this layer");
   if (pl.smem > kSmemBudget)
     return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel needs %zu bytes of shared memory", pl.smem);
   const int64_t need = small_m_workspace_bytes(L, M);
@@ -524,7 +587,12 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   memcpy(&p.shift, &sb, sizeof(float));
 
   cudaError_t e;
-  if (pl.fast) {
+  if (pl.unpacked) {
+    if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
+      return set_error(SACQ_ERR_ALIGNMENT, "small-M MMA kernel: q must be 16-byte aligned");
+    p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
+    e = launch_small_m_mma_unpacked(pl, p, s);
+  } else if (pl.fast) {
     if (reinterpret_cast<uintptr_t>(q) % 8 != 0 || d.in_features % 8 != 0)
       return set_error(SACQ_ERR_ALIGNMENT, "quantized activations must be 8-byte aligned with K %% 8 == 0");
     p.out_mul = ldexpf(1.f, (pl.mma && pl.staged) ? -L->cb8_exp_shift : -L->cb_exp_shift);

@@ -87,6 +87,7 @@ struct Plan {
   int r8;                    // warp-MMA variant: 8-row sub-blocks per tile (1, 2 or 4)
   bool staged;               // warp-MMA variant with bulk-copied tiles in shared memory
   int act_bufs;              // ... and how many activation tile buffers fit (1 or 2)
+  bool unpacked;             // warp-MMA variant that unpacks indices to 16 bits in shared memory
   size_t smem;
 };
 
@@ -139,6 +140,10 @@ cudaError_t launch_kernel_pdl(const Plan& pl, const SmallMParams& p, cudaStream_
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s);
 // Shared memory the staged warp-MMA kernel needs for (layer, r8); 0 if it cannot run it.
 size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps, int act_bufs);
+
+// linear_small_m_unpacked.cu
+cudaError_t launch_small_m_mma_unpacked(const Plan& pl, const SmallMParams& p, cudaStream_t s);
+size_t small_m_mma_unpacked_smem(int C, int D, int K, int64_t row_bytes, int num_groups, int r8, int warps);
 
 }  // namespace smallm
 }  // namespace sacq

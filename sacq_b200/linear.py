@@ -316,8 +316,10 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
 
     # ------------------------------------------------------------------ extras
     def set_kernel(self, which: str | int) -> None:
-        """Force a GEMM kernel: 'auto' (0), 'small' (1), 'large' (2), 'small_simt' (3), 'small_mma' (4)."""
-        code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5}.get(which, which)
+        """Force a GEMM kernel: 'auto' (0), 'small' (1), 'large' (2), 'small_simt' (3), 'small_mma' (4),
+        'small_mma_direct' (5), 'small_mma_unpacked' (6)."""
+        code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5,
+                "small_mma_unpacked": 6}.get(which, which)
         _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
         self._ws_bytes.clear()
         self._host_bytes.clear()

@@ -160,7 +160,7 @@ def test_weight_fp8_producer_matches_reference_fixture(name):
 
 # --------------------------------------------------------------------------- quantized linear
 
-ALL_SMALL = ("auto", "small_simt", "small_mma", "small_mma_direct")
+ALL_SMALL = ("auto", "small_simt", "small_mma", "small_mma_direct", "small_mma_unpacked")
 ALL_KERNELS = ALL_SMALL + ("large",)
 
 
@@ -173,7 +173,12 @@ def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=ALL_SMALL):
         mod.set_kernel(k)
         if k == "large" and mod._lib.sacq_layer_kernel_for(mod._handle, q.shape[0]) < 0:
             continue                                   # geometry outside the tensor-core kernel
-        y = mod.linear_a8(q, sc)
+        try:
+            y = mod.linear_a8(q, sc)
+        except Exception as e:                         # the forced variant may not take this geometry
+            if k == "small_mma_unpacked" and getattr(e, "code", 0) == -2:
+                continue
+            raise
         torch.cuda.synchronize()
         assert y.dtype == torch.bfloat16
         err = O.rel_frobenius(y.float().cpu().numpy(), ref)
@@ -341,6 +346,28 @@ def test_linear_grouped_and_ragged_geometries(N, K, d, C, G):
     for M in (1, 3, 17):
         q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M)))
         _check_linear(mod, q_bits, s, w_bits, None)
+
+
+@pytest.mark.parametrize("N,K,C,G", [(2048, 2048, 128, 64), (6144, 2048, 1024, 64), (1536, 1536, 64, 64),
+                                     (2048, 6144, 32, 64), (1000, 2048, 2048, 128), (520, 1024, 512, 32)])
+def test_linear_deployed_layouts(N, K, C, G):
+    """The layouts of the reference's frozen decode selection: dim-4 vectors, 64-wide scale
+    groups, 5- to 11-bit indices; on the index-unpacking warp-MMA variant, with a shift."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=4, codebook_size=C, group_size=G, seed=N + C, device="cuda", iters=1)
+    p["shift"] = torch.tensor(-0.00390625, dtype=torch.bfloat16)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    assert np.array_equal(bf16_bits(mod.dequantize_weight()), w_bits)
+    for M in (1, 16, 41):
+        q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M)))
+        outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias),
+                             kernels=("auto", "small_simt", "small_mma_unpacked"))
+        assert "small_mma_unpacked" in outs
+        assert torch.equal(outs["auto"][0], outs["small_mma_unpacked"][0])
 
 
 def test_linear_properties_and_edges():
