@@ -135,7 +135,10 @@ SACQ_API int sacq_linear_bf16(const sacq_layer_t* layer, const void* x_bf16, int
  * (the reference's CPU-side callers hand the module host tensors and read host tensors
  * back, SHIM:456-541): copies x (bf16 [M, K], contiguous; pinned memory makes the copies
  * asynchronous) to the device, runs sacq_linear_bf16 and copies y (bf16 [M, N]) back, all
- * on `stream`, without synchronising.  `dev_scratch` is caller-owned device memory of
+ * on `stream`, without synchronising.  When a host buffer is pinned (page-locked and mapped,
+ * 16-byte aligned) and its transfer is at most 1 MiB, no copy engine is involved: the
+ * quantizer kernel reads x from host memory directly and a copy kernel stores y to host
+ * memory; the bytes crossing the bus are the same.  `dev_scratch` is caller-owned device memory of
  * sacq_host_forward_scratch_bytes(layer, M) bytes, 256-byte aligned, zero-filled once
  * before its first use; it may be reused by later calls on the same stream. */
 SACQ_API int sacq_linear_bf16_host(const sacq_layer_t* layer, const void* x_host, int64_t M, void* y_host,

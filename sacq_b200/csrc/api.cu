@@ -290,6 +290,21 @@ HostForwardLayout host_forward_layout(const sacq_layer* L, int64_t M) {
   h.total = h.y + up(M * L->d.out_features * 2);
   return h;
 }
+
+// Transfers up to this size bypass the copy engine when the host buffer is pinned: the
+// quantizer reads the activations straight from host memory and a copy kernel pushes the
+// result back (each copy-engine hand-over on a stream costs more than the transfer itself).
+constexpr int64_t kDirectHostIoBytes = 1 << 20;
+
+// Device alias of a pinned (page-locked, mapped) host pointer, or null.
+void* pinned_alias(const void* host) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, host) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
+}
 }  // namespace
 
 SACQ_API int64_t sacq_host_forward_scratch_bytes(const sacq_layer_t* L, int64_t M) {
@@ -314,10 +329,19 @@ SACQ_API int sacq_linear_bf16_host(const sacq_layer_t* L, const void* x_host, in
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint8_t* base = static_cast<uint8_t*>(dev_scratch);
   const int64_t K = L->d.in_features, N = L->d.out_features;
-  SACQ_CUDA_TRY(cudaMemcpyAsync(base + h.x, x_host, (size_t)(M * K * 2), cudaMemcpyHostToDevice, s));
-  const int rc = sacq_linear_bf16(L, base + h.x, K, M, base + h.q, reinterpret_cast<float*>(base + h.scale),
+  const void* x_dev = base + h.x;
+  void* x_alias = M * K * 2 <= kDirectHostIoBytes && reinterpret_cast<uintptr_t>(x_host) % 16 == 0
+                      ? pinned_alias(x_host) : nullptr;
+  if (x_alias != nullptr)
+    x_dev = x_alias;                                   // the quantizer reads the pinned buffer itself
+  else
+    SACQ_CUDA_TRY(cudaMemcpyAsync(base + h.x, x_host, (size_t)(M * K * 2), cudaMemcpyHostToDevice, s));
+  const int rc = sacq_linear_bf16(L, x_dev, K, M, base + h.q, reinterpret_cast<float*>(base + h.scale),
                                   base + h.y, N, base + h.ws, h.scale, stream);
   if (rc != SACQ_OK) return rc;
+  void* y_alias = M * N * 2 <= kDirectHostIoBytes && reinterpret_cast<uintptr_t>(y_host) % 16 == 0
+                      ? pinned_alias(y_host) : nullptr;
+  if (y_alias != nullptr) return launch_copy_to_host(base + h.y, y_alias, M * N * 2, L->num_sms, s);
   SACQ_CUDA_TRY(cudaMemcpyAsync(y_host, base + h.y, (size_t)(M * N * 2), cudaMemcpyDeviceToHost, s));
   return SACQ_OK;
 }

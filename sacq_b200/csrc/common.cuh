@@ -58,6 +58,7 @@ int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s);
 int launch_decode_weight_fp8(const sacq_layer* L, const float* sw, void* wq, cudaStream_t s);
 int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
 int launch_build_tables(sacq_layer* L, cudaStream_t s);
+int launch_copy_to_host(const void* src, void* dst, int64_t bytes, int num_sms, cudaStream_t s);
 
 bool small_m_supported(const sacq_layer* L);
 int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M);

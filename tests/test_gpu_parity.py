@@ -412,6 +412,35 @@ def test_linear_properties_and_edges():
         mod(torch.zeros(2, K, dtype=torch.bfloat16))
 
 
+@pytest.mark.parametrize("M,pinned", [(1, True), (16, True), (3, False), (700, True), (700, False)])
+def test_host_forward_routes(M, pinned):
+    """Host-buffer forward: pinned buffers up to 1 MiB are read and written by the kernels
+    themselves, larger or pageable ones go through copies; the bytes are those of the device
+    forward every time.  M = 700 x 2048 x 2 B is above the direct-transfer limit."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    N, K = 1000, 2048                                   # N*2 bytes per row is not a multiple of 16
+    p = make_payload(N, K, seed=21, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(3)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    x = make_activations(M, K, seed=M)
+    xh = x.pin_memory() if pinned else x.clone()
+    yh = torch.full((M, N), 5.0, dtype=torch.bfloat16)
+    yh = yh.pin_memory() if pinned else yh
+    before = mod._lib.sacq_launch_count()
+    out = mod.forward_host(xh, yh)
+    torch.cuda.synchronize()
+    launches = mod._lib.sacq_launch_count() - before
+    assert out is yh and torch.equal(yh, mod(x.cuda()).cpu())
+    direct = pinned and M * N * 2 <= (1 << 20)
+    assert launches == (3 if direct else 2)             # quantizer + GEMM (+ the copy-out kernel)
+    # a second call on the same buffers gives the same bytes
+    again = mod.forward_host(xh, yh.clone() if not pinned else yh)
+    torch.cuda.synchronize()
+    assert torch.equal(again, yh)
+
+
 def test_c_abi_error_codes_on_device():
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear, _lib
