@@ -169,10 +169,11 @@ SACQ_API int64_t sacq_static_scratch_bytes(void);
  * (its own choice of variant), 2 = large-M kernel, 3 = small-M CUDA-core variant,
  * 4 = small-M warp-MMA variant, 5 = warp-MMA variant without shared-memory staging,
  * 6 = warp-MMA variant that unpacks the indices in shared memory (any index width, any
- * group size that is a multiple of 32).  Returns SACQ_ERR_UNSUPPORTED from the next forward
+ * group size that is a multiple of 32), 7 = tensor-core kernel for grouped scales.  Returns SACQ_ERR_UNSUPPORTED from the next forward
  * if the forced kernel cannot run the layer. */
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* layer, int which);
-/* Which kernel a forward with M rows would use (1 or 2), or a negative error. */
+/* Which kernel a forward with M rows would use (1 = small-M, 2 = large-M tensor-core kernel
+ * for per-channel scales, 3 = tensor-core kernel for grouped scales), or a negative error. */
 SACQ_API int sacq_layer_kernel_for(const sacq_layer_t* layer, int64_t M);
 
 /* Reads the layer's device-side status word (synchronises the device): 0, or a

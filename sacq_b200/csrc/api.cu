@@ -61,7 +61,12 @@ int64_t small_m_slab_rows(const sacq_layer* L) {
   return chunks * 16;
 }
 
+// Rows from which the grouped tensor-core kernel beats the index-unpacking warp-MMA kernel
+// (which walks the weights once per 16-token chunk).
+constexpr int64_t kGroupedMinM = 48;
+
 int pick_kernel(const sacq_layer* L, int64_t M) {
+  if (L->force_kernel == 7) return large_m_grouped_supported(L) ? 3 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 1 || L->force_kernel >= 3)
     return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 2) return large_m_supported(L) ? 2 : SACQ_ERR_UNSUPPORTED;
@@ -73,6 +78,8 @@ int pick_kernel(const sacq_layer* L, int64_t M) {
   if (large_m_supported(L)) {
     if (M > 64) return 2;
     if (M > 32 && L->d.out_features >= 32 * (int64_t)L->num_sms) return 2;
+  } else if (M >= kGroupedMinM && large_m_grouped_supported(L)) {
+    return 3;                                          // grouped scales, odd index widths, a shift
   }
   return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
 }
@@ -220,7 +227,7 @@ SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, 
 
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
-  if (which < 0 || which > 6) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..6", which);
+  if (which < 0 || which > 7) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..7", which);
   L->force_kernel = which;
   return SACQ_OK;
 }
@@ -234,6 +241,7 @@ SACQ_API int sacq_layer_kernel_for(const sacq_layer_t* L, int64_t M) {
 
 SACQ_API int64_t sacq_workspace_bytes(const sacq_layer_t* L, int64_t M) {
   if (L == nullptr || M < 0) return 0;
+  if (pick_kernel(L, M) == 3) return kCounterBytes + large_m_grouped_workspace_bytes(L, M);
   const int64_t slab = small_m_slab_rows(L);
   return small_m_workspace_bytes(L, M < slab ? M : slab);
 }
@@ -253,6 +261,13 @@ SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* s
   const int k = pick_kernel(L, M);
   if (k < 0) return set_error(k, "no kernel can run this layer geometry");
   if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s);
+  if (k == 3) {
+    if (workspace == nullptr || workspace_bytes < kCounterBytes)
+      return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
+                       (long long)sacq_workspace_bytes(L, M), (long long)workspace_bytes);
+    return launch_large_m_grouped(L, q, scale, M, y_out, ldy, static_cast<uint8_t*>(workspace) + kCounterBytes,
+                                  workspace_bytes - kCounterBytes, s);
+  }
   const int64_t slab = small_m_slab_rows(L);
   for (int64_t m0 = 0; m0 < M; m0 += slab) {
     const int64_t rows = (M - m0) < slab ? (M - m0) : slab;

@@ -29,12 +29,13 @@ struct sacq_layer {
   int64_t row_bits;          // (K/d) * b
   bool rows_16b_aligned;     // every row of the packed stream starts on a 16-byte boundary
   int num_sms;
-  int force_kernel;          // 0 auto, 1 small-M, 2 large-M
+  int force_kernel;          // 0 auto, 1 small-M, 2 large-M, 3..6 small-M variants, 7 grouped tensor-core
   // derived device tables (owned)
   __half* cb_f16;            // [C, d] codebook * 2^cb_exp_shift as fp16 (small-M kernel)
   uint8_t* cb_hilo;          // [C][2][d] e4m3 high/low split of codebook * 2^cb8_exp_shift (large-M kernel)
   int cb_exp_shift;          // power-of-two normalisation folded back in the epilogue
   int cb8_exp_shift;
+  int sc_exp_shift;          // max |scale| * 2^sc_exp_shift lies in [0.5, 1) (grouped tensor-core kernel)
   int* d_status;             // device status word, 0 = ok
   int64_t resident_bytes;
   sacq::LargeMPlan* large_plan;
@@ -69,6 +70,11 @@ bool large_m_supported(const sacq_layer* L);
 int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    cudaStream_t s);
 void large_m_release(sacq_layer* L);
+
+bool large_m_grouped_supported(const sacq_layer* L);
+int64_t large_m_grouped_workspace_bytes(const sacq_layer* L, int64_t M);
+int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                           void* ws, int64_t ws_bytes, cudaStream_t s);
 
 // ----------------------------------------------------------------------------
 // device side

@@ -245,9 +245,27 @@ int launch_build_tables(sacq_layer* L, cudaStream_t s) {
   }
   float h_max = 0.f;
   if (e == cudaSuccess) e = cudaMemcpyAsync(&h_max, d_max, sizeof(float), cudaMemcpyDeviceToHost, s);
+  // largest |scale|, for the power-of-two normalisation of the grouped tensor-core kernel
+  float h_smax = 0.f;
+  const int64_t n_scales = d.out_features * L->num_groups;
+  if (e == cudaSuccess && n_scales > 0) {
+    e = cudaMemsetAsync(d_max, 0, sizeof(float), s);
+    if (e == cudaSuccess) {
+      codebook_absmax_kernel<<<grid_for(n_scales, 256, L->num_sms), 256, 0, s>>>(
+          static_cast<const uint16_t*>(d.scales), n_scales, d_max);
+      count_launch();
+      e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&h_smax, d_max, sizeof(float), cudaMemcpyDeviceToHost, s);
+  }
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   cudaFree(d_max);
   if (e != cudaSuccess) return cuda_fail(e, "codebook absmax");
+  {
+    int sx = 0;
+    if (h_smax > 0.f) (void)frexpf(h_smax, &sx);
+    L->sc_exp_shift = -sx;
+  }
   int ex = 0;
   if (h_max > 0.f) {
     (void)frexpf(h_max, &ex);  // h_max = f * 2^ex, f in [0.5, 1)

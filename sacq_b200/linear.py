@@ -317,9 +317,9 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
     # ------------------------------------------------------------------ extras
     def set_kernel(self, which: str | int) -> None:
         """Force a GEMM kernel: 'auto' (0), 'small' (1), 'large' (2), 'small_simt' (3), 'small_mma' (4),
-        'small_mma_direct' (5), 'small_mma_unpacked' (6)."""
+        'small_mma_direct' (5), 'small_mma_unpacked' (6), 'large_grouped' (7)."""
         code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5,
-                "small_mma_unpacked": 6}.get(which, which)
+                "small_mma_unpacked": 6, "large_grouped": 7}.get(which, which)
         _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
         self._ws_bytes.clear()
         self._host_bytes.clear()
@@ -328,7 +328,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         k = self._lib.sacq_layer_kernel_for(self._handle, m)
         if k < 0:
             _lib.check(k)
-        return {1: "small", 2: "large"}[k]
+        return {1: "small", 2: "large", 3: "large_grouped"}[k]
 
     def device_status(self) -> int:
         st = ctypes.c_int(0)

@@ -171,7 +171,7 @@ def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=ALL_SMALL):
     outs = {}
     for k in kernels:
         mod.set_kernel(k)
-        if k == "large" and mod._lib.sacq_layer_kernel_for(mod._handle, q.shape[0]) < 0:
+        if k in ("large", "large_grouped") and mod._lib.sacq_layer_kernel_for(mod._handle, q.shape[0]) < 0:
             continue                                   # geometry outside the tensor-core kernel
         try:
             y = mod.linear_a8(q, sc)
@@ -368,6 +368,38 @@ def test_linear_deployed_layouts(N, K, C, G):
                              kernels=("auto", "small_simt", "small_mma_unpacked"))
         assert "small_mma_unpacked" in outs
         assert torch.equal(outs["auto"][0], outs["small_mma_unpacked"][0])
+
+
+@pytest.mark.parametrize("N,K,d,C,G,M", [
+    (2048, 2048, 4, 128, 64, 149), (6144, 2048, 4, 1024, 64, 300), (1536, 1536, 4, 64, 64, 41),
+    (2048, 6144, 4, 32, 64, 256), (1000, 2048, 4, 2048, 128, 129), (136, 1024, 8, 512, 64, 77),
+    (520, 1024, 8, 4096, 256, 1), (2048, 2048, 8, 4096, 2048, 1300)])
+def test_linear_grouped_tensor_core(N, K, d, C, G, M):
+    """Grouped scales on the tcgen05 kind::f16 kernel: the deployed dim-4 / group-64 layouts at
+    prefill sizes, partial tiles in M and N, one and two token sub-tiles, a token count above
+    one widening slab, a shift and a bias."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N + M, device="cuda", iters=1)
+    p["shift"] = torch.tensor(0.001953125, dtype=torch.bfloat16)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(7)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 2)))
+    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=("large_grouped", "small"))
+    assert "large_grouped" in outs
+    a, b = outs["large_grouped"][0].float().cpu().numpy(), outs["small"][0].float().cpu().numpy()
+    assert O.rel_frobenius(a, b) < 5e-3
+    if M >= 48 and G < K:
+        assert mod.kernel_for(M) == "large_grouped"
+    # rows of a wider output buffer beyond N stay untouched
+    q = torch.from_numpy(q_bits).cuda().view(torch.float8_e4m3fn)
+    out = torch.full((M, N + 24), 3.0, dtype=torch.bfloat16, device="cuda")
+    mod.set_kernel("large_grouped")
+    mod.linear_a8(q, torch.from_numpy(s).cuda(), out=out[:, :N])
+    mod.set_kernel("auto")
+    assert torch.equal(out[:, :N], outs["large_grouped"][0]) and float(out[:, N:].float().min()) == 3.0
 
 
 def test_linear_properties_and_edges():
