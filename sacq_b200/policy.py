@@ -75,14 +75,14 @@ class _Block(torch.nn.Module):
             self.n3 = torch.nn.LayerNorm(hidden, device=f.device, dtype=torch.bfloat16)
 
     def _attend(self, q, k, v):
+        # [1, heads, tokens, head_dim] views: the 4-D form lets PyTorch pick a fused attention
+        # kernel, and grouped-query attention needs no materialised key/value repeats
         t, s = q.shape[0], k.shape[0]
-        q = q.view(t, self.heads, self.head_dim).transpose(0, 1)
-        k = k.view(s, -1, self.head_dim).transpose(0, 1)
-        v = v.view(s, -1, self.head_dim).transpose(0, 1)
-        if k.shape[0] != self.heads:
-            rep = self.heads // k.shape[0]
-            k, v = k.repeat_interleave(rep, 0), v.repeat_interleave(rep, 0)
-        return F.scaled_dot_product_attention(q, k, v).transpose(0, 1).reshape(t, self.hidden)
+        q = q.view(1, t, self.heads, self.head_dim).transpose(1, 2)
+        k = k.view(1, s, -1, self.head_dim).transpose(1, 2)
+        v = v.view(1, s, -1, self.head_dim).transpose(1, 2)
+        out = F.scaled_dot_product_attention(q, k, v, enable_gqa=k.shape[1] != self.heads)
+        return out.transpose(1, 2).reshape(t, self.hidden)
 
     def cross_kv(self, ctx):
         return tuple(forward_shared((self.ck, self.cv), ctx))
