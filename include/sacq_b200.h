@@ -124,6 +124,41 @@ SACQ_API int64_t sacq_workspace_counter_bytes(void);
 SACQ_API int sacq_linear_a8(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M, void* y_out,
                    int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Activation function fused into the per-token quantizer (the producer of the MLP's down
+ * projection; the reference fuses this stage for its INT8 path,
+ * int8_swiglu_lookup_fusion_20261028_r1.py:9-21).  One launch, the [M, K] intermediate is
+ * never written:
+ *   SACQ_ACT_SILU_MUL: y = bf16( bf16(silu(a)) * b )      a = gate, b = up projection output
+ *   SACQ_ACT_GELU:     y = bf16( gelu(a) )  (erf form)     b is ignored
+ * followed by sacq_quant_act_fp8's arithmetic on y; the bytes equal quantizing the result of
+ * the separate bf16 tensor operations.  a, b: bf16 [M, pitch] with pitch >= K elements. */
+#define SACQ_ACT_SILU_MUL 0
+#define SACQ_ACT_GELU 1
+SACQ_API int sacq_act_quant_fp8(int kind, const void* a_bf16, int64_t a_pitch, const void* b_bf16, int64_t b_pitch,
+                                int64_t M, int64_t K, void* q_out, float* scale_out, void* stream);
+
+/* sacq_linear_a8 with a residual added in the GEMM epilogue, as the reference's down-projection
+ * epilogue does (int8_ffdown_residual_epilogue_20261028_r2.py:8-24):
+ *   y[m,n] = bf16( bf16( s[m] * sum_k q[m,k] * W[n,k] + bias[n] ) + residual[m,n] )
+ * -- the two bf16 roundings of `linear(x) + residual` evaluated as two tensor operations.
+ * residual: bf16 [M, ldr] (ldr >= N); it must not overlap y_out. */
+SACQ_API int sacq_linear_a8_residual(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M,
+                                     const void* residual, int64_t ldr, void* y_out, int64_t ldy, void* workspace,
+                                     int64_t workspace_bytes, void* stream);
+
+/* Sibling projections that read the same activations (q/k/v, gate/up): the result of
+ * sacq_linear_a8 for every layer, on one set of quantized activations
+ * (int8_shared_padded_activation_20261028_r1.py:44-63 shares the quantized input,
+ * int8_grouped_qkv_aligned_frozen_20261028_r1.py:9-40 and int8_grouped_gateup_20261028_r1.py:7-54
+ * group the GEMMs).  Up to four layers of one geometry (same K, vector_dim, index width,
+ * codebook size and group size, out_features a multiple of 8) on the small-M kernel run as ONE
+ * launch that splits the grid between the layers; anything else runs one launch per layer.
+ * `workspace` must be large enough for the largest sacq_workspace_bytes(layer, M).  Results are
+ * byte-identical to separate sacq_linear_a8 calls. */
+SACQ_API int sacq_linear_a8_multi(const sacq_layer_t* const* layers, int num_layers, const void* q, const float* scale,
+                                  int64_t M, void* const* y_outs, const int64_t* ldys, void* workspace,
+                                  int64_t workspace_bytes, void* stream);
+
 /* Convenience: sacq_quant_act_fp8 + sacq_linear_a8 for a bf16 input (the module's
  * forward(x), SHIM:456-541).  `q_scratch` (M*K bytes) and `scale_scratch` (M floats)
  * are caller-provided device buffers. */

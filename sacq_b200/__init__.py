@@ -7,7 +7,7 @@ does, and fails loudly when the CUDA library has not been built."""
 from .packing import index_bits_for, index_window_bytes, pack_indices, pack_payload, unpack_indices  # noqa: F401
 
 __all__ = [
-    "PrecomputedPackedVectorCodebookLinear", "forward_shared", "quantize_rows", "pack_indices", "unpack_indices",
+    "PrecomputedPackedVectorCodebookLinear", "forward_shared", "linear_a8_multi", "quantize_rows", "act_quantize_rows", "pack_indices", "unpack_indices",
     "pack_payload", "index_bits_for", "index_window_bytes",
 ]
 
@@ -19,6 +19,12 @@ def __getattr__(name):
     if name == "forward_shared":
         from .linear import forward_shared
         return forward_shared
+    if name == "linear_a8_multi":
+        from .linear import linear_a8_multi
+        return linear_a8_multi
+    if name == "act_quantize_rows":
+        from .activation import act_quantize_rows
+        return act_quantize_rows
     if name == "quantize_rows":
         from .activation import quantize_rows
         return quantize_rows

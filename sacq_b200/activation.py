@@ -32,3 +32,35 @@ def quantize_rows(x: torch.Tensor, mode: str = "fp8_e4m3fn", out: torch.Tensor |
             _lib.check(lib.sacq_quant_act_fp8(x.data_ptr(), x.stride(0), m, k, q.data_ptr(), s.data_ptr(),
                                               torch.cuda.current_stream().cuda_stream))
     return (q.view(torch.float8_e4m3fn) if q.dtype == torch.uint8 else q), s
+
+
+def act_quantize_rows(kind: str, a: torch.Tensor, b: torch.Tensor | None = None):
+    """Activation function fused into the per-token quantizer (``sacq_act_quant_fp8``):
+
+    * ``kind='silu_mul'``: the bytes of ``quantize_rows(F.silu(a) * b)`` (gated MLP);
+    * ``kind='gelu'``:     the bytes of ``quantize_rows(F.gelu(a))`` (erf form);
+
+    in one launch, without materialising the ``[M, K]`` intermediate."""
+    kinds = {"silu_mul": 0, "gelu": 1}
+    if kind not in kinds:
+        raise ValueError(f"unknown activation kind {kind!r}")
+    if a.ndim != 2 or a.dtype != torch.bfloat16 or not a.is_cuda:
+        raise TypeError("act_quantize_rows expects 2-D bfloat16 CUDA tensors")
+    if kind == "silu_mul":
+        if b is None or b.shape != a.shape or b.dtype != torch.bfloat16 or b.device != a.device:
+            raise TypeError("silu_mul needs a second bfloat16 tensor of the same shape and device")
+        if b.stride(1) != 1:
+            b = b.contiguous()
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    lib = _lib.load()
+    m, k = a.shape
+    q = torch.empty((m, k), dtype=torch.uint8, device=a.device)
+    s = torch.empty((m, 1), dtype=torch.float32, device=a.device)
+    if m > 0 and k > 0:
+        with torch.cuda.device(a.device):
+            _lib.check(lib.sacq_act_quant_fp8(kinds[kind], a.data_ptr(), a.stride(0),
+                                              b.data_ptr() if kind == "silu_mul" else None,
+                                              b.stride(0) if kind == "silu_mul" else 0, m, k, q.data_ptr(),
+                                              s.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return q.view(torch.float8_e4m3fn), s

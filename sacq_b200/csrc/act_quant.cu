@@ -124,3 +124,112 @@ int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, voi
 }
 
 }  // namespace sacq
+
+// ----------------------------------------------------------------------------
+// Activation function fused into the quantizer.
+//
+// The MLP of a transformer block feeds its down projection with act(gate) * up (gated) or
+// act(x); run as separate tensor operations that is two or three elementwise kernels and a
+// round trip of the [M, K] intermediate before the quantizer reads it again.  Here one launch
+// produces the e4m3 row and its scale directly; the intermediate is never written.  The
+// arithmetic follows the tensor operations it replaces, rounding to bf16 where they do, so the
+// bytes equal quantize_rows(silu(gate) * up) and quantize_rows(gelu(x)) (the reference fuses
+// the same stage for its INT8 path, int8_swiglu_lookup_fusion_20261028_r1.py:9-21).
+// ----------------------------------------------------------------------------
+namespace sacq {
+
+namespace {
+
+__device__ __forceinline__ float round_bf16(float v) { return bf16_bits_to_float(float_to_bf16_bits(v)); }
+
+// KIND 0: bf16(bf16(silu(a)) * b); KIND 1: bf16(gelu(a)), erf form.
+template <int KIND>
+__device__ __forceinline__ float act_value(float a, float b) {
+  if constexpr (KIND == 0) {
+    const float s = round_bf16(a / (1.0f + expf(-a)));
+    return round_bf16(s * b);
+  } else {
+    return round_bf16(a * 0.5f * (1.0f + erff(a * 0.70710678118654752440f)));
+  }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreads)
+act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint16_t* __restrict__ b, int64_t b_pitch,
+                     int64_t K, uint8_t* __restrict__ q, float* __restrict__ scale_out) {
+  extern __shared__ uint16_t yrow[];                  // the row's bf16 values, kept on chip between the passes
+  __shared__ float red[kThreads / 32];
+  __shared__ float s_scale;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int64_t m = blockIdx.x;
+  const uint16_t* arow = a + m * a_pitch;
+  const uint16_t* brow = KIND == 0 ? b + m * b_pitch : nullptr;
+  float mx = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += kThreads) {
+    const float av = bf16_bits_to_float(__ldg(arow + k));
+    const float bv = KIND == 0 ? bf16_bits_to_float(__ldg(brow + k)) : 0.f;
+    const float y = act_value<KIND>(av, bv);
+    yrow[k] = float_to_bf16_bits(y);
+    mx = fmaxf(mx, fabsf(y));
+  }
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < kThreads / 32 ? red[threadIdx.x] : 0.f;
+    v = warp_max(v);
+    if (threadIdx.x == 0) {
+      const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
+      s_scale = s;
+      scale_out[m] = s;
+    }
+  }
+  __syncthreads();
+  const float s = s_scale;
+  uint8_t* qrow = q + m * K;
+  for (int64_t k2 = 2 * (int64_t)threadIdx.x; k2 < K; k2 += 2 * kThreads) {
+    const float y0 = bf16_bits_to_float(yrow[k2]);
+    const float y1 = k2 + 1 < K ? bf16_bits_to_float(yrow[k2 + 1]) : 0.f;
+    const uint32_t pair = float2_to_e4m3x2(clamp448(__fdiv_rn(y0, s)), clamp448(__fdiv_rn(y1, s)));
+    if (k2 + 1 < K && (reinterpret_cast<uintptr_t>(qrow + k2) & 1) == 0)
+      *reinterpret_cast<uint16_t*>(qrow + k2) = (uint16_t)pair;
+    else {
+      qrow[k2] = (uint8_t)(pair & 0xff);
+      if (k2 + 1 < K) qrow[k2 + 1] = (uint8_t)(pair >> 8);
+    }
+  }
+}
+
+}  // namespace
+
+int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, int64_t M, int64_t K,
+                         void* q, float* scale, cudaStream_t s) {
+  if (M == 0 || K == 0) return SACQ_OK;
+  if (M > 2147483647LL) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
+  const size_t smem = (size_t)K * sizeof(uint16_t);
+  if (smem > 200 * 1024) return set_error(SACQ_ERR_UNSUPPORTED, "K=%lld: a row does not fit shared memory", (long long)K);
+  static bool configured[2][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int ki = kind == 0 ? 0 : 1;
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[ki][dev])) {
+    const cudaError_t e = ki == 0 ? cudaFuncSetAttribute(act_quant_fp8_kernel<0>,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                                  : cudaFuncSetAttribute(act_quant_fp8_kernel<1>,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+    if (dev >= 0 && dev < 64) configured[ki][dev] = true;
+  }
+  if (ki == 0)
+    act_quant_fp8_kernel<0><<<(unsigned)M, kThreads, smem, s>>>(static_cast<const uint16_t*>(a), a_pitch,
+                                                               static_cast<const uint16_t*>(b), b_pitch, K,
+                                                               static_cast<uint8_t*>(q), scale);
+  else
+    act_quant_fp8_kernel<1><<<(unsigned)M, kThreads, smem, s>>>(static_cast<const uint16_t*>(a), a_pitch, nullptr, 0, K,
+                                                               static_cast<uint8_t*>(q), scale);
+  count_launch();
+  SACQ_CUDA_TRY(cudaGetLastError());
+  return SACQ_OK;
+}
+
+}  // namespace sacq

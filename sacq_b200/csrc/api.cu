@@ -225,6 +225,22 @@ SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, 
   return launch_quant_act_fp8(x_bf16, x_pitch, M, K, q_out, scale_out, static_cast<cudaStream_t>(stream));
 }
 
+SACQ_API int sacq_act_quant_fp8(int kind, const void* a_bf16, int64_t a_pitch, const void* b_bf16, int64_t b_pitch,
+                                int64_t M, int64_t K, void* q_out, float* scale_out, void* stream) {
+  if (kind != SACQ_ACT_SILU_MUL && kind != SACQ_ACT_GELU)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "unknown activation kind %d", kind);
+  if (M < 0 || K < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "negative size (M=%lld K=%lld)", (long long)M,
+                                       (long long)K);
+  if (M == 0) return SACQ_OK;
+  if (K == 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "K must be positive");
+  if (a_bf16 == nullptr || q_out == nullptr || scale_out == nullptr || (kind == SACQ_ACT_SILU_MUL && b_bf16 == nullptr))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (a_pitch < K || (kind == SACQ_ACT_SILU_MUL && b_pitch < K))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "row pitch smaller than K=%lld", (long long)K);
+  return launch_act_quant_fp8(kind, a_bf16, a_pitch, b_bf16, b_pitch, M, K, q_out, scale_out,
+                              static_cast<cudaStream_t>(stream));
+}
+
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
   if (which < 0 || which > 7) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..7", which);
@@ -246,8 +262,10 @@ SACQ_API int64_t sacq_workspace_bytes(const sacq_layer_t* L, int64_t M) {
   return small_m_workspace_bytes(L, M < slab ? M : slab);
 }
 
-SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,
-                   void* workspace, int64_t workspace_bytes, void* stream) {
+namespace {
+// Common body of sacq_linear_a8 and sacq_linear_a8_residual.
+int linear_a8_impl(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, const void* residual,
+                   int64_t ldr, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream) {
   if (int rc = check_layer(L)) return rc;
   if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
   if (M == 0 || L->d.out_features == 0) return SACQ_OK;
@@ -256,23 +274,78 @@ SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* s
   if (ldy < L->d.out_features)
     return set_error(SACQ_ERR_INVALID_ARGUMENT, "ldy=%lld smaller than out_features=%lld", (long long)ldy,
                      (long long)L->d.out_features);
+  if (residual != nullptr && ldr < L->d.out_features)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "ldr=%lld smaller than out_features=%lld", (long long)ldr,
+                     (long long)L->d.out_features);
   DeviceGuard guard(L->d.device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int k = pick_kernel(L, M);
   if (k < 0) return set_error(k, "no kernel can run this layer geometry");
-  if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s);
+  if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s, residual, ldr);
   if (k == 3) {
     if (workspace == nullptr || workspace_bytes < kCounterBytes)
       return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
                        (long long)sacq_workspace_bytes(L, M), (long long)workspace_bytes);
     return launch_large_m_grouped(L, q, scale, M, y_out, ldy, static_cast<uint8_t*>(workspace) + kCounterBytes,
-                                  workspace_bytes - kCounterBytes, s);
+                                  workspace_bytes - kCounterBytes, s, residual, ldr);
   }
   const int64_t slab = small_m_slab_rows(L);
   for (int64_t m0 = 0; m0 < M; m0 += slab) {
     const int64_t rows = (M - m0) < slab ? (M - m0) : slab;
     const int rc = launch_small_m(L, static_cast<const uint8_t*>(q) + m0 * L->d.in_features, scale + m0, rows,
-                                  static_cast<uint16_t*>(y_out) + m0 * ldy, ldy, workspace, workspace_bytes, s);
+                                  static_cast<uint16_t*>(y_out) + m0 * ldy, ldy, workspace, workspace_bytes, s,
+                                  residual ? static_cast<const uint16_t*>(residual) + m0 * ldr : nullptr, ldr);
+    if (rc != SACQ_OK) return rc;
+  }
+  return SACQ_OK;
+}
+}  // namespace
+
+SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,
+                   void* workspace, int64_t workspace_bytes, void* stream) {
+  return linear_a8_impl(L, q, scale, M, nullptr, 0, y_out, ldy, workspace, workspace_bytes, stream);
+}
+
+SACQ_API int sacq_linear_a8_residual(const sacq_layer_t* L, const void* q, const float* scale, int64_t M,
+                                     const void* residual, int64_t ldr, void* y_out, int64_t ldy, void* workspace,
+                                     int64_t workspace_bytes, void* stream) {
+  if (residual == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "residual is null");
+  return linear_a8_impl(L, q, scale, M, residual, ldr, y_out, ldy, workspace, workspace_bytes, stream);
+}
+
+SACQ_API int sacq_linear_a8_multi(const sacq_layer_t* const* layers, int num_layers, const void* q, const float* scale,
+                                  int64_t M, void* const* y_outs, const int64_t* ldys, void* workspace,
+                                  int64_t workspace_bytes, void* stream) {
+  if (layers == nullptr || y_outs == nullptr || ldys == nullptr || num_layers <= 0)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument or no layers");
+  for (int l = 0; l < num_layers; ++l) {
+    if (int rc = check_layer(layers[l])) return rc;
+    if (layers[l]->d.in_features != layers[0]->d.in_features)
+      return set_error(SACQ_ERR_INVALID_ARGUMENT, "layers that share an input must have the same in_features");
+    if (layers[l]->d.device != layers[0]->d.device)
+      return set_error(SACQ_ERR_INVALID_ARGUMENT, "layers that share an input must be on one device");
+    if (y_outs[l] == nullptr && layers[l]->d.out_features > 0 && M > 0)
+      return set_error(SACQ_ERR_INVALID_ARGUMENT, "null output for layer %d", l);
+    if (ldys[l] < layers[l]->d.out_features)
+      return set_error(SACQ_ERR_INVALID_ARGUMENT, "ldy=%lld smaller than out_features=%lld", (long long)ldys[l],
+                       (long long)layers[l]->d.out_features);
+  }
+  if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
+  if (M == 0) return SACQ_OK;
+  if (q == nullptr || scale == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  {
+    // one launch when every layer would use the staged small-M kernel on a common geometry
+    bool small = num_layers >= 2;
+    for (int l = 0; l < num_layers && small; ++l) small = pick_kernel(layers[l], M) == 1;
+    if (small) {
+      DeviceGuard guard(layers[0]->d.device);
+      const int rc = launch_small_m_multi(layers, num_layers, q, scale, M, y_outs, ldys,
+                                          static_cast<cudaStream_t>(stream));
+      if (rc != SACQ_ERR_UNSUPPORTED) return rc;
+    }
+  }
+  for (int l = 0; l < num_layers; ++l) {
+    const int rc = sacq_linear_a8(layers[l], q, scale, M, y_outs[l], ldys[l], workspace, workspace_bytes, stream);
     if (rc != SACQ_OK) return rc;
   }
   return SACQ_OK;

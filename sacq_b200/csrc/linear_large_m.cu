@@ -90,6 +90,8 @@ struct LargeMParams {
   const uint16_t* bias;         // bf16 [N] or null
   const float* act_scale;       // [M]
   uint16_t* y;                  // bf16 [M, ldy]
+  const uint16_t* residual;     // bf16 [M, ldr] added to the rounded output, or null
+  int64_t ldr;
   int* status;
   int64_t ldy;
   int M, N, K, C;
@@ -317,6 +319,14 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + c0), r);
           if (m < p.M) {
             uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
+            const uint16_t* rrow = p.residual ? p.residual + (int64_t)m * p.ldr + n0 + c0 : nullptr;
+            // bf16(v), or bf16(bf16(v) + residual): the two roundings of `linear(x) + residual`
+            auto fin = [&](float v, int c) -> uint32_t {
+              uint16_t o = float_to_bf16_bits(v);
+              if (rrow != nullptr)
+                o = float_to_bf16_bits(__fadd_rn(bf16_bits_to_float(o), bf16_bits_to_float(__ldg(rrow + c))));
+              return (uint32_t)o;
+            };
             const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
             if (vec) {
 #pragma unroll
@@ -327,7 +337,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   const int c = v * 8 + 2 * j;
                   const float y0 = fmaf(sa, __uint_as_float(r[c]) * swp[c0 + c], bp[c0 + c]);
                   const float y1 = fmaf(sa, __uint_as_float(r[c + 1]) * swp[c0 + c + 1], bp[c0 + c + 1]);
-                  o[j] = (uint32_t)float_to_bf16_bits(y0) | ((uint32_t)float_to_bf16_bits(y1) << 16);
+                  o[j] = fin(y0, c) | (fin(y1, c + 1) << 16);
                 }
                 *reinterpret_cast<uint4*>(yrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
               }
@@ -335,7 +345,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
               for (int c = 0; c < 32; ++c)
                 if (n0 + c0 + c < p.N)
-                  yrow[c] = float_to_bf16_bits(fmaf(sa, __uint_as_float(r[c]) * swp[c0 + c], bp[c0 + c]));
+                  yrow[c] = (uint16_t)fin(fmaf(sa, __uint_as_float(r[c]) * swp[c0 + c], bp[c0 + c]), c);
             }
           }
         }
@@ -447,7 +457,7 @@ void large_m_release(sacq_layer* L) {
 }
 
 int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                   cudaStream_t s) {
+                   cudaStream_t s, const void* residual, int64_t ldr) {
   const sacq_layer_desc& d = L->d;
   if (!large_m_supported(L)) return set_error(SACQ_ERR_UNSUPPORTED, "large-M kernel cannot run this layer geometry");
   if (M <= 0 || d.out_features == 0) return SACQ_OK;
@@ -496,6 +506,8 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
   p.y = static_cast<uint16_t*>(y);
   p.status = L->d_status;
   p.ldy = ldy;
+  p.residual = static_cast<const uint16_t*>(residual);
+  p.ldr = ldr;
   p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features; p.C = d.codebook_size;
   p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
   // Two M sub-tiles per CTA as soon as the halved grid still covers every SM.

@@ -44,6 +44,8 @@ struct GroupedParams {
   const float* act_scale;       // [M]
   const float* xsum;            // [M] sum_k q[m,k] (read only when shift != 0)
   uint16_t* y;                  // bf16 [M, ldy]
+  const uint16_t* residual;     // bf16 [M, ldr] added to the rounded output, or null
+  int64_t ldr;
   int* status;
   int64_t ldy;
   int M, N, K, C;
@@ -329,6 +331,14 @@ large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + c0), r);
           if (m < p.M) {
             uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
+            const uint16_t* rrow = p.residual ? p.residual + (int64_t)m * p.ldr + n0 + c0 : nullptr;
+            // bf16(v), or bf16(bf16(v) + residual): the two roundings of `linear(x) + residual`
+            auto fin = [&](float v, int c) -> uint32_t {
+              uint16_t o = float_to_bf16_bits(v);
+              if (rrow != nullptr)
+                o = float_to_bf16_bits(__fadd_rn(bf16_bits_to_float(o), bf16_bits_to_float(__ldg(rrow + c))));
+              return (uint32_t)o;
+            };
             const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
             if (vec) {
 #pragma unroll
@@ -339,7 +349,7 @@ large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                   const int c = v * 8 + 2 * j;
                   const float y0 = fmaf(sa, fmaf(__uint_as_float(r[c]), p.out_mul, add), bp[c0 + c]);
                   const float y1 = fmaf(sa, fmaf(__uint_as_float(r[c + 1]), p.out_mul, add), bp[c0 + c + 1]);
-                  o[j] = (uint32_t)float_to_bf16_bits(y0) | ((uint32_t)float_to_bf16_bits(y1) << 16);
+                  o[j] = fin(y0, c) | (fin(y1, c + 1) << 16);
                 }
                 *reinterpret_cast<uint4*>(yrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
               }
@@ -347,7 +357,7 @@ large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
               for (int c = 0; c < 32; ++c)
                 if (n0 + c0 + c < p.N)
-                  yrow[c] = float_to_bf16_bits(fmaf(sa, fmaf(__uint_as_float(r[c]), p.out_mul, add), bp[c0 + c]));
+                  yrow[c] = (uint16_t)fin(fmaf(sa, fmaf(__uint_as_float(r[c]), p.out_mul, add), bp[c0 + c]), c);
             }
           }
         }
@@ -433,7 +443,7 @@ int64_t large_m_grouped_workspace_bytes(const sacq_layer* L, int64_t M) {
 }
 
 int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                           void* ws, int64_t ws_bytes, cudaStream_t s) {
+                           void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr) {
   const sacq_layer_desc& d = L->d;
   if (!large_m_grouped_supported(L))
     return set_error(SACQ_ERR_UNSUPPORTED, "grouped tensor-core kernel cannot run this layer geometry");
@@ -493,6 +503,8 @@ int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scal
     if (rc != SACQ_OK) return rc;
     p.act_scale = scale + m0;
     p.y = static_cast<uint16_t*>(y) + m0 * ldy;
+    p.residual = residual ? static_cast<const uint16_t*>(residual) + m0 * ldr : nullptr;
+    p.ldr = ldr;
     p.M = (int)rows;
     const dim3 grid((unsigned)((N + bn - 1) / bn), (unsigned)m_tiles);
     p.kbs = grouped_kbs_for(L, bn, mt);

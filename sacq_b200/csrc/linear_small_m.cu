@@ -66,7 +66,7 @@ __device__ __forceinline__ void finish_rows(const SmallMParams& p, int chunk, in
   for (int m = 0; m < MT; ++m) {
     if (m0 + m < p.M) {
       const float sa = __ldg(p.act_scale + m0 + m);
-      p.y[(int64_t)(m0 + m) * p.ldy + n] = float_to_bf16_bits(fmaf(sa, val[m], b));
+      store_out(p, m0 + m, n, fmaf(sa, val[m], b));
     }
   }
 }
@@ -382,7 +382,9 @@ bool plan_unpacked(const sacq_layer* L, Plan& pl) {
 // M from which the warp-MMA variant is preferred over the CUDA-core one.
 constexpr int64_t kMmaMinM = 1;
 
-Plan make_plan(const sacq_layer* L, int64_t M) {
+// halves_req: 0 = free choice of the tile height; 2 / 1 = only tile heights whose staged kernel
+// runs two / one warp per span (the summation order of an output depends on that, not on N).
+Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
   const sacq_layer_desc& d = L->d;
   Plan pl{};
   pl.fast = fast_eligible(L);
@@ -426,6 +428,7 @@ Plan make_plan(const sacq_layer* L, int64_t M) {
     bool best_staged = false;
     double best_cost = -1.0;
     for (int r8 = 1; r8 <= 4; r8 *= 2) {
+      if ((halves_req == 2 && r8 > 2) || (halves_req == 1 && r8 <= 2)) continue;
       const int64_t row_tiles = (sub + r8 - 1) / r8;
       // staged kernel: a CTA walks row tiles and, inside each, all token chunks; the fixed
       // start-up (launch, codebook copy) is paid once.  Unit = one sub-block of one span set.
@@ -540,26 +543,10 @@ int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M) {
   return bytes;
 }
 
-int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                   void* ws, int64_t ws_bytes, cudaStream_t s) {
+namespace {
+SmallMParams fill_params(const sacq_layer* L, const Plan& pl, const void* q, const float* scale, int64_t M, void* y,
+                         int64_t ldy, void* ws) {
   const sacq_layer_desc& d = L->d;
-  if (M == 0 || d.out_features == 0) return SACQ_OK;
-  if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
-  const Plan pl = make_plan(L, M);
-  if (L->force_kernel == 6 && !pl.unpacked)
-    return set_error(SACQ_ERR_UNSUPPORTED, "index-unpacking warp-MMA variant cannot run this layer");
-  if (pl.smem > kSmemBudget)
-    return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel needs %zu bytes of shared memory", pl.smem);
-  const int64_t need = small_m_workspace_bytes(L, M);
-  if (pl.num_sg > 1 && (int64_t)pl.chunks * pl.row_blocks * (int64_t)sizeof(int) > sacq_workspace_counter_bytes())
-    return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: %d x %d row-block counters exceed the counter region",
-                     pl.chunks, pl.row_blocks);
-  if (pl.num_sg > 1 && (ws == nullptr || ws_bytes < need))
-    return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given", (long long)need,
-                     (long long)ws_bytes);
-  if (pl.num_sg > 1 && reinterpret_cast<uintptr_t>(ws) % 16 != 0)
-    return set_error(SACQ_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
-
   SmallMParams p{};
   p.packed = static_cast<const uint8_t*>(d.packed);
   p.cb_f16 = L->cb_f16;
@@ -583,9 +570,36 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   p.span_idx = pl.span_idx; p.spans_per_row = pl.spans_per_row; p.spans_per_item = pl.spans_per_item;
   p.num_sg = pl.num_sg; p.row_blocks = pl.row_blocks; p.chunks = pl.chunks; p.num_items = pl.num_items;
   p.act_bufs = pl.act_bufs > 0 ? pl.act_bufs : 1;
-  uint32_t sb = (uint32_t)d.shift_bf16 << 16;
+  const uint32_t sb = (uint32_t)d.shift_bf16 << 16;
   memcpy(&p.shift, &sb, sizeof(float));
+  p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
+  return p;
+}
+}  // namespace
 
+int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                   void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr) {
+  const sacq_layer_desc& d = L->d;
+  if (M == 0 || d.out_features == 0) return SACQ_OK;
+  if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
+  const Plan pl = make_plan(L, M);
+  if (L->force_kernel == 6 && !pl.unpacked)
+    return set_error(SACQ_ERR_UNSUPPORTED, "index-unpacking warp-MMA variant cannot run this layer");
+  if (pl.smem > kSmemBudget)
+    return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel needs %zu bytes of shared memory", pl.smem);
+  const int64_t need = small_m_workspace_bytes(L, M);
+  if (pl.num_sg > 1 && (int64_t)pl.chunks * pl.row_blocks * (int64_t)sizeof(int) > sacq_workspace_counter_bytes())
+    return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: %d x %d row-block counters exceed the counter region",
+                     pl.chunks, pl.row_blocks);
+  if (pl.num_sg > 1 && (ws == nullptr || ws_bytes < need))
+    return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given", (long long)need,
+                     (long long)ws_bytes);
+  if (pl.num_sg > 1 && reinterpret_cast<uintptr_t>(ws) % 16 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
+
+  SmallMParams p = fill_params(L, pl, q, scale, M, y, ldy, ws);
+  p.residual = static_cast<const uint16_t*>(residual);
+  p.ldr = ldr;
   cudaError_t e;
   if (pl.unpacked) {
     if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
@@ -612,6 +626,105 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   }
   count_launch();
   if (e != cudaSuccess) return cuda_fail(e, "small-M launch");
+  return SACQ_OK;
+}
+
+
+// Several layers on the same quantized activations in one launch of the staged warp-MMA
+// kernel.  Returns SACQ_ERR_UNSUPPORTED (and launches nothing) when the layers do not share a
+// geometry that kernel can run; the caller then falls back to one launch per layer.
+int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
+                         void* const* ys, const int64_t* ldys, cudaStream_t s) {
+  if (n < 2 || n > kMaxMulti || M <= 0 || M > (1 << 20)) return SACQ_ERR_UNSUPPORTED;
+  const sacq_layer* L0 = layers[0];
+  int64_t n_total = 0;
+  for (int l = 0; l < n; ++l) {
+    const sacq_layer_desc& a = layers[l]->d;
+    const sacq_layer_desc& b = L0->d;
+    if (a.in_features != b.in_features || a.vector_dim != b.vector_dim || a.index_bits != b.index_bits ||
+        a.codebook_size != b.codebook_size || a.group_size != b.group_size || a.device != b.device ||
+        layers[l]->force_kernel != 0 || a.out_features <= 0 || a.out_features % 8 != 0)
+      return SACQ_ERR_UNSUPPORTED;
+    n_total += a.out_features;
+  }
+  if (reinterpret_cast<uintptr_t>(q) % 16 != 0) return SACQ_ERR_UNSUPPORTED;
+  // Every layer alone must be on the staged kernel with the same warps-per-span class: the
+  // order in which an output's partial sums are added depends on it, and the results of
+  // the shared launch are to be byte-identical to separate launches.
+  int halves = 0;
+  for (int l = 0; l < n; ++l) {
+    const Plan one = make_plan(layers[l], M);
+    if (!one.mma || !one.staged || one.unpacked) return SACQ_ERR_UNSUPPORTED;
+    const int h = one.r8 <= 2 ? 2 : 1;
+    if (halves != 0 && h != halves) return SACQ_ERR_UNSUPPORTED;
+    halves = h;
+  }
+  // plan for the concatenation of the layers' rows: tile height and CTA count
+  sacq_layer virt = *L0;
+  virt.d.out_features = n_total;
+  Plan pl = make_plan(&virt, M, halves);
+  if (!pl.mma || !pl.staged || pl.unpacked || pl.smem > kSmemBudget || (pl.r8 <= 2 ? 2 : 1) != halves)
+    return SACQ_ERR_UNSUPPORTED;
+  const int rows_per_tile = 8 * pl.r8;
+  int rb[kMaxMulti], stride[kMaxMulti];
+  int64_t rb_total = 0;
+  for (int l = 0; l < n; ++l) {
+    rb[l] = (int)((layers[l]->d.out_features + rows_per_tile - 1) / rows_per_tile);
+    rb_total += rb[l];
+  }
+  int64_t stride_total = L0->num_sms / pl.chunks;
+  if (stride_total < n) return SACQ_ERR_UNSUPPORTED;            // fewer CTA groups than layers
+  if (stride_total > rb_total) stride_total = rb_total;
+  int64_t used = 0;
+  for (int l = 0; l < n; ++l) {
+    int64_t v = stride_total * rb[l] / rb_total;
+    if (v < 1) v = 1;
+    if (v > rb[l]) v = rb[l];
+    stride[l] = (int)v;
+    used += v;
+  }
+  while (used > stride_total) {                                  // rounding up of small layers: take from the best served
+    int best = -1;
+    for (int l = 0; l < n; ++l)
+      if (stride[l] > 1 && (best < 0 || (double)rb[l] / stride[l] < (double)rb[best] / stride[best])) best = l;
+    if (best < 0) return SACQ_ERR_UNSUPPORTED;
+    --stride[best];
+    --used;
+  }
+  while (used < stride_total) {                                  // spare CTA groups go to the layer with the longest walk
+    int best = -1;
+    for (int l = 0; l < n; ++l)
+      if (stride[l] < rb[l] && (best < 0 || (double)rb[l] / stride[l] > (double)rb[best] / stride[best])) best = l;
+    if (best < 0) break;
+    ++stride[best];
+    ++used;
+  }
+  MultiParams g{};
+  g.base = fill_params(L0, pl, q, scale, M, ys[0], ldys[0], nullptr);
+  g.n_layers = n;
+  int cta = 0;
+  for (int l = 0; l < n; ++l) {
+    const sacq_layer* L = layers[l];
+    g.cta_begin[l] = cta;
+    cta += stride[l] * pl.chunks;
+    g.packed[l] = static_cast<const uint8_t*>(L->d.packed);
+    g.cb_hilo[l] = L->cb_hilo;
+    g.scales[l] = static_cast<const uint16_t*>(L->d.scales);
+    g.bias[l] = static_cast<const uint16_t*>(L->d.bias);
+    g.status[l] = L->d_status;
+    g.y[l] = static_cast<uint16_t*>(ys[l]);
+    g.ldy[l] = ldys[l];
+    g.N[l] = (int)L->d.out_features;
+    g.row_blocks[l] = rb[l];
+    g.out_mul[l] = ldexpf(1.f, -L->cb8_exp_shift);
+    const uint32_t sb = (uint32_t)L->d.shift_bf16 << 16;
+    memcpy(&g.shift[l], &sb, sizeof(float));
+  }
+  g.cta_begin[n] = cta;
+  pl.grid = cta;
+  const cudaError_t e = launch_small_m_mma_multi(pl, g, s);
+  count_launch();
+  if (e != cudaSuccess) return cuda_fail(e, "small-M multi-layer launch");
   return SACQ_OK;
 }
 }  // namespace sacq

@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const Sm
       const int n = cur_n_base + r * 8 + 2 * (ln & 3) + (j & 1);
       if (m < p.M && n < p.N) {
         const float b = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
-        p.y[(int64_t)m * p.ldy + n] = float_to_bf16_bits(fmaf(__ldg(p.act_scale + m), v, b));
+        store_out(p, m, n, fmaf(__ldg(p.act_scale + m), v, b));
       }
     }
     __syncthreads();                           // red is reused by the next tile
@@ -306,8 +306,9 @@ __device__ __forceinline__ void mma_m16n8k32_e4m3(float (&c)[4], uint32_t a0, ui
 
 // HALVES = warps sharing one 32-index span (each takes 8/HALVES of its MMA steps): with
 // two, a CTA runs up to 16 lighter warps, which hides more of the gather -> MMA latency.
+// `cta` of `ncta` CTAs work on the layer described by p (a launch may cover several layers).
 template <int D, int BITS, int R8, int HALVES>
-__global__ void __launch_bounds__(kMaxWarps * 32 * HALVES, 1) small_m_mma_staged_kernel(const SmallMParams p) {
+__device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta, const int ncta) {
   constexpr int NS = 8 / HALVES;           // MMA steps (vectors per lane) of one work item
   constexpr int NQ = NS * D / 16;          // uint4 loads covering them per token row
   extern __shared__ __align__(128) uint8_t smem[];
@@ -369,9 +370,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32 * HALVES, 1) small_m_mma_staged
   // This CTA's share: one token chunk (fixed for the CTA's lifetime, so its activation
   // tile is copied once) and the row tiles rt_first, rt_first + rt_stride, ...  The host
   // makes gridDim.x a multiple of the chunk count.
-  const int chunk = blockIdx.x % p.chunks;
-  const int first_rt = blockIdx.x / p.chunks;
-  const int rt_stride = gridDim.x / p.chunks;
+  const int chunk = cta % p.chunks;
+  const int first_rt = cta / p.chunks;
+  const int rt_stride = ncta / p.chunks;
   const int m_base = chunk * 16;
   const int toks_here = min(16, p.M - m_base);
   uint8_t* act_s = act_base;
@@ -569,7 +570,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32 * HALVES, 1) small_m_mma_staged
       const int ml = (ln >> 2) + ((j & 2) ? 8 : 0);
       const int n = n_base + r * 8 + 2 * (ln & 3) + (j & 1);
       if (ml < toks_here && n < p.N) {
-        p.y[(int64_t)(m_base + ml) * p.ldy + n] = float_to_bf16_bits(fmaf(sa_s[ml], v, rowb_s[n - n_base]));
+        store_out(p, m_base + ml, n, fmaf(sa_s[ml], v, rowb_s[n - n_base]));
       }
     }
     __syncthreads();                                   // red and the row constants are reused next
@@ -583,12 +584,71 @@ __global__ void __launch_bounds__(kMaxWarps * 32 * HALVES, 1) small_m_mma_staged
   }
 }
 
+template <int D, int BITS, int R8, int HALVES>
+__global__ void __launch_bounds__(kMaxWarps * 32 * HALVES, 1) small_m_mma_staged_kernel(const SmallMParams p) {
+  staged_body<D, BITS, R8, HALVES>(p, (int)blockIdx.x, (int)gridDim.x);
+}
+
+// Several layers that read the same quantized activations (q/k/v, gate/up) in one launch:
+// CTAs [cta_begin[l], cta_begin[l+1]) work on layer l.  Same geometry (K, d, index width,
+// codebook size, grouping) for all layers; only the per-layer buffers and N differ.
+template <int D, int BITS, int R8, int HALVES>
+__global__ void __launch_bounds__(kMaxWarps * 32 * HALVES, 1) small_m_mma_staged_multi_kernel(const MultiParams g) {
+  int l = 0;
+  while (l + 1 < g.n_layers && (int)blockIdx.x >= g.cta_begin[l + 1]) ++l;
+  SmallMParams p = g.base;
+  p.packed = g.packed[l];
+  p.cb_hilo = g.cb_hilo[l];
+  p.scales = g.scales[l];
+  p.bias = g.bias[l];
+  p.status = g.status[l];
+  p.y = g.y[l];
+  p.ldy = g.ldy[l];
+  p.N = g.N[l];
+  p.row_blocks = g.row_blocks[l];
+  p.out_mul = g.out_mul[l];
+  p.shift = g.shift[l];
+  staged_body<D, BITS, R8, HALVES>(p, (int)blockIdx.x - g.cta_begin[l], g.cta_begin[l + 1] - g.cta_begin[l]);
+}
+
 template <int D, int BITS>
 cudaError_t launch_staged(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
   switch (pl.r8) {
     case 1: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 1, 2>>(pl, p, s);
     case 2: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 2, 2>>(pl, p, s);
     default: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 4, 1>>(pl, p, s);
+  }
+}
+
+template <auto Kern>
+cudaError_t launch_multi_kernel(const Plan& pl, const MultiParams& g, cudaStream_t s) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)pl.grid);
+  cfg.blockDim = dim3((unsigned)(pl.warps * 32));
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, Kern, g);
+}
+
+template <int D, int BITS>
+cudaError_t launch_staged_multi(const Plan& pl, const MultiParams& g, cudaStream_t s) {
+  switch (pl.r8) {
+    case 1: return launch_multi_kernel<small_m_mma_staged_multi_kernel<D, BITS, 1, 2>>(pl, g, s);
+    case 2: return launch_multi_kernel<small_m_mma_staged_multi_kernel<D, BITS, 2, 2>>(pl, g, s);
+    default: return launch_multi_kernel<small_m_mma_staged_multi_kernel<D, BITS, 4, 1>>(pl, g, s);
   }
 }
 
@@ -610,6 +670,17 @@ cudaError_t launch_cb(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
 
 size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps, int act_bufs) {
   return staged_layout(C, D, K, row_bytes, r8, warps, act_bufs).total;
+}
+
+cudaError_t launch_small_m_mma_multi(const Plan& pl, const MultiParams& g, cudaStream_t s) {
+  if (!pl.staged) return cudaErrorInvalidValue;
+  if (pl.D == 8 && pl.BITS == 12) return launch_staged_multi<8, 12>(pl, g, s);
+  if (pl.D == 8 && pl.BITS == 8) return launch_staged_multi<8, 8>(pl, g, s);
+  if (pl.D == 8 && pl.BITS == 16) return launch_staged_multi<8, 16>(pl, g, s);
+  if (pl.D == 4 && pl.BITS == 12) return launch_staged_multi<4, 12>(pl, g, s);
+  if (pl.D == 4 && pl.BITS == 8) return launch_staged_multi<4, 8>(pl, g, s);
+  if (pl.D == 4 && pl.BITS == 16) return launch_staged_multi<4, 16>(pl, g, s);
+  return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s) {

@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(kMaxWarpsU * 32, 1) small_m_mma_unpacked_kerne
       const int ml = (ln >> 2) + ((j & 2) ? 8 : 0);
       const int nl = r * 8 + 2 * (ln & 3) + (j & 1);
       if (ml < toks_here && n_base + nl < p.N)
-        p.y[(int64_t)(m_base + ml) * p.ldy + n_base + nl] = float_to_bf16_bits(fmaf(sa_s[ml], v, rowb_s[nl]));
+        store_out(p, m_base + ml, n_base + nl, fmaf(sa_s[ml], v, rowb_s[nl]));
     }
     __syncthreads();                                                  // red, indices and row constants are reused
   }

@@ -25,6 +25,8 @@ struct SmallMParams {
   int* status;                 // layer status word (bounded waits report here)
   const float* act_scale;      // [M]
   uint16_t* y;                 // bf16 [M, ldy]
+  const uint16_t* residual;    // bf16 [M, ldr] added to the rounded output, or null
+  int64_t ldr;
   float* partial;              // [num_sg][M][N] (only when num_sg > 1)
   int* counters;               // [chunks * row_blocks]
   int64_t ldy;
@@ -45,6 +47,35 @@ struct SmallMParams {
   float out_mul;               // 2^-cb_exp_shift (fast) or 1 (generic)
   float shift;
 };
+
+// Up to four layers sharing one set of quantized activations in a single launch of the staged
+// warp-MMA kernel.  `base` carries everything the layers have in common.
+constexpr int kMaxMulti = 4;
+struct MultiParams {
+  SmallMParams base;
+  int n_layers;
+  int cta_begin[kMaxMulti + 1];
+  const uint8_t* packed[kMaxMulti];
+  const uint8_t* cb_hilo[kMaxMulti];
+  const uint16_t* scales[kMaxMulti];
+  const uint16_t* bias[kMaxMulti];
+  int* status[kMaxMulti];
+  uint16_t* y[kMaxMulti];
+  int64_t ldy[kMaxMulti];
+  int N[kMaxMulti];
+  int row_blocks[kMaxMulti];
+  float out_mul[kMaxMulti];
+  float shift[kMaxMulti];
+};
+
+// Output store shared by every small-M variant: y = bf16(v), or bf16(bf16(v) + residual) --
+// the two roundings of `linear(x) + residual` computed as two bf16 tensor operations.
+__device__ __forceinline__ void store_out(const SmallMParams& p, int64_t m, int64_t n, float v) {
+  uint16_t o = float_to_bf16_bits(v);
+  if (p.residual != nullptr)
+    o = float_to_bf16_bits(__fadd_rn(bf16_bits_to_float(o), bf16_bits_to_float(__ldg(p.residual + m * p.ldr + n))));
+  p.y[m * p.ldy + n] = o;
+}
 
 __device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 
@@ -138,6 +169,7 @@ cudaError_t launch_kernel_pdl(const Plan& pl, const SmallMParams& p, cudaStream_
 
 // linear_small_m_mma.cu
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s);
+cudaError_t launch_small_m_mma_multi(const Plan& pl, const MultiParams& g, cudaStream_t s);
 // Shared memory the staged warp-MMA kernel needs for (layer, r8); 0 if it cannot run it.
 size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps, int act_bufs);
 

@@ -227,8 +227,11 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
             _lib.check(self._lib.sacq_decode_weight_fp8(self._handle, sw.data_ptr(), wq.data_ptr(), _stream_ptr()))
         return wq.view(torch.float8_e4m3fn)
 
-    def linear_a8(self, q: torch.Tensor, scale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """GEMM on already-quantized activations: q e4m3 ``[M, K]``, scale fp32 ``[M]`` -> bf16 ``[M, N]``."""
+    def linear_a8(self, q: torch.Tensor, scale: torch.Tensor, out: torch.Tensor | None = None,
+                  residual: torch.Tensor | None = None) -> torch.Tensor:
+        """GEMM on already-quantized activations: q e4m3 ``[M, K]``, scale fp32 ``[M]`` -> bf16 ``[M, N]``.
+        ``residual`` (bf16 ``[M, N]``) is added in the GEMM epilogue: the bytes of
+        ``linear_a8(q, scale) + residual``."""
         if q.dim() != 2 or q.shape[1] != self.in_features:
             raise ValueError("q must be [M, in_features]")
         if not q.is_cuda or q.device != self.codebook.device:
@@ -245,10 +248,33 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         ws = _Workspace.get(q.device)
         need = int(self._lib.sacq_workspace_bytes(self._handle, m))
         buf = ws.scratch(need)
+        if residual is not None:
+            if residual.dtype != torch.bfloat16 or tuple(residual.shape) != (m, self.out_features) or \
+                    residual.device != q.device or residual.stride(-1) != 1:
+                raise ValueError("residual must be a bf16 [M, out_features] tensor on the layer's device")
         with torch.cuda.device(q.device):
-            _lib.check(self._lib.sacq_linear_a8(self._handle, q.data_ptr(), scale.data_ptr(), m, out.data_ptr(),
-                                                out.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
+            if residual is None:
+                _lib.check(self._lib.sacq_linear_a8(self._handle, q.data_ptr(), scale.data_ptr(), m, out.data_ptr(),
+                                                    out.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
+            elif m > 0 and self.out_features > 0:
+                _lib.check(self._lib.sacq_linear_a8_residual(self._handle, q.data_ptr(), scale.data_ptr(), m,
+                                                             residual.data_ptr(), residual.stride(0), out.data_ptr(),
+                                                             out.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
         return out
+
+    def forward_residual(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """``self(x) + residual`` with the addition done in the GEMM epilogue (bf16 operands)."""
+        from .activation import quantize_rows
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Linear shape mismatch")
+        a = x.reshape(-1, self.in_features)
+        if a.dtype != torch.bfloat16:
+            a = a.to(torch.bfloat16)
+        q, s = quantize_rows(a.contiguous() if a.stride(-1) != 1 else a)
+        r = residual.reshape(-1, self.out_features)
+        y = self.linear_a8(q, s, residual=r if r.dtype == torch.bfloat16 else r.to(torch.bfloat16))
+        y = y.reshape(*x.shape[:-1], self.out_features)
+        return y if x.dtype == torch.bfloat16 else y.to(x.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape[-1] != self.in_features:
@@ -361,8 +387,41 @@ def forward_shared(layers, x: torch.Tensor):
     if a.dtype != torch.bfloat16:
         a = a.to(torch.bfloat16)
     q, s = quantize_rows(a.contiguous() if a.stride(-1) != 1 else a)
+    ys = linear_a8_multi(layers, q, s)
     outs = []
-    for layer in layers:
-        y = layer.linear_a8(q, s).reshape(*x.shape[:-1], layer.out_features)
+    for layer, y in zip(layers, ys):
+        y = y.reshape(*x.shape[:-1], layer.out_features)
         outs.append(y if x.dtype == torch.bfloat16 else y.to(x.dtype))
+    return outs
+
+
+def linear_a8_multi(layers, q: torch.Tensor, scale: torch.Tensor):
+    """GEMMs of several layers on one set of quantized activations (``sacq_linear_a8_multi``):
+    layers of one geometry run as a single launch at small M.  Returns one bf16 ``[M, N_l]``
+    tensor per layer, byte-identical to ``layer.linear_a8(q, scale)``."""
+    import ctypes
+    layers = list(layers)
+    first = layers[0]
+    if q.dim() != 2 or any(l.in_features != q.shape[1] for l in layers):
+        raise ValueError("q must be [M, in_features] of every layer")
+    if not q.is_cuda or any(l.codebook.device != q.device for l in layers):
+        raise ValueError("Matching CUDA operands required")
+    if q.element_size() != 1:
+        raise TypeError("q must hold e4m3 bytes")
+    q = q.contiguous()
+    scale = scale.reshape(-1).to(torch.float32).contiguous()
+    m = q.shape[0]
+    if scale.numel() != m:
+        raise ValueError("scale must have one entry per row of q")
+    outs = [torch.empty((m, l.out_features), dtype=torch.bfloat16, device=q.device) for l in layers]
+    n = len(layers)
+    lib = first._lib
+    need = max(int(lib.sacq_workspace_bytes(l._handle, m)) for l in layers)
+    buf = _Workspace.get(q.device).scratch(need)
+    handles = (ctypes.c_void_p * n)(*[l._handle.value for l in layers])
+    ys = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+    ldys = (ctypes.c_int64 * n)(*[o.stride(0) for o in outs])
+    with torch.cuda.device(q.device):
+        _lib.check(lib.sacq_linear_a8_multi(handles, n, q.data_ptr(), scale.data_ptr(), m, ys, ldys, buf.data_ptr(),
+                                            buf.numel(), _stream_ptr()))
     return outs

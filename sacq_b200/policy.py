@@ -22,6 +22,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
+from .activation import act_quantize_rows
 from .linear import PrecomputedPackedVectorCodebookLinear, forward_shared
 from .synthetic import make_payload
 
@@ -94,17 +95,18 @@ class _Block(torch.nn.Module):
         else:
             h = self.n1(x)
         q, k, v = forward_shared((self.q, self.k, self.v), h)      # one activation quantization for q/k/v
-        x = x + self.o(self._attend(q, k, v))
+        x = self.o.forward_residual(self._attend(q, k, v), x)            # residual added in the GEMM epilogue
         if self.cross:
             h = self.n3(x)
-            x = x + self.co(self._attend(self.cq(h), cross_kv[0], cross_kv[1]))
+            x = self.co.forward_residual(self._attend(self.cq(h), cross_kv[0], cross_kv[1]), x)
         h = self.n2(x) * (1 + m[3]) + m[2] if self.adaln else self.n2(x)
+        # the activation function runs inside the quantizer of the down projection
         if self.gated:
             gate, up = forward_shared((self.gate, self.up), h)
-            h = F.silu(gate) * up
+            q, s = act_quantize_rows("silu_mul", gate, up)
         else:
-            h = F.gelu(self.up(h))
-        return x + self.down(h)
+            q, s = act_quantize_rows("gelu", self.up(h))
+        return self.down.linear_a8(q, s, residual=x)
 
 
 class SyntheticGr00tPolicy(torch.nn.Module):

@@ -402,6 +402,108 @@ def test_linear_grouped_tensor_core(N, K, d, C, G, M):
     assert torch.equal(out[:, :N], outs["large_grouped"][0]) and float(out[:, N:].float().min()) == 3.0
 
 
+@pytest.mark.parametrize("K,Ns,d,C", [(2048, (2048, 1024, 1024), 8, 4096), (2048, (6144, 6144), 8, 4096),
+                                        (1536, (1536, 1536, 1536, 1536), 8, 4096), (1024, (512, 256), 4, 256),
+                                        (2048, (1024, 1000), 8, 4096)])
+def test_sibling_layers_in_one_launch(K, Ns, d, C):
+    """q/k/v and gate/up style groups on shared quantized activations: one launch at small M
+    for layers of one geometry, byte-identical to separate calls; a group the single launch
+    cannot take (an out_features that is not a multiple of 8, the tensor-core range of M)
+    falls back to one launch per layer with the same bytes."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, forward_shared, linear_a8_multi, quantize_rows
+    from sacq_b200.synthetic import make_activations, make_payload
+    mods = []
+    for i, N in enumerate(Ns):
+        p = make_payload(N, K, vector_dim=d, codebook_size=C, seed=10 * i + N % 7, device="cuda", iters=1)
+        bias = (torch.randn(N, generator=torch.Generator().manual_seed(i)) * 0.05).to(torch.bfloat16) if i % 2 else None
+        mods.append(PrecomputedPackedVectorCodebookLinear(p, bias, "cuda"))
+    lib = mods[0]._lib
+    for M in (1, 16, 33, 64, 200):
+        x = make_activations(M, K, seed=M + 11).cuda()
+        q, s = quantize_rows(x)
+        want = [m.linear_a8(q, s) for m in mods]
+        before = lib.sacq_launch_count()
+        got = linear_a8_multi(mods, q, s)
+        launches = lib.sacq_launch_count() - before
+        torch.cuda.synchronize()
+        for a, b in zip(want, got):
+            assert torch.equal(a, b)
+        assert launches in (1, len(mods)), (M, launches)
+        if M <= 16 and all(N % 8 == 0 for N in Ns):
+            assert launches == 1, (M, launches)
+        if any(N % 8 for N in Ns) or any(m.kernel_for(M) != "small" for m in mods):
+            assert launches == len(mods), (M, launches)
+        for a, b in zip(want, forward_shared(mods, x)):
+            assert torch.equal(a, b)
+    assert all(m.device_status() == 0 for m in mods)
+
+
+@pytest.mark.parametrize("N,K,d,C,G,Ms", [(2048, 2048, 8, 4096, None, (1, 16, 40, 300)),
+                                            (1000, 1024, 4, 256, None, (3, 130)),
+                                            (1536, 1536, 4, 64, 64, (16, 41, 149)),
+                                            (264, 512, 8, 65536, None, (5,)), (40, 128, 4, 32, 64, (2,))])
+def test_linear_residual_epilogue(N, K, d, C, G, Ms):
+    """Residual added in the epilogue of every GEMM kernel (warp-MMA staged / unpacked / direct,
+    CUDA-core, both tcgen05 kernels): the bytes of `linear_a8(q, s) + residual`."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N, device="cuda", iters=1,
+                     sample_size=max(65536, 2 * C), fit=(C < 65536))
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    for M in Ms:
+        x = make_activations(M, K, seed=M).cuda()
+        q, s = quantize_rows(x)
+        res = (torch.randn(M, N, generator=torch.Generator().manual_seed(M)) * 0.5).to(torch.bfloat16).cuda()
+        wide = torch.zeros(M, N + 8, dtype=torch.bfloat16, device="cuda")
+        wide[:, :N] = res
+        for k in ("auto", "small", "small_simt", "small_mma_direct", "small_mma_unpacked", "large", "large_grouped"):
+            mod.set_kernel(k)
+            try:
+                plain = mod.linear_a8(q, s)
+            except Exception as e:
+                if getattr(e, "code", 0) == -2:
+                    continue                      # this variant cannot run the geometry
+                raise
+            want = plain + res
+            assert torch.equal(mod.linear_a8(q, s, residual=res), want), (k, M)
+            assert torch.equal(mod.linear_a8(q, s, residual=wide[:, :N]), want), (k, M)
+        mod.set_kernel("auto")
+        assert torch.equal(mod.forward_residual(x, res), mod(x) + res)
+    assert mod.device_status() == 0
+    with pytest.raises(ValueError):
+        mod.linear_a8(q, s, residual=res[:, :-1])
+
+
+@pytest.mark.parametrize("M,K", [(1, 6144), (16, 6144), (300, 6144), (256, 4096), (5, 100), (3, 7)])
+def test_activation_fused_into_quantizer(M, K):
+    """silu(gate) * up and gelu(x) fused into the quantizer: the bytes and scales of quantizing
+    the result of the separate bf16 tensor operations."""
+    _need_gpu()
+    import torch.nn.functional as F
+    from sacq_b200 import act_quantize_rows, quantize_rows
+    g = torch.Generator().manual_seed(M * 7 + K)
+    a = (torch.randn(M, K, generator=g) * 2.0).to(torch.bfloat16).cuda()
+    b = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    a[0, 0] = 30.0                                       # saturated and tiny arguments
+    a[-1, -1] = -30.0
+    for kind, ref in (("silu_mul", F.silu(a) * b), ("gelu", F.gelu(a))):
+        q, s = act_quantize_rows(kind, a, b if kind == "silu_mul" else None)
+        qr, sr = quantize_rows(ref)
+        assert torch.equal(s.view(torch.int32), sr.view(torch.int32)), kind
+        assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8)), kind
+    wide = torch.zeros(M, K + 8, dtype=torch.bfloat16, device="cuda")
+    wide[:, :K] = a
+    q2, s2 = act_quantize_rows("gelu", wide[:, :K])
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s2, s)
+    z, zs = act_quantize_rows("gelu", torch.zeros(2, K, dtype=torch.bfloat16, device="cuda"))
+    assert int(z.view(torch.uint8).max()) == 0 and float(zs.min()) == 1.0
+    with pytest.raises(TypeError):
+        act_quantize_rows("silu_mul", a)
+
+
 def test_linear_properties_and_edges():
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
