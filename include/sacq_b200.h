@@ -124,6 +124,19 @@ SACQ_API int64_t sacq_workspace_counter_bytes(void);
 SACQ_API int sacq_linear_a8(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M, void* y_out,
                    int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* INT8 per-token activations, the format of the reference's deployed recipe
+ * (quantize_rows(x, 'int8_symmetric'), perrow_a8_candidate_r3.py:17-25):
+ *   s = max|x| / 127 per row (1 for an all-zero row), q = int8(round_half_even(clamp(x / s, -127, 127))).
+ * sacq_linear_a8i is sacq_linear_a8 for such activations: the same exact weights (no 8-bit
+ * rounding of the weights, unlike the reference's INT8 GEMM), int8 widened to fp16 in front of
+ * fp16 tensor-core MMAs (tcgen05 kind::f16 from 48 rows, warp MMAs below).  Its workspace is
+ * sacq_workspace_bytes_int8(layer, M) bytes, 256-byte aligned, zero-filled once. */
+SACQ_API int sacq_quant_act_int8(const void* x_bf16, int64_t x_pitch, int64_t M, int64_t K, void* q_out,
+                                 float* scale_out, void* stream);
+SACQ_API int64_t sacq_workspace_bytes_int8(const sacq_layer_t* layer, int64_t M);
+SACQ_API int sacq_linear_a8i(const sacq_layer_t* layer, const void* q_int8, const float* scale, int64_t M, void* y_out,
+                             int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Activation function fused into the per-token quantizer (the producer of the MLP's down
  * projection; the reference fuses this stage for its INT8 path,
  * int8_swiglu_lookup_fusion_20261028_r1.py:9-21).  One launch, the [M, K] intermediate is

@@ -4,7 +4,9 @@ Same contract as the reference's ``quantize_rows(x, mode)``
 (gr00t_libero/acceleration/sources/libero_pro_eval/inference_acceleration_2026_10_11/
 a8_accuracy_recovery_2026_10_20_r1/perrow_a8_candidate_r3.py:17-25) for
 ``mode == 'fp8_e4m3fn'``: returns ``(encoded [M, K] float8_e4m3fn, scale [M, 1] float32)``
-with ``scale = absmax / 448`` per row (1 for an all-zero row).
+with ``scale = absmax / 448`` per row (1 for an all-zero row), and for
+``mode == 'int8_symmetric'`` (the deployed recipe): ``(encoded [M, K] int8, scale)`` with
+``scale = absmax / 127`` and round-half-to-even.
 """
 from __future__ import annotations
 
@@ -17,8 +19,8 @@ def quantize_rows(x: torch.Tensor, mode: str = "fp8_e4m3fn", out: torch.Tensor |
                   scale_out: torch.Tensor | None = None):
     if x.ndim != 2 or x.dtype != torch.bfloat16:
         raise TypeError("quantize_rows expects a 2-D bfloat16 tensor")
-    if mode != "fp8_e4m3fn":
-        raise ValueError(f"unsupported mode {mode!r}; this implementation provides 'fp8_e4m3fn'")
+    if mode not in ("fp8_e4m3fn", "int8_symmetric"):
+        raise ValueError(f"unsupported mode {mode!r}; this implementation provides 'fp8_e4m3fn' and 'int8_symmetric'")
     if not x.is_cuda:
         raise ValueError("quantize_rows needs a CUDA tensor; there is no CPU path")
     lib = _lib.load()
@@ -28,9 +30,12 @@ def quantize_rows(x: torch.Tensor, mode: str = "fp8_e4m3fn", out: torch.Tensor |
     q = out if out is not None else torch.empty((m, k), dtype=torch.uint8, device=x.device)
     s = scale_out if scale_out is not None else torch.empty((m, 1), dtype=torch.float32, device=x.device)
     if m > 0 and k > 0:
+        fn = lib.sacq_quant_act_fp8 if mode == "fp8_e4m3fn" else lib.sacq_quant_act_int8
         with torch.cuda.device(x.device):
-            _lib.check(lib.sacq_quant_act_fp8(x.data_ptr(), x.stride(0), m, k, q.data_ptr(), s.data_ptr(),
-                                              torch.cuda.current_stream().cuda_stream))
+            _lib.check(fn(x.data_ptr(), x.stride(0), m, k, q.data_ptr(), s.data_ptr(),
+                          torch.cuda.current_stream().cuda_stream))
+    if mode == "int8_symmetric":
+        return (q.view(torch.int8) if q.dtype == torch.uint8 else q), s
     return (q.view(torch.float8_e4m3fn) if q.dtype == torch.uint8 else q), s
 
 

@@ -17,8 +17,21 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kMaxChunksPerThread = 4;  // 16-byte chunks a thread keeps in registers: K <= 8192 stays on chip
 
+// Two encoded values of one row -> two bytes.  I8: round-half-to-even to int8 in [-127, 127]
+// (quantize_rows(x, 'int8_symmetric'), perrow_a8_candidate_r3.py:17-25); else e4m3.
+template <bool I8>
+__device__ __forceinline__ uint32_t encode2(float z0, float z1, float s) {
+  if constexpr (I8) {
+    const int a = __float2int_rn(fminf(fmaxf(__fdiv_rn(z0, s), -127.f), 127.f));
+    const int b = __float2int_rn(fminf(fmaxf(__fdiv_rn(z1, s), -127.f), 127.f));
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8);
+  } else {
+    return float2_to_e4m3x2(clamp448(__fdiv_rn(z0, s)), clamp448(__fdiv_rn(z1, s)));
+  }
+}
+
 // One CTA per row.  VEC: rows are 16-byte aligned and K % 8 == 0.
-template <bool VEC>
+template <bool VEC, bool I8 = false>
 __global__ void __launch_bounds__(kThreads)
 quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, uint8_t* __restrict__ q,
                      float* __restrict__ scale_out) {
@@ -67,7 +80,7 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
     float v = tid < kThreads / 32 ? red[tid] : 0.f;
     v = warp_max(v);
     if (tid == 0) {
-      const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
+      const float s = v > 0.f ? __fdiv_rn(v, I8 ? 127.0f : kE4M3Max) : 1.0f;
       s_scale = s;
       scale_out[m] = s;
     }
@@ -81,10 +94,9 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
       uint32_t o[2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const uint32_t a = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] & 0xffff), s)),
-                                            clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] >> 16), s)));
-        const uint32_t b = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] & 0xffff), s)),
-                                            clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] >> 16), s)));
+        const uint32_t a = encode2<I8>(bf16_bits_to_float(w[2 * j] & 0xffff), bf16_bits_to_float(w[2 * j] >> 16), s);
+        const uint32_t b = encode2<I8>(bf16_bits_to_float(w[2 * j + 1] & 0xffff),
+                                       bf16_bits_to_float(w[2 * j + 1] >> 16), s);
         o[j] = a | (b << 16);
       }
       *(reinterpret_cast<uint2*>(qrow) + ch) = make_uint2(o[0], o[1]);
@@ -99,12 +111,29 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
   } else {
     for (int64_t k = tid; k < K; k += kThreads) {
       const float z = bf16_bits_to_float(__ldg(row + k));
-      qrow[k] = (uint8_t)(float2_to_e4m3x2(clamp448(__fdiv_rn(z, s)), 0.f) & 0xff);
+      qrow[k] = (uint8_t)(encode2<I8>(z, 0.f, s) & 0xff);
     }
   }
 }
 
 }  // namespace
+
+int launch_quant_act_int8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale,
+                          cudaStream_t s) {
+  if (M == 0 || K == 0) return SACQ_OK;
+  const bool vec = (K % 8 == 0) && (pitch % 8 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(q) % 8 == 0);
+  if (M > 2147483647LL) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
+  if (vec)
+    quant_act_fp8_kernel<true, true><<<(unsigned)M, kThreads, 0, s>>>(static_cast<const uint16_t*>(x), pitch, K,
+                                                                     static_cast<uint8_t*>(q), scale);
+  else
+    quant_act_fp8_kernel<false, true><<<(unsigned)M, kThreads, 0, s>>>(static_cast<const uint16_t*>(x), pitch, K,
+                                                                      static_cast<uint8_t*>(q), scale);
+  count_launch();
+  SACQ_CUDA_TRY(cudaGetLastError());
+  return SACQ_OK;
+}
 
 int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale,
                          cudaStream_t s) {

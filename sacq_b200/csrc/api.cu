@@ -301,6 +301,68 @@ int linear_a8_impl(const sacq_layer_t* L, const void* q, const float* scale, int
 }
 }  // namespace
 
+namespace {
+// INT8 activations run on the kernels that widen the activation bytes to fp16 themselves:
+// the grouped tensor-core kernel (tcgen05 kind::f16) from kGroupedMinM rows, below that the
+// fp16 warp-MMA kernel where the layer's geometry allows it, else the CUDA-core kernel.
+int int8_small_selector(const sacq_layer* L) { return small_m_int8_selector(L); }
+}  // namespace
+
+SACQ_API int sacq_quant_act_int8(const void* x_bf16, int64_t x_pitch, int64_t M, int64_t K, void* q_out, float* scale_out,
+                                 void* stream) {
+  if (M < 0 || K < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "negative size (M=%lld K=%lld)", (long long)M,
+                                       (long long)K);
+  if (M == 0) return SACQ_OK;
+  if (x_pitch < K) return set_error(SACQ_ERR_INVALID_ARGUMENT, "row pitch %lld smaller than K=%lld",
+                                    (long long)x_pitch, (long long)K);
+  if (scale_out == nullptr || ((x_bf16 == nullptr || q_out == nullptr) && K > 0))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (K == 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "K must be positive");
+  return launch_quant_act_int8(x_bf16, x_pitch, M, K, q_out, scale_out, static_cast<cudaStream_t>(stream));
+}
+
+SACQ_API int64_t sacq_workspace_bytes_int8(const sacq_layer_t* L, int64_t M) {
+  if (L == nullptr || M < 0) return 0;
+  if (M >= kGroupedMinM && large_m_grouped_supported(L)) return kCounterBytes + large_m_grouped_workspace_bytes(L, M);
+  sacq_layer view = *L;
+  view.force_kernel = int8_small_selector(L);
+  const int64_t slab = small_m_slab_rows(L);
+  return small_m_workspace_bytes(&view, M < slab ? M : slab);
+}
+
+SACQ_API int sacq_linear_a8i(const sacq_layer_t* L, const void* q_int8, const float* scale, int64_t M, void* y_out,
+                             int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
+  if (M == 0 || L->d.out_features == 0) return SACQ_OK;
+  if (q_int8 == nullptr || scale == nullptr || y_out == nullptr)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (ldy < L->d.out_features)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "ldy=%lld smaller than out_features=%lld", (long long)ldy,
+                     (long long)L->d.out_features);
+  DeviceGuard guard(L->d.device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M >= kGroupedMinM && large_m_grouped_supported(L)) {
+    if (workspace == nullptr || workspace_bytes < kCounterBytes)
+      return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
+                       (long long)sacq_workspace_bytes_int8(L, M), (long long)workspace_bytes);
+    return launch_large_m_grouped(L, q_int8, scale, M, y_out, ldy, static_cast<uint8_t*>(workspace) + kCounterBytes,
+                                  workspace_bytes - kCounterBytes, s, nullptr, 0, 1);
+  }
+  if (!small_m_supported(L)) return set_error(SACQ_ERR_UNSUPPORTED, "no kernel can run this layer geometry");
+  sacq_layer view = *L;
+  view.force_kernel = int8_small_selector(L);
+  const int64_t slab = small_m_slab_rows(L);
+  for (int64_t m0 = 0; m0 < M; m0 += slab) {
+    const int64_t rows = (M - m0) < slab ? (M - m0) : slab;
+    const int rc = launch_small_m(&view, static_cast<const uint8_t*>(q_int8) + m0 * L->d.in_features, scale + m0, rows,
+                                  static_cast<uint16_t*>(y_out) + m0 * ldy, ldy, workspace, workspace_bytes, s, nullptr,
+                                  0, 1);
+    if (rc != SACQ_OK) return rc;
+  }
+  return SACQ_OK;
+}
+
 SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,
                    void* workspace, int64_t workspace_bytes, void* stream) {
   return linear_a8_impl(L, q, scale, M, nullptr, 0, y_out, ldy, workspace, workspace_bytes, stream);

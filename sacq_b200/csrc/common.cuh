@@ -58,16 +58,20 @@ int launch_dequant_bf16(const sacq_layer* L, void* w_out, cudaStream_t s);
 int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s);
 int launch_decode_weight_fp8(const sacq_layer* L, const float* sw, void* wq, cudaStream_t s);
 int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
+int launch_quant_act_int8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
 int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, int64_t M, int64_t K,
                          void* q, float* scale, cudaStream_t s);
 int launch_build_tables(sacq_layer* L, cudaStream_t s);
 int launch_copy_to_host(const void* src, void* dst, int64_t bytes, int num_sms, cudaStream_t s);
 
 bool small_m_supported(const sacq_layer* L);
+// Kernel selector (5 = fp16 warp-MMA, 3 = CUDA-core) of the small-M variant that takes int8 activations.
+int small_m_int8_selector(const sacq_layer* L);
 int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M);
 // `residual` (bf16 [M, ldr], may be null) is added to the rounded output in every GEMM epilogue.
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                   void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0);
+                   void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0,
+                   int act_int8 = 0);
 
 int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
                          void* const* ys, const int64_t* ldys, cudaStream_t s);
@@ -81,7 +85,7 @@ bool large_m_grouped_supported(const sacq_layer* L);
 int64_t large_m_grouped_workspace_bytes(const sacq_layer* L, int64_t M);
 int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                            void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr,
-                           int64_t ldr = 0);
+                           int64_t ldr = 0, int act_int8 = 0);
 
 // ----------------------------------------------------------------------------
 // device side

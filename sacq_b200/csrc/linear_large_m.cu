@@ -10,10 +10,11 @@
 //     shared-memory codebook and write them into two K-major, 128B-swizzled B tiles --
 //     the canonical UMMA layout, produced by threads instead of by TMA -- then
 //     fence.proxy.async and arrive on the stage's mbarrier.
-//   * warp 1 (one lane)  : issues tcgen05.mma kind::f8f6f4 (M128 N128 K32), two per K
-//     step (A x B_hi, A x B_lo) into one fp32 accumulator in TMEM, and tcgen05.commit
-//     to release the stage.
-//   * warps 2..9 again   : epilogue.  tcgen05.ld the accumulator, apply
+//   * warp 1 (one lane)  : issues tcgen05.mma kind::f8f6f4; with one token sub-tile ONE per K step with the two B
+//     tiles as a single operand of N = 2*BN rows (M128 N256 K32 for BN = 128): A x B_hi
+//     lands in accumulator columns [0, BN), A x B_lo in [BN, 2*BN) of TMEM; tcgen05.commit
+//     releases the stage.
+//   * warps 2..9 again   : epilogue.  tcgen05.ld both accumulator halves, add them, apply
 //     fma(s[m], acc * scale[n], bias[n]) in the reference's order
 //     (int8_ordered_epilogue_20261028_r1.py:11-22) and store bf16.
 //
@@ -132,7 +133,13 @@ __host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, 
 // Smaller BN trades tensor-core efficiency for more CTAs when M is only a few tiles.  MT = 2
 // gives the CTA two 128-token sub-tiles (two TMEM accumulators) that share every expanded
 // B tile: the shared-memory gathers, not the MMAs, are what limits this kernel.
-template <int D, int BITS, int BN, int MT>
+// MERGE: the high and the low B tile are issued as ONE MMA of N = 2*BN (they are adjacent in
+// shared memory, so they form one K-major operand): A x hi lands in accumulator columns
+// [0, BN), A x lo in [BN, 2*BN), and the epilogue adds them.  A small-N MMA is bound by its
+// shared-memory operand reads, so reading the A tile once instead of twice is what counts at
+// small and medium M; with two token sub-tiles (large M) two N = BN MMAs into one accumulator
+// measured faster.
+template <int D, int BITS, int BN, int MT, bool MERGE>
 __global__ void __launch_bounds__(kThreads, 1)
 large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
                const LargeMParams p) {
@@ -143,7 +150,8 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr int PARTS = kExpanderThreads / BN;        // expander threads per weight row
   constexpr int CPT = 8 / PARTS;                      // 16-byte chunks each of them writes per K block
   constexpr int IPC = 16 / D;                         // indices per chunk
-  constexpr uint32_t kIdesc = make_idesc(BN);
+  constexpr int ACC_COLS = MERGE ? 2 * BN : BN;       // accumulator columns per token sub-tile
+  constexpr uint32_t kIdesc = make_idesc(ACC_COLS);
   constexpr int B_TILE = BN * kBK;
   constexpr int kStages = stages_for(MT);
   constexpr int A_BYTES = MT * kTileBytes;
@@ -183,7 +191,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_idx);
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), (uint32_t)(BN * MT));
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), (uint32_t)(ACC_COLS * MT));
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -221,16 +229,16 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = base + L.stage_off + st * L.stage_bytes;
-        const uint64_t bh_desc = make_smem_desc(a_addr + A_BYTES);
-        const uint64_t bl_desc = make_smem_desc(a_addr + A_BYTES + B_TILE);
+        const uint64_t b_desc = make_smem_desc(a_addr + A_BYTES);            // high half (and, merged, both)
+        const uint64_t bl_desc = make_smem_desc(a_addr + A_BYTES + B_TILE);   // low half
 #pragma unroll
         for (int ks = 0; ks < kBK / 32; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32) >> 4);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const uint64_t a_desc = make_smem_desc(a_addr + mt * kTileBytes);
-            umma_f8(tmem_base + (uint32_t)(mt * BN), a_desc + adv, bh_desc + adv, kIdesc, (kb | ks) != 0);
-            umma_f8(tmem_base + (uint32_t)(mt * BN), a_desc + adv, bl_desc + adv, kIdesc, 1);
+            umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+            if constexpr (!MERGE) umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, bl_desc + adv, kIdesc, 1);
           }
         }
         umma_commit(bar(EMPTY + st));
@@ -316,7 +324,13 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int cc = col_half; cc < BN / 32; cc += 2) {
           const int c0 = cc * 32;
           uint32_t r[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + c0), r);
+          tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0), r);
+          if constexpr (MERGE) {
+            uint32_t rl[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * ACC_COLS + BN + c0), rl);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) + __uint_as_float(rl[c]));
+          }
           if (m < p.M) {
             uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
             const uint16_t* rrow = p.residual ? p.residual + (int64_t)m * p.ldr + n0 + c0 : nullptr;
@@ -356,7 +370,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // ---- common exit: every thread arrives here, also after an aborted wait
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(BN * MT));
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(ACC_COLS * MT));
 }
 
 
@@ -412,29 +426,32 @@ namespace {
 
 int sb_bytes_for(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
 
-template <int D, int BITS, int BN, int MT>
+template <int D, int BITS, int BN, int MT, bool MERGE>
 cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, dim3 grid, cudaStream_t s) {
   const size_t smem = make_layout(BN, MT, 2 * (kBK / D) * BITS / 8, p.C * 2 * D).total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN, MT, MERGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  large_m_kernel<D, BITS, BN, MT><<<grid, kThreads, smem, s>>>(ta, ti, p);
+  // (Programmatic dependent launch behind the quantizer was measured and is not used here: the
+  // early-resident 200 KB CTAs slowed the kernels around them more than the overlap gained.)
+  large_m_kernel<D, BITS, BN, MT, MERGE><<<grid, kThreads, smem, s>>>(ta, ti, p);
   return cudaGetLastError();
 }
 
 template <int D, int BITS>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, int bn, int mt, dim3 grid,
                        cudaStream_t s) {
-  if (bn == 32) return launch_bn<D, BITS, 32, 1>(ta, ti, p, grid, s);
-  if (bn == 64) return launch_bn<D, BITS, 64, 1>(ta, ti, p, grid, s);
-  if (mt == 2) return launch_bn<D, BITS, 128, 2>(ta, ti, p, grid, s);
-  return launch_bn<D, BITS, 128, 1>(ta, ti, p, grid, s);
+  // one token sub-tile: merged high/low MMA; two sub-tiles (large grids): separate MMAs
+  if (bn == 32) return launch_bn<D, BITS, 32, 1, true>(ta, ti, p, grid, s);
+  if (bn == 64) return launch_bn<D, BITS, 64, 1, true>(ta, ti, p, grid, s);
+  if (mt == 2) return launch_bn<D, BITS, 128, 2, false>(ta, ti, p, grid, s);
+  return launch_bn<D, BITS, 128, 1, true>(ta, ti, p, grid, s);
 }
 
 }  // namespace
@@ -529,6 +546,5 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
   if (e != cudaSuccess) return cuda_fail(e, "large-M launch");
   return SACQ_OK;
 }
-
 
 }  // namespace sacq

@@ -77,7 +77,8 @@ __host__ __device__ inline GroupedLayout grouped_layout(int bn, int mt, int bits
   return L;
 }
 
-// e4m3 [M, K] -> fp16 [M, K] (exact) and xsum[m] = sum_k q[m, k]; one CTA per token row.
+// e4m3 (or int8, I8) [M, K] -> fp16 [M, K] (exact) and xsum[m] = sum_k q[m, k]; one CTA per token row.
+template <bool I8>
 __global__ void __launch_bounds__(256) widen_act_kernel(const uint8_t* __restrict__ q, int64_t K,
                                                         __half* __restrict__ a16, float* __restrict__ xsum) {
   __shared__ float red[8];
@@ -91,12 +92,19 @@ __global__ void __launch_bounds__(256) widen_act_kernel(const uint8_t* __restric
     const uint32_t in[2] = {v.x, v.y};
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      const __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in[j] & 0xffff), __NV_E4M3);
-      const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in[j] >> 16), __NV_E4M3);
-      w[2 * j] = (uint32_t)a.x | ((uint32_t)a.y << 16);
-      w[2 * j + 1] = (uint32_t)b.x | ((uint32_t)b.y << 16);
-      sum += __half2float(__ushort_as_half(a.x)) + __half2float(__ushort_as_half(a.y)) +
-             __half2float(__ushort_as_half(b.x)) + __half2float(__ushort_as_half(b.y));
+      __half h[4];
+      if constexpr (I8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __int2half_rn((int)(int8_t)((in[j] >> (8 * e)) & 0xff));
+      } else {
+        const __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in[j] & 0xffff), __NV_E4M3);
+        const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(in[j] >> 16), __NV_E4M3);
+        h[0] = __ushort_as_half(a.x); h[1] = __ushort_as_half(a.y);
+        h[2] = __ushort_as_half(b.x); h[3] = __ushort_as_half(b.y);
+      }
+      w[2 * j] = (uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
+      w[2 * j + 1] = (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
+      sum += __half2float(h[0]) + __half2float(h[1]) + __half2float(h[2]) + __half2float(h[3]);
     }
     dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
   }
@@ -443,7 +451,8 @@ int64_t large_m_grouped_workspace_bytes(const sacq_layer* L, int64_t M) {
 }
 
 int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                           void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr) {
+                           void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr,
+                           int act_int8) {
   const sacq_layer_desc& d = L->d;
   if (!large_m_grouped_supported(L))
     return set_error(SACQ_ERR_UNSUPPORTED, "grouped tensor-core kernel cannot run this layer geometry");
@@ -477,7 +486,10 @@ int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scal
 
   for (int64_t m0 = 0; m0 < M; m0 += slab) {
     const int64_t rows = (M - m0) < slab ? (M - m0) : slab;
-    widen_act_kernel<<<(unsigned)rows, 256, 0, s>>>(static_cast<const uint8_t*>(q) + m0 * K, K, a16, xsum);
+    if (act_int8)
+      widen_act_kernel<true><<<(unsigned)rows, 256, 0, s>>>(static_cast<const uint8_t*>(q) + m0 * K, K, a16, xsum);
+    else
+      widen_act_kernel<false><<<(unsigned)rows, 256, 0, s>>>(static_cast<const uint8_t*>(q) + m0 * K, K, a16, xsum);
     count_launch();
     SACQ_CUDA_TRY(cudaGetLastError());
     // tile shape: two token sub-tiles per CTA above 128 rows; BN by waves x (fixed + per-row cost)

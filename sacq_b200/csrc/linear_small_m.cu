@@ -139,8 +139,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_kernel(const SmallM
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
       CwVec h;
-      e4m3x4_to_h2(o[m].x, h.x, h.y);
-      if constexpr (D == 8) e4m3x4_to_h2(o[m].y, h.z, h.w);
+      act4_to_h2(p.act_int8, o[m].x, h.x, h.y);
+      if constexpr (D == 8) act4_to_h2(p.act_int8, o[m].y, h.z, h.w);
       xs[m * kSpanIdx + lane] = h;
       if (p.shift != 0.f) {
         float t = __low2float(as_h2(h.x)) + __high2float(as_h2(h.x)) + __low2float(as_h2(h.y)) +
@@ -274,7 +274,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32) small_m_generic_kernel(const S
           float v = 0.f;
           if (m0 + m < p.M) {
             const uint8_t b = __ldg(p.q + (int64_t)(m0 + m) * p.K + kbase + k);
-            v = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3)));
+            v = p.act_int8 ? (float)(int8_t)b
+                           : __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3)));
           }
           xs[m * span_k + k] = v;
           t += v;
@@ -531,6 +532,8 @@ cudaError_t launch_generic(const Plan& pl, const SmallMParams& p, cudaStream_t s
 
 }  // namespace
 
+int small_m_int8_selector(const sacq_layer* L) { return fast_eligible(L) ? 5 : 3; }
+
 bool small_m_supported(const sacq_layer* L) {
   return L->d.index_bits <= 24 && L->d.vector_dim <= 64;
 }
@@ -578,7 +581,7 @@ SmallMParams fill_params(const sacq_layer* L, const Plan& pl, const void* q, con
 }  // namespace
 
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                   void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr) {
+                   void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr, int act_int8) {
   const sacq_layer_desc& d = L->d;
   if (M == 0 || d.out_features == 0) return SACQ_OK;
   if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
@@ -600,6 +603,9 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   SmallMParams p = fill_params(L, pl, q, scale, M, y, ldy, ws);
   p.residual = static_cast<const uint16_t*>(residual);
   p.ldr = ldr;
+  p.act_int8 = act_int8;
+  if (act_int8 && pl.mma && (pl.staged || pl.unpacked))
+    return set_error(SACQ_ERR_UNSUPPORTED, "the FP8 warp-MMA variants cannot take int8 activations");
   cudaError_t e;
   if (pl.unpacked) {
     if (reinterpret_cast<uintptr_t>(q) % 16 != 0)

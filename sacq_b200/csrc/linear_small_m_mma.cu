@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const Sm
 
     int sp = warp;
     for (; sp < p.spans_per_row; sp += nwarps) {
-      // ---- A fragments: widen the e4m3 bytes to fp16 (exact)
+      // ---- A fragments: widen the e4m3 (or int8) bytes to fp16 (exact)
       uint32_t fa[8][AREG], fb[8][AREG];
       {
         const uint32_t* wa = reinterpret_cast<const uint32_t*>(qa);
@@ -132,13 +132,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const Sm
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
           if constexpr (D == 8) {
-            e4m3x4_to_h2(wa[2 * s], fa[s][0], fa[s][1]);
-            e4m3x4_to_h2(wa[2 * s + 1], fa[s][2], fa[s][3]);
-            e4m3x4_to_h2(wb[2 * s], fb[s][0], fb[s][1]);
-            e4m3x4_to_h2(wb[2 * s + 1], fb[s][2], fb[s][3]);
+            act4_to_h2(p.act_int8, wa[2 * s], fa[s][0], fa[s][1]);
+            act4_to_h2(p.act_int8, wa[2 * s + 1], fa[s][2], fa[s][3]);
+            act4_to_h2(p.act_int8, wb[2 * s], fb[s][0], fb[s][1]);
+            act4_to_h2(p.act_int8, wb[2 * s + 1], fb[s][2], fb[s][3]);
           } else {
-            e4m3x4_to_h2(wa[s], fa[s][0], fa[s][1]);
-            e4m3x4_to_h2(wb[s], fb[s][0], fb[s][1]);
+            act4_to_h2(p.act_int8, wa[s], fa[s][0], fa[s][1]);
+            act4_to_h2(p.act_int8, wb[s], fb[s][0], fb[s][1]);
           }
         }
       }

@@ -46,6 +46,7 @@ struct SmallMParams {
   int64_t num_items;
   float out_mul;               // 2^-cb_exp_shift (fast) or 1 (generic)
   float shift;
+  int act_int8;                // activations are int8 (the deployed recipe) instead of e4m3
 };
 
 // Up to four layers sharing one set of quantized activations in a single launch of the staged
@@ -85,6 +86,18 @@ __device__ __forceinline__ void e4m3x4_to_h2(uint32_t v, uint32_t& lo, uint32_t&
   const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v >> 16), __NV_E4M3);
   lo = (uint32_t)a.x | ((uint32_t)a.y << 16);
   hi = (uint32_t)b.x | ((uint32_t)b.y << 16);
+}
+
+// int8 x4 (one 32-bit word) -> 2 x half2, exact.
+__device__ __forceinline__ void s8x4_to_h2(uint32_t v, uint32_t& lo, uint32_t& hi) {
+  const __half2 a = __halves2half2(__int2half_rn((int)(int8_t)(v & 0xff)), __int2half_rn((int)(int8_t)((v >> 8) & 0xff)));
+  const __half2 b = __halves2half2(__int2half_rn((int)(int8_t)((v >> 16) & 0xff)), __int2half_rn((int)(int8_t)(v >> 24)));
+  lo = *reinterpret_cast<const uint32_t*>(&a);
+  hi = *reinterpret_cast<const uint32_t*>(&b);
+}
+// Four activation bytes of either format -> 2 x half2.
+__device__ __forceinline__ void act4_to_h2(int act_int8, uint32_t v, uint32_t& lo, uint32_t& hi) {
+  if (act_int8) s8x4_to_h2(v, lo, hi); else e4m3x4_to_h2(v, lo, hi);
 }
 
 // 8 consecutive fields of BITS bits held in BITS/4 words.

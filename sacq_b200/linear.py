@@ -262,6 +262,40 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
                                                              out.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
         return out
 
+    def linear_a8i(self, q: torch.Tensor, scale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """GEMM on INT8 per-token activations (``quantize_rows(x, 'int8_symmetric')``): q int8
+        ``[M, K]``, scale fp32 ``[M]`` -> bf16 ``[M, N]``, with the exact (not re-quantized) weights."""
+        if q.dim() != 2 or q.shape[1] != self.in_features:
+            raise ValueError("q must be [M, in_features]")
+        if not q.is_cuda or q.device != self.codebook.device:
+            raise ValueError("Matching CUDA operands required")
+        if q.dtype != torch.int8:
+            raise TypeError("q must be int8")
+        q = q.contiguous()
+        scale = scale.reshape(-1).to(torch.float32).contiguous()
+        m = q.shape[0]
+        if scale.numel() != m:
+            raise ValueError("scale must have one entry per row of q")
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=q.device)
+        buf = _Workspace.get(q.device).scratch(int(self._lib.sacq_workspace_bytes_int8(self._handle, m)))
+        with torch.cuda.device(q.device):
+            _lib.check(self._lib.sacq_linear_a8i(self._handle, q.data_ptr(), scale.data_ptr(), m, out.data_ptr(),
+                                                 out.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr()))
+        return out
+
+    def forward_int8(self, x: torch.Tensor) -> torch.Tensor:
+        """``forward`` with INT8 instead of FP8 per-token activations."""
+        from .activation import quantize_rows
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Linear shape mismatch")
+        a = x.reshape(-1, self.in_features)
+        if a.dtype != torch.bfloat16:
+            a = a.to(torch.bfloat16)
+        q, s = quantize_rows(a.contiguous() if a.stride(-1) != 1 else a, "int8_symmetric")
+        y = self.linear_a8i(q, s).reshape(*x.shape[:-1], self.out_features)
+        return y if x.dtype == torch.bfloat16 else y.to(x.dtype)
+
     def forward_residual(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         """``self(x) + residual`` with the addition done in the GEMM epilogue (bf16 operands)."""
         from .activation import quantize_rows

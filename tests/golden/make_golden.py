@@ -68,6 +68,7 @@ def make_activations(m, k, seed, zero_row=False):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only-int8", action="store_true", help="regenerate act_int8.npz only")
     args = ap.parse_args()
     ref = args.reference
     sys.path.insert(0, ref)
@@ -85,6 +86,22 @@ def main():
     perrow = load_by_path("ref_perrow", os.path.join(ref, SRC, "a8_accuracy_recovery_2026_10_20_r1",
                                                      "perrow_a8_candidate_r3.py"))
     rtn = load_by_path("ref_rtn", os.path.join(ref, SRC, "a8_rtn_r2.py"))
+
+    # ---- 0. INT8 per-token quantizer (the deployed recipe's activation format) ----
+    # rows spanning magnitudes, an all-zero row, and rows built so that x/scale lands on
+    # exact .5 ties (round-half-to-even) and on the clamp boundary
+    xi = make_activations(7, 512, seed=901, zero_row=True)
+    ties = torch.zeros(512)
+    ties[0] = 127.0                                      # row maximum -> scale 1.0
+    ties[1:128] = torch.arange(1, 128).float() - 0.5     # 0.5, 1.5, ... 126.5
+    ties[128:255] = -(torch.arange(1, 128).float() - 0.5)
+    xi[5] = ties.to(torch.bfloat16)
+    qi, si = perrow.quantize_rows(xi, "int8_symmetric")
+    np.savez_compressed(os.path.join(HERE, "act_int8.npz"), x=bf16_bits(xi), q=qi.numpy().astype(np.int8),
+                        s=si.numpy())
+    if args.only_int8:
+        print("act_int8.npz written")
+        return
 
     # ---- 1. bit-packing known answers -------------------------------------
     pack = {}

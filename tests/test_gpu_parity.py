@@ -504,6 +504,50 @@ def test_activation_fused_into_quantizer(M, K):
         act_quantize_rows("silu_mul", a)
 
 
+def test_int8_activation_quantizer():
+    """quantize_rows(x, 'int8_symmetric'): bytes and scale bits of the reference fixture and of
+    the oracle on larger and ragged inputs."""
+    _need_gpu()
+    from sacq_b200 import quantize_rows
+    from sacq_b200.synthetic import make_activations
+    f = load_golden("act_int8")
+    q, s = quantize_rows(from_bf16_bits(f["x"]).cuda(), "int8_symmetric")
+    assert q.dtype == torch.int8
+    assert np.array_equal(q.cpu().numpy(), f["q"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), f["s"].view(np.uint32))
+    for M, K in ((1, 2048), (64, 6144), (3, 100), (5, 8200), (2, 7)):
+        x = make_activations(M, K, seed=M + K)
+        qo, so = O.quantize_rows_int8(bf16_bits(x))
+        q, s = quantize_rows(x.cuda(), "int8_symmetric")
+        assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy().view(np.uint32), so.view(np.uint32))
+
+
+@pytest.mark.parametrize("N,K,d,C,G", [(2048, 2048, 8, 4096, None), (1536, 1536, 4, 64, 64), (6144, 2048, 4, 1024, 64),
+                                       (1000, 1024, 4, 256, None), (100, 256, 4, 2048, 64), (264, 512, 8, 65536, None)])
+def test_linear_int8_activations(N, K, d, C, G):
+    """GEMM on INT8 per-token activations against the oracle (exact weights, reconstruct then
+    matmul): fp16 warp-MMA and CUDA-core kernels at small M, tcgen05 kind::f16 from 48 rows."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N + 3, device="cuda", iters=1,
+                     sample_size=max(65536, 2 * C), fit=(C < 65536))
+    p["shift"] = torch.tensor(0.00390625, dtype=torch.bfloat16)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    for M in (1, 16, 47, 48, 300):
+        x = make_activations(M, K, seed=M)
+        qo, so = O.quantize_rows_int8(bf16_bits(x))
+        ref = O.linear_a8i_reference(qo, so, w_bits, bf16_bits(bias))
+        q, s = quantize_rows(x.cuda(), "int8_symmetric")
+        y = mod.linear_a8i(q, s)
+        torch.cuda.synchronize()
+        assert O.rel_frobenius(y.float().cpu().numpy(), ref) <= GEMM_TOL, M
+        assert torch.equal(y, mod.linear_a8i(q, s)) and torch.equal(y, mod.forward_int8(x.cuda()))
+    assert mod.device_status() == 0
+
+
 def test_linear_properties_and_edges():
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows

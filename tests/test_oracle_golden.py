@@ -109,3 +109,13 @@ def test_scalar_formats():
     assert np.array_equal(prod, f["mul_out"])
     summed = O.f32_to_bf16_bits(O.bf16_bits_to_f32(prod) + O.bf16_bits_to_f32(f["add_c"])[0])
     assert np.array_equal(summed, f["add_out"])
+
+
+def test_int8_activation_quantizer_matches_reference_fixture():
+    """quantize_rows(x, 'int8_symmetric') of the reference: bytes and scale bits, including
+    the round-half-to-even ties and the all-zero row."""
+    f = load_golden("act_int8")
+    q, s = O.quantize_rows_int8(f["x"])
+    assert np.array_equal(q, f["q"])
+    assert np.array_equal(s.view(np.uint32), f["s"].view(np.uint32))
+    assert list(q[5, 1:5]) == [0, 2, 2, 4] and float(s[1, 0]) == 1.0
