@@ -124,6 +124,26 @@ SACQ_API int64_t sacq_workspace_counter_bytes(void);
 SACQ_API int sacq_linear_a8(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M, void* y_out,
                    int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Output-split (column-parallel) layers across the GPUs of one node: the GEMM whose epilogue
+ * writes every output element to this GPU's buffer AND to the buffers of `num_peers` other
+ * GPUs (plain peer stores over NVLink, no multicast), so the exchange of the column blocks
+ * overlaps the computation instead of following it as an all-gather.  y_out and peer_outs[i]
+ * point at the first column this rank owns inside each [M, ldy] result buffer (the caller adds
+ * its column offset); all buffers share the row pitch ldy.  The caller orders the launch
+ * against the peers' use of their buffers (a barrier between producing and consuming, two
+ * buffers alternating).  The reference has no counterpart (single GPU).
+ *
+ * sacq_peer_buffer_*: device buffers that other processes of the node can map through CUDA IPC
+ * (`handle` is SACQ_PEER_HANDLE_BYTES bytes to be sent to the peers by any host channel). */
+#define SACQ_PEER_HANDLE_BYTES 64
+SACQ_API int sacq_linear_a8_bcast(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M, void* y_out,
+                                  void* const* peer_outs, int num_peers, int64_t ldy, void* workspace,
+                                  int64_t workspace_bytes, void* stream);
+SACQ_API int sacq_peer_buffer_create(int device, int64_t bytes, void** dev_ptr, void* handle_out);
+SACQ_API int sacq_peer_buffer_open(int device, const void* handle, void** dev_ptr);
+SACQ_API int sacq_peer_buffer_close(int device, void* dev_ptr);
+SACQ_API int sacq_peer_buffer_destroy(int device, void* dev_ptr);
+
 /* INT8 per-token activations, the format of the reference's deployed recipe
  * (quantize_rows(x, 'int8_symmetric'), perrow_a8_candidate_r3.py:17-25):
  *   s = max|x| / 127 per row (1 for an all-zero row), q = int8(round_half_even(clamp(x / s, -127, 127))).

@@ -68,6 +68,11 @@ SIGNATURES = {
     "sacq_workspace_counter_bytes": (_i64, []),
     "sacq_linear_a8": (_int, [_vp, _vp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "sacq_linear_a8_residual": (_int, [_vp, _vp, _fp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "sacq_linear_a8_bcast": (_int, [_vp, _vp, _fp, _i64, _vp, ctypes.POINTER(_vp), _int, _i64, _vp, _i64, _vp]),
+    "sacq_peer_buffer_create": (_int, [_int, _i64, ctypes.POINTER(_vp), _vp]),
+    "sacq_peer_buffer_open": (_int, [_int, _vp, ctypes.POINTER(_vp)]),
+    "sacq_peer_buffer_close": (_int, [_int, _vp]),
+    "sacq_peer_buffer_destroy": (_int, [_int, _vp]),
     "sacq_linear_a8_multi": (_int, [ctypes.POINTER(_vp), _int, _vp, _fp, _i64, ctypes.POINTER(_vp),
                                     ctypes.POINTER(_i64), _vp, _i64, _vp]),
     "sacq_linear_bf16": (_int, [_vp, _vp, _i64, _i64, _vp, _fp, _vp, _i64, _vp, _i64, _vp]),

@@ -55,18 +55,28 @@ def main():
         payload = make_payload(n, k, seed=1, iters=1, device=dev)
         for chunks in sorted({1, args.chunks}):
             layer = ColumnParallelCodebookLinear(payload, None, str(dev), chunks=chunks)
+            fused = None
+            if chunks == 1 and world > 1:
+                fused = ColumnParallelCodebookLinear(payload, None, str(dev), fused_exchange=True,
+                                                     max_tokens=max(int(v) for v in args.ms.split(",")))
             for m in [int(v) for v in args.ms.split(",")]:
                 x = make_activations(m, k, seed=m).to(dev)
                 q, s = layer.local.quantize_activations(x)
                 t_gemm = _time(lambda: layer.local.linear_a8(q, s), args.reps, dev)
                 t_full = _time(lambda: layer(x), args.reps, dev)
+                t_fused = None
+                if chunks == 1 and world > 1 and fused is not None:
+                    t_fused = _time(lambda: fused(x), args.reps, dev)
                 if rank == 0:
                     print(json.dumps({
                         "shape_KxN": f"{k}x{n}", "M": m, "gpus": world, "chunks": chunks,
                         "gemm_only_us": round(t_gemm, 2), "forward_with_gather_us": round(t_full, 2),
+                        "forward_fused_exchange_us": None if t_fused is None else round(t_fused, 2),
                         "tokens_per_s": m / (t_full * 1e-6),
                         "algorithmic_tflops_gemm_only": 2.0 * m * n * k / (t_gemm * 1e-6) / 1e12,
                         "gather_bytes_per_rank": 2 * m * n // world}), flush=True)
+            if fused is not None:
+                fused.close()
     dist.destroy_process_group()
 
 

@@ -14,6 +14,13 @@ trainer's gradient all-reduce); this module is new work on top of the same paylo
 
 Nothing here waits on the device: the gather of chunk ``i`` runs on a side stream while
 the GEMM of chunk ``i+1`` runs on the compute stream.
+
+``fused_exchange=True`` replaces the all-gather by the GEMM itself: the result buffers of all
+ranks are mapped into every process (CUDA IPC), and the GEMM epilogue stores each output
+element into the local buffer and into every peer's buffer (``sacq_linear_a8_bcast``, plain
+peer stores over NVLink), so the exchange overlaps the computation tile by tile.  What is left
+after the kernel is a one-element all-reduce that orders the ranks; two buffers alternate so
+a rank may start the next call while a slower peer still reads the previous result.
 """
 from __future__ import annotations
 
@@ -76,6 +83,61 @@ def gather_columns(y_local: torch.Tensor, group=None, out: torch.Tensor | None =
     return full
 
 
+class _RawCuda:
+    """A raw device pointer presented through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerBuffers:
+    """``copies`` result buffers per rank, each mapped into every rank of the group.
+
+    ``local[c]`` is this rank's buffer ``c`` (a uint8 tensor), ``peers[c]`` the device addresses
+    of the other ranks' buffer ``c`` in this process, in rank order without this rank."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None, copies: int = 2):
+        import ctypes
+        from . import _lib
+        self._lib = _lib.load()
+        self.device = torch.device(device)
+        self.nbytes = int(nbytes)
+        self.group = group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self._own, self._opened, self.local, self.peers = [], [], [], []
+        dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._dev_index = dev_index
+        for _ in range(copies):
+            ptr = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(self._lib.sacq_peer_buffer_create(dev_index, self.nbytes, ctypes.byref(ptr), handle))
+            self._own.append(ptr.value)
+            everyone = [None] * world
+            dist.all_gather_object(everyone, handle.raw, group=group)
+            addrs = []
+            for r in range(world):
+                if r == rank:
+                    continue
+                p = ctypes.c_void_p()
+                _lib.check(self._lib.sacq_peer_buffer_open(dev_index, everyone[r], ctypes.byref(p)))
+                self._opened.append(p.value)
+                addrs.append(p.value)
+            self.peers.append(addrs)
+            self.local.append(torch.as_tensor(_RawCuda(ptr.value, self.nbytes), device=self.device))
+
+    def close(self):
+        """Unmap the peers' buffers and free this rank's (collective: every rank calls it)."""
+        if self._lib is None:
+            return
+        torch.cuda.synchronize(self.device)
+        for p in self._opened:
+            self._lib.sacq_peer_buffer_close(self._dev_index, p)
+        dist.barrier(group=self.group)                 # nobody still maps a buffer that is about to go
+        for p in self._own:
+            self._lib.sacq_peer_buffer_destroy(self._dev_index, p)
+        self._own, self._opened, self.local, self.peers, self._lib = [], [], [], [], None
+
+
 class ColumnParallelCodebookLinear(torch.nn.Module):
     """One rank's slice of a quantized linear plus the all-gather of the result.
 
@@ -83,7 +145,8 @@ class ColumnParallelCodebookLinear(torch.nn.Module):
     ``[..., N]`` output on every rank.  ``chunks > 1`` splits the token dimension so the
     gather of one chunk overlaps the GEMM of the next."""
 
-    def __init__(self, payload: dict, bias: torch.Tensor | None, device: str, group=None, chunks: int = 1):
+    def __init__(self, payload: dict, bias: torch.Tensor | None, device: str, group=None, chunks: int = 1,
+                 fused_exchange: bool = False, max_tokens: int = 8192):
         super().__init__()
         from .linear import PrecomputedPackedVectorCodebookLinear
         self.group = group
@@ -97,12 +160,56 @@ class ColumnParallelCodebookLinear(torch.nn.Module):
                                                            device)
         self.chunks = max(1, int(chunks))
         self._comm_stream = None
+        self.fused_exchange = bool(fused_exchange) and self.world > 1
+        self.max_tokens = int(max_tokens)
+        self._peer = None
+        self._turn = 0
+        if self.fused_exchange:
+            self._peer = PeerBuffers(self.max_tokens * self.out_features * 2, torch.device(device), group)
+            self._order = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def close(self):
+        if self._peer is not None:
+            self._peer.close()
+            self._peer = None
+
+    def _forward_fused(self, a: torch.Tensor) -> torch.Tensor:
+        """GEMM with the exchange in its epilogue.  Returns a view of one of the two mapped
+        result buffers: it stays valid until the call after the next one."""
+        import ctypes
+        from . import _lib
+        from .activation import quantize_rows
+        from .linear import _Workspace, _stream_ptr
+        m, n = a.shape[0], self.out_features
+        if m > self.max_tokens:
+            raise ValueError(f"{m} tokens exceed max_tokens={self.max_tokens} of the mapped result buffers")
+        if a.dtype != torch.bfloat16:
+            a = a.to(torch.bfloat16)
+        q, s = quantize_rows(a.contiguous() if a.stride(-1) != 1 else a)
+        c = self._turn
+        self._turn ^= 1
+        col0 = self.rank * (n // self.world)
+        full = self._peer.local[c][: m * n * 2].view(torch.bfloat16).view(m, n)
+        lib, layer = self.local._lib, self.local
+        peers = (ctypes.c_void_p * (self.world - 1))(*[p + col0 * 2 for p in self._peer.peers[c]])
+        buf = _Workspace.get(a.device).scratch(int(lib.sacq_workspace_bytes(layer._handle, m)))
+        with torch.cuda.device(a.device):
+            _lib.check(lib.sacq_linear_a8_bcast(layer._handle, q.data_ptr(), s.data_ptr(), m,
+                                                full.data_ptr() + col0 * 2, peers, self.world - 1, n,
+                                                buf.data_ptr(), buf.numel(), _stream_ptr()))
+        # orders the ranks: when it completes here, every rank's kernel (and its peer stores) has
+        dist.all_reduce(self._order, group=self.group)
+        return full
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         a = x.reshape(-1, self.in_features)
         m = a.shape[0]
         if self.world == 1:
             return self.local(x)
+        if self.fused_exchange:
+            full = self._forward_fused(a)
+            full = full if x.dtype == torch.bfloat16 else full.to(x.dtype)
+            return full.reshape(*x.shape[:-1], self.out_features)
         n_local = self.out_features // self.world
         if self.chunks == 1 or m < self.chunks:
             full = gather_columns(self.local(a), self.group)

@@ -265,7 +265,8 @@ SACQ_API int64_t sacq_workspace_bytes(const sacq_layer_t* L, int64_t M) {
 namespace {
 // Common body of sacq_linear_a8 and sacq_linear_a8_residual.
 int linear_a8_impl(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, const void* residual,
-                   int64_t ldr, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream) {
+                   int64_t ldr, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream,
+                   const BcastDst* bc = nullptr) {
   if (int rc = check_layer(L)) return rc;
   if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
   if (M == 0 || L->d.out_features == 0) return SACQ_OK;
@@ -281,20 +282,26 @@ int linear_a8_impl(const sacq_layer_t* L, const void* q, const float* scale, int
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int k = pick_kernel(L, M);
   if (k < 0) return set_error(k, "no kernel can run this layer geometry");
-  if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s, residual, ldr);
+  if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s, residual, ldr, bc);
   if (k == 3) {
     if (workspace == nullptr || workspace_bytes < kCounterBytes)
       return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
                        (long long)sacq_workspace_bytes(L, M), (long long)workspace_bytes);
     return launch_large_m_grouped(L, q, scale, M, y_out, ldy, static_cast<uint8_t*>(workspace) + kCounterBytes,
-                                  workspace_bytes - kCounterBytes, s, residual, ldr);
+                                  workspace_bytes - kCounterBytes, s, residual, ldr, 0, bc);
   }
   const int64_t slab = small_m_slab_rows(L);
   for (int64_t m0 = 0; m0 < M; m0 += slab) {
     const int64_t rows = (M - m0) < slab ? (M - m0) : slab;
+    BcastDst slab_bc{};
+    if (bc != nullptr) {
+      slab_bc.n = bc->n;
+      for (int i = 0; i < bc->n; ++i) slab_bc.ptr[i] = static_cast<uint16_t*>(bc->ptr[i]) + m0 * ldy;
+    }
     const int rc = launch_small_m(L, static_cast<const uint8_t*>(q) + m0 * L->d.in_features, scale + m0, rows,
                                   static_cast<uint16_t*>(y_out) + m0 * ldy, ldy, workspace, workspace_bytes, s,
-                                  residual ? static_cast<const uint16_t*>(residual) + m0 * ldr : nullptr, ldr);
+                                  residual ? static_cast<const uint16_t*>(residual) + m0 * ldr : nullptr, ldr, 0,
+                                  bc ? &slab_bc : nullptr);
     if (rc != SACQ_OK) return rc;
   }
   return SACQ_OK;
@@ -366,6 +373,65 @@ SACQ_API int sacq_linear_a8i(const sacq_layer_t* L, const void* q_int8, const fl
 SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,
                    void* workspace, int64_t workspace_bytes, void* stream) {
   return linear_a8_impl(L, q, scale, M, nullptr, 0, y_out, ldy, workspace, workspace_bytes, stream);
+}
+
+SACQ_API int sacq_linear_a8_bcast(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out,
+                                  void* const* peer_outs, int num_peers, int64_t ldy, void* workspace,
+                                  int64_t workspace_bytes, void* stream) {
+  if (num_peers < 0 || num_peers > kMaxBcast)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "num_peers=%d outside [0, %d]", num_peers, kMaxBcast);
+  if (num_peers > 0 && peer_outs == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "peer_outs is null");
+  BcastDst bc{};
+  bc.n = num_peers;
+  for (int i = 0; i < num_peers; ++i) {
+    if (peer_outs[i] == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "peer output %d is null", i);
+    bc.ptr[i] = peer_outs[i];
+  }
+  return linear_a8_impl(L, q, scale, M, nullptr, 0, y_out, ldy, workspace, workspace_bytes, stream, &bc);
+}
+
+// ---- buffers that other processes of the node can map (CUDA IPC) -------------------------
+SACQ_API int sacq_peer_buffer_create(int device, int64_t bytes, void** dev_ptr, void* handle_out) {
+  if (dev_ptr == nullptr || handle_out == nullptr || bytes <= 0)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument or non-positive size");
+  DeviceGuard guard(device);
+  if (!guard.ok) return set_error(SACQ_ERR_CUDA, "cannot make device %d current", device);
+  void* p = nullptr;
+  SACQ_CUDA_TRY(cudaMalloc(&p, (size_t)bytes));
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "cudaIpcGetMemHandle");
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == SACQ_PEER_HANDLE_BYTES, "handle size");
+  memcpy(handle_out, &h, sizeof(h));
+  *dev_ptr = p;
+  return SACQ_OK;
+}
+
+SACQ_API int sacq_peer_buffer_open(int device, const void* handle, void** dev_ptr) {
+  if (dev_ptr == nullptr || handle == nullptr) return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard guard(device);
+  if (!guard.ok) return set_error(SACQ_ERR_CUDA, "cannot make device %d current", device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  SACQ_CUDA_TRY(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return SACQ_OK;
+}
+
+SACQ_API int sacq_peer_buffer_close(int device, void* dev_ptr) {
+  if (dev_ptr == nullptr) return SACQ_OK;
+  DeviceGuard guard(device);
+  SACQ_CUDA_TRY(cudaIpcCloseMemHandle(dev_ptr));
+  return SACQ_OK;
+}
+
+SACQ_API int sacq_peer_buffer_destroy(int device, void* dev_ptr) {
+  if (dev_ptr == nullptr) return SACQ_OK;
+  DeviceGuard guard(device);
+  SACQ_CUDA_TRY(cudaFree(dev_ptr));
+  return SACQ_OK;
 }
 
 SACQ_API int sacq_linear_a8_residual(const sacq_layer_t* L, const void* q, const float* scale, int64_t M,

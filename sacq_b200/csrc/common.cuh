@@ -68,24 +68,32 @@ bool small_m_supported(const sacq_layer* L);
 // Kernel selector (5 = fp16 warp-MMA, 3 = CUDA-core) of the small-M variant that takes int8 activations.
 int small_m_int8_selector(const sacq_layer* L);
 int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M);
+// Further copies of a GEMM's output, written by the same epilogue: buffers of other GPUs of the
+// node mapped into this process (plain peer stores over NVLink), same row pitch as y.
+constexpr int kMaxBcast = 7;
+struct BcastDst {
+  void* ptr[kMaxBcast];
+  int n;
+};
+
 // `residual` (bf16 [M, ldr], may be null) is added to the rounded output in every GEMM epilogue.
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0,
-                   int act_int8 = 0);
+                   int act_int8 = 0, const BcastDst* bc = nullptr);
 
 int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
                          void* const* ys, const int64_t* ldys, cudaStream_t s);
 
 bool large_m_supported(const sacq_layer* L);
 int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                   cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0);
+                   cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0, const BcastDst* bc = nullptr);
 void large_m_release(sacq_layer* L);
 
 bool large_m_grouped_supported(const sacq_layer* L);
 int64_t large_m_grouped_workspace_bytes(const sacq_layer* L, int64_t M);
 int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                            void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr,
-                           int64_t ldr = 0, int act_int8 = 0);
+                           int64_t ldr = 0, int act_int8 = 0, const BcastDst* bc = nullptr);
 
 // ----------------------------------------------------------------------------
 // device side

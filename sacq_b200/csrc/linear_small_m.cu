@@ -581,7 +581,8 @@ SmallMParams fill_params(const sacq_layer* L, const Plan& pl, const void* q, con
 }  // namespace
 
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
-                   void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr, int act_int8) {
+                   void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr, int act_int8,
+                   const BcastDst* bc) {
   const sacq_layer_desc& d = L->d;
   if (M == 0 || d.out_features == 0) return SACQ_OK;
   if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
@@ -604,6 +605,10 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   p.residual = static_cast<const uint16_t*>(residual);
   p.ldr = ldr;
   p.act_int8 = act_int8;
+  if (bc != nullptr) {
+    p.n_bc = bc->n;
+    for (int i = 0; i < bc->n; ++i) p.ybc[i] = static_cast<uint16_t*>(bc->ptr[i]);
+  }
   if (act_int8 && pl.mma && (pl.staged || pl.unpacked))
     return set_error(SACQ_ERR_UNSUPPORTED, "the FP8 warp-MMA variants cannot take int8 activations");
   cudaError_t e;

@@ -47,6 +47,8 @@ struct SmallMParams {
   float out_mul;               // 2^-cb_exp_shift (fast) or 1 (generic)
   float shift;
   int act_int8;                // activations are int8 (the deployed recipe) instead of e4m3
+  int n_bc;                    // further copies of the output (peer GPUs' buffers), same pitch as y
+  uint16_t* ybc[kMaxBcast];
 };
 
 // Up to four layers sharing one set of quantized activations in a single launch of the staged
@@ -76,6 +78,7 @@ __device__ __forceinline__ void store_out(const SmallMParams& p, int64_t m, int6
   if (p.residual != nullptr)
     o = float_to_bf16_bits(__fadd_rn(bf16_bits_to_float(o), bf16_bits_to_float(__ldg(p.residual + m * p.ldr + n))));
   p.y[m * p.ldy + n] = o;
+  for (int i = 0; i < p.n_bc; ++i) p.ybc[i][m * p.ldy + n] = o;
 }
 
 __device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }

@@ -151,6 +151,50 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+// AND of a predicate over the 256 expander threads (named barrier 1): makes a per-thread
+// "every wait succeeded" flag uniform before code that uses expander_barrier().
+__device__ __forceinline__ bool expander_all(bool v) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "barrier.cta.red.and.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)v), "n"(kExpanderThreads)
+      : "memory");
+  return r != 0;
+}
+
+// Epilogue, second half: the expander warps have staged a [128 rows][BN] bf16 tile in shared
+// memory (row pitch `pitch` bytes); all 256 of their threads store it with 16-byte chunks that
+// are consecutive within a row, so a warp writes whole 256-byte row segments -- to y and to
+// every further copy of the output (peer GPUs' buffers: large contiguous stores are what
+// NVLink moves efficiently).  `et` = thread index among the expanders.
+template <int BN>
+__device__ __forceinline__ void store_staged_tile(const uint8_t* stg, int pitch, int et, int m_first, int M, int n0, int N,
+                                                  uint16_t* y, int64_t ldy, uint16_t* const* ybc, int n_bc) {
+  constexpr int CH = BN / 8;                          // 16-byte chunks per row
+  for (int idx = et; idx < kBM * CH; idx += kExpanderThreads) {
+    const int row = idx / CH, ch = idx - row * CH;
+    const int m = m_first + row, n = n0 + ch * 8;
+    if (m >= M || n >= N) continue;
+    const uint4 v = *reinterpret_cast<const uint4*>(stg + row * pitch + ch * 16);
+    const int64_t off = (int64_t)m * ldy + n;
+    for (int i = -1; i < n_bc; ++i) {
+      uint16_t* dst = (i < 0 ? y : ybc[i]) + off;
+      if (n + 8 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        *reinterpret_cast<uint4*>(dst) = v;
+      } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (n + e < N) dst[e] = (uint16_t)(w[e >> 1] >> (16 * (e & 1)));
+      }
+    }
+  }
+}
+
 }  // namespace umma
 
 // 2-D byte tensor [rows][row_bytes] with a [box_rows][box_bytes] box (linear_large_m.cu).

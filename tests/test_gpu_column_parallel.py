@@ -35,6 +35,17 @@ def _worker(rank, world, port, ret):
             got = split(x)
             torch.cuda.synchronize()
             ok = ok and tuple(got.shape) == (m, n) and torch.equal(got, want)
+            # the exchange inside the GEMM epilogue (peer stores into IPC-mapped buffers): same bytes,
+            # also on the second and third call (the two result buffers alternate)
+            fused = ColumnParallelCodebookLinear(payload, bias, f"cuda:{rank}", fused_exchange=True, max_tokens=m)
+            for rep in range(3):
+                got2 = fused(x)
+                torch.cuda.synchronize()
+                ok = ok and tuple(got2.shape) == (m, n) and torch.equal(got2, want)
+            x2 = make_activations(max(1, m // 2), k, seed=m + 1).cuda()
+            ok = ok and torch.equal(fused(x2), full(x2))
+            torch.cuda.synchronize()
+            fused.close()
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
