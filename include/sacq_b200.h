@@ -170,6 +170,16 @@ SACQ_API int sacq_linear_a8i(const sacq_layer_t* layer, const void* q_int8, cons
 SACQ_API int sacq_act_quant_fp8(int kind, const void* a_bf16, int64_t a_pitch, const void* b_bf16, int64_t b_pitch,
                                 int64_t M, int64_t K, void* q_out, float* scale_out, void* stream);
 
+/* AdaLN modulation fused into the quantizer (the reference fuses the same stage,
+ * codex_adaln_sharedmax_fusion_20261029_r2.py): for a normalised input x [M, K] and per-channel
+ * vectors scale, shift [K] (bf16),
+ *   y = bf16( bf16( x * bf16(1 + scale) ) + shift )
+ * -- the three bf16 roundings of `x * (1 + scale) + shift` as tensor operations -- followed by
+ * sacq_quant_act_fp8's arithmetic on y, in one launch. */
+SACQ_API int sacq_modulate_quant_fp8(const void* x_bf16, int64_t x_pitch, const void* scale_vec_bf16,
+                                     const void* shift_vec_bf16, int64_t M, int64_t K, void* q_out, float* scale_out,
+                                     void* stream);
+
 /* sacq_linear_a8 with a residual added in the GEMM epilogue, as the reference's down-projection
  * epilogue does (int8_ffdown_residual_epilogue_20261028_r2.py:8-24):
  *   y[m,n] = bf16( bf16( s[m] * sum_k q[m,k] * W[n,k] + bias[n] ) + residual[m,n] )

@@ -69,3 +69,27 @@ def act_quantize_rows(kind: str, a: torch.Tensor, b: torch.Tensor | None = None)
                                               b.stride(0) if kind == "silu_mul" else 0, m, k, q.data_ptr(),
                                               s.data_ptr(), torch.cuda.current_stream().cuda_stream))
     return q.view(torch.float8_e4m3fn), s
+
+
+def modulate_quantize_rows(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor):
+    """AdaLN modulation fused into the quantizer (``sacq_modulate_quant_fp8``): the bytes of
+    ``quantize_rows(x * (1 + scale) + shift)`` for bf16 ``x [M, K]`` and bf16 vectors
+    ``scale, shift [K]``, in one launch."""
+    if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_cuda:
+        raise TypeError("modulate_quantize_rows expects a 2-D bfloat16 CUDA tensor")
+    k = x.shape[1]
+    for v in (scale, shift):
+        if v.dtype != torch.bfloat16 or v.numel() != k or v.device != x.device:
+            raise TypeError("scale and shift must be bfloat16 vectors of K elements on x's device")
+    scale, shift = scale.reshape(-1).contiguous(), shift.reshape(-1).contiguous()
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    lib = _lib.load()
+    m = x.shape[0]
+    q = torch.empty((m, k), dtype=torch.uint8, device=x.device)
+    s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
+    if m > 0 and k > 0:
+        with torch.cuda.device(x.device):
+            _lib.check(lib.sacq_modulate_quant_fp8(x.data_ptr(), x.stride(0), scale.data_ptr(), shift.data_ptr(), m, k,
+                                                   q.data_ptr(), s.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return q.view(torch.float8_e4m3fn), s

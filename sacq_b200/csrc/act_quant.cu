@@ -171,33 +171,38 @@ namespace {
 
 __device__ __forceinline__ float round_bf16(float v) { return bf16_bits_to_float(float_to_bf16_bits(v)); }
 
-// KIND 0: bf16(bf16(silu(a)) * b); KIND 1: bf16(gelu(a)), erf form.
+// KIND 0: bf16(bf16(silu(a)) * b); KIND 1: bf16(gelu(a)), erf form;
+// KIND 2: bf16(bf16(a * bf16(1 + b)) + c), the AdaLN modulation a * (1 + scale) + shift.
 template <int KIND>
-__device__ __forceinline__ float act_value(float a, float b) {
+__device__ __forceinline__ float act_value(float a, float b, float c) {
   if constexpr (KIND == 0) {
     const float s = round_bf16(a / (1.0f + expf(-a)));
     return round_bf16(s * b);
-  } else {
+  } else if constexpr (KIND == 1) {
     return round_bf16(a * 0.5f * (1.0f + erff(a * 0.70710678118654752440f)));
+  } else {
+    return round_bf16(round_bf16(a * round_bf16(1.0f + b)) + c);
   }
 }
 
 template <int KIND>
 __global__ void __launch_bounds__(kThreads)
 act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint16_t* __restrict__ b, int64_t b_pitch,
-                     int64_t K, uint8_t* __restrict__ q, float* __restrict__ scale_out) {
+                     const uint16_t* __restrict__ c, int64_t K, uint8_t* __restrict__ q,
+                     float* __restrict__ scale_out) {
   extern __shared__ uint16_t yrow[];                  // the row's bf16 values, kept on chip between the passes
   __shared__ float red[kThreads / 32];
   __shared__ float s_scale;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t m = blockIdx.x;
   const uint16_t* arow = a + m * a_pitch;
-  const uint16_t* brow = KIND == 0 ? b + m * b_pitch : nullptr;
+  const uint16_t* brow = KIND == 1 ? nullptr : b + m * b_pitch;      // pitch 0: one vector for every row
   float mx = 0.f;
   for (int64_t k = threadIdx.x; k < K; k += kThreads) {
     const float av = bf16_bits_to_float(__ldg(arow + k));
-    const float bv = KIND == 0 ? bf16_bits_to_float(__ldg(brow + k)) : 0.f;
-    const float y = act_value<KIND>(av, bv);
+    const float bv = KIND == 1 ? 0.f : bf16_bits_to_float(__ldg(brow + k));
+    const float cv = KIND == 2 ? bf16_bits_to_float(__ldg(c + k)) : 0.f;
+    const float y = act_value<KIND>(av, bv, cv);
     yrow[k] = float_to_bf16_bits(y);
     mx = fmaxf(mx, fabsf(y));
   }
@@ -231,31 +236,33 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
 
 }  // namespace
 
-int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, int64_t M, int64_t K,
-                         void* q, float* scale, cudaStream_t s) {
+int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, const void* c,
+                         int64_t M, int64_t K, void* q, float* scale, cudaStream_t s) {
   if (M == 0 || K == 0) return SACQ_OK;
   if (M > 2147483647LL) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   const size_t smem = (size_t)K * sizeof(uint16_t);
   if (smem > 200 * 1024) return set_error(SACQ_ERR_UNSUPPORTED, "K=%lld: a row does not fit shared memory", (long long)K);
-  static bool configured[2][64] = {};
+  static bool configured[3][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  const int ki = kind == 0 ? 0 : 1;
+  const int ki = kind;
   if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[ki][dev])) {
-    const cudaError_t e = ki == 0 ? cudaFuncSetAttribute(act_quant_fp8_kernel<0>,
-                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
-                                  : cudaFuncSetAttribute(act_quant_fp8_kernel<1>,
-                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    const void* fn = ki == 0 ? (const void*)act_quant_fp8_kernel<0>
+                             : (ki == 1 ? (const void*)act_quant_fp8_kernel<1> : (const void*)act_quant_fp8_kernel<2>);
+    const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
     if (dev >= 0 && dev < 64) configured[ki][dev] = true;
   }
+  const uint16_t* ap = static_cast<const uint16_t*>(a);
+  const uint16_t* bp = static_cast<const uint16_t*>(b);
+  const uint16_t* cp = static_cast<const uint16_t*>(c);
+  uint8_t* qp = static_cast<uint8_t*>(q);
   if (ki == 0)
-    act_quant_fp8_kernel<0><<<(unsigned)M, kThreads, smem, s>>>(static_cast<const uint16_t*>(a), a_pitch,
-                                                               static_cast<const uint16_t*>(b), b_pitch, K,
-                                                               static_cast<uint8_t*>(q), scale);
+    act_quant_fp8_kernel<0><<<(unsigned)M, kThreads, smem, s>>>(ap, a_pitch, bp, b_pitch, nullptr, K, qp, scale);
+  else if (ki == 1)
+    act_quant_fp8_kernel<1><<<(unsigned)M, kThreads, smem, s>>>(ap, a_pitch, nullptr, 0, nullptr, K, qp, scale);
   else
-    act_quant_fp8_kernel<1><<<(unsigned)M, kThreads, smem, s>>>(static_cast<const uint16_t*>(a), a_pitch, nullptr, 0, K,
-                                                               static_cast<uint8_t*>(q), scale);
+    act_quant_fp8_kernel<2><<<(unsigned)M, kThreads, smem, s>>>(ap, a_pitch, bp, 0, cp, K, qp, scale);
   count_launch();
   SACQ_CUDA_TRY(cudaGetLastError());
   return SACQ_OK;

@@ -237,7 +237,22 @@ SACQ_API int sacq_act_quant_fp8(int kind, const void* a_bf16, int64_t a_pitch, c
     return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
   if (a_pitch < K || (kind == SACQ_ACT_SILU_MUL && b_pitch < K))
     return set_error(SACQ_ERR_INVALID_ARGUMENT, "row pitch smaller than K=%lld", (long long)K);
-  return launch_act_quant_fp8(kind, a_bf16, a_pitch, b_bf16, b_pitch, M, K, q_out, scale_out,
+  return launch_act_quant_fp8(kind, a_bf16, a_pitch, b_bf16, b_pitch, nullptr, M, K, q_out, scale_out,
+                              static_cast<cudaStream_t>(stream));
+}
+
+SACQ_API int sacq_modulate_quant_fp8(const void* x_bf16, int64_t x_pitch, const void* scale_vec_bf16,
+                                     const void* shift_vec_bf16, int64_t M, int64_t K, void* q_out, float* scale_out,
+                                     void* stream) {
+  if (M < 0 || K < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "negative size (M=%lld K=%lld)", (long long)M,
+                                       (long long)K);
+  if (M == 0) return SACQ_OK;
+  if (K == 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "K must be positive");
+  if (x_bf16 == nullptr || scale_vec_bf16 == nullptr || shift_vec_bf16 == nullptr || q_out == nullptr ||
+      scale_out == nullptr)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (x_pitch < K) return set_error(SACQ_ERR_INVALID_ARGUMENT, "row pitch smaller than K=%lld", (long long)K);
+  return launch_act_quant_fp8(2, x_bf16, x_pitch, scale_vec_bf16, 0, shift_vec_bf16, M, K, q_out, scale_out,
                               static_cast<cudaStream_t>(stream));
 }
 

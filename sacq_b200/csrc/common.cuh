@@ -59,8 +59,8 @@ int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s);
 int launch_decode_weight_fp8(const sacq_layer* L, const float* sw, void* wq, cudaStream_t s);
 int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
 int launch_quant_act_int8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
-int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, int64_t M, int64_t K,
-                         void* q, float* scale, cudaStream_t s);
+int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, const void* c,
+                         int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
 int launch_build_tables(sacq_layer* L, cudaStream_t s);
 int launch_copy_to_host(const void* src, void* dst, int64_t bytes, int num_sms, cudaStream_t s);
 

@@ -22,8 +22,8 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .activation import act_quantize_rows
-from .linear import PrecomputedPackedVectorCodebookLinear, forward_shared
+from .activation import act_quantize_rows, modulate_quantize_rows
+from .linear import PrecomputedPackedVectorCodebookLinear, forward_shared, linear_a8_multi
 from .synthetic import make_payload
 
 
@@ -90,23 +90,28 @@ class _Block(torch.nn.Module):
 
     def forward(self, x, cond=None, cross_kv=None):
         if self.adaln:
+            # AdaLN: norm(x) * (1 + scale) + shift runs inside the quantizer of the projections it feeds
             m = self.mod(cond).view(4, self.hidden)
-            h = self.n1(x) * (1 + m[1]) + m[0]
+            qa, sa = modulate_quantize_rows(self.n1(x), m[1], m[0])
+            q, k, v = linear_a8_multi((self.q, self.k, self.v), qa, sa)
         else:
-            h = self.n1(x)
-        q, k, v = forward_shared((self.q, self.k, self.v), h)      # one activation quantization for q/k/v
+            q, k, v = forward_shared((self.q, self.k, self.v), self.n1(x))   # one quantization for q/k/v
         x = self.o.forward_residual(self._attend(q, k, v), x)            # residual added in the GEMM epilogue
         if self.cross:
             h = self.n3(x)
             x = self.co.forward_residual(self._attend(self.cq(h), cross_kv[0], cross_kv[1]), x)
-        h = self.n2(x) * (1 + m[3]) + m[2] if self.adaln else self.n2(x)
         # the activation function runs inside the quantizer of the down projection
         if self.gated:
-            gate, up = forward_shared((self.gate, self.up), h)
-            q, s = act_quantize_rows("silu_mul", gate, up)
+            gate, up = forward_shared((self.gate, self.up), self.n2(x))
+            qd, sd = act_quantize_rows("silu_mul", gate, up)
         else:
-            q, s = act_quantize_rows("gelu", self.up(h))
-        return self.down.linear_a8(q, s, residual=x)
+            if self.adaln:
+                qu, su = modulate_quantize_rows(self.n2(x), m[3], m[2])
+                up = self.up.linear_a8(qu, su)
+            else:
+                up = self.up(self.n2(x))
+            qd, sd = act_quantize_rows("gelu", up)
+        return self.down.linear_a8(qd, sd, residual=x)
 
 
 class SyntheticGr00tPolicy(torch.nn.Module):

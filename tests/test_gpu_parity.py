@@ -548,6 +548,24 @@ def test_linear_int8_activations(N, K, d, C, G):
     assert mod.device_status() == 0
 
 
+@pytest.mark.parametrize("M,K", [(16, 1536), (1, 2048), (300, 1024), (5, 100)])
+def test_modulation_fused_into_quantizer(M, K):
+    """x * (1 + scale) + shift fused into the quantizer: bytes and scales of quantizing the
+    result of the three bf16 tensor operations."""
+    _need_gpu()
+    from sacq_b200 import modulate_quantize_rows, quantize_rows
+    g = torch.Generator().manual_seed(M + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    sc = (torch.randn(K, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    sh = (torch.randn(K, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    q, s = modulate_quantize_rows(x, sc, sh)
+    qr, sr = quantize_rows(x * (1 + sc) + sh)
+    assert torch.equal(s.view(torch.int32), sr.view(torch.int32))
+    assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+    with pytest.raises(TypeError):
+        modulate_quantize_rows(x, sc[:-1], sh)
+
+
 def test_linear_properties_and_edges():
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
