@@ -185,12 +185,14 @@ __device__ __forceinline__ float act_value(float a, float b, float c) {
   }
 }
 
-template <int KIND>
+// VEC: every row of a, b, c and q is 16-byte (q: 8-byte) aligned and K % 8 == 0: 8 elements per
+// load and store instead of one.
+template <int KIND, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint16_t* __restrict__ b, int64_t b_pitch,
                      const uint16_t* __restrict__ c, int64_t K, uint8_t* __restrict__ q,
                      float* __restrict__ scale_out) {
-  extern __shared__ uint16_t yrow[];                  // the row's bf16 values, kept on chip between the passes
+  extern __shared__ __align__(16) uint16_t yrow[];    // the row's bf16 values, kept on chip between the passes
   __shared__ float red[kThreads / 32];
   __shared__ float s_scale;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -198,13 +200,35 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
   const uint16_t* arow = a + m * a_pitch;
   const uint16_t* brow = KIND == 1 ? nullptr : b + m * b_pitch;      // pitch 0: one vector for every row
   float mx = 0.f;
-  for (int64_t k = threadIdx.x; k < K; k += kThreads) {
-    const float av = bf16_bits_to_float(__ldg(arow + k));
-    const float bv = KIND == 1 ? 0.f : bf16_bits_to_float(__ldg(brow + k));
-    const float cv = KIND == 2 ? bf16_bits_to_float(__ldg(c + k)) : 0.f;
-    const float y = act_value<KIND>(av, bv, cv);
-    yrow[k] = float_to_bf16_bits(y);
-    mx = fmaxf(mx, fabsf(y));
+  if constexpr (VEC) {
+    for (int64_t ch = threadIdx.x; ch < (K >> 3); ch += kThreads) {
+      const uint4 a4 = __ldg(reinterpret_cast<const uint4*>(arow) + ch);
+      uint4 b4 = make_uint4(0, 0, 0, 0), c4 = make_uint4(0, 0, 0, 0);
+      if constexpr (KIND != 1) b4 = __ldg(reinterpret_cast<const uint4*>(brow) + ch);
+      if constexpr (KIND == 2) c4 = __ldg(reinterpret_cast<const uint4*>(c) + ch);
+      const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w}, bw[4] = {b4.x, b4.y, b4.z, b4.w},
+                     cw[4] = {c4.x, c4.y, c4.z, c4.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float y0 = act_value<KIND>(bf16_bits_to_float(aw[j] & 0xffff), bf16_bits_to_float(bw[j] & 0xffff),
+                                         bf16_bits_to_float(cw[j] & 0xffff));
+        const float y1 = act_value<KIND>(bf16_bits_to_float(aw[j] >> 16), bf16_bits_to_float(bw[j] >> 16),
+                                         bf16_bits_to_float(cw[j] >> 16));
+        mx = fmaxf(mx, fmaxf(fabsf(y0), fabsf(y1)));
+        o[j] = (uint32_t)float_to_bf16_bits(y0) | ((uint32_t)float_to_bf16_bits(y1) << 16);
+      }
+      reinterpret_cast<uint4*>(yrow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  } else {
+    for (int64_t k = threadIdx.x; k < K; k += kThreads) {
+      const float av = bf16_bits_to_float(__ldg(arow + k));
+      const float bv = KIND == 1 ? 0.f : bf16_bits_to_float(__ldg(brow + k));
+      const float cv = KIND == 2 ? bf16_bits_to_float(__ldg(c + k)) : 0.f;
+      const float y = act_value<KIND>(av, bv, cv);
+      yrow[k] = float_to_bf16_bits(y);
+      mx = fmaxf(mx, fabsf(y));
+    }
   }
   mx = warp_max(mx);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
@@ -221,6 +245,23 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
   __syncthreads();
   const float s = s_scale;
   uint8_t* qrow = q + m * K;
+  if constexpr (VEC) {
+    for (int64_t ch = threadIdx.x; ch < (K >> 3); ch += kThreads) {
+      const uint4 y4 = reinterpret_cast<const uint4*>(yrow)[ch];
+      const uint32_t w[4] = {y4.x, y4.y, y4.z, y4.w};
+      uint32_t o[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t lo = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] & 0xffff), s)),
+                                             clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] >> 16), s)));
+        const uint32_t hi = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] & 0xffff), s)),
+                                             clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] >> 16), s)));
+        o[j] = lo | (hi << 16);
+      }
+      *(reinterpret_cast<uint2*>(qrow) + ch) = make_uint2(o[0], o[1]);
+    }
+    return;
+  }
   for (int64_t k2 = 2 * (int64_t)threadIdx.x; k2 < K; k2 += 2 * kThreads) {
     const float y0 = bf16_bits_to_float(yrow[k2]);
     const float y1 = k2 + 1 < K ? bf16_bits_to_float(yrow[k2 + 1]) : 0.f;
@@ -242,27 +283,29 @@ int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b
   if (M > 2147483647LL) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   const size_t smem = (size_t)K * sizeof(uint16_t);
   if (smem > 200 * 1024) return set_error(SACQ_ERR_UNSUPPORTED, "K=%lld: a row does not fit shared memory", (long long)K);
-  static bool configured[3][64] = {};
+  const bool vec = (K % 8 == 0) && (a_pitch % 8 == 0) && (reinterpret_cast<uintptr_t>(a) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(q) % 8 == 0) &&
+                   (kind == 1 || ((kind == 2 || b_pitch % 8 == 0) && reinterpret_cast<uintptr_t>(b) % 16 == 0)) &&
+                   (kind != 2 || reinterpret_cast<uintptr_t>(c) % 16 == 0);
+  const void* fns[3][2] = {{(const void*)act_quant_fp8_kernel<0, false>, (const void*)act_quant_fp8_kernel<0, true>},
+                           {(const void*)act_quant_fp8_kernel<1, false>, (const void*)act_quant_fp8_kernel<1, true>},
+                           {(const void*)act_quant_fp8_kernel<2, false>, (const void*)act_quant_fp8_kernel<2, true>}};
+  const void* fn = fns[kind][vec ? 1 : 0];
+  static bool configured[3][2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  const int ki = kind;
-  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[ki][dev])) {
-    const void* fn = ki == 0 ? (const void*)act_quant_fp8_kernel<0>
-                             : (ki == 1 ? (const void*)act_quant_fp8_kernel<1> : (const void*)act_quant_fp8_kernel<2>);
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[kind][vec ? 1 : 0][dev])) {
     const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
-    if (dev >= 0 && dev < 64) configured[ki][dev] = true;
+    if (dev >= 0 && dev < 64) configured[kind][vec ? 1 : 0][dev] = true;
   }
   const uint16_t* ap = static_cast<const uint16_t*>(a);
-  const uint16_t* bp = static_cast<const uint16_t*>(b);
-  const uint16_t* cp = static_cast<const uint16_t*>(c);
+  const uint16_t* bp = kind == 1 ? nullptr : static_cast<const uint16_t*>(b);
+  const uint16_t* cp = kind == 2 ? static_cast<const uint16_t*>(c) : nullptr;
+  int64_t bpitch = kind == 0 ? b_pitch : 0;
   uint8_t* qp = static_cast<uint8_t*>(q);
-  if (ki == 0)
-    act_quant_fp8_kernel<0><<<(unsigned)M, kThreads, smem, s>>>(ap, a_pitch, bp, b_pitch, nullptr, K, qp, scale);
-  else if (ki == 1)
-    act_quant_fp8_kernel<1><<<(unsigned)M, kThreads, smem, s>>>(ap, a_pitch, nullptr, 0, nullptr, K, qp, scale);
-  else
-    act_quant_fp8_kernel<2><<<(unsigned)M, kThreads, smem, s>>>(ap, a_pitch, bp, 0, cp, K, qp, scale);
+  void* args[] = {&ap, &a_pitch, &bp, &bpitch, &cp, &K, &qp, &scale};
+  SACQ_CUDA_TRY(cudaLaunchKernel(fn, dim3((unsigned)M), dim3(kThreads), args, smem, s));
   count_launch();
   SACQ_CUDA_TRY(cudaGetLastError());
   return SACQ_OK;
