@@ -62,8 +62,15 @@ int64_t small_m_slab_rows(const sacq_layer* L) {
 }
 
 // Rows from which the grouped tensor-core kernel beats the index-unpacking warp-MMA kernel
-// (which walks the weights once per 16-token chunk).
-constexpr int64_t kGroupedMinM = 48;
+// (which walks the weights once per 16-token chunk).  Measured crossovers: 33 rows on layers
+// wide enough to give the tensor-core grid a CTA for most SMs (N = 6144), 48-64 rows at
+// N = 2048, about 96 rows below that.
+int64_t grouped_min_m(const sacq_layer* L) {
+  if (L->d.out_features >= 32 * (int64_t)L->num_sms) return 33;
+  return L->d.out_features >= 2048 ? 48 : 96;
+}
+// INT8 activations have no FP8 warp-MMA path, so the tensor-core kernel takes over earlier.
+constexpr int64_t kGroupedMinMInt8 = 48;
 
 int pick_kernel(const sacq_layer* L, int64_t M) {
   if (L->force_kernel == 7) return large_m_grouped_supported(L) ? 3 : SACQ_ERR_UNSUPPORTED;
@@ -78,7 +85,7 @@ int pick_kernel(const sacq_layer* L, int64_t M) {
   if (large_m_supported(L)) {
     if (M > 64) return 2;
     if (M > 32 && L->d.out_features >= 32 * (int64_t)L->num_sms) return 2;
-  } else if (M >= kGroupedMinM && large_m_grouped_supported(L)) {
+  } else if (M >= grouped_min_m(L) && large_m_grouped_supported(L)) {
     return 3;                                          // grouped scales, odd index widths, a shift
   }
   return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
@@ -345,7 +352,7 @@ SACQ_API int sacq_quant_act_int8(const void* x_bf16, int64_t x_pitch, int64_t M,
 
 SACQ_API int64_t sacq_workspace_bytes_int8(const sacq_layer_t* L, int64_t M) {
   if (L == nullptr || M < 0) return 0;
-  if (M >= kGroupedMinM && large_m_grouped_supported(L)) return kCounterBytes + large_m_grouped_workspace_bytes(L, M);
+  if (M >= kGroupedMinMInt8 && large_m_grouped_supported(L)) return kCounterBytes + large_m_grouped_workspace_bytes(L, M);
   sacq_layer view = *L;
   view.force_kernel = int8_small_selector(L);
   const int64_t slab = small_m_slab_rows(L);
@@ -364,7 +371,7 @@ SACQ_API int sacq_linear_a8i(const sacq_layer_t* L, const void* q_int8, const fl
                      (long long)L->d.out_features);
   DeviceGuard guard(L->d.device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (M >= kGroupedMinM && large_m_grouped_supported(L)) {
+  if (M >= kGroupedMinMInt8 && large_m_grouped_supported(L)) {
     if (workspace == nullptr || workspace_bytes < kCounterBytes)
       return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
                        (long long)sacq_workspace_bytes_int8(L, M), (long long)workspace_bytes);

@@ -538,18 +538,23 @@ int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scal
       widen_act_kernel<false><<<(unsigned)rows, 256, 0, s>>>(static_cast<const uint8_t*>(q) + m0 * K, K, a16, xsum);
     count_launch();
     SACQ_CUDA_TRY(cudaGetLastError());
-    // tile shape: two token sub-tiles per CTA above 128 rows; BN by waves x (fixed + per-row cost)
-    const int mt = rows > kBM ? 2 : 1;
-    const int64_t m_tiles = (rows + kBM * mt - 1) / (kBM * mt);
-    int bn = 0;
+    // Tile shape: (token sub-tiles per CTA, weight rows per CTA) with the smallest
+    // waves x time-per-CTA, where the time per CTA was fitted to measurements at K = 2048:
+    // about 1.2 us fixed + 7.8 us per token sub-tile (MMA issue, bound by the operand reads of
+    // the A tile) + 0.17 us per weight row (expansion); all three scale with K alike.
+    int mt = 1, bn = 0;
     double best = 1e30;
-    for (int cand = 128; cand >= 32; cand >>= 1) {
-      if (grouped_stages_for(L, cand, mt, 1) < 2) continue;
-      const int64_t tiles = ((N + cand - 1) / cand) * m_tiles;
-      const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
-      const double cost = (double)waves * (0.3 + 0.9 * cand / 128.0);
-      if (cost < best - 1e-9) { best = cost; bn = cand; }
+    for (int cand_mt = 1; cand_mt <= (rows > kBM ? 2 : 1); ++cand_mt) {
+      const int64_t m_tiles_c = (rows + kBM * cand_mt - 1) / (kBM * cand_mt);
+      for (int cand = 128; cand >= 32; cand >>= 1) {
+        if (grouped_stages_for(L, cand, cand_mt, 1) < 2) continue;
+        const int64_t tiles = ((N + cand - 1) / cand) * m_tiles_c;
+        const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
+        const double cost = (double)waves * (1.2 + 7.8 * cand_mt + 0.169 * cand);
+        if (cost < best - 1e-9) { best = cost; bn = cand; mt = cand_mt; }
+      }
     }
+    const int64_t m_tiles = (rows + kBM * mt - 1) / (kBM * mt);
     if (bn == 0) return set_error(SACQ_ERR_UNSUPPORTED, "grouped tensor-core kernel: no tile fits shared memory");
     CUtensorMap ta, ti;
     int rc = encode_bytes_2d(&ta, a16, (uint64_t)(K * 2), (uint64_t)rows, (uint64_t)(K * 2), 128, kBM,
