@@ -499,10 +499,14 @@ cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& ti, const LargeM
 template <int D, int BITS>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, int bn, int mt, dim3 grid,
                        cudaStream_t s) {
-  // one token sub-tile: merged high/low MMA; two sub-tiles (large grids): separate MMAs
+  // merged high/low MMA everywhere it measured faster or equal: all shapes but 2 x 128 x 128
+  if (mt == 2) {
+    if (bn == 32) return launch_bn<D, BITS, 32, 2, true>(ta, ti, p, grid, s);
+    if (bn == 64) return launch_bn<D, BITS, 64, 2, true>(ta, ti, p, grid, s);
+    return launch_bn<D, BITS, 128, 2, false>(ta, ti, p, grid, s);
+  }
   if (bn == 32) return launch_bn<D, BITS, 32, 1, true>(ta, ti, p, grid, s);
   if (bn == 64) return launch_bn<D, BITS, 64, 1, true>(ta, ti, p, grid, s);
-  if (mt == 2) return launch_bn<D, BITS, 128, 2, false>(ta, ti, p, grid, s);
   return launch_bn<D, BITS, 128, 1, true>(ta, ti, p, grid, s);
 }
 
@@ -540,18 +544,27 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
     plan->have[0] = plan->have[1] = plan->have[2] = false;
     Lm->large_plan = plan;
   }
-  // Tile width.  A CTA's time per K block is roughly a fixed pipeline latency plus the
-  // expansion of BN rows (measured: about 0.3 us + 0.9 us * BN/128), and the grid runs in
-  // ceil(tiles / SMs) waves; take the BN with the smallest product.
-  const int64_t m_tiles = (M + kBM - 1) / kBM;
-  int bn = 128;
-  double best = 1e30;
-  for (int cand = 128; cand >= 32; cand >>= 1) {
-    const int64_t tiles = ((d.out_features + cand - 1) / cand) * m_tiles;
-    const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
-    const double cost = (double)waves * (0.3 + 0.9 * cand / 128.0);
-    if (cost < best - 1e-9) { best = cost; bn = cand; }
+  // Tile shape: (token sub-tiles per CTA, weight rows per CTA) with the smallest
+  // waves x time-per-CTA.  Fitted to measurements (us): a CTA takes about
+  // 3.4 + K/2048 * (4.8 + 0.0755 * BN + 3.0 * (MT - 1)): fixed prologue/epilogue, pipeline
+  // latency per K block, expansion per weight row, MMA issue per extra sub-tile.
+  const size_t cb_bytes_sel = (size_t)d.codebook_size * d.vector_dim * 2;
+  int bn = 0, mt = 1;
+  {
+    double best = 1e30;
+    for (int cand_mt = 1; cand_mt <= (M > kBM ? 2 : 1); ++cand_mt) {
+      const int64_t m_tiles = (M + kBM * cand_mt - 1) / (kBM * cand_mt);
+      for (int cand = 128; cand >= 32; cand >>= 1) {
+        if (make_layout(cand, cand_mt, sb_bytes_for(L), (int)cb_bytes_sel).total + 1024 > 227 * 1024) continue;
+        const int64_t tiles = ((d.out_features + cand - 1) / cand) * m_tiles;
+        const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
+        const double per_cta = 3.4 + (double)d.in_features / 2048.0 * (4.8 + 0.0755 * cand + 3.0 * (cand_mt - 1));
+        const double cost = (double)waves * per_cta;
+        if (cost < best - 1e-9) { best = cost; bn = cand; mt = cand_mt; }
+      }
+    }
   }
+  if (bn == 0) return set_error(SACQ_ERR_UNSUPPORTED, "large-M kernel: no tile fits shared memory");
   const int bi = bn == 32 ? 0 : (bn == 64 ? 1 : 2);
   if (!Lm->large_plan->have[bi]) {
     const uint64_t row_bytes = (uint64_t)(L->row_bits / 8);
@@ -583,11 +596,6 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
   }
   p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features; p.C = d.codebook_size;
   p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
-  // Two M sub-tiles per CTA as soon as the halved grid still covers every SM.
-  int mt = 1;
-  if (bn == 128 && ((d.out_features + 127) / 128) * ((M + 2 * kBM - 1) / (2 * kBM)) >= (int64_t)L->num_sms &&
-      make_layout(128, 2, sb_bytes_for(L), d.codebook_size * d.vector_dim * 2).total + 1024 <= 227 * 1024)
-    mt = 2;
   const dim3 grid((unsigned)((d.out_features + bn - 1) / bn), (unsigned)((M + kBM * mt - 1) / (kBM * mt)));
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   cudaError_t e;
