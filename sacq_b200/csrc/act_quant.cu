@@ -260,17 +260,17 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
       }
       *(reinterpret_cast<uint2*>(qrow) + ch) = make_uint2(o[0], o[1]);
     }
-    return;
-  }
-  for (int64_t k2 = 2 * (int64_t)threadIdx.x; k2 < K; k2 += 2 * kThreads) {
-    const float y0 = bf16_bits_to_float(yrow[k2]);
-    const float y1 = k2 + 1 < K ? bf16_bits_to_float(yrow[k2 + 1]) : 0.f;
-    const uint32_t pair = float2_to_e4m3x2(clamp448(__fdiv_rn(y0, s)), clamp448(__fdiv_rn(y1, s)));
-    if (k2 + 1 < K && (reinterpret_cast<uintptr_t>(qrow + k2) & 1) == 0)
-      *reinterpret_cast<uint16_t*>(qrow + k2) = (uint16_t)pair;
-    else {
-      qrow[k2] = (uint8_t)(pair & 0xff);
-      if (k2 + 1 < K) qrow[k2 + 1] = (uint8_t)(pair >> 8);
+  } else {
+    for (int64_t k2 = 2 * (int64_t)threadIdx.x; k2 < K; k2 += 2 * kThreads) {
+      const float y0 = bf16_bits_to_float(yrow[k2]);
+      const float y1 = k2 + 1 < K ? bf16_bits_to_float(yrow[k2 + 1]) : 0.f;
+      const uint32_t pair = float2_to_e4m3x2(clamp448(__fdiv_rn(y0, s)), clamp448(__fdiv_rn(y1, s)));
+      if (k2 + 1 < K && (reinterpret_cast<uintptr_t>(qrow + k2) & 1) == 0)
+        *reinterpret_cast<uint16_t*>(qrow + k2) = (uint16_t)pair;
+      else {
+        qrow[k2] = (uint8_t)(pair & 0xff);
+        if (k2 + 1 < K) qrow[k2 + 1] = (uint8_t)(pair >> 8);
+      }
     }
   }
 }

@@ -40,7 +40,7 @@ __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_
 // needs neither global scratch nor arrival counters.
 template <int D, int BITS, bool CB_SMEM, int R8>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const SmallMParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;   // D halfs
   constexpr int WPG = BITS / 4;            // 32-bit words holding a lane's 8 indices
   constexpr int AREG = D / 2;              // half2 registers per activation vector
@@ -314,8 +314,6 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   extern __shared__ __align__(128) uint8_t smem[];
   using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;
   constexpr int WPG = BITS / 4;
-  constexpr int AREG = D / 2;
-  constexpr int QV = D / 4;
   constexpr int kFrag = R8 * 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nwarps = blockDim.x >> 5;
