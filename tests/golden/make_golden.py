@@ -67,7 +67,7 @@ def make_activations(m, k, seed, zero_row=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the SACQ reference tree")
     ap.add_argument("--only-int8", action="store_true", help="regenerate act_int8.npz only")
     args = ap.parse_args()
     ref = args.reference
