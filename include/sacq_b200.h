@@ -170,6 +170,19 @@ SACQ_API int sacq_linear_a8i(const sacq_layer_t* layer, const void* q_int8, cons
 SACQ_API int sacq_act_quant_fp8(int kind, const void* a_bf16, int64_t a_pitch, const void* b_bf16, int64_t b_pitch,
                                 int64_t M, int64_t K, void* q_out, float* scale_out, void* stream);
 
+/* LayerNorm, optionally followed by the AdaLN modulation, fused into the quantizer (the
+ * reference fuses these stages in codex_norm3_regpack_20261029_r1/kernel.cu:150 and
+ * codex_adaln_sharedmax_20261029_r2/kernel.cu:140):
+ *   y = bf16( (x - mean) / sqrt(var + eps) * gamma + beta )          gamma, beta: bf16 [K] or null
+ *   y = bf16( bf16( y * bf16(1 + s) ) + t )                           when mod_scale / mod_shift are given
+ * followed by sacq_quant_act_fp8's arithmetic on y.  mean and the centred variance are fp32
+ * sums over the row; their order differs from a framework LayerNorm's, so y matches it to one
+ * bf16 ulp, not to the bit.  y_out (bf16 [M, y_pitch]) receives y when it is not null. */
+SACQ_API int sacq_layernorm_quant_fp8(const void* x_bf16, int64_t x_pitch, const void* gamma_bf16, const void* beta_bf16,
+                                      float eps, const void* mod_scale_bf16, const void* mod_shift_bf16, int64_t M,
+                                      int64_t K, void* y_out_bf16, int64_t y_pitch, void* q_out, float* scale_out,
+                                      void* stream);
+
 /* AdaLN modulation fused into the quantizer (the reference fuses the same stage,
  * codex_adaln_sharedmax_fusion_20261029_r2.py): for a normalised input x [M, K] and per-channel
  * vectors scale, shift [K] (bf16),

@@ -7,7 +7,7 @@ does, and fails loudly when the CUDA library has not been built."""
 from .packing import index_bits_for, index_window_bytes, pack_indices, pack_payload, unpack_indices  # noqa: F401
 
 __all__ = [
-    "PrecomputedPackedVectorCodebookLinear", "forward_shared", "linear_a8_multi", "quantize_rows", "act_quantize_rows", "modulate_quantize_rows", "pack_indices", "unpack_indices",
+    "PrecomputedPackedVectorCodebookLinear", "forward_shared", "linear_a8_multi", "quantize_rows", "act_quantize_rows", "modulate_quantize_rows", "layernorm_quantize_rows", "pack_indices", "unpack_indices",
     "pack_payload", "index_bits_for", "index_window_bytes",
 ]
 
@@ -22,6 +22,9 @@ def __getattr__(name):
     if name == "linear_a8_multi":
         from .linear import linear_a8_multi
         return linear_a8_multi
+    if name == "layernorm_quantize_rows":
+        from .activation import layernorm_quantize_rows
+        return layernorm_quantize_rows
     if name == "modulate_quantize_rows":
         from .activation import modulate_quantize_rows
         return modulate_quantize_rows

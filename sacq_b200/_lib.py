@@ -61,6 +61,8 @@ SIGNATURES = {
     "sacq_quant_act_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _fp, _vp]),
     "sacq_workspace_bytes_int8": (_i64, [_vp, _i64]),
     "sacq_linear_a8i": (_int, [_vp, _vp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "sacq_layernorm_quant_fp8": (_int, [_vp, _i64, _vp, _vp, ctypes.c_float, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _fp,
+                                        _vp]),
     "sacq_modulate_quant_fp8": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _fp, _vp]),
     "sacq_act_quant_fp8": (_int, [_int, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _fp, _vp]),
     "sacq_weight_row_scale": (_int, [_vp, _fp, _vp]),

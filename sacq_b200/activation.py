@@ -93,3 +93,40 @@ def modulate_quantize_rows(x: torch.Tensor, scale: torch.Tensor, shift: torch.Te
             _lib.check(lib.sacq_modulate_quant_fp8(x.data_ptr(), x.stride(0), scale.data_ptr(), shift.data_ptr(), m, k,
                                                    q.data_ptr(), s.data_ptr(), torch.cuda.current_stream().cuda_stream))
     return q.view(torch.float8_e4m3fn), s
+
+
+def layernorm_quantize_rows(x: torch.Tensor, weight: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                            eps: float = 1e-5, mod_scale: torch.Tensor | None = None,
+                            mod_shift: torch.Tensor | None = None, return_normalized: bool = False):
+    """LayerNorm over the last dimension, optionally the AdaLN modulation ``y * (1 + s) + t``,
+    and the per-token FP8 quantizer in one launch (``sacq_layernorm_quant_fp8``).  Returns
+    ``(q, scale)`` or ``(q, scale, y)`` with the bf16 normalised tensor.  ``y`` agrees with
+    ``torch.nn.functional.layer_norm`` to one bf16 ulp (different reduction order); ``q`` and
+    ``scale`` are exactly ``quantize_rows(y)``."""
+    if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_cuda:
+        raise TypeError("layernorm_quantize_rows expects a 2-D bfloat16 CUDA tensor")
+    k = x.shape[1]
+    vecs = []
+    for v in (weight, bias, mod_scale, mod_shift):
+        if v is not None:
+            if v.dtype != torch.bfloat16 or v.numel() != k or v.device != x.device:
+                raise TypeError("weight, bias and modulation vectors must be bfloat16 with K elements on x's device")
+            v = v.reshape(-1).contiguous()
+        vecs.append(v)
+    if (vecs[2] is None) != (vecs[3] is None):
+        raise ValueError("modulation needs both its scale and its shift vector")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    lib = _lib.load()
+    m = x.shape[0]
+    q = torch.empty((m, k), dtype=torch.uint8, device=x.device)
+    s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
+    y = torch.empty((m, k), dtype=torch.bfloat16, device=x.device) if return_normalized else None
+    if m > 0 and k > 0:
+        ptr = [None if v is None else v.data_ptr() for v in vecs]
+        with torch.cuda.device(x.device):
+            _lib.check(lib.sacq_layernorm_quant_fp8(x.data_ptr(), x.stride(0), ptr[0], ptr[1], float(eps), ptr[2], ptr[3],
+                                                    m, k, None if y is None else y.data_ptr(), k, q.data_ptr(),
+                                                    s.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    q = q.view(torch.float8_e4m3fn)
+    return (q, s, y) if return_normalized else (q, s)

@@ -312,3 +312,118 @@ int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b
 }
 
 }  // namespace sacq
+
+// ----------------------------------------------------------------------------
+// LayerNorm (+ AdaLN modulation) fused into the quantizer.
+//
+// A pre-norm transformer block normalises its input only to feed quantized projections, so
+// the normalised tensor need not exist in memory: one launch reads x once, keeps the row in
+// shared memory, and emits the e4m3 row and its scale (the reference fuses this stage in
+// codex_norm3_regpack_20261029_r1/kernel.cu and codex_adaln_sharedmax_20261029_r2/kernel.cu
+// for its INT8 path).  Arithmetic: fp32 mean, fp32 centred variance (two passes over the
+// on-chip row), rstd = 1 / sqrt(var + eps), y = bf16((x - mean) * rstd * gamma + beta),
+// optionally the AdaLN modulation bf16(bf16(y * bf16(1 + s)) + t), then the quantizer.  The
+// reduction order differs from a framework LayerNorm's, so y agrees with it to one bf16 ulp,
+// not to the bit; the quantizer's bytes are exactly those of quantizing this kernel's own y.
+// ----------------------------------------------------------------------------
+namespace sacq {
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();                                   // red may still be read from the previous call
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) t += red[i];   // same order in every thread
+  return t;
+}
+
+template <bool MOD>
+__global__ void __launch_bounds__(kThreads)
+layernorm_quant_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, const uint16_t* __restrict__ gamma,
+                           const uint16_t* __restrict__ beta, float eps, const uint16_t* __restrict__ mod_scale,
+                           const uint16_t* __restrict__ mod_shift, int64_t K, uint16_t* __restrict__ y_out,
+                           int64_t y_pitch, uint8_t* __restrict__ q, float* __restrict__ scale_out) {
+  extern __shared__ __align__(16) float xrow[];       // the row in fp32, later its bf16 result in place
+  __shared__ float red[kThreads / 32];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int64_t m = blockIdx.x;
+  const uint16_t* row = x + m * pitch;
+  float sum = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += kThreads) {
+    const float v = bf16_bits_to_float(__ldg(row + k));
+    xrow[k] = v;
+    sum += v;
+  }
+  const float mean = block_sum(sum, red) / (float)K;
+  float sq = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += kThreads) {
+    const float dlt = xrow[k] - mean;
+    sq += dlt * dlt;
+  }
+  const float var = block_sum(sq, red) / (float)K;
+  const float rstd = 1.0f / sqrtf(var + eps);
+  float mx = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += kThreads) {
+    float y = (xrow[k] - mean) * rstd;
+    if (gamma != nullptr) y = y * bf16_bits_to_float(__ldg(gamma + k));
+    if (beta != nullptr) y = y + bf16_bits_to_float(__ldg(beta + k));
+    y = round_bf16(y);
+    if constexpr (MOD)
+      y = round_bf16(round_bf16(y * round_bf16(1.0f + bf16_bits_to_float(__ldg(mod_scale + k)))) +
+                     bf16_bits_to_float(__ldg(mod_shift + k)));
+    xrow[k] = y;
+    if (y_out != nullptr) y_out[m * y_pitch + k] = float_to_bf16_bits(y);
+    mx = fmaxf(mx, fabsf(y));
+  }
+  // absmax over the CTA (max is order-independent)
+  mx = warp_max(mx);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  float v = 0.f;
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) v = fmaxf(v, red[i]);
+  const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
+  if (threadIdx.x == 0) scale_out[m] = s;
+  uint8_t* qrow = q + m * K;
+  for (int64_t k = threadIdx.x; k < K; k += kThreads)
+    qrow[k] = (uint8_t)(float2_to_e4m3x2(clamp448(__fdiv_rn(xrow[k], s)), 0.f) & 0xff);
+}
+
+}  // namespace
+
+int launch_layernorm_quant_fp8(const void* x, int64_t pitch, const void* gamma, const void* beta, float eps,
+                               const void* mod_scale, const void* mod_shift, int64_t M, int64_t K, void* y_out,
+                               int64_t y_pitch, void* q, float* scale, cudaStream_t s) {
+  if (M == 0 || K == 0) return SACQ_OK;
+  if (M > 2147483647LL) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
+  const size_t smem = (size_t)K * sizeof(float);
+  if (smem > 200 * 1024) return set_error(SACQ_ERR_UNSUPPORTED, "K=%lld: a row does not fit shared memory", (long long)K);
+  const bool mod = mod_scale != nullptr;
+  const void* fn = mod ? (const void*)layernorm_quant_fp8_kernel<true> : (const void*)layernorm_quant_fp8_kernel<false>;
+  static bool configured[2][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[mod][dev])) {
+    const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute");
+    if (dev >= 0 && dev < 64) configured[mod][dev] = true;
+  }
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const uint16_t* gp = static_cast<const uint16_t*>(gamma);
+  const uint16_t* bp = static_cast<const uint16_t*>(beta);
+  const uint16_t* sp = static_cast<const uint16_t*>(mod_scale);
+  const uint16_t* tp = static_cast<const uint16_t*>(mod_shift);
+  uint16_t* yp = static_cast<uint16_t*>(y_out);
+  uint8_t* qp = static_cast<uint8_t*>(q);
+  void* args[] = {&xp, &pitch, &gp, &bp, &eps, &sp, &tp, &K, &yp, &y_pitch, &qp, &scale};
+  SACQ_CUDA_TRY(cudaLaunchKernel(fn, dim3((unsigned)M), dim3(kThreads), args, smem, s));
+  count_launch();
+  return SACQ_OK;
+}
+
+}  // namespace sacq

@@ -248,6 +248,25 @@ SACQ_API int sacq_act_quant_fp8(int kind, const void* a_bf16, int64_t a_pitch, c
                               static_cast<cudaStream_t>(stream));
 }
 
+SACQ_API int sacq_layernorm_quant_fp8(const void* x_bf16, int64_t x_pitch, const void* gamma_bf16, const void* beta_bf16,
+                                      float eps, const void* mod_scale_bf16, const void* mod_shift_bf16, int64_t M,
+                                      int64_t K, void* y_out_bf16, int64_t y_pitch, void* q_out, float* scale_out,
+                                      void* stream) {
+  if (M < 0 || K < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "negative size (M=%lld K=%lld)", (long long)M,
+                                       (long long)K);
+  if (M == 0) return SACQ_OK;
+  if (K == 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "K must be positive");
+  if (x_bf16 == nullptr || q_out == nullptr || scale_out == nullptr)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if ((mod_scale_bf16 == nullptr) != (mod_shift_bf16 == nullptr))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "modulation needs both its scale and its shift vector");
+  if (x_pitch < K || (y_out_bf16 != nullptr && y_pitch < K))
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "row pitch smaller than K=%lld", (long long)K);
+  if (!(eps >= 0.f)) return set_error(SACQ_ERR_INVALID_ARGUMENT, "eps must be non-negative");
+  return launch_layernorm_quant_fp8(x_bf16, x_pitch, gamma_bf16, beta_bf16, eps, mod_scale_bf16, mod_shift_bf16, M, K,
+                                    y_out_bf16, y_pitch, q_out, scale_out, static_cast<cudaStream_t>(stream));
+}
+
 SACQ_API int sacq_modulate_quant_fp8(const void* x_bf16, int64_t x_pitch, const void* scale_vec_bf16,
                                      const void* shift_vec_bf16, int64_t M, int64_t K, void* q_out, float* scale_out,
                                      void* stream) {

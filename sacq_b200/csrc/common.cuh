@@ -61,6 +61,9 @@ int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, voi
 int launch_quant_act_int8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
 int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, const void* c,
                          int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
+int launch_layernorm_quant_fp8(const void* x, int64_t pitch, const void* gamma, const void* beta, float eps,
+                               const void* mod_scale, const void* mod_shift, int64_t M, int64_t K, void* y_out,
+                               int64_t y_pitch, void* q, float* scale, cudaStream_t s);
 int launch_build_tables(sacq_layer* L, cudaStream_t s);
 int launch_copy_to_host(const void* src, void* dst, int64_t bytes, int num_sms, cudaStream_t s);
 

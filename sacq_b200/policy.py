@@ -12,7 +12,8 @@ reproduces is the *workload* a policy query puts on the quantized-linear path:
     horizon, cross-attention to the language tokens, MLP 6144, AdaLN timestep modulation,
     4 Euler flow-matching steps (the loop structure of gr00t_n1d7.py:396-434).
 
-Attention, norms and activations use stock PyTorch; every projection is a
+Attention uses stock PyTorch; norms, AdaLN modulation, activation functions and residual
+adds run inside this library's quantizer and GEMM kernels; every projection is a
 ``PrecomputedPackedVectorCodebookLinear`` (dim-8 vectors, 4096-entry codebook,
 per-output-channel scales).  The cross-attention keys/values depend only on the language
 tokens and are computed once per query, not once per denoising step.
@@ -22,7 +23,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .activation import act_quantize_rows, modulate_quantize_rows
+from .activation import act_quantize_rows, layernorm_quantize_rows
 from .linear import PrecomputedPackedVectorCodebookLinear, forward_shared, linear_a8_multi
 from .synthetic import make_payload
 
@@ -88,29 +89,25 @@ class _Block(torch.nn.Module):
     def cross_kv(self, ctx):
         return tuple(forward_shared((self.ck, self.cv), ctx))
 
+    def _norm_quant(self, norm, x, scale=None, shift=None):
+        """LayerNorm (+ AdaLN modulation) inside the quantizer of the projections it feeds."""
+        return layernorm_quantize_rows(x, norm.weight, norm.bias, norm.eps, mod_scale=scale, mod_shift=shift)
+
     def forward(self, x, cond=None, cross_kv=None):
-        if self.adaln:
-            # AdaLN: norm(x) * (1 + scale) + shift runs inside the quantizer of the projections it feeds
-            m = self.mod(cond).view(4, self.hidden)
-            qa, sa = modulate_quantize_rows(self.n1(x), m[1], m[0])
-            q, k, v = linear_a8_multi((self.q, self.k, self.v), qa, sa)
-        else:
-            q, k, v = forward_shared((self.q, self.k, self.v), self.n1(x))   # one quantization for q/k/v
+        m = self.mod(cond).view(4, self.hidden) if self.adaln else (None,) * 4
+        qa, sa = self._norm_quant(self.n1, x, m[1], m[0])
+        q, k, v = linear_a8_multi((self.q, self.k, self.v), qa, sa)        # one launch for q/k/v at small M
         x = self.o.forward_residual(self._attend(q, k, v), x)            # residual added in the GEMM epilogue
         if self.cross:
-            h = self.n3(x)
-            x = self.co.forward_residual(self._attend(self.cq(h), cross_kv[0], cross_kv[1]), x)
+            qc, sc = self._norm_quant(self.n3, x)
+            x = self.co.forward_residual(self._attend(self.cq.linear_a8(qc, sc), cross_kv[0], cross_kv[1]), x)
+        qu, su = self._norm_quant(self.n2, x, m[3], m[2])
         # the activation function runs inside the quantizer of the down projection
         if self.gated:
-            gate, up = forward_shared((self.gate, self.up), self.n2(x))
+            gate, up = linear_a8_multi((self.gate, self.up), qu, su)
             qd, sd = act_quantize_rows("silu_mul", gate, up)
         else:
-            if self.adaln:
-                qu, su = modulate_quantize_rows(self.n2(x), m[3], m[2])
-                up = self.up.linear_a8(qu, su)
-            else:
-                up = self.up(self.n2(x))
-            qd, sd = act_quantize_rows("gelu", up)
+            qd, sd = act_quantize_rows("gelu", self.up.linear_a8(qu, su))
         return self.down.linear_a8(qd, sd, residual=x)
 
 

@@ -569,6 +569,46 @@ def test_modulation_fused_into_quantizer(M, K):
         modulate_quantize_rows(x, sc[:-1], sh)
 
 
+@pytest.mark.parametrize("M,K,affine", [(16, 1536, False), (300, 2048, True), (256, 1024, True), (3, 100, True)])
+def test_layernorm_fused_into_quantizer(M, K, affine):
+    """LayerNorm (+ AdaLN modulation) + quantizer in one launch.  The normalised tensor must
+    agree with the float64 oracle and with PyTorch's LayerNorm to one bf16 ulp (the reduction
+    order differs, so not to the bit); the quantized bytes and scales must be exactly those of
+    quantizing the kernel's own normalised tensor, with and without the modulation."""
+    _need_gpu()
+    import torch.nn.functional as F
+    from sacq_b200 import layernorm_quantize_rows, quantize_rows
+    g = torch.Generator().manual_seed(M + K)
+    x = (torch.randn(M, K, generator=g) * 1.7 + 0.3).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16) if affine else None
+    b = (0.1 * torch.randn(K, generator=g)).to(torch.bfloat16) if affine else None
+    xc, wc, bc = x.cuda(), None if w is None else w.cuda(), None if b is None else b.cuda()
+    q, s, y = layernorm_quantize_rows(xc, wc, bc, 1e-5, return_normalized=True)
+    qr, sr = quantize_rows(y)
+    assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8)) and torch.equal(s.view(torch.int32), sr.view(torch.int32))
+    q2, s2 = layernorm_quantize_rows(xc, wc, bc, 1e-5)
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s2, s)
+
+    def ulp_check(ours, ref):
+        ours, ref = ours.float(), ref.float()
+        ulp = torch.maximum(ref.abs(), torch.tensor(1e-30)) * 2.0 ** -7      # one bf16 ulp is at most 2^-7 relative
+        assert bool(((ours - ref).abs() <= ulp + 1e-6).all())
+        assert float((ours != ref).float().mean()) < 0.01                   # and almost all values are identical
+    ref64 = O.layernorm_bf16_reference(bf16_bits(x), None if w is None else bf16_bits(w),
+                                       None if b is None else bf16_bits(b), 1e-5)
+    ulp_check(y.cpu(), torch.from_numpy(ref64))
+    ulp_check(y, F.layer_norm(xc, (K,), wc, bc, 1e-5))
+    # with the AdaLN modulation: exactly the three bf16 operations applied to the kernel's own y
+    sc = (torch.randn(K, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    sh = (torch.randn(K, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    qm, sm, ym = layernorm_quantize_rows(xc, wc, bc, 1e-5, mod_scale=sc, mod_shift=sh, return_normalized=True)
+    assert torch.equal(ym, y * (1 + sc) + sh)
+    qmr, smr = quantize_rows(ym)
+    assert torch.equal(qm.view(torch.uint8), qmr.view(torch.uint8)) and torch.equal(sm.view(torch.int32), smr.view(torch.int32))
+    with pytest.raises(ValueError):
+        layernorm_quantize_rows(xc, wc, bc, 1e-5, mod_scale=sc)
+
+
 def test_linear_properties_and_edges():
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows

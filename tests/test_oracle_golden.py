@@ -119,3 +119,17 @@ def test_int8_activation_quantizer_matches_reference_fixture():
     assert np.array_equal(q, f["q"])
     assert np.array_equal(s.view(np.uint32), f["s"].view(np.uint32))
     assert list(q[5, 1:5]) == [0, 2, 2, 4] and float(s[1, 0]) == 1.0
+
+
+def test_layernorm_reference_against_torch_cpu():
+    """The float64 LayerNorm reference agrees with PyTorch's CPU LayerNorm to one bf16 ulp."""
+    import torch
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(7, 384, generator=g) * 2 + 0.5).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(384, generator=g)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(384, generator=g)).to(torch.bfloat16)
+    bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    ours = O.layernorm_bf16_reference(bits(x), bits(w), bits(b), 1e-5)
+    ref = torch.nn.functional.layer_norm(x.float(), (384,), w.float(), b.float(), 1e-5).to(torch.bfloat16).float().numpy()
+    assert np.all(np.abs(ours - ref) <= np.maximum(np.abs(ref), 1e-30) * 2.0 ** -7 + 1e-6)
+    assert np.mean(ours != ref) < 0.01
