@@ -207,8 +207,9 @@ SACQ_API int sacq_linear_a8_residual(const sacq_layer_t* layer, const void* q, c
  * (int8_shared_padded_activation_20261028_r1.py:44-63 shares the quantized input,
  * int8_grouped_qkv_aligned_frozen_20261028_r1.py:9-40 and int8_grouped_gateup_20261028_r1.py:7-54
  * group the GEMMs).  Up to four layers of one geometry (same K, vector_dim, index width,
- * codebook size and group size, out_features a multiple of 8) on the small-M kernel run as ONE
- * launch that splits the grid between the layers; anything else runs one launch per layer.
+ * codebook size and group size) run as ONE launch when they would all use the small-M warp-MMA
+ * kernel (out_features a multiple of 8; the grid is split between the layers) or all the FP8
+ * tensor-core kernel (the layer is a grid dimension); anything else runs one launch per layer.
  * `workspace` must be large enough for the largest sacq_workspace_bytes(layer, M).  Results are
  * byte-identical to separate sacq_linear_a8 calls. */
 SACQ_API int sacq_linear_a8_multi(const sacq_layer_t* const* layers, int num_layers, const void* q, const float* scale,

@@ -512,6 +512,15 @@ SACQ_API int sacq_linear_a8_multi(const sacq_layer_t* const* layers, int num_lay
                                           static_cast<cudaStream_t>(stream));
       if (rc != SACQ_ERR_UNSUPPORTED) return rc;
     }
+    // ... or the FP8 tensor-core kernel (blockIdx.z = layer)
+    bool large = num_layers >= 2;
+    for (int l = 0; l < num_layers && large; ++l) large = pick_kernel(layers[l], M) == 2;
+    if (large) {
+      DeviceGuard guard(layers[0]->d.device);
+      const int rc = launch_large_m_multi(layers, num_layers, q, scale, M, y_outs, ldys,
+                                          static_cast<cudaStream_t>(stream));
+      if (rc != SACQ_ERR_UNSUPPORTED) return rc;
+    }
   }
   for (int l = 0; l < num_layers; ++l) {
     const int rc = sacq_linear_a8(layers[l], q, scale, M, y_outs[l], ldys[l], workspace, workspace_bytes, stream);

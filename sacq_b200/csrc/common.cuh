@@ -90,6 +90,8 @@ int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, 
 bool large_m_supported(const sacq_layer* L);
 int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0, const BcastDst* bc = nullptr);
+int launch_large_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
+                         void* const* ys, const int64_t* ldys, cudaStream_t s);
 void large_m_release(sacq_layer* L);
 
 bool large_m_grouped_supported(const sacq_layer* L);

@@ -101,6 +101,13 @@ struct LargeMParams {
   float out_mul;                // 2^-cb8_exp_shift
 };
 
+// Up to four layers of one geometry in one launch (blockIdx.z = layer).
+constexpr int kMaxLayersPerLaunch = 4;
+struct alignas(64) LargeMMulti {
+  CUtensorMap idx[kMaxLayersPerLaunch];     // packed-index tile maps, one per layer
+  LargeMParams layer[kMaxLayersPerLaunch];
+};
+
 // Shared-memory carve-up (offsets from a 1024-byte aligned base).
 struct SmemLayout {
   uint32_t stage_off;      // stages x {MT x A 16 KB, B_hi, B_lo of BN x 128 bytes}
@@ -143,8 +150,12 @@ __host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, 
 // measured faster.
 template <int D, int BITS, int BN, int MT, bool MERGE>
 __global__ void __launch_bounds__(kThreads, 1)
-large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
-               const LargeMParams p) {
+large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ LargeMMulti mp) {
+  // blockIdx.z selects the layer: sibling projections that read the same activations run as
+  // one launch; grid.x covers the widest of them, CTAs beyond a narrower layer leave at once
+  const LargeMParams& p = mp.layer[blockIdx.z];
+  const CUtensorMap* tmap_idx_p = &mp.idx[blockIdx.z];
+  if ((int)blockIdx.x * BN >= p.N) return;
   constexpr int IDX_PER_KB = kBK / D;                 // indices per row per K block
   constexpr int KB_BYTES = IDX_PER_KB * BITS / 8;     // index bytes per row per K block
   constexpr int SB_BYTES = 2 * KB_BYTES;              // ... per super block (two K blocks): multiple of 16
@@ -191,7 +202,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&tmap_a);
-    prefetch_tensormap(&tmap_idx);
+    prefetch_tensormap(tmap_idx_p);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), (uint32_t)(ACC_COLS * MT));
   tc_fence_before();
@@ -207,7 +218,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int sb = kb >> 1, slot = sb & 1;
           if (!mbar_wait(bar(IDX_EMPTY + slot), ((sb >> 1) & 1) ^ 1, abort_flag, p.status)) break;
           mbar_arrive_expect_tx(bar(IDX_FULL + slot), BN * SB_BYTES);
-          tma_load_2d(base + L.idx_off + slot * BN * SB_BYTES, &tmap_idx, sb * SB_BYTES, n0, bar(IDX_FULL + slot));
+          tma_load_2d(base + L.idx_off + slot * BN * SB_BYTES, tmap_idx_p, sb * SB_BYTES, n0, bar(IDX_FULL + slot));
         }
         const int st = kb % kStages;
         if (!mbar_wait(bar(EMPTY + st), ((kb / kStages) & 1) ^ 1, abort_flag, p.status)) break;
@@ -479,8 +490,8 @@ namespace {
 int sb_bytes_for(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
 
 template <int D, int BITS, int BN, int MT, bool MERGE>
-cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, dim3 grid, cudaStream_t s) {
-  const size_t smem = make_layout(BN, MT, 2 * (kBK / D) * BITS / 8, p.C * 2 * D).total + 1024;
+cudaError_t launch_bn(const CUtensorMap& ta, const LargeMMulti& mp, dim3 grid, cudaStream_t s) {
+  const size_t smem = make_layout(BN, MT, 2 * (kBK / D) * BITS / 8, mp.layer[0].C * 2 * D).total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -492,22 +503,21 @@ cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& ti, const LargeM
   }
   // (Programmatic dependent launch behind the quantizer was measured and is not used here: the
   // early-resident 200 KB CTAs slowed the kernels around them more than the overlap gained.)
-  large_m_kernel<D, BITS, BN, MT, MERGE><<<grid, kThreads, smem, s>>>(ta, ti, p);
+  large_m_kernel<D, BITS, BN, MT, MERGE><<<grid, kThreads, smem, s>>>(ta, mp);
   return cudaGetLastError();
 }
 
 template <int D, int BITS>
-cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& ti, const LargeMParams& p, int bn, int mt, dim3 grid,
-                       cudaStream_t s) {
+cudaError_t launch_one(const CUtensorMap& ta, const LargeMMulti& mp, int bn, int mt, dim3 grid, cudaStream_t s) {
   // merged high/low MMA everywhere it measured faster or equal: all shapes but 2 x 128 x 128
   if (mt == 2) {
-    if (bn == 32) return launch_bn<D, BITS, 32, 2, true>(ta, ti, p, grid, s);
-    if (bn == 64) return launch_bn<D, BITS, 64, 2, true>(ta, ti, p, grid, s);
-    return launch_bn<D, BITS, 128, 2, false>(ta, ti, p, grid, s);
+    if (bn == 32) return launch_bn<D, BITS, 32, 2, true>(ta, mp, grid, s);
+    if (bn == 64) return launch_bn<D, BITS, 64, 2, true>(ta, mp, grid, s);
+    return launch_bn<D, BITS, 128, 2, false>(ta, mp, grid, s);
   }
-  if (bn == 32) return launch_bn<D, BITS, 32, 1, true>(ta, ti, p, grid, s);
-  if (bn == 64) return launch_bn<D, BITS, 64, 1, true>(ta, ti, p, grid, s);
-  return launch_bn<D, BITS, 128, 1, true>(ta, ti, p, grid, s);
+  if (bn == 32) return launch_bn<D, BITS, 32, 1, true>(ta, mp, grid, s);
+  if (bn == 64) return launch_bn<D, BITS, 64, 1, true>(ta, mp, grid, s);
+  return launch_bn<D, BITS, 128, 1, true>(ta, mp, grid, s);
 }
 
 }  // namespace
@@ -529,6 +539,114 @@ void large_m_release(sacq_layer* L) {
   L->large_plan = nullptr;
 }
 
+namespace {
+
+// Whether a tile shape issues the high and the low B tile as one MMA (the summation order of an
+// output element depends on this and on nothing else of the tile shape).
+inline bool tile_merges(int bn, int mt) { return !(bn == 128 && mt == 2); }
+
+// Tile shape: (token sub-tiles per CTA, weight rows per CTA) with the smallest
+// waves x time-per-CTA.  Fitted to measurements (us): a CTA takes about
+// 3.4 + K/2048 * (4.8 + 0.0755 * BN + 3.0 * (MT - 1)): fixed prologue/epilogue, pipeline
+// latency per K block, expansion per weight row, MMA issue per extra sub-tile.
+// merge_req: -1 free, 0 / 1 only shapes with that tile_merges() value.
+bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers, int merge_req, int& bn, int& mt) {
+  const sacq_layer_desc& d = L->d;
+  const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
+  bn = 0;
+  mt = 1;
+  double best = 1e30;
+  for (int cand_mt = 1; cand_mt <= (M > kBM ? 2 : 1); ++cand_mt) {
+    const int64_t m_tiles = (M + kBM * cand_mt - 1) / (kBM * cand_mt);
+    for (int cand = 128; cand >= 32; cand >>= 1) {
+      if (merge_req >= 0 && (int)tile_merges(cand, cand_mt) != merge_req) continue;
+      if (make_layout(cand, cand_mt, sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) continue;
+      int64_t tiles = 0;
+      for (int l = 0; l < n_layers; ++l) tiles += ((ns[l] + cand - 1) / cand) * m_tiles;
+      const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
+      const double per_cta = 3.4 + (double)d.in_features / 2048.0 * (4.8 + 0.0755 * cand + 3.0 * (cand_mt - 1));
+      const double cost = (double)waves * per_cta;
+      if (cost < best - 1e-9) { best = cost; bn = cand; mt = cand_mt; }
+    }
+  }
+  return bn != 0;
+}
+
+int ensure_idx_map(sacq_layer* Lm, int bn, const CUtensorMap** out) {
+  if (Lm->large_plan == nullptr) {
+    LargeMPlan* plan = new LargeMPlan();
+    plan->sb_bytes = sb_bytes_for(Lm);
+    plan->have[0] = plan->have[1] = plan->have[2] = false;
+    Lm->large_plan = plan;
+  }
+  const int bi = bn == 32 ? 0 : (bn == 64 ? 1 : 2);
+  if (!Lm->large_plan->have[bi]) {
+    const uint64_t row_bytes = (uint64_t)(Lm->row_bits / 8);
+    const int rc = encode_bytes_2d(&Lm->large_plan->tmap_idx[bi], Lm->d.packed, row_bytes, (uint64_t)Lm->d.out_features,
+                                   row_bytes, (uint32_t)Lm->large_plan->sb_bytes, (uint32_t)bn,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != SACQ_OK) return rc;
+    Lm->large_plan->have[bi] = true;
+  }
+  *out = &Lm->large_plan->tmap_idx[bi];
+  return SACQ_OK;
+}
+
+// n layers (n = 1: the plain launch) on one set of quantized activations.
+int launch_layers(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
+                  void* const* ys, const int64_t* ldys, int bn, int mt, cudaStream_t s, const void* residual,
+                  int64_t ldr, const BcastDst* bc) {
+  const sacq_layer* L0 = layers[0];
+  const sacq_layer_desc& d0 = L0->d;
+  CUtensorMap ta;
+  {
+    const int rc = encode_bytes_2d(&ta, q, (uint64_t)d0.in_features, (uint64_t)M, (uint64_t)d0.in_features, kBK, kBM,
+                                   CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SACQ_OK) return rc;
+  }
+  LargeMMulti mp{};
+  int64_t widest = 0;
+  for (int l = 0; l < n; ++l) {
+    const sacq_layer* L = layers[l];
+    const CUtensorMap* ti = nullptr;
+    const int rc = ensure_idx_map(const_cast<sacq_layer*>(L), bn, &ti);
+    if (rc != SACQ_OK) return rc;
+    mp.idx[l] = *ti;
+    LargeMParams& p = mp.layer[l];
+    p.cb_hilo = L->cb_hilo;
+    p.scales = static_cast<const uint16_t*>(L->d.scales);
+    p.bias = static_cast<const uint16_t*>(L->d.bias);
+    p.act_scale = scale;
+    p.y = static_cast<uint16_t*>(ys[l]);
+    p.status = L->d_status;
+    p.ldy = ldys[l];
+    p.residual = static_cast<const uint16_t*>(residual);
+    p.ldr = ldr;
+    if (bc != nullptr) {
+      p.n_bc = bc->n;
+      for (int i = 0; i < bc->n; ++i) p.ybc[i] = static_cast<uint16_t*>(bc->ptr[i]);
+    }
+    p.M = (int)M; p.N = (int)L->d.out_features; p.K = (int)L->d.in_features; p.C = L->d.codebook_size;
+    p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
+    if (L->d.out_features > widest) widest = L->d.out_features;
+  }
+  const dim3 grid((unsigned)((widest + bn - 1) / bn), (unsigned)((M + kBM * mt - 1) / (kBM * mt)), (unsigned)n);
+  if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
+  cudaError_t e;
+  const int D = d0.vector_dim, B = d0.index_bits;
+  if (D == 8 && B == 12) e = launch_one<8, 12>(ta, mp, bn, mt, grid, s);
+  else if (D == 8 && B == 8) e = launch_one<8, 8>(ta, mp, bn, mt, grid, s);
+  else if (D == 8 && B == 16) e = launch_one<8, 16>(ta, mp, bn, mt, grid, s);
+  else if (D == 4 && B == 12) e = launch_one<4, 12>(ta, mp, bn, mt, grid, s);
+  else if (D == 4 && B == 8) e = launch_one<4, 8>(ta, mp, bn, mt, grid, s);
+  else e = launch_one<4, 16>(ta, mp, bn, mt, grid, s);
+  count_launch();
+  if (e != cudaSuccess) return cuda_fail(e, "large-M launch");
+  return SACQ_OK;
+}
+
+}  // namespace
+
 int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    cudaStream_t s, const void* residual, int64_t ldr, const BcastDst* bc) {
   const sacq_layer_desc& d = L->d;
@@ -537,78 +655,41 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
   if (M > (1 << 30)) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld too large", (long long)M);
   if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
     return set_error(SACQ_ERR_ALIGNMENT, "large-M kernel: quantized activations must be 16-byte aligned");
-  sacq_layer* Lm = const_cast<sacq_layer*>(L);
-  if (Lm->large_plan == nullptr) {
-    LargeMPlan* plan = new LargeMPlan();
-    plan->sb_bytes = sb_bytes_for(L);
-    plan->have[0] = plan->have[1] = plan->have[2] = false;
-    Lm->large_plan = plan;
-  }
-  // Tile shape: (token sub-tiles per CTA, weight rows per CTA) with the smallest
-  // waves x time-per-CTA.  Fitted to measurements (us): a CTA takes about
-  // 3.4 + K/2048 * (4.8 + 0.0755 * BN + 3.0 * (MT - 1)): fixed prologue/epilogue, pipeline
-  // latency per K block, expansion per weight row, MMA issue per extra sub-tile.
-  const size_t cb_bytes_sel = (size_t)d.codebook_size * d.vector_dim * 2;
   int bn = 0, mt = 1;
-  {
-    double best = 1e30;
-    for (int cand_mt = 1; cand_mt <= (M > kBM ? 2 : 1); ++cand_mt) {
-      const int64_t m_tiles = (M + kBM * cand_mt - 1) / (kBM * cand_mt);
-      for (int cand = 128; cand >= 32; cand >>= 1) {
-        if (make_layout(cand, cand_mt, sb_bytes_for(L), (int)cb_bytes_sel).total + 1024 > 227 * 1024) continue;
-        const int64_t tiles = ((d.out_features + cand - 1) / cand) * m_tiles;
-        const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
-        const double per_cta = 3.4 + (double)d.in_features / 2048.0 * (4.8 + 0.0755 * cand + 3.0 * (cand_mt - 1));
-        const double cost = (double)waves * per_cta;
-        if (cost < best - 1e-9) { best = cost; bn = cand; mt = cand_mt; }
-      }
-    }
+  const int64_t n_rows = d.out_features;
+  if (!choose_tile(L, M, &n_rows, 1, -1, bn, mt))
+    return set_error(SACQ_ERR_UNSUPPORTED, "large-M kernel: no tile fits shared memory");
+  return launch_layers(&L, 1, q, scale, M, &y, &ldy, bn, mt, s, residual, ldr, bc);
+}
+
+// Several layers of one geometry on the same quantized activations as ONE launch.  Returns
+// SACQ_ERR_UNSUPPORTED (nothing launched) when they cannot share one: the caller falls back
+// to one launch per layer.  The shared tile shape is restricted to the high/low issue mode
+// every layer would use alone, so the results are byte-identical to separate launches.
+int launch_large_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
+                         void* const* ys, const int64_t* ldys, cudaStream_t s) {
+  if (n < 2 || n > kMaxLayersPerLaunch || M <= 0 || M > (1 << 30)) return SACQ_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(q) % 16 != 0) return SACQ_ERR_UNSUPPORTED;
+  const sacq_layer_desc& d0 = layers[0]->d;
+  int64_t ns[kMaxLayersPerLaunch];
+  int merge = -1;
+  for (int l = 0; l < n; ++l) {
+    const sacq_layer* L = layers[l];
+    const sacq_layer_desc& d = L->d;
+    if (!large_m_supported(L) || d.in_features != d0.in_features || d.vector_dim != d0.vector_dim ||
+        d.index_bits != d0.index_bits || d.codebook_size != d0.codebook_size || d.device != d0.device ||
+        d.out_features <= 0)
+      return SACQ_ERR_UNSUPPORTED;
+    ns[l] = d.out_features;
+    int bn1 = 0, mt1 = 1;
+    if (!choose_tile(L, M, &ns[l], 1, -1, bn1, mt1)) return SACQ_ERR_UNSUPPORTED;
+    const int m1 = (int)tile_merges(bn1, mt1);
+    if (merge >= 0 && m1 != merge) return SACQ_ERR_UNSUPPORTED;
+    merge = m1;
   }
-  if (bn == 0) return set_error(SACQ_ERR_UNSUPPORTED, "large-M kernel: no tile fits shared memory");
-  const int bi = bn == 32 ? 0 : (bn == 64 ? 1 : 2);
-  if (!Lm->large_plan->have[bi]) {
-    const uint64_t row_bytes = (uint64_t)(L->row_bits / 8);
-    const int rc = encode_bytes_2d(&Lm->large_plan->tmap_idx[bi], d.packed, row_bytes, (uint64_t)d.out_features,
-                                   row_bytes, (uint32_t)Lm->large_plan->sb_bytes, (uint32_t)bn,
-                                   CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc != SACQ_OK) return rc;
-    Lm->large_plan->have[bi] = true;
-  }
-  CUtensorMap ta;
-  {
-    const int rc = encode_bytes_2d(&ta, q, (uint64_t)d.in_features, (uint64_t)M, (uint64_t)d.in_features, kBK, kBM,
-                                   CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != SACQ_OK) return rc;
-  }
-  LargeMParams p{};
-  p.cb_hilo = L->cb_hilo;
-  p.scales = static_cast<const uint16_t*>(d.scales);
-  p.bias = static_cast<const uint16_t*>(d.bias);
-  p.act_scale = scale;
-  p.y = static_cast<uint16_t*>(y);
-  p.status = L->d_status;
-  p.ldy = ldy;
-  p.residual = static_cast<const uint16_t*>(residual);
-  p.ldr = ldr;
-  if (bc != nullptr) {
-    p.n_bc = bc->n;
-    for (int i = 0; i < bc->n; ++i) p.ybc[i] = static_cast<uint16_t*>(bc->ptr[i]);
-  }
-  p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features; p.C = d.codebook_size;
-  p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
-  const dim3 grid((unsigned)((d.out_features + bn - 1) / bn), (unsigned)((M + kBM * mt - 1) / (kBM * mt)));
-  if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
-  cudaError_t e;
-  const int D = d.vector_dim, B = d.index_bits;
-  if (D == 8 && B == 12) e = launch_one<8, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
-  else if (D == 8 && B == 8) e = launch_one<8, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
-  else if (D == 8 && B == 16) e = launch_one<8, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
-  else if (D == 4 && B == 12) e = launch_one<4, 12>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
-  else if (D == 4 && B == 8) e = launch_one<4, 8>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
-  else e = launch_one<4, 16>(ta, Lm->large_plan->tmap_idx[bi], p, bn, mt, grid, s);
-  count_launch();
-  if (e != cudaSuccess) return cuda_fail(e, "large-M launch");
-  return SACQ_OK;
+  int bn = 0, mt = 1;
+  if (!choose_tile(layers[0], M, ns, n, merge, bn, mt)) return SACQ_ERR_UNSUPPORTED;
+  return launch_layers(layers, n, q, scale, M, ys, ldys, bn, mt, s, nullptr, 0, nullptr);
 }
 
 }  // namespace sacq
