@@ -23,7 +23,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .activation import act_quantize_rows, layernorm_quantize_rows
+from .activation import act_quantize_rows, layernorm_quantize_rows, quantize_rows
 from .linear import PrecomputedPackedVectorCodebookLinear, forward_shared, linear_a8_multi
 from .synthetic import make_payload
 
@@ -93,8 +93,11 @@ class _Block(torch.nn.Module):
         """LayerNorm (+ AdaLN modulation) inside the quantizer of the projections it feeds."""
         return layernorm_quantize_rows(x, norm.weight, norm.bias, norm.eps, mod_scale=scale, mod_shift=shift)
 
-    def forward(self, x, cond=None, cross_kv=None):
-        m = self.mod(cond).view(4, self.hidden) if self.adaln else (None,) * 4
+    def forward(self, x, cond=None, cross_kv=None, modulation=None):
+        if self.adaln:
+            m = (self.mod(cond) if modulation is None else modulation).view(4, self.hidden)
+        else:
+            m = (None,) * 4
         qa, sa = self._norm_quant(self.n1, x, m[1], m[0])
         q, k, v = linear_a8_multi((self.q, self.k, self.v), qa, sa)        # one launch for q/k/v at small M
         x = self.o.forward_residual(self._attend(q, k, v), x)            # residual added in the GEMM epilogue
@@ -155,13 +158,21 @@ class SyntheticGr00tPolicy(torch.nn.Module):
         for blk in self.llm:
             tokens = blk(tokens)
         kv = [blk.cross_kv(tokens) for blk in self.dit]
+        # the AdaLN modulation vectors depend on the denoising step only: all blocks' modulation
+        # layers read the same one-row input, so they run four to a launch, ahead of the loop
+        mods = []
+        for step in range(self.STEPS):
+            qc, sc = quantize_rows(self.time_embed[step: step + 1])
+            per_block = []
+            for i in range(0, len(self.dit), 4):
+                per_block += linear_a8_multi([blk.mod for blk in self.dit[i: i + 4]], qc, sc)
+            mods.append(per_block)
         actions = noise
         dt = 1.0 / self.STEPS
         for step in range(self.STEPS):
             h = actions @ self.action_in
-            cond = self.time_embed[step: step + 1]
-            for blk, ckv in zip(self.dit, kv):
-                h = blk(h, cond=cond, cross_kv=ckv)
+            for blk, ckv, mod in zip(self.dit, kv, mods[step]):
+                h = blk(h, cross_kv=ckv, modulation=mod)
             actions = actions + dt * (h @ self.action_out)
         return actions
 
