@@ -40,6 +40,10 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
   // A GEMM launched with programmatic stream serialization may start its prologue now; it
   // waits for this grid to finish before it reads q or the scales.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // This grid is itself launched that way behind whatever precedes it on the stream (so its
+  // launch latency overlaps that kernel's tail): wait for it before touching x, q or the scales
+  // (the kernel in front may have produced x, or may still be reading q).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t m = blockIdx.x;
   const uint16_t* row = x + m * pitch;
   uint8_t* qrow = q + m * K;
@@ -141,14 +145,22 @@ int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, voi
   const bool vec = (K % 8 == 0) && (pitch % 8 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(q) % 8 == 0);
   if (M > 2147483647LL) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)M);
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  uint8_t* qp = static_cast<uint8_t*>(q);
   if (vec)
-    quant_act_fp8_kernel<true><<<(unsigned)M, kThreads, 0, s>>>(static_cast<const uint16_t*>(x), pitch, K,
-                                                               static_cast<uint8_t*>(q), scale);
+    SACQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quant_act_fp8_kernel<true, false>, xp, pitch, K, qp, scale));
   else
-    quant_act_fp8_kernel<false><<<(unsigned)M, kThreads, 0, s>>>(static_cast<const uint16_t*>(x), pitch, K,
-                                                                static_cast<uint8_t*>(q), scale);
+    SACQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quant_act_fp8_kernel<false, false>, xp, pitch, K, qp, scale));
   count_launch();
-  SACQ_CUDA_TRY(cudaGetLastError());
   return SACQ_OK;
 }
 
@@ -196,6 +208,7 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
   __shared__ float red[kThreads / 32];
   __shared__ float s_scale;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // launched behind the producer of a / b with programmatic serialization
   const int64_t m = blockIdx.x;
   const uint16_t* arow = a + m * a_pitch;
   const uint16_t* brow = KIND == 1 ? nullptr : b + m * b_pitch;      // pitch 0: one vector for every row
@@ -305,7 +318,17 @@ int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b
   int64_t bpitch = kind == 0 ? b_pitch : 0;
   uint8_t* qp = static_cast<uint8_t*>(q);
   void* args[] = {&ap, &a_pitch, &bp, &bpitch, &cp, &K, &qp, &scale};
-  SACQ_CUDA_TRY(cudaLaunchKernel(fn, dim3((unsigned)M), dim3(kThreads), args, smem, s));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)M);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SACQ_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, args));
   count_launch();
   SACQ_CUDA_TRY(cudaGetLastError());
   return SACQ_OK;
@@ -350,6 +373,7 @@ layernorm_quant_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, const 
   extern __shared__ __align__(16) float xrow[];       // the row in fp32, later its bf16 result in place
   __shared__ float red[kThreads / 32];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // launched behind the producer of x with programmatic serialization
   const int64_t m = blockIdx.x;
   const uint16_t* row = x + m * pitch;
   float sum = 0.f;
@@ -421,7 +445,17 @@ int launch_layernorm_quant_fp8(const void* x, int64_t pitch, const void* gamma, 
   uint16_t* yp = static_cast<uint16_t*>(y_out);
   uint8_t* qp = static_cast<uint8_t*>(q);
   void* args[] = {&xp, &pitch, &gp, &bp, &eps, &sp, &tp, &K, &yp, &y_pitch, &qp, &scale};
-  SACQ_CUDA_TRY(cudaLaunchKernel(fn, dim3((unsigned)M), dim3(kThreads), args, smem, s));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)M);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SACQ_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, args));
   count_launch();
   return SACQ_OK;
 }

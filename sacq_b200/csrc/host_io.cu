@@ -13,6 +13,7 @@ namespace {
 
 __global__ void __launch_bounds__(256) copy_to_host_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
                                                            int64_t bytes) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // src is written by the previous kernel of the stream
   const int64_t n16 = bytes >> 4;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;

@@ -156,6 +156,9 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const LargeMParams& p = mp.layer[blockIdx.z];
   const CUtensorMap* tmap_idx_p = &mp.idx[blockIdx.z];
   if ((int)blockIdx.x * BN >= p.N) return;
+  // the next kernel of the stream, if launched with programmatic serialization, may be scheduled
+  // from here on (its launch latency overlaps this grid); it waits for this grid before it touches memory
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int IDX_PER_KB = kBK / D;                 // indices per row per K block
   constexpr int KB_BYTES = IDX_PER_KB * BITS / 8;     // index bytes per row per K block
   constexpr int SB_BYTES = 2 * KB_BYTES;              // ... per super block (two K blocks): multiple of 16

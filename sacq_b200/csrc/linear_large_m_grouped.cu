@@ -128,6 +128,9 @@ template <int D, int BN, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
                        const GroupedParams p) {
+  // the next kernel of the stream, if launched with programmatic serialization, may be scheduled
+  // from here on (its launch latency overlaps this grid); it waits for this grid before it touches memory
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int IDX_PER_KB = kBKh / D;                // indices per row per K block
   constexpr int KB_PER_SB = kSbIdx / IDX_PER_KB;      // K blocks per index super-block
   constexpr int IPC = 8 / D;                          // indices per 16-byte chunk (8 weights)

@@ -380,6 +380,9 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
     bulk_copy_g2s(smem + L.cb_off, p.cb_hilo, cb_bytes, bar_cb);    // layer constants: may overlap
     if (first_rt < p.row_blocks) issue_idx(first_rt, 0);            // the previous kernel of the stream
   }
+  // the next kernel of the stream (a quantizer or another GEMM launched with programmatic
+  // serialization) may be scheduled from here on; it waits for this grid before it touches memory
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");                // activations come from that kernel
   if (threadIdx.x < 16 && first_rt < p.row_blocks) {
     issue_act(chunk, 0);

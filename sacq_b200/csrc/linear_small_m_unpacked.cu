@@ -149,6 +149,9 @@ __global__ void __launch_bounds__(kMaxWarpsU * 32, 1) small_m_mma_unpacked_kerne
     bulk_g2s(smem + L.cb_off, p.cb_hilo, cb_bytes, bar_cb);           // layer constants: may overlap the
     if (first_rt < p.row_blocks) issue_packed(first_rt, 0);           // previous kernel of the stream
   }
+  // the next kernel of the stream, if launched with programmatic serialization, may be scheduled
+  // from here on (its launch latency overlaps this grid); it waits for this grid before it touches memory
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");                  // activations come from that kernel
   if (threadIdx.x < 16 && first_rt < p.row_blocks) {
     const int m = threadIdx.x;
