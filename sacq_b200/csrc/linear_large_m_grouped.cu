@@ -289,10 +289,12 @@ large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           const __half2 s2 = __half2half2(sh);
           const uint32_t* w32 = reinterpret_cast<const uint32_t*>(idx_slot + row * sb_bytes);
           uint32_t o[4];
+          // the chunk's one or two index fields sit in one 64-bit window of the row's bit stream
+          const int bit0 = first * p.bits;
+          const uint64_t win = (((uint64_t)w32[(bit0 >> 5) + 1] << 32) | w32[bit0 >> 5]) >> (bit0 & 31);
 #pragma unroll
           for (int j = 0; j < IPC; ++j) {
-            const int bit = (first + j) * p.bits;
-            const uint32_t idx = __funnelshift_r(w32[bit >> 5], w32[(bit >> 5) + 1], bit & 31) & mask;
+            const uint32_t idx = (uint32_t)(win >> (j * p.bits)) & mask;
             const CwVec cw = cbs[idx];
             if constexpr (D == 8) {
               const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
