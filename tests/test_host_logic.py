@@ -124,3 +124,47 @@ def test_module_refuses_cpu():
         sacq_b200.quantize_rows(torch.zeros(2, 8, dtype=torch.bfloat16))
     with pytest.raises(TypeError):
         sacq_b200.quantize_rows(torch.zeros(2, 8))
+
+
+def test_fused_quantizers_refuse_cpu_and_bad_arguments():
+    """The fused producers validate their arguments before touching the device and have no CPU path."""
+    import torch
+    from sacq_b200 import (act_quantize_rows, layernorm_quantize_rows, linear_a8_multi, modulate_quantize_rows,
+                           quantize_rows)
+    x = torch.zeros(2, 16, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        quantize_rows(x)                                   # CPU tensor
+    with pytest.raises(ValueError):
+        quantize_rows(x, "int4")
+    with pytest.raises(ValueError):
+        act_quantize_rows("relu", x)
+    with pytest.raises(TypeError):
+        act_quantize_rows("gelu", x)                        # CPU tensor
+    with pytest.raises(TypeError):
+        modulate_quantize_rows(x, x[0], x[0])
+    with pytest.raises(TypeError):
+        layernorm_quantize_rows(x.float())
+    with pytest.raises(TypeError):
+        layernorm_quantize_rows(x)
+    with pytest.raises(Exception):
+        linear_a8_multi([], x.view(torch.uint8), torch.ones(2))
+
+
+def test_c_abi_argument_errors_of_the_new_entry_points_without_gpu():
+    """Argument checks that run before any CUDA call."""
+    import ctypes
+    from sacq_b200 import _lib
+    lib = _lib.load()
+    assert lib.sacq_act_quant_fp8(7, None, 0, None, 0, 1, 8, None, None, None) == -1
+    assert "activation kind" in _lib.last_error()
+    assert lib.sacq_act_quant_fp8(1, None, 0, None, 0, 1, 8, None, None, None) == -1
+    assert lib.sacq_modulate_quant_fp8(None, 0, None, None, 1, 8, None, None, None) == -1
+    assert lib.sacq_layernorm_quant_fp8(None, 0, None, None, ctypes.c_float(1e-5), None, None, 1, 8, None, 0, None,
+                                        None, None) == -1
+    assert lib.sacq_quant_act_int8(None, 0, -1, 8, None, None, None) == -1
+    assert lib.sacq_linear_a8_multi(None, 0, None, None, 1, None, None, None, 0, None) == -1
+    assert lib.sacq_linear_a8_bcast(None, None, None, 1, None, None, 9, 0, None, 0, None) == -1
+    assert lib.sacq_linear_a8_residual(None, None, None, 1, None, 0, None, 0, None, 0, None) == -1
+    assert lib.sacq_peer_buffer_create(0, 0, None, None) == -1
+    assert lib.sacq_workspace_bytes_int8(None, 4) == 0
+    assert lib.sacq_act_quant_fp8(0, None, 0, None, 0, 0, 8, None, None, None) == 0      # M = 0 is a no-op
