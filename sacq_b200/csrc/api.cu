@@ -88,6 +88,8 @@ int pick_kernel(const sacq_layer* L, int64_t M) {
     // ... and from 49 rows on deep layers: four 16-token chunks of K = 6144 cost the warp-MMA
     // kernel 28.8 us, the tensor-core kernel 24.5 us (measured at N = 2048).
     if (M > 48 && L->d.in_features >= 4096) return 2;
+    // ... and on layers of 2048 or more rows (2048 x 2048 at M = 64: 9.8 us against 8.9 us)
+    if (M > 48 && L->d.out_features >= 2048) return 2;
   } else if (M >= grouped_min_m(L) && large_m_grouped_supported(L)) {
     return 3;                                          // grouped scales, odd index widths, a shift
   }

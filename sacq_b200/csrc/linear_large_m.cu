@@ -121,13 +121,18 @@ struct SmemLayout {
   uint32_t total;
 };
 
-__host__ __device__ constexpr int stages_for(int mt) { return mt == 2 ? 2 : kMaxStages; }
+// A pipeline stage holds kbs K blocks (1 or 2; 2 = exactly one index super-block): every
+// barrier round trip costs each role several hundred cycles, so narrow tiles, whose K blocks
+// are cheap, take two per stage.  Stages: 3 where they fit, else 2.
+__host__ __device__ constexpr int stages_for(int bn, int mt, int kbs) {
+  return kbs == 2 ? (bn == 32 ? 3 : 2) : (mt == 2 ? 2 : kMaxStages);
+}
 
-__host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, int cb_bytes) {
+__host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, int cb_bytes, int kbs = 1) {
   SmemLayout L;
   L.stage_off = 0;
-  L.stage_bytes = mt * kTileBytes + 2 * bn * kBK;
-  L.idx_off = stages_for(mt) * L.stage_bytes;
+  L.stage_bytes = kbs * (mt * kTileBytes + 2 * bn * kBK);
+  L.idx_off = stages_for(bn, mt, kbs) * L.stage_bytes;
   L.cb_off = L.idx_off + 2 * bn * sb_bytes;
   L.cb_off = (L.cb_off + 127) & ~127u;
   L.sw_off = L.cb_off + ((cb_bytes + 127) & ~127);
@@ -148,7 +153,7 @@ __host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, 
 // shared-memory operand reads, so reading the A tile once instead of twice is what counts at
 // small and medium M; with two token sub-tiles (large M) two N = BN MMAs into one accumulator
 // measured faster.
-template <int D, int BITS, int BN, int MT, bool MERGE>
+template <int D, int BITS, int BN, int MT, bool MERGE, int KBS>
 __global__ void __launch_bounds__(kThreads, 1)
 large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ LargeMMulti mp) {
   // blockIdx.z selects the layer: sibling projections that read the same activations run as
@@ -169,14 +174,15 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr int ACC_COLS = MERGE ? 2 * BN : BN;       // accumulator columns per token sub-tile
   constexpr uint32_t kIdesc = make_idesc(ACC_COLS);
   constexpr int B_TILE = BN * kBK;
-  constexpr int kStages = stages_for(MT);
-  constexpr int A_BYTES = MT * kTileBytes;
+  constexpr int kStages = stages_for(BN, MT, KBS);
+  constexpr int A_BYTES = MT * kTileBytes;            // A tiles of one K block
+  constexpr int B_OFF = KBS * A_BYTES;                // the stage's B tiles follow all of its A tiles
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
-  const SmemLayout L = make_layout(BN, MT, SB_BYTES, p.C * CW_BYTES);
+  const SmemLayout L = make_layout(BN, MT, SB_BYTES, p.C * CW_BYTES, KBS);
 
   // barrier indices
   constexpr int A_FULL = 0, B_FULL = kMaxStages, EMPTY = 2 * kMaxStages, IDX_FULL = 3 * kMaxStages,
@@ -216,20 +222,23 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if ((kb & 1) == 0) {
-          const int sb = kb >> 1, slot = sb & 1;
+      for (int it = 0; it < num_kb / KBS; ++it) {
+        const int kb0 = it * KBS;
+        if ((kb0 & 1) == 0) {
+          const int sb = kb0 >> 1, slot = sb & 1;
           if (!mbar_wait(bar(IDX_EMPTY + slot), ((sb >> 1) & 1) ^ 1, abort_flag, p.status)) break;
           mbar_arrive_expect_tx(bar(IDX_FULL + slot), BN * SB_BYTES);
           tma_load_2d(base + L.idx_off + slot * BN * SB_BYTES, tmap_idx_p, sb * SB_BYTES, n0, bar(IDX_FULL + slot));
         }
-        const int st = kb % kStages;
-        if (!mbar_wait(bar(EMPTY + st), ((kb / kStages) & 1) ^ 1, abort_flag, p.status)) break;
-        mbar_arrive_expect_tx(bar(A_FULL + st), A_BYTES);
+        const int st = it % kStages;
+        if (!mbar_wait(bar(EMPTY + st), ((it / kStages) & 1) ^ 1, abort_flag, p.status)) break;
+        mbar_arrive_expect_tx(bar(A_FULL + st), KBS * A_BYTES);
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(base + L.stage_off + st * L.stage_bytes + mt * kTileBytes, &tmap_a, kb * kBK, m0 + mt * kBM,
-                      bar(A_FULL + st));
+        for (int kk = 0; kk < KBS; ++kk)
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            tma_load_2d(base + L.stage_off + st * L.stage_bytes + kk * A_BYTES + mt * kTileBytes, &tmap_a,
+                        (kb0 + kk) * kBK, m0 + mt * kBM, bar(A_FULL + st));
       }
     }
     __syncwarp();
@@ -237,24 +246,29 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int st = kb % kStages;
-        const uint32_t ph = (kb / kStages) & 1;
+      for (int it = 0; it < num_kb / KBS && ok; ++it) {
+        const int st = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
         ok = mbar_wait(bar(A_FULL + st), ph, abort_flag, p.status) &&
              mbar_wait(bar(B_FULL + st), ph, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = base + L.stage_off + st * L.stage_bytes;
-        const uint64_t b_desc = make_smem_desc(a_addr + A_BYTES);            // high half (and, merged, both)
-        const uint64_t bl_desc = make_smem_desc(a_addr + A_BYTES + B_TILE);   // low half
+        const uint32_t s_addr = base + L.stage_off + st * L.stage_bytes;
 #pragma unroll
-        for (int ks = 0; ks < kBK / 32; ++ks) {
-          const uint64_t adv = (uint64_t)((ks * 32) >> 4);
+        for (int kk = 0; kk < KBS; ++kk) {
+          const uint32_t a_addr = s_addr + kk * A_BYTES;
+          const uint64_t b_desc = make_smem_desc(s_addr + B_OFF + kk * 2 * B_TILE);            // high half (and, merged, both)
+          const uint64_t bl_desc = make_smem_desc(s_addr + B_OFF + kk * 2 * B_TILE + B_TILE);   // low half
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            const uint64_t a_desc = make_smem_desc(a_addr + mt * kTileBytes);
-            umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
-            if constexpr (!MERGE) umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, bl_desc + adv, kIdesc, 1);
+          for (int ks = 0; ks < kBK / 32; ++ks) {
+            const uint64_t adv = (uint64_t)((ks * 32) >> 4);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint64_t a_desc = make_smem_desc(a_addr + mt * kTileBytes);
+              umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, b_desc + adv, kIdesc, (it | kk | ks) != 0);
+              if constexpr (!MERGE)
+                umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, bl_desc + adv, kIdesc, 1);
+            }
           }
         }
         umma_commit(bar(EMPTY + st));
@@ -283,17 +297,21 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     const uint8_t* cbs = sm + L.cb_off;
     bool ok = true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int sb = kb >> 1, slot = sb & 1;
-      const int st = kb % kStages;
+    for (int it = 0; it < num_kb / KBS && ok; ++it) {
+      const int kb0 = it * KBS;
+      const int sb = kb0 >> 1, slot = sb & 1;
+      const int st = it % kStages;
       ok = mbar_wait(bar(IDX_FULL + slot), (sb >> 1) & 1, abort_flag, p.status) &&
-           mbar_wait(bar(EMPTY + st), ((kb / kStages) & 1) ^ 1, abort_flag, p.status);
+           mbar_wait(bar(EMPTY + st), ((it / kStages) & 1) ^ 1, abort_flag, p.status);
       if (!ok) break;
+#pragma unroll
+      for (int kk = 0; kk < KBS; ++kk) {
+      const int kb = kb0 + kk;
       // this thread's CPT * IPC indices of the row's K block
       uint32_t idx[CPT * IPC];
       load_fields<BITS, CPT * IPC>(sm + L.idx_off + slot * BN * SB_BYTES + row * SB_BYTES + (kb & 1) * KB_BYTES,
                                    part * CPT * IPC, idx);
-      uint8_t* bhi = sm + L.stage_off + st * L.stage_bytes + A_BYTES + row * 128;
+      uint8_t* bhi = sm + L.stage_off + st * L.stage_bytes + B_OFF + kk * 2 * B_TILE + row * 128;
       uint8_t* blo = bhi + B_TILE;
       const int sw = row & 7;
 #pragma unroll
@@ -315,10 +333,12 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         *reinterpret_cast<uint4*>(bhi + ((chunk ^ sw) * 16)) = hi4;
         *reinterpret_cast<uint4*>(blo + ((chunk ^ sw) * 16)) = lo4;
       }
+      }
       fence_proxy_async();                            // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) {                                // one arrival per warp keeps the barrier off the critical path
         mbar_arrive(bar(B_FULL + st));
+        const int kb = kb0 + KBS - 1;                 // last K block of this stage
         if ((kb & 1) == 1 || kb == num_kb - 1) mbar_arrive(bar(IDX_EMPTY + slot));
       }
     }
@@ -492,21 +512,21 @@ namespace {
 
 int sb_bytes_for(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
 
-template <int D, int BITS, int BN, int MT, bool MERGE>
+template <int D, int BITS, int BN, int MT, bool MERGE, int KBS = 1>
 cudaError_t launch_bn(const CUtensorMap& ta, const LargeMMulti& mp, dim3 grid, cudaStream_t s) {
-  const size_t smem = make_layout(BN, MT, 2 * (kBK / D) * BITS / 8, mp.layer[0].C * 2 * D).total + 1024;
+  const size_t smem = make_layout(BN, MT, 2 * (kBK / D) * BITS / 8, mp.layer[0].C * 2 * D, KBS).total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN, MT, MERGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN, MT, MERGE, KBS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   // (Programmatic dependent launch behind the quantizer was measured and is not used here: the
   // early-resident 200 KB CTAs slowed the kernels around them more than the overlap gained.)
-  large_m_kernel<D, BITS, BN, MT, MERGE><<<grid, kThreads, smem, s>>>(ta, mp);
+  large_m_kernel<D, BITS, BN, MT, MERGE, KBS><<<grid, kThreads, smem, s>>>(ta, mp);
   return cudaGetLastError();
 }
 
@@ -518,8 +538,10 @@ cudaError_t launch_one(const CUtensorMap& ta, const LargeMMulti& mp, int bn, int
     if (bn == 64) return launch_bn<D, BITS, 64, 2, true>(ta, mp, grid, s);
     return launch_bn<D, BITS, 128, 2, false>(ta, mp, grid, s);
   }
-  if (bn == 32) return launch_bn<D, BITS, 32, 1, true>(ta, mp, grid, s);
-  if (bn == 64) return launch_bn<D, BITS, 64, 1, true>(ta, mp, grid, s);
+  // narrow tiles with one token sub-tile: two K blocks per pipeline stage when that fits
+  const bool two = make_layout(bn, 1, 2 * (kBK / D) * BITS / 8, mp.layer[0].C * 2 * D, 2).total + 1024 <= 227 * 1024;
+  if (bn == 32) return two ? launch_bn<D, BITS, 32, 1, true, 2>(ta, mp, grid, s) : launch_bn<D, BITS, 32, 1, true>(ta, mp, grid, s);
+  if (bn == 64) return two ? launch_bn<D, BITS, 64, 1, true, 2>(ta, mp, grid, s) : launch_bn<D, BITS, 64, 1, true>(ta, mp, grid, s);
   return launch_bn<D, BITS, 128, 1, true>(ta, mp, grid, s);
 }
 
@@ -551,7 +573,8 @@ inline bool tile_merges(int bn, int mt) { return !(bn == 128 && mt == 2); }
 // Tile shape: (token sub-tiles per CTA, weight rows per CTA) with the smallest
 // waves x time-per-CTA.  Fitted to measurements (us): a CTA takes about
 // 3.4 + K/2048 * (4.8 + 0.0755 * BN + 3.0 * (MT - 1)): fixed prologue/epilogue, pipeline
-// latency per K block, expansion per weight row, MMA issue per extra sub-tile.
+// latency per K block (halved, 2.4, where a stage holds two K blocks: one sub-tile of 32 or
+// 64 rows), expansion per weight row, MMA issue per extra sub-tile.
 // merge_req: -1 free, 0 / 1 only shapes with that tile_merges() value.
 bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers, int merge_req, int& bn, int& mt) {
   const sacq_layer_desc& d = L->d;
@@ -567,7 +590,10 @@ bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers
       int64_t tiles = 0;
       for (int l = 0; l < n_layers; ++l) tiles += ((ns[l] + cand - 1) / cand) * m_tiles;
       const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
-      const double per_cta = 3.4 + (double)d.in_features / 2048.0 * (4.8 + 0.0755 * cand + 3.0 * (cand_mt - 1));
+      const bool two_kb = cand_mt == 1 && cand <= 64 &&
+                          make_layout(cand, 1, sb_bytes_for(L), (int)cb_bytes, 2).total + 1024 <= 227 * 1024;
+      const double per_cta = 3.4 + (double)d.in_features / 2048.0 *
+                                       ((two_kb ? 2.4 : 4.8) + 0.0755 * cand + 3.0 * (cand_mt - 1));
       const double cost = (double)waves * per_cta;
       if (cost < best - 1e-9) { best = cost; bn = cand; mt = cand_mt; }
     }
