@@ -306,7 +306,7 @@ def gpu_main(args):
                     "d2h_bytes_per_step": sum(M * N * 2 for _, K, N, M in calls),
                     "ms_per_step": sec_e2e / args.steps * 1e3},
             "gpu_launches": int(full_launches * args.steps),
-            "roofline": {"bound": "hbm", "kernel": "small_m_mma_staged_kernel (packed-index GEMM, M<=64)",
+            "roofline": {"bound": "hbm", "kernel": "small_m_mma_staged_kernel (packed-index GEMM; the M=64 calls of layers with N>=2048 run on large_m_kernel)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg * DRAM_TRAFFIC_RATIO,
                          "traffic_note": "dram bytes read+written per launch = algorithmic bytes x 0.94, the ratio "
