@@ -78,13 +78,13 @@ int pick_kernel(const sacq_layer* L, int64_t M) {
     return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 2) return large_m_supported(L) ? 2 : SACQ_ERR_UNSUPPORTED;
   // A shape rule, not a backend switch.  Above 64 rows the tcgen05 kernel always wins.
-  // Between 33 and 64 rows the small-M kernel walks its row tiles once per 16-token chunk
+  // Between 17 and 64 rows the small-M kernel walks its row tiles once per 16-token chunk
   // while one tensor-core M tile covers them all; that pays off once the layer has enough
   // output rows to give the tensor-core grid a CTA for most SMs (measured: N = 6144 yes,
   // N <= 2048 no).
   if (large_m_supported(L)) {
     if (M > 64) return 2;
-    if (M > 32 && L->d.out_features >= 32 * (int64_t)L->num_sms) return 2;
+    if (M > 16 && L->d.out_features >= 32 * (int64_t)L->num_sms) return 2;   // 2048x6144 at M = 32: 14.1 us against 11.3 us
     // ... and from 49 rows on deep layers: four 16-token chunks of K = 6144 cost the warp-MMA
     // kernel 28.8 us, the tensor-core kernel 24.5 us (measured at N = 2048).
     if (M > 48 && L->d.in_features >= 4096) return 2;
