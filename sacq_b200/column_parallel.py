@@ -6,8 +6,10 @@ owns rows ``[r*N/g, (r+1)*N/g)`` -- a contiguous byte range of the packed stream
 a row's bits end on a byte boundary -- computes ``y[:, rows]`` with the single-GPU kernels
 and the ranks exchange their column blocks with ONE all-gather over NVLink (NCCL through
 ``torch.distributed``).  Activations and their per-token scales are replicated, so each
-output element is produced by exactly one GPU with the single-GPU summation order: the
-gathered result is bit-identical to the one-GPU result.
+output element is produced by exactly one GPU.  The gathered result is bit-identical to the
+one-GPU result whenever the shard and the whole layer sum an output in the same order (always
+on the tensor-core kernel, whose order does not depend on the tile shape; on the small-M
+kernel when both pick the same tile class), and otherwise equal up to the last bf16 bit.
 
 The reference has no multi-GPU inference path (its only collective is the calibration
 trainer's gradient all-reduce); this module is new work on top of the same payload format.

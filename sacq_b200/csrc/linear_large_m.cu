@@ -151,8 +151,10 @@ __host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, 
 // shared memory, so they form one K-major operand): A x hi lands in accumulator columns
 // [0, BN), A x lo in [BN, 2*BN), and the epilogue adds them.  A small-N MMA is bound by its
 // shared-memory operand reads, so reading the A tile once instead of twice is what counts at
-// small and medium M; with two token sub-tiles (large M) two N = BN MMAs into one accumulator
-// measured faster.
+// small and medium M; at large M it measures the same as two N = BN MMAs into one accumulator.
+// Every launch uses MERGE = true: the order in which an output element is summed then does not
+// depend on the tile shape, so the shards of a split layer reproduce the whole layer bit for bit
+// (MERGE = false is kept for measurements only).
 template <int D, int BITS, int BN, int MT, bool MERGE, int KBS>
 __global__ void __launch_bounds__(kThreads, 1)
 large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ LargeMMulti mp) {
@@ -532,11 +534,12 @@ cudaError_t launch_bn(const CUtensorMap& ta, const LargeMMulti& mp, dim3 grid, c
 
 template <int D, int BITS>
 cudaError_t launch_one(const CUtensorMap& ta, const LargeMMulti& mp, int bn, int mt, dim3 grid, cudaStream_t s) {
-  // merged high/low MMA everywhere it measured faster or equal: all shapes but 2 x 128 x 128
+  // every tile shape issues the high and the low tile as one MMA: an output's summation order
+  // is then the same for all shapes (a layer's shards reproduce the whole layer bit for bit)
   if (mt == 2) {
     if (bn == 32) return launch_bn<D, BITS, 32, 2, true>(ta, mp, grid, s);
     if (bn == 64) return launch_bn<D, BITS, 64, 2, true>(ta, mp, grid, s);
-    return launch_bn<D, BITS, 128, 2, false>(ta, mp, grid, s);
+    return launch_bn<D, BITS, 128, 2, true>(ta, mp, grid, s);
   }
   // narrow tiles with one token sub-tile: two K blocks per pipeline stage when that fits
   const bool two = make_layout(bn, 1, 2 * (kBK / D) * BITS / 8, mp.layer[0].C * 2 * D, 2).total + 1024 <= 227 * 1024;
@@ -568,7 +571,7 @@ namespace {
 
 // Whether a tile shape issues the high and the low B tile as one MMA (the summation order of an
 // output element depends on this and on nothing else of the tile shape).
-inline bool tile_merges(int bn, int mt) { return !(bn == 128 && mt == 2); }
+inline bool tile_merges(int, int) { return true; }
 
 // Tile shape: (token sub-tiles per CTA, weight rows per CTA) with the smallest
 // waves x time-per-CTA.  Fitted to measurements (us): a CTA takes about
