@@ -71,6 +71,15 @@ def quant_rows(x_bits: np.ndarray):
     return q, s
 
 
+def quant_rows_int8(x_bits: np.ndarray):
+    x = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    M, K = x.shape
+    q = np.empty((M, K), dtype=np.int8)
+    s = np.empty((M, 1), dtype=np.float32)
+    lib().sacq_oracle_quant_rows_int8(_p(x), ctypes.c_int64(M), ctypes.c_int64(K), _p(q), _p(s))
+    return q, s
+
+
 def linear(packed, bits, codebook_bits, scales_bits, shift_bits, bias_bits, N, K, G, q_bits, act_scale) -> np.ndarray:
     packed = np.ascontiguousarray(packed, dtype=np.uint8)
     cb = np.ascontiguousarray(codebook_bits, dtype=np.uint16)

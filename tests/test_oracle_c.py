@@ -22,6 +22,13 @@ def test_c_activation_quantizer(golden_layer):
     assert np.array_equal(s.view(np.uint32), g["act_scale"].view(np.uint32))
 
 
+def test_c_int8_activation_quantizer():
+    from conftest import load_golden
+    f = load_golden("act_int8")
+    q, s = C.quant_rows_int8(f["x"])
+    assert np.array_equal(q, f["q"]) and np.array_equal(s.view(np.uint32), f["s"].view(np.uint32))
+
+
 def test_c_linear(golden_layer):
     g = golden_layer
     N, K, G, bits = int(g["N"]), int(g["K"]), int(g["G"]), int(g["index_bits"])
