@@ -346,6 +346,14 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
 
     // ---- epilogue: this warp's TMEM lane quarter, half of the 128 columns
+    // the token scales of this warp's rows are fetched before the wait for the accumulator, so
+    // their global-memory latency is off the critical path
+    float sa_pre[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int m = m0 + mt * kBM + (warp & 3) * 32 + lane;
+      sa_pre[mt] = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+    }
     if (ok) ok = mbar_wait(bar(ACC_FULL), 0, abort_flag, p.status);
     ok = expander_all(ok);                            // uniform over the expanders: tcgen05.ld and the staging barriers are collective
     if (ok) {
@@ -363,7 +371,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const int m = m0 + mt * kBM + quarter * 32 + lane;
-          const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+          const float sa = sa_pre[mt];
 #pragma unroll
           for (int cc = col_half; cc < BN / 32; cc += 2) {
             const int c0 = cc * 32;
@@ -413,7 +421,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const int m = m0 + mt * kBM + quarter * 32 + lane;
-          const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+          const float sa = sa_pre[mt];
           uint8_t* srow = stg + (quarter * 32 + lane) * SP;
 #pragma unroll
           for (int cc = col_half; cc < BN / 32; cc += 2) {

@@ -327,6 +327,14 @@ large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     }
 
     // ---- epilogue: this warp's TMEM lane quarter, half of the 32-column groups
+    // the token scales of this warp's rows are fetched before the wait for the accumulator, so
+    // their global-memory latency is off the critical path
+    float sa_pre[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int m = m0 + mt * kBM + (warp & 3) * 32 + lane;
+      sa_pre[mt] = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+    }
     if (ok) ok = mbar_wait(bar(ACC_FULL), 0, abort_flag, p.status);
     ok = expander_all(ok);                            // uniform over the expanders: tcgen05.ld and the staging barriers are collective
     if (ok) {
@@ -342,7 +350,7 @@ large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const int m = m0 + mt * kBM + quarter * 32 + lane;
-          const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+          const float sa = sa_pre[mt];
           const float add = (m < p.M && p.shift != 0.f) ? p.shift * __ldg(p.xsum + m) : 0.f;
 #pragma unroll
           for (int cc = col_half; cc < BN / 32; cc += 2) {
@@ -387,7 +395,7 @@ large_m_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const int m = m0 + mt * kBM + quarter * 32 + lane;
-          const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+          const float sa = sa_pre[mt];
           const float add = (m < p.M && p.shift != 0.f) ? p.shift * __ldg(p.xsum + m) : 0.f;
           uint8_t* srow = stg + (quarter * 32 + lane) * SP;
 #pragma unroll
