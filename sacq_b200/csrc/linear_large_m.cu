@@ -188,7 +188,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   // barrier indices
   constexpr int A_FULL = 0, B_FULL = kMaxStages, EMPTY = 2 * kMaxStages, IDX_FULL = 3 * kMaxStages,
-                IDX_EMPTY = 3 * kMaxStages + 2, ACC_FULL = 3 * kMaxStages + 4;
+                IDX_EMPTY = 3 * kMaxStages + 2, ACC_FULL = 3 * kMaxStages + 4, CB_FULL = 3 * kMaxStages + 5;
   const uint32_t bars = base + L.bar_off;
   auto bar = [&](int i) { return bars + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + L.misc_off);
@@ -198,6 +198,8 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int n0 = blockIdx.x * BN;
   const int m0 = blockIdx.y * (kBM * MT);
   const int num_kb = p.K / kBK;
+  const uint32_t cb_bytes = (uint32_t)(p.C * CW_BYTES);
+  const bool cb_bulk = (cb_bytes & 15u) == 0;         // bulk copies move multiples of 16 bytes
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -210,6 +212,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(bar(IDX_EMPTY + i), kExpanderThreads / 32);
     }
     mbar_init(bar(ACC_FULL), 1);
+    mbar_init(bar(CB_FULL), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&tmap_a);
@@ -224,6 +227,10 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      if (cb_bulk) {                                  // the codebook: one bulk copy, ahead of everything else
+        mbar_arrive_expect_tx(bar(CB_FULL), cb_bytes);
+        bulk_load(base + L.cb_off, p.cb_hilo, cb_bytes, bar(CB_FULL));
+      }
       for (int it = 0; it < num_kb / KBS; ++it) {
         const int kb0 = it * KBS;
         if ((kb0 & 1) == 0) {
@@ -285,10 +292,12 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int part = et / BN;                        // which CPT chunks of the row's 8 this thread writes
     {
       // codebook (hi/lo) and the per-column epilogue constants
-      const uint4* src = reinterpret_cast<const uint4*>(p.cb_hilo);
-      uint4* dst = reinterpret_cast<uint4*>(sm + L.cb_off);
-      const int n16 = (p.C * CW_BYTES) >> 4;
-      for (int i = et; i < n16; i += kExpanderThreads) cp_async_16(dst + i, src + i);
+      if (!cb_bulk) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.cb_hilo);
+        uint4* dst = reinterpret_cast<uint4*>(sm + L.cb_off);
+        const int n16 = (p.C * CW_BYTES) >> 4;
+        for (int i = et; i < n16; i += kExpanderThreads) cp_async_16(dst + i, src + i);
+      }
       if (et < BN) {
         const int n = min(n0 + et, p.N - 1);
         reinterpret_cast<float*>(sm + L.sw_off)[et] = bf16_bits_to_float(__ldg(p.scales + n)) * p.out_mul;
@@ -299,6 +308,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     const uint8_t* cbs = sm + L.cb_off;
     bool ok = true;
+    if (cb_bulk) ok = mbar_wait(bar(CB_FULL), 0, abort_flag, p.status);
     for (int it = 0; it < num_kb / KBS && ok; ++it) {
       const int kb0 = it * KBS;
       const int sb = kb0 >> 1, slot = sb & 1;
