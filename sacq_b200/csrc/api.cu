@@ -170,7 +170,8 @@ SACQ_API int sacq_layer_create(const sacq_layer_desc* desc, sacq_layer_t** out_l
                      prop.major, prop.minor);
   }
   L->num_sms = prop.multiProcessorCount;
-  const int64_t count = (int64_t)d.codebook_size * d.vector_dim;
+  L->cb_entries = (d.codebook_size + 1) & ~1;
+  const int64_t count = (int64_t)L->cb_entries * d.vector_dim;
   cudaError_t e = cudaMalloc(&L->cb_f16, (size_t)count * sizeof(__half));
   if (e == cudaSuccess) e = cudaMalloc(&L->cb_hilo, (size_t)count * 2);
   if (e == cudaSuccess) e = cudaMalloc(&L->d_status, sizeof(int));

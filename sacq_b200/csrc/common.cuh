@@ -30,9 +30,10 @@ struct sacq_layer {
   bool rows_16b_aligned;     // every row of the packed stream starts on a 16-byte boundary
   int num_sms;
   int force_kernel;          // 0 auto, 1 small-M, 2 large-M, 3..6 small-M variants, 7 grouped tensor-core
+  int cb_entries;            // codebook entries rounded up to even: the derived tables are whole 16-byte units
   // derived device tables (owned)
-  __half* cb_f16;            // [C, d] codebook * 2^cb_exp_shift as fp16 (small-M kernel)
-  uint8_t* cb_hilo;          // [C][2][d] e4m3 high/low split of codebook * 2^cb8_exp_shift (large-M kernel)
+  __half* cb_f16;            // [cb_entries, d] (zero padded) codebook * 2^cb_exp_shift as fp16 (small-M kernel)
+  uint8_t* cb_hilo;          // [cb_entries][2][d] (zero padded) e4m3 high/low split of codebook * 2^cb8_exp_shift (large-M kernel)
   int cb_exp_shift;          // power-of-two normalisation folded back in the epilogue
   int cb8_exp_shift;
   int sc_exp_shift;          // max |scale| * 2^sc_exp_shift lies in [0.5, 1) (grouped tensor-core kernel)

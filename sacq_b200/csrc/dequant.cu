@@ -237,6 +237,10 @@ int launch_build_tables(sacq_layer* L, cudaStream_t s) {
   float* d_max = nullptr;
   SACQ_CUDA_TRY(cudaMalloc(&d_max, sizeof(float)));
   cudaError_t e = cudaMemsetAsync(d_max, 0, sizeof(float), s);
+  // the tables hold an even number of entries (whole 16-byte units); the padding entry is zero
+  const size_t padded = (size_t)L->cb_entries * d.vector_dim;
+  if (e == cudaSuccess) e = cudaMemsetAsync(L->cb_f16, 0, padded * sizeof(__half), s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(L->cb_hilo, 0, padded * 2, s);
   if (e == cudaSuccess) {
     codebook_absmax_kernel<<<grid_for(count, 256, L->num_sms), 256, 0, s>>>(
         static_cast<const uint16_t*>(d.codebook), count, d_max);

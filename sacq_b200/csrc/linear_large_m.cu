@@ -575,7 +575,7 @@ bool large_m_supported(const sacq_layer* L) {
   if (!L->rows_16b_aligned) return false;
   if (d.in_features % (2 * kBK) != 0) return false;
   if (L->num_groups != 1 || d.shift_bf16 != 0) return false;
-  const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
+  const size_t cb_bytes = (size_t)L->cb_entries * d.vector_dim * 2;
   if (make_layout(kMaxBN, 1, sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) return false;
   return true;
 }
@@ -599,7 +599,7 @@ inline bool tile_merges(int, int) { return true; }
 // merge_req: -1 free, 0 / 1 only shapes with that tile_merges() value.
 bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers, int merge_req, int& bn, int& mt) {
   const sacq_layer_desc& d = L->d;
-  const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
+  const size_t cb_bytes = (size_t)L->cb_entries * d.vector_dim * 2;
   bn = 0;
   mt = 1;
   double best = 1e30;
@@ -676,7 +676,7 @@ int launch_layers(const sacq_layer* const* layers, int n, const void* q, const f
       p.n_bc = bc->n;
       for (int i = 0; i < bc->n; ++i) p.ybc[i] = static_cast<uint16_t*>(bc->ptr[i]);
     }
-    p.M = (int)M; p.N = (int)L->d.out_features; p.K = (int)L->d.in_features; p.C = L->d.codebook_size;
+    p.M = (int)M; p.N = (int)L->d.out_features; p.K = (int)L->d.in_features; p.C = L->cb_entries;
     p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
     if (L->d.out_features > widest) widest = L->d.out_features;
   }

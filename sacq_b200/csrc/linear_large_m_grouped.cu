@@ -468,7 +468,7 @@ cudaError_t launch_d(const CUtensorMap& ta, const CUtensorMap& ti, const Grouped
 }
 
 size_t grouped_smem(const sacq_layer* L, int bn, int mt, int stages, int kbs) {
-  return grouped_layout(bn, mt, L->d.index_bits, L->d.codebook_size * L->d.vector_dim * 2, (int)L->num_groups,
+  return grouped_layout(bn, mt, L->d.index_bits, L->cb_entries * L->d.vector_dim * 2, (int)L->num_groups,
                         stages, kbs).total + 1024;
 }
 
@@ -499,7 +499,7 @@ bool large_m_grouped_supported(const sacq_layer* L) {
   if (d.index_bits < 1 || d.index_bits > 16) return false;
   if (!L->rows_16b_aligned) return false;
   if (d.in_features % kBKh != 0 || d.group_size % kBKh != 0) return false;
-  if (((size_t)d.codebook_size * d.vector_dim * 2) % 16 != 0) return false;
+  if (((size_t)L->cb_entries * d.vector_dim * 2) % 16 != 0) return false;
   return grouped_stages_for(L, 32, 1, 1) >= 2;
 }
 
@@ -535,7 +535,7 @@ int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scal
   p.bias = static_cast<const uint16_t*>(d.bias);
   p.status = L->d_status;
   p.ldy = ldy;
-  p.N = (int)N; p.K = (int)K; p.C = d.codebook_size;
+  p.N = (int)N; p.K = (int)K; p.C = L->cb_entries;
   p.bits = d.index_bits; p.num_groups = (int)L->num_groups; p.group_size = d.group_size;
   p.scale_mul = ldexpf(kPreScale, L->sc_exp_shift);
   p.out_mul = ldexpf(1.f / kPreScale, -(L->cb_exp_shift + L->sc_exp_shift));

@@ -337,7 +337,7 @@ bool unpacked_eligible(const sacq_layer* L) {
   if (!L->rows_16b_aligned) return false;
   if (d.in_features % (8 * d.vector_dim) != 0 || d.in_features % 32 != 0) return false;
   if (d.group_size % 32 != 0) return false;
-  const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
+  const size_t cb_bytes = (size_t)L->cb_entries * d.vector_dim * 2;
   if (cb_bytes > 64 * 1024 || cb_bytes % 16 != 0) return false;
   return true;
 }
@@ -353,7 +353,7 @@ bool plan_unpacked(const sacq_layer* L, Plan& pl) {
   double best_cost = -1.0;
   int best = 0;
   for (int r8 = 1; r8 <= 4; r8 *= 2) {
-    const size_t need = small_m_mma_unpacked_smem(d.codebook_size, d.vector_dim, (int)d.in_features, L->row_bits / 8,
+    const size_t need = small_m_mma_unpacked_smem(L->cb_entries, d.vector_dim, (int)d.in_features, L->row_bits / 8,
                                                   (int)L->num_groups, r8, warps);
     if (need > kSmemBudget) continue;
     const int64_t row_tiles = (sub + r8 - 1) / r8;
@@ -375,7 +375,7 @@ bool plan_unpacked(const sacq_layer* L, Plan& pl) {
   pl.grid = (int)(stride * pl.chunks);
   if (pl.grid < 1) pl.grid = 1;
   pl.act_bufs = 1;
-  pl.smem = small_m_mma_unpacked_smem(d.codebook_size, d.vector_dim, (int)d.in_features, L->row_bits / 8,
+  pl.smem = small_m_mma_unpacked_smem(L->cb_entries, d.vector_dim, (int)d.in_features, L->row_bits / 8,
                                       (int)L->num_groups, best, warps);
   return true;
 }
@@ -397,7 +397,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
   pl.BITS = d.index_bits;
   if (pl.fast) {
     pl.span_idx = kSpanIdx;
-    const size_t cb_bytes = (size_t)d.codebook_size * d.vector_dim * 2;
+    const size_t cb_bytes = (size_t)L->cb_entries * d.vector_dim * 2;
     pl.cb_smem = cb_bytes <= 64 * 1024;
   } else {
     // largest span (<= 32 vectors) that stays inside one scale group and divides the row
@@ -423,7 +423,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
     // tile = 16 tokens x 8*r8 rows; the CTA's warps split the K spans.
     const int64_t sub = (d.out_features + 7) / 8;
     pl.warps = pl.spans_per_row < kMaxWarps ? pl.spans_per_row : kMaxWarps;
-    const size_t cb_bytes = pl.cb_smem ? (size_t)d.codebook_size * d.vector_dim * 2 : 0;
+    const size_t cb_bytes = pl.cb_smem ? (size_t)L->cb_entries * d.vector_dim * 2 : 0;
     const bool staged_ok = pl.cb_smem && L->force_kernel != 5 && d.in_features % 16 == 0 && cb_bytes % 16 == 0;
     int best = 1;
     bool best_staged = false;
@@ -437,7 +437,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
       const int halves = r8 <= 2 ? 2 : 1;
       const int st_warps = pl.spans_per_row * halves < kMaxWarps * halves ? pl.spans_per_row * halves
                                                                           : kMaxWarps * halves;
-      const size_t need = small_m_mma_staged_smem(d.codebook_size, d.vector_dim, (int)d.in_features,
+      const size_t need = small_m_mma_staged_smem(L->cb_entries, d.vector_dim, (int)d.in_features,
                                                   L->row_bits / 8, r8, st_warps, 1);
       if (staged_ok && need <= kSmemBudget) {
         // CTAs are grouped per token chunk: a group walks the row tiles with this stride
@@ -474,7 +474,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
       const int halves = pl.r8 <= 2 ? 2 : 1;
       pl.warps = pl.spans_per_row * halves < kMaxWarps * halves ? pl.spans_per_row * halves : kMaxWarps * halves;
     }
-    pl.smem = pl.staged ? small_m_mma_staged_smem(d.codebook_size, d.vector_dim, (int)d.in_features, L->row_bits / 8,
+    pl.smem = pl.staged ? small_m_mma_staged_smem(L->cb_entries, d.vector_dim, (int)d.in_features, L->row_bits / 8,
                                                   pl.r8, pl.warps, pl.act_bufs)
                         : cb_bytes + (size_t)pl.warps * pl.r8 * 4 * 32 * sizeof(float);
     return pl;
@@ -494,7 +494,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
   int64_t warps_needed = (pl.num_items + pl.grid - 1) / pl.grid;
   pl.warps = (int)(warps_needed < 1 ? 1 : (warps_needed > kMaxWarps ? kMaxWarps : warps_needed));
   if (pl.fast) {
-    const size_t cb_bytes = pl.cb_smem ? (size_t)d.codebook_size * d.vector_dim * 2 : 0;
+    const size_t cb_bytes = pl.cb_smem ? (size_t)L->cb_entries * d.vector_dim * 2 : 0;
     pl.smem = cb_bytes + (pl.mma ? 0 : (size_t)pl.warps * pl.MT * kSpanIdx * d.vector_dim * 2);
   } else {
     const size_t per_warp = (size_t)pl.MT * pl.span_idx * d.vector_dim * 4;
@@ -569,7 +569,7 @@ SmallMParams fill_params(const sacq_layer* L, const Plan& pl, const void* q, con
   p.vpr = (int)L->vectors_per_row;
   p.d = d.vector_dim; p.bits = d.index_bits;
   p.num_groups = (int)L->num_groups; p.group_size = d.group_size;
-  p.C = d.codebook_size;
+  p.C = L->cb_entries;
   p.span_idx = pl.span_idx; p.spans_per_row = pl.spans_per_row; p.spans_per_item = pl.spans_per_item;
   p.num_sg = pl.num_sg; p.row_blocks = pl.row_blocks; p.chunks = pl.chunks; p.num_items = pl.num_items;
   p.act_bufs = pl.act_bufs > 0 ? pl.act_bufs : 1;

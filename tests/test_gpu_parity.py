@@ -308,10 +308,31 @@ def test_linear_large_m_two_subtiles():
     assert mod.device_status() == 0
 
 
+@pytest.mark.parametrize("M", [5, 70])
+@pytest.mark.parametrize("C,G", [(251, None), (81, 64), (1001, 64)])
+def test_linear_odd_codebook_size(M, C, G):
+    """d = 4 with an odd number of codewords: the codebook's byte size is not a multiple of 16, and the
+    last codeword (about 1/C of all weights use it) must still reach every kernel's shared-memory copy."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    N, K = 264, 1024
+    kw = {} if G is None else {"group_size": G}
+    p = make_payload(N, K, vector_dim=4, codebook_size=C, seed=C + M, device="cuda", iters=1, **kw)
+    mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
+    w_bits = oracle_weight(p)
+    assert np.array_equal(mod.dequantize_weight().view(torch.int16).cpu().numpy().view(np.uint16), w_bits)
+    q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 9)))
+    outs = _check_linear(mod, q_bits, s, w_bits, None, kernels=ALL_KERNELS + ("large_grouped",))
+    assert "auto" in outs and "small_simt" in outs
+    assert "large" in outs if G is None else "large_grouped" in outs
+
+
 @pytest.mark.parametrize("M,N,K,d,C", [(77, 200, 512, 8, 4096), (300, 1000, 256, 8, 256), (129, 136, 768, 4, 4096),
-                                       (1, 128, 256, 8, 4096), (128, 128, 1024, 4, 256)])
+                                       (1, 128, 256, 8, 4096), (128, 128, 1024, 4, 256), (65, 136, 512, 4, 251)])
 def test_linear_large_m_ragged(M, N, K, d, C):
-    """Partial tiles in M and N, both vector widths, 8- and 12-bit indices."""
+    """Partial tiles in M and N, both vector widths, 8- and 12-bit indices, a codebook whose byte size
+    is not a multiple of 16 (staged by plain copies instead of the bulk copy)."""
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear
     from sacq_b200.synthetic import make_activations, make_payload
