@@ -22,12 +22,12 @@ def test_random_geometries(seed):
     checked = 0
     for it in range(40):
         d = rng.choice([4, 8])
-        C = rng.choice([16, 32, 64, 128, 256, 512, 1024, 2048, 4096])
+        C = rng.choice([3, 16, 32, 64, 81, 128, 251, 256, 512, 1000, 1024, 2048, 3000, 4096])
         K = rng.choice([256, 512, 768, 1024, 1536, 2048, 3072])
         G = rng.choice([None, None, 64, 128, 256])
         if G is not None and K % G:
             G = None
-        N = rng.choice([8, 24, 40, 64, 100, 128, 136, 256, 520, 1000, 1024, 1536, 2048, 3072])
+        N = rng.choice([1, 7, 8, 24, 40, 64, 100, 101, 128, 136, 256, 333, 520, 1000, 1024, 1536, 2048, 3072])
         M = rng.choice([1, 2, 3, 5, 8, 16, 17, 31, 33, 48, 49, 64, 65, 96, 127, 128, 129, 200, 256, 300, 513])
         p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=100 * seed + it, device="cuda", iters=1,
                          fit=False)
