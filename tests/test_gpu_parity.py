@@ -326,6 +326,13 @@ def test_linear_odd_codebook_size(M, C, G):
     outs = _check_linear(mod, q_bits, s, w_bits, None, kernels=ALL_KERNELS + ("large_grouped",))
     assert "auto" in outs and "small_simt" in outs
     assert "large" in outs if G is None else "large_grouped" in outs
+    # the INT8 path reads the same derived tables
+    from sacq_b200 import quantize_rows
+    x = make_activations(M, K, seed=M + 9)
+    qo, so = O.quantize_rows_int8(bf16_bits(x))
+    q8, s8 = quantize_rows(x.cuda(), "int8_symmetric")
+    y8 = mod.linear_a8i(q8, s8)
+    assert O.rel_frobenius(y8.float().cpu().numpy(), O.linear_a8i_reference(qo, so, w_bits, None)) <= GEMM_TOL
 
 
 @pytest.mark.parametrize("M,N,K,d,C", [(77, 200, 512, 8, 4096), (300, 1000, 256, 8, 256), (129, 136, 768, 4, 4096),
