@@ -119,8 +119,11 @@ SACQ_API int64_t sacq_workspace_counter_bytes(void);
  * reconstruction's precision:
  *   y[m,n] = bf16( s[m] * sum_k q[m,k] * W[n,k]  + bias[n] )
  * q: e4m3 bytes [M, K]; scale: float [M]; y_out: bf16 [M, ldy] (ldy >= N elements).
- * Chooses the small-M (CUDA-core, HBM-bound) or the large-M (TMA + tcgen05) kernel
- * from M and the layer geometry alone. */
+ * Chooses the kernel from M and the layer geometry alone: warp-MMA kernels that gather
+ * codewords straight into mma.sync fragments up to a few dozen rows, TMA + tcgen05 kernels
+ * above that (expanded weight tiles in shared memory, or in tensor memory from 1024 rows);
+ * a layer with a non-zero shift runs on the kernel that rebuilds the reference's two-rounding
+ * reconstruction per weight. */
 SACQ_API int sacq_linear_a8(const sacq_layer_t* layer, const void* q, const float* scale, int64_t M, void* y_out,
                    int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
 
@@ -156,6 +159,27 @@ SACQ_API int sacq_quant_act_int8(const void* x_bf16, int64_t x_pitch, int64_t M,
 SACQ_API int64_t sacq_workspace_bytes_int8(const sacq_layer_t* layer, int64_t M);
 SACQ_API int sacq_linear_a8i(const sacq_layer_t* layer, const void* q_int8, const float* scale, int64_t M, void* y_out,
                              int64_t ldy, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The reference's deployed INT8 recipe as integer work (`projection_format: int8_symmetric`,
+ * dynamic per-token activation x per-output-row weight, perrow_a8_candidate_r3.py:52-69):
+ *   sw[n]   = max_k |W[n,k]| / 127 (1 for a zero row)                 sacq_weight_row_scale_int8
+ *   wq[n,k] = int8(round_half_even(clamp(W[n,k] / sw[n], -127, 127)))  sacq_decode_weight_int8
+ *   acc     = q_int8 (per-token, sacq_quant_act_int8) x wq^T, int32, exact
+ *   y[m,n]  = bf16(fma(sa[m], float(acc) * sw[n], bias[n]))  or  bf16(sa[m] * (float(acc) * sw[n])) without bias
+ * -- the rounding of int8_direct_integer_round_20261028_r1.py:6-9 and the epilogue order of
+ * int8_small_m_gemm_20261028_r1.py:7-32 / int8_ordered_epilogue_20261028_r1.py:11-22.  Integer
+ * accumulation is exact, so y is bit-identical to any correct evaluation of these formulas.
+ * sacq_linear_w8a8_int8 decodes the int8 weight rows per call into `workspace`
+ * (sacq_workspace_bytes_w8a8 bytes, 256-byte aligned; nothing expanded is kept between calls, as in
+ * the reference) and runs a tcgen05 kind::i8 GEMM on them.  `w_scale` is the vector written by
+ * sacq_weight_row_scale_int8 (the reference keeps it as a small per-layer buffer).  in_features must
+ * be a multiple of 16. */
+SACQ_API int sacq_weight_row_scale_int8(const sacq_layer_t* layer, float* sw_out, void* stream);
+SACQ_API int sacq_decode_weight_int8(const sacq_layer_t* layer, const float* sw, void* wq_out, void* stream);
+SACQ_API int64_t sacq_workspace_bytes_w8a8(const sacq_layer_t* layer, int64_t M);
+SACQ_API int sacq_linear_w8a8_int8(const sacq_layer_t* layer, const void* q_int8, const float* act_scale,
+                                   const float* w_scale, int64_t M, void* y_out, int64_t ldy, void* workspace,
+                                   int64_t workspace_bytes, void* stream);
 
 /* Activation function fused into the per-token quantizer (the producer of the MLP's down
  * projection; the reference fuses this stage for its INT8 path,
@@ -258,14 +282,17 @@ SACQ_API int sacq_linear_a8_static_scratch(const sacq_layer_t* layer, const void
 SACQ_API int64_t sacq_static_scratch_bytes(void);
 
 /* Forces a GEMM kernel (for tests and benchmarks): 0 = automatic, 1 = small-M kernel
- * (its own choice of variant), 2 = large-M kernel, 3 = small-M CUDA-core variant,
- * 4 = small-M warp-MMA variant, 5 = warp-MMA variant without shared-memory staging,
- * 6 = warp-MMA variant that unpacks the indices in shared memory (any index width, any
- * group size that is a multiple of 32), 7 = tensor-core kernel for grouped scales.  Returns SACQ_ERR_UNSUPPORTED from the next forward
- * if the forced kernel cannot run the layer. */
+ * (its own choice of variant), 2 = tensor-core kernel with expanded weight tiles in shared
+ * memory, 3 = small-M CUDA-core variant, 4 = small-M warp-MMA variant, 5 = warp-MMA variant
+ * without shared-memory staging, 6 = warp-MMA variant that unpacks the indices in shared memory
+ * (any index width, any group size that is a multiple of 32), 7 = tensor-core kernel for grouped
+ * scales, 8 = tensor-core kernel with the expanded weights in tensor memory (9, 10, 11: the same
+ * with 1, 2, 3 token sub-tiles of 128 per CTA).  Returns SACQ_ERR_UNSUPPORTED from the next
+ * forward if the forced kernel cannot run the layer. */
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* layer, int which);
-/* Which kernel a forward with M rows would use (1 = small-M, 2 = large-M tensor-core kernel
- * for per-channel scales, 3 = tensor-core kernel for grouped scales), or a negative error. */
+/* Which kernel a forward with M rows would use (1 = small-M, 2 = tensor-core kernel with
+ * shared-memory weight tiles, 3 = tensor-core kernel for grouped scales, 4 = tensor-core kernel
+ * with tensor-memory weights), or a negative error. */
 SACQ_API int sacq_layer_kernel_for(const sacq_layer_t* layer, int64_t M);
 
 /* Reads the layer's device-side status word (synchronises the device): 0, or a

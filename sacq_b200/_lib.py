@@ -67,6 +67,10 @@ SIGNATURES = {
     "sacq_act_quant_fp8": (_int, [_int, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _fp, _vp]),
     "sacq_weight_row_scale": (_int, [_vp, _fp, _vp]),
     "sacq_decode_weight_fp8": (_int, [_vp, _fp, _vp, _vp]),
+    "sacq_weight_row_scale_int8": (_int, [_vp, _fp, _vp]),
+    "sacq_decode_weight_int8": (_int, [_vp, _fp, _vp, _vp]),
+    "sacq_workspace_bytes_w8a8": (_i64, [_vp, _i64]),
+    "sacq_linear_w8a8_int8": (_int, [_vp, _vp, _fp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "sacq_workspace_bytes": (_i64, [_vp, _i64]),
     "sacq_workspace_counter_bytes": (_i64, []),
     "sacq_linear_a8": (_int, [_vp, _vp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),

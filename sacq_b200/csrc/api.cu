@@ -69,15 +69,25 @@ int64_t grouped_min_m(const sacq_layer* L) {
   if (L->d.out_features >= 32 * (int64_t)L->num_sms) return 33;
   return L->d.out_features >= 2048 ? 48 : 96;
 }
+constexpr int64_t kTmemMinM = 1024;
+constexpr int64_t kTmemMinMBigCodebook = 128;
 // INT8 activations have no FP8 warp-MMA path, so the tensor-core kernel takes over earlier.
 constexpr int64_t kGroupedMinMInt8 = 48;
 
 int pick_kernel(const sacq_layer* L, int64_t M) {
   if (L->force_kernel == 7) return large_m_grouped_supported(L) ? 3 : SACQ_ERR_UNSUPPORTED;
+  if (L->force_kernel >= 8) return large_m_tmem_supported(L) ? 4 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 1 || L->force_kernel >= 3)
     return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 2) return large_m_supported(L) ? 2 : SACQ_ERR_UNSUPPORTED;
-  // A shape rule, not a backend switch.  Above 64 rows the tcgen05 kernel always wins.
+  // A shape rule, not a backend switch.  From kTmemMinM rows the tensor-core kernel that keeps
+  // the expanded weights in tensor memory wins on every layer shape (its 128-row tiles need that
+  // many tokens to fill the device).  The threshold does not depend on the layer's width, so
+  // the row shards of a split layer run the kernel the whole layer would, and reproduce it
+  // bit for bit.  Layers whose codebook does not fit shared memory have no other tensor-core
+  // kernel and switch earlier.
+  if (large_m_tmem_supported(L) && (M >= kTmemMinM || (M >= kTmemMinMBigCodebook && !large_m_supported(L)))) return 4;
+  // Above 64 rows the tcgen05 kernel always wins.
   // Between 17 and 64 rows the small-M kernel walks its row tiles once per 16-token chunk
   // while one tensor-core M tile covers them all; that pays off once the layer has enough
   // output rows to give the tensor-core grid a CTA for most SMs (measured: N = 6144 yes,
@@ -290,7 +300,7 @@ SACQ_API int sacq_modulate_quant_fp8(const void* x_bf16, int64_t x_pitch, const 
 
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
-  if (which < 0 || which > 7) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..7", which);
+  if (which < 0 || which > 11) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..11", which);
   L->force_kernel = which;
   return SACQ_OK;
 }
@@ -330,6 +340,9 @@ int linear_a8_impl(const sacq_layer_t* L, const void* q, const float* scale, int
   const int k = pick_kernel(L, M);
   if (k < 0) return set_error(k, "no kernel can run this layer geometry");
   if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s, residual, ldr, bc);
+  if (k == 4)
+    return launch_large_m_tmem(L, q, scale, M, y_out, ldy, s, residual, ldr, bc,
+                               L->force_kernel >= 9 ? L->force_kernel - 8 : 0);
   if (k == 3) {
     if (workspace == nullptr || workspace_bytes < kCounterBytes)
       return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
@@ -415,6 +428,52 @@ SACQ_API int sacq_linear_a8i(const sacq_layer_t* L, const void* q_int8, const fl
     if (rc != SACQ_OK) return rc;
   }
   return SACQ_OK;
+}
+
+SACQ_API int sacq_weight_row_scale_int8(const sacq_layer_t* L, float* sw_out, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (sw_out == nullptr && L->d.out_features > 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "sw_out is null");
+  DeviceGuard guard(L->d.device);
+  return launch_weight_row_scale(L, sw_out, static_cast<cudaStream_t>(stream), 127.0f);
+}
+
+SACQ_API int sacq_decode_weight_int8(const sacq_layer_t* L, const float* sw, void* wq_out, void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if ((sw == nullptr || wq_out == nullptr) && L->d.out_features > 0)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard guard(L->d.device);
+  return launch_decode_weight_int8(L, sw, wq_out, static_cast<cudaStream_t>(stream));
+}
+
+SACQ_API int64_t sacq_workspace_bytes_w8a8(const sacq_layer_t* L, int64_t M) {
+  if (L == nullptr || M < 0) return 0;
+  return ((L->d.out_features * L->d.in_features + 255) & ~(int64_t)255);
+}
+
+SACQ_API int sacq_linear_w8a8_int8(const sacq_layer_t* L, const void* q_int8, const float* act_scale, const float* w_scale,
+                                   int64_t M, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
+                                   void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
+  if (M == 0 || L->d.out_features == 0) return SACQ_OK;
+  if (q_int8 == nullptr || act_scale == nullptr || w_scale == nullptr || y_out == nullptr)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (ldy < L->d.out_features)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "ldy=%lld smaller than out_features=%lld", (long long)ldy,
+                     (long long)L->d.out_features);
+  if (!dense_i8_supported(L))
+    return set_error(SACQ_ERR_UNSUPPORTED, "INT8 recipe needs in_features to be a multiple of 16");
+  const int64_t need = sacq_workspace_bytes_w8a8(L, M);
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given", (long long)need,
+                     (long long)workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+  DeviceGuard guard(L->d.device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // per call, as the reference does: packed stream -> int8 weight rows, then the dense integer GEMM
+  if (int rc = launch_decode_weight_int8(L, w_scale, workspace, s)) return rc;
+  return launch_dense_i8(L, q_int8, act_scale, workspace, w_scale, M, y_out, ldy, s);
 }
 
 SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,

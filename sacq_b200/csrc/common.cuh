@@ -44,6 +44,12 @@ struct sacq_layer {
 
 namespace sacq {
 
+// A non-zero shift (either sign of zero counts as none).  The fast kernels contract codewords and
+// apply scale and shift afterwards; that drops the two bf16 roundings of the reference's
+// reconstruction, which a shift larger than the weights makes visible.  Shifted layers therefore
+// run on kernels that rebuild bf16(bf16(c * s) + shift) per weight.
+inline bool has_shift(const sacq_layer* L) { return (L->d.shift_bf16 & 0x7fffu) != 0; }
+
 int set_error(int code, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 void count_launch(int n = 1);
@@ -56,8 +62,9 @@ void count_launch(int n = 1);
 
 // kernel entry points implemented in the other translation units
 int launch_dequant_bf16(const sacq_layer* L, void* w_out, cudaStream_t s);
-int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s);
+int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s, float limit = kE4M3Max);
 int launch_decode_weight_fp8(const sacq_layer* L, const float* sw, void* wq, cudaStream_t s);
+int launch_decode_weight_int8(const sacq_layer* L, const float* sw, void* wq, cudaStream_t s);
 int launch_quant_act_fp8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
 int launch_quant_act_int8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale, cudaStream_t s);
 int launch_act_quant_fp8(int kind, const void* a, int64_t a_pitch, const void* b, int64_t b_pitch, const void* c,
@@ -72,6 +79,7 @@ bool small_m_supported(const sacq_layer* L);
 // Kernel selector (5 = fp16 warp-MMA, 3 = CUDA-core) of the small-M variant that takes int8 activations.
 int small_m_int8_selector(const sacq_layer* L);
 int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M);
+void small_m_scratch_need(const sacq_layer* L, int64_t M, int64_t* bytes, int64_t* counters);
 // Further copies of a GEMM's output, written by the same epilogue: buffers of other GPUs of the
 // node mapped into this process (plain peer stores over NVLink), same row pitch as y.
 constexpr int kMaxBcast = 7;
@@ -94,6 +102,18 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
 int launch_large_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
                          void* const* ys, const int64_t* ldys, cudaStream_t s);
 void large_m_release(sacq_layer* L);
+
+// Tensor-core kernel that keeps the expanded weights in tensor memory (linear_large_m_tmem.cu).
+bool large_m_tmem_supported(const sacq_layer* L);
+int large_m_tmem_pick_nt(const sacq_layer* L, int64_t M);
+int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                        cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0, const BcastDst* bc = nullptr,
+                        int nt_force = 0);
+
+// Dense int8 x int8 -> int32 GEMM of the reference's deployed INT8 recipe (linear_dense_i8.cu).
+bool dense_i8_supported(const sacq_layer* L);
+int launch_dense_i8(const sacq_layer* L, const void* q, const float* act_scale, const void* wq, const float* w_scale,
+                    int64_t M, void* y, int64_t ldy, cudaStream_t s);
 
 bool large_m_grouped_supported(const sacq_layer* L);
 int64_t large_m_grouped_workspace_bytes(const sacq_layer* L, int64_t M);

@@ -76,11 +76,11 @@ dequant_bf16_kernel(const uint32_t* __restrict__ words, const uint16_t* __restri
   }
 }
 
-// One warp per output row: max |W[n,:]| / 448.
+// One warp per output row: max |W[n,:]| / limit (448 for e4m3, 127 for int8).
 __global__ void __launch_bounds__(256)
 weight_row_scale_kernel(const uint32_t* __restrict__ words, const uint16_t* __restrict__ cb,
                         const uint16_t* __restrict__ scales, float* __restrict__ sw, int64_t N, int vpr, int d,
-                        int bits, int group_size, int num_groups, float shift) {
+                        int bits, int group_size, int num_groups, float shift, float limit) {
   const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (n >= N) return;
   const int lane = threadIdx.x & 31;
@@ -94,7 +94,7 @@ weight_row_scale_kernel(const uint32_t* __restrict__ words, const uint16_t* __re
     }
   }
   m = warp_max(m);
-  if (lane == 0) sw[n] = m > 0.f ? __fdiv_rn(m, kE4M3Max) : 1.0f;
+  if (lane == 0) sw[n] = m > 0.f ? __fdiv_rn(m, limit) : 1.0f;
 }
 
 // One thread per d-vector: e4m3(clamp(W / sw[n])).
@@ -127,6 +127,35 @@ decode_weight_fp8_kernel(const uint32_t* __restrict__ words, const uint16_t* __r
   }
 }
 
+// One thread per d-vector: int8(round_half_even(clamp(W / sw[n], -127, 127))), the weight bytes
+// of the reference's INT8 recipe (perrow_a8_candidate_r3.py:57-60; the conversion is the
+// cvt.rni.sat.s8.f32 of int8_direct_integer_round_20261028_r1.py:6-9).
+__global__ void __launch_bounds__(256)
+decode_weight_int8_kernel(const uint32_t* __restrict__ words, const uint16_t* __restrict__ cb,
+                          const uint16_t* __restrict__ scales, const float* __restrict__ sw,
+                          int8_t* __restrict__ wq, int64_t total_vectors, int vpr, int d, int bits, int group_size,
+                          int num_groups, float shift) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vectors; i += stride) {
+    const uint32_t idx = extract_index(words, i, bits);
+    const int64_t n = i / vpr;
+    const int v = (int)(i - n * vpr);
+    const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
+    const float row = __ldg(sw + n);
+    auto enc = [&](int j) -> uint32_t {
+      const float a = bf16_bits_to_float(reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j), s, shift));
+      const float q = fminf(fmaxf(__fdiv_rn(a, row), -127.f), 127.f);
+      return (uint32_t)(__float2int_rn(q) & 0xff);
+    };
+    if ((d & 3) == 0 && ((reinterpret_cast<uintptr_t>(wq) & 3) == 0)) {
+      for (int j = 0; j < d; j += 4)
+        *reinterpret_cast<uint32_t*>(wq + i * d + j) = enc(j) | (enc(j + 1) << 8) | (enc(j + 2) << 16) | (enc(j + 3) << 24);
+    } else {
+      for (int j = 0; j < d; ++j) wq[i * d + j] = (int8_t)enc(j);
+    }
+  }
+}
+
 // ---- derived tables -------------------------------------------------------
 
 __global__ void codebook_absmax_kernel(const uint16_t* __restrict__ cb, int64_t count, float* __restrict__ out) {
@@ -137,6 +166,17 @@ __global__ void codebook_absmax_kernel(const uint16_t* __restrict__ cb, int64_t 
   }
   m = warp_max(m);
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));  // m >= 0
+}
+
+// Largest index of the packed stream (a payload whose indices reach past the codebook would make
+// every kernel read out of bounds; the reference's CPU gather raises IndexError for it).
+__global__ void index_max_kernel(const uint32_t* __restrict__ words, int64_t count, int bits, unsigned* __restrict__ out) {
+  unsigned m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
+    m = max(m, extract_index(words, i, bits));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(out, m);
 }
 
 // cb_f16[i] = fp16(c * 2^e16); cb_hilo[c][0][j] = e4m3(c * 2^e8), cb_hilo[c][1][j] = e4m3(c*2^e8 - hi)
@@ -201,7 +241,7 @@ int launch_dequant_bf16(const sacq_layer* L, void* w_out, cudaStream_t s) {
   return SACQ_OK;
 }
 
-int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s) {
+int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s, float limit) {
   const sacq_layer_desc& d = L->d;
   if (d.out_features == 0) return SACQ_OK;
   const int warps = 8;
@@ -209,7 +249,20 @@ int launch_weight_row_scale(const sacq_layer* L, float* sw, cudaStream_t s) {
   weight_row_scale_kernel<<<grid, warps * 32, 0, s>>>(
       static_cast<const uint32_t*>(d.packed), static_cast<const uint16_t*>(d.codebook),
       static_cast<const uint16_t*>(d.scales), sw, d.out_features, (int)L->vectors_per_row, d.vector_dim,
-      d.index_bits, d.group_size, (int)L->num_groups, host_bf16_to_float(d.shift_bf16));
+      d.index_bits, d.group_size, (int)L->num_groups, host_bf16_to_float(d.shift_bf16), limit);
+  count_launch();
+  SACQ_CUDA_TRY(cudaGetLastError());
+  return SACQ_OK;
+}
+
+int launch_decode_weight_int8(const sacq_layer* L, const float* sw, void* wq, cudaStream_t s) {
+  const sacq_layer_desc& d = L->d;
+  const int64_t total = d.out_features * L->vectors_per_row;
+  if (total == 0) return SACQ_OK;
+  decode_weight_int8_kernel<<<grid_for(total, 256, L->num_sms), 256, 0, s>>>(
+      static_cast<const uint32_t*>(d.packed), static_cast<const uint16_t*>(d.codebook),
+      static_cast<const uint16_t*>(d.scales), sw, static_cast<int8_t*>(wq), total, (int)L->vectors_per_row,
+      d.vector_dim, d.index_bits, d.group_size, (int)L->num_groups, host_bf16_to_float(d.shift_bf16));
   count_launch();
   SACQ_CUDA_TRY(cudaGetLastError());
   return SACQ_OK;
@@ -262,9 +315,26 @@ int launch_build_tables(sacq_layer* L, cudaStream_t s) {
     }
     if (e == cudaSuccess) e = cudaMemcpyAsync(&h_smax, d_max, sizeof(float), cudaMemcpyDeviceToHost, s);
   }
+  // every index must address a codeword (only a codebook smaller than 2^bits leaves room for one that does not)
+  unsigned h_imax = 0;
+  const int64_t n_idx = d.out_features * L->vectors_per_row;
+  const bool check_idx = n_idx > 0 && (int64_t)d.codebook_size < (1LL << d.index_bits);
+  if (e == cudaSuccess && check_idx) {
+    e = cudaMemsetAsync(d_max, 0, sizeof(float), s);
+    if (e == cudaSuccess) {
+      index_max_kernel<<<grid_for(n_idx, 256, L->num_sms), 256, 0, s>>>(static_cast<const uint32_t*>(d.packed), n_idx,
+                                                                       d.index_bits, reinterpret_cast<unsigned*>(d_max));
+      count_launch();
+      e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&h_imax, d_max, sizeof(unsigned), cudaMemcpyDeviceToHost, s);
+  }
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   cudaFree(d_max);
   if (e != cudaSuccess) return cuda_fail(e, "codebook absmax");
+  if (check_idx && h_imax >= (unsigned)d.codebook_size)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "packed stream holds index %u but the codebook has %d entries", h_imax,
+                     d.codebook_size);
   {
     int sx = 0;
     if (h_smax > 0.f) (void)frexpf(h_smax, &sx);

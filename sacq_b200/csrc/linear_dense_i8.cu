@@ -1,0 +1,235 @@
+// The reference's deployed INT8 recipe as integer work on the 5th-generation tensor cores
+// (sm_100a): per-token int8 activations x per-output-row int8 weights -> int32, then
+//   y[m,n] = bf16( fma(sa[m], float(acc[m,n]) * sw[n], bias[n]) )        (bias given)
+//   y[m,n] = bf16( sa[m] * (float(acc[m,n]) * sw[n]) )                   (no bias)
+// -- weight scale first, then token scale, the bias inside one fused multiply-add
+// (int8_small_m_gemm_20261028_r1.py:7-32, int8_ordered_epilogue_20261028_r1.py:11-22).
+// Integer accumulation is exact, so the output bytes are a function of the operands alone:
+// this path can be, and is tested to be, bit-identical to a CPU restatement of the recipe.
+//
+// Like the reference (perrow_a8_candidate_r3.py:52-63: "no persistent decoded weight cache")
+// the int8 weight matrix is produced per call from the packed stream into the caller's
+// workspace (decode_weight_int8_kernel, dequant.cu) and consumed by a plain dense GEMM:
+//   warp 0 (one lane) : TMA producer, 128 x 128-byte tiles of activations and weights,
+//                       SWIZZLE_128B, no multicast;
+//   warp 1 (one lane) : tcgen05.mma kind::i8 (M128 x N128 x K32), int32 accumulator in TMEM;
+//   warps 2..5        : epilogue, one TMEM lane quarter each.
+// Every mbarrier wait is bounded (status word + CTA-wide abort flag), as in the other
+// tensor-core kernels.
+#include <cuda.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace sacq {
+
+namespace {
+
+using namespace umma;
+
+constexpr int kDBN = 128;                 // weight rows per tile = accumulator columns
+constexpr int kDBK = 128;                 // bytes per K block
+constexpr int kDStages = 6;
+constexpr int kDTile = kBM * kDBK;        // 16 KB
+constexpr int kDThreads = 6 * 32;
+
+struct DenseParams {
+  const float* act_scale;       // [M]
+  const float* w_scale;         // [N]
+  const uint16_t* bias;         // bf16 [N] or null
+  uint16_t* y;                  // bf16 [M, ldy]
+  int64_t ldy;
+  int* status;
+  int M, N, K;
+};
+
+// kind::i8 instruction descriptor: int32 accumulate, A = B = signed 8-bit, both K-major.
+__host__ __device__ constexpr uint32_t make_idesc_i8(int bn) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kDThreads, 1)
+dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const __grid_constant__ DenseParams p) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  constexpr uint32_t kStageBytes = 2 * kDTile;
+  constexpr uint32_t kSwOff = kDStages * kStageBytes, kBiasOff = kSwOff + kDBN * 4, kBarOff = kBiasOff + kDBN * 4,
+                     kMiscOff = kBarOff + 16 * 8;
+  constexpr int FULL = 0, EMPTY = kDStages, ACC_FULL = 2 * kDStages;
+  const uint32_t bars = base + kBarOff;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kMiscOff + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kDBN, m0 = blockIdx.y * kBM;
+  const int num_kb = (p.K + kDBK - 1) / kDBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kDStages; ++i) {
+      mbar_init(bar(FULL + i), 1);
+      mbar_init(bar(EMPTY + i), 1);
+    }
+    mbar_init(bar(ACC_FULL), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kDBN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int st = kb % kDStages;
+        if (!mbar_wait(bar(EMPTY + st), ((kb / kDStages) & 1) ^ 1, abort_flag, p.status)) break;
+        mbar_arrive_expect_tx(bar(FULL + st), kStageBytes);
+        tma_load_2d(base + st * kStageBytes, &tmap_a, kb * kDBK, m0, bar(FULL + st));
+        tma_load_2d(base + st * kStageBytes + kDTile, &tmap_b, kb * kDBK, n0, bar(FULL + st));
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t kIdesc = make_idesc_i8(kDBN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int st = kb % kDStages;
+        ok = mbar_wait(bar(FULL + st), (kb / kDStages) & 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t a_desc = make_smem_desc(base + st * kStageBytes);
+        const uint64_t b_desc = make_smem_desc(base + st * kStageBytes + kDTile);
+#pragma unroll
+        for (int ks = 0; ks < kDBK / 32; ++ks) {
+          const uint64_t adv = (uint64_t)((ks * 32) >> 4);
+          umma_i8(tmem_base, a_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+        }
+        umma_commit(bar(EMPTY + st));
+      }
+      if (ok) umma_commit(bar(ACC_FULL));
+    }
+    __syncwarp();
+  } else {
+    const int et = threadIdx.x - 64;                  // 0..127
+    {
+      const int n = min(n0 + et, p.N - 1);
+      reinterpret_cast<float*>(sm + kSwOff)[et] = __ldg(p.w_scale + n);
+      reinterpret_cast<float*>(sm + kBiasOff)[et] = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    const int quarter = warp & 3;
+    const int m = m0 + quarter * 32 + lane;
+    const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+    const bool ok = mbar_wait(bar(ACC_FULL), 0, abort_flag, p.status);   // tcgen05.ld below is per warp: no CTA-wide collective
+    if (__all_sync(0xffffffffu, ok)) {
+      tc_fence_after();
+      const float* swp = reinterpret_cast<const float*>(sm + kSwOff);
+      const float* bp = reinterpret_cast<const float*>(sm + kBiasOff);
+      const bool has_bias = p.bias != nullptr;
+#pragma unroll 1
+      for (int cc = 0; cc < kDBN / 32; ++cc) {
+        const int c0 = cc * 32;
+        if (n0 + c0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        if (m < p.M) {
+          uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
+          // weight scale first, then the token scale; the bias rides in the same fused multiply-add
+          auto fin = [&](int c) -> uint32_t {
+            const float scaled = __fmul_rn(__int2float_rn((int)r[c]), swp[c0 + c]);
+            const float v = has_bias ? fmaf(sa, scaled, bp[c0 + c]) : __fmul_rn(sa, scaled);
+            return (uint32_t)float_to_bf16_bits(v);
+          };
+          const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
+          if (vec) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o[j] = fin(v * 8 + 2 * j) | (fin(v * 8 + 2 * j + 1) << 16);
+              *reinterpret_cast<uint4*>(yrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (n0 + c0 + c < p.N) yrow[c] = (uint16_t)fin(c);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kDBN);
+}
+
+constexpr size_t kDenseSmem = kDStages * 2 * kDTile + 2 * kDBN * 4 + 16 * 8 + 64 + 1024;
+
+}  // namespace
+
+bool dense_i8_supported(const sacq_layer* L) { return L->d.in_features % 16 == 0 && L->d.in_features >= 16; }
+
+// y = epilogue(q [M,K] int8 x wq [N,K] int8): the dense part of the INT8 recipe.
+int launch_dense_i8(const sacq_layer* L, const void* q, const float* act_scale, const void* wq, const float* w_scale,
+                    int64_t M, void* y, int64_t ldy, cudaStream_t s) {
+  const sacq_layer_desc& d = L->d;
+  if (M <= 0 || d.out_features == 0) return SACQ_OK;
+  if (!dense_i8_supported(L))
+    return set_error(SACQ_ERR_UNSUPPORTED, "INT8 GEMM needs in_features to be a multiple of 16, got %lld",
+                     (long long)d.in_features);
+  if (reinterpret_cast<uintptr_t>(q) % 16 != 0 || reinterpret_cast<uintptr_t>(wq) % 16 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "INT8 GEMM operands must be 16-byte aligned");
+  if ((int64_t)d.in_features * 127 * 127 > 2147483647LL)
+    return set_error(SACQ_ERR_UNSUPPORTED, "in_features=%lld could overflow the int32 accumulator", (long long)d.in_features);
+  CUtensorMap ta, tb;
+  int rc = encode_bytes_2d(&ta, q, (uint64_t)d.in_features, (uint64_t)M, (uint64_t)d.in_features, kDBK, kBM,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != SACQ_OK) return rc;
+  rc = encode_bytes_2d(&tb, wq, (uint64_t)d.in_features, (uint64_t)d.out_features, (uint64_t)d.in_features, kDBK, kDBN,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != SACQ_OK) return rc;
+  DenseParams p{};
+  p.act_scale = act_scale;
+  p.w_scale = w_scale;
+  p.bias = static_cast<const uint16_t*>(d.bias);
+  p.y = static_cast<uint16_t*>(y);
+  p.ldy = ldy;
+  p.status = L->d_status;
+  p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    SACQ_CUDA_TRY(cudaFuncSetAttribute(dense_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const dim3 grid((unsigned)((d.out_features + kDBN - 1) / kDBN), (unsigned)((M + kBM - 1) / kBM), 1);
+  if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
+  dense_i8_kernel<<<grid, kDThreads, kDenseSmem, s>>>(ta, tb, p);
+  count_launch();
+  SACQ_CUDA_TRY(cudaGetLastError());
+  return SACQ_OK;
+}
+
+}  // namespace sacq

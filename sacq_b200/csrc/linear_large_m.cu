@@ -34,6 +34,8 @@
 #include <cuda.h>
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -574,7 +576,7 @@ bool large_m_supported(const sacq_layer* L) {
   if (d.index_bits != 8 && d.index_bits != 12 && d.index_bits != 16) return false;
   if (!L->rows_16b_aligned) return false;
   if (d.in_features % (2 * kBK) != 0) return false;
-  if (L->num_groups != 1 || d.shift_bf16 != 0) return false;
+  if (L->num_groups != 1 || has_shift(L)) return false;
   const size_t cb_bytes = (size_t)L->cb_entries * d.vector_dim * 2;
   if (make_layout(kMaxBN, 1, sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) return false;
   return true;
@@ -622,7 +624,10 @@ bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers
   return bn != 0;
 }
 
+std::mutex g_plan_mutex;   // layers build their index tile maps on first use, possibly from several host threads
+
 int ensure_idx_map(sacq_layer* Lm, int bn, const CUtensorMap** out) {
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
   if (Lm->large_plan == nullptr) {
     LargeMPlan* plan = new LargeMPlan();
     plan->sb_bytes = sb_bytes_for(Lm);
@@ -696,6 +701,10 @@ int launch_layers(const sacq_layer* const* layers, int n, const void* q, const f
 }
 
 }  // namespace
+
+int large_m_index_map(const sacq_layer* L, int rows, const CUtensorMap** out) {
+  return ensure_idx_map(const_cast<sacq_layer*>(L), rows, out);
+}
 
 int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    cudaStream_t s, const void* residual, int64_t ldr, const BcastDst* bc) {

@@ -500,6 +500,7 @@ bool large_m_grouped_supported(const sacq_layer* L) {
   if (!L->rows_16b_aligned) return false;
   if (d.in_features % kBKh != 0 || d.group_size % kBKh != 0) return false;
   if (((size_t)L->cb_entries * d.vector_dim * 2) % 16 != 0) return false;
+  if (has_shift(L)) return false;
   return grouped_stages_for(L, 32, 1, 1) >= 2;
 }
 

@@ -260,16 +260,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32) small_m_generic_kernel(const S
     const int sp_begin = sg * p.spans_per_item;
     const int sp_end = min(sp_begin + p.spans_per_item, p.spans_per_row);
 
-    float acc[MT], xsum[MT];
+    float acc[MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) { acc[m] = 0.f; xsum[m] = 0.f; }
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
 
     for (int sp = sp_begin; sp < sp_end; ++sp) {
       __syncwarp();
       const int kbase = sp * span_k;
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        float t = 0.f;
         for (int k = lane; k < span_k; k += 32) {
           float v = 0.f;
           if (m0 + m < p.M) {
@@ -278,15 +277,29 @@ __global__ void __launch_bounds__(kMaxWarps * 32) small_m_generic_kernel(const S
                            : __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3)));
           }
           xs[m * span_k + k] = v;
-          t += v;
         }
-        if (p.shift != 0.f) xsum[m] += warp_sum(t);
       }
       __syncwarp();
       float sacc[MT];
 #pragma unroll
       for (int m = 0; m < MT; ++m) sacc[m] = 0.f;
       const int64_t i0 = (int64_t)nr * p.vpr + (int64_t)sp * p.span_idx;
+      const int g = kbase / p.group_size;
+      const float s = bf16_bits_to_float(__ldg(p.scales + (int64_t)nr * p.num_groups + g));
+      if (p.shift != 0.f) {
+        // A shifted layer is contracted against the reference's reconstruction itself,
+        // bf16(bf16(c * s) + shift) (cosmos_quant_shim.py:451-453): a large shift leaves the
+        // weight only a few significant bits, so both roundings have to be reproduced.
+        for (int i = 0; i < p.span_idx; ++i) {
+          const uint32_t idx = extract_index(words, i0 + i, p.bits);
+          for (int j = 0; j < p.d; ++j) {
+            const float w = bf16_bits_to_float(reconstruct_bf16(__ldg(p.cb_bf16 + (int64_t)idx * p.d + j), s, p.shift));
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[m] = fmaf(w, xs[m * span_k + i * p.d + j], acc[m]);
+          }
+        }
+        continue;
+      }
       for (int i = 0; i < p.span_idx; ++i) {
         const uint32_t idx = extract_index(words, i0 + i, p.bits);
         for (int j = 0; j < p.d; ++j) {
@@ -295,14 +308,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32) small_m_generic_kernel(const S
           for (int m = 0; m < MT; ++m) sacc[m] = fmaf(c, xs[m * span_k + i * p.d + j], sacc[m]);
         }
       }
-      const int g = kbase / p.group_size;
-      const float s = bf16_bits_to_float(__ldg(p.scales + (int64_t)nr * p.num_groups + g));
 #pragma unroll
       for (int m = 0; m < MT; ++m) acc[m] = fmaf(s, sacc[m], acc[m]);
     }
     float val[MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) val[m] = fmaf(acc[m], p.out_mul, p.shift * xsum[m]);
+    for (int m = 0; m < MT; ++m) val[m] = acc[m] * p.out_mul;
     finish_rows<MT>(p, chunk, rb, sg, val, n, row_ok);
   }
 }
@@ -325,6 +336,7 @@ bool fast_eligible(const sacq_layer* L) {
   const int span_k = kSpanIdx * d.vector_dim;
   if (d.in_features % span_k != 0) return false;
   if (d.group_size % span_k != 0) return false;
+  if (has_shift(L)) return false;            // shifted layers need the exact reconstruction (generic kernel)
   return true;
 }
 
@@ -339,6 +351,7 @@ bool unpacked_eligible(const sacq_layer* L) {
   if (d.group_size % 32 != 0) return false;
   const size_t cb_bytes = (size_t)L->cb_entries * d.vector_dim * 2;
   if (cb_bytes > 64 * 1024 || cb_bytes % 16 != 0) return false;
+  if (has_shift(L)) return false;
   return true;
 }
 
@@ -546,6 +559,14 @@ int64_t small_m_workspace_bytes(const sacq_layer* L, int64_t M) {
   return bytes;
 }
 
+// Scratch bytes (counter region included) and arrival counters the launch plan for (layer, M)
+// uses; both come from the same plan launch_small_m() will make.
+void small_m_scratch_need(const sacq_layer* L, int64_t M, int64_t* bytes, int64_t* counters) {
+  const Plan pl = make_plan(L, M);
+  *bytes = small_m_workspace_bytes(L, M);
+  *counters = pl.num_sg > 1 ? (int64_t)pl.chunks * pl.row_blocks : 0;
+}
+
 namespace {
 SmallMParams fill_params(const sacq_layer* L, const Plan& pl, const void* q, const float* scale, int64_t M, void* y,
                          int64_t ldy, void* ws) {
@@ -589,6 +610,8 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   const Plan pl = make_plan(L, M);
   if (L->force_kernel == 6 && !pl.unpacked)
     return set_error(SACQ_ERR_UNSUPPORTED, "index-unpacking warp-MMA variant cannot run this layer");
+  if ((L->force_kernel == 4 || L->force_kernel == 5) && !pl.mma)
+    return set_error(SACQ_ERR_UNSUPPORTED, "warp-MMA variant cannot run this layer");
   if (pl.smem > kSmemBudget)
     return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel needs %zu bytes of shared memory", pl.smem);
   const int64_t need = small_m_workspace_bytes(L, M);

@@ -10,6 +10,8 @@
 // (kStaticScratchBytes) until the process exits.
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace sacq {
@@ -22,20 +24,22 @@ constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB, counters included
 // address the kernel needs comes from cudaGetSymbolAddress, once per device.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-void* g_scratch_ptr[64] = {};
+std::atomic<void*> g_scratch_ptr[64] = {};   // per device; every writer stores the same address
 
 int static_scratch_for_current_device(void** out) {
   int dev = -1;
   SACQ_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return set_error(SACQ_ERR_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
-  if (g_scratch_ptr[dev] == nullptr) {
+  void* cached = g_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* ptr = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
     if (ptr == nullptr) return set_error(SACQ_ERR_CUDA, "static scratch has no device address on device %d", dev);
-    g_scratch_ptr[dev] = ptr;
+    g_scratch_ptr[dev].store(ptr, std::memory_order_release);
+    cached = ptr;
   }
-  *out = g_scratch_ptr[dev];
+  *out = cached;
   return SACQ_OK;
 }
 
@@ -68,16 +72,14 @@ SACQ_API int sacq_linear_a8_static_scratch(const sacq_layer_t* L, const void* q,
     // the split-K CUDA-core variant is the one that needs scratch; run exactly that one
     sacq_layer view = *L;
     view.force_kernel = 3;
-    const int64_t need = small_m_workspace_bytes(&view, M);
-    const int64_t row_blocks = (L->d.out_features + 31) / 32;
-    const int64_t chunks = (M + 15) / 16;
-    if (need > (int64_t)kStaticScratchBytes ||
-        row_blocks * chunks * (int64_t)sizeof(int) > sacq_workspace_counter_bytes()) {
+    int64_t need = 0, counters = 0;
+    small_m_scratch_need(&view, M, &need, &counters);
+    if (need > (int64_t)kStaticScratchBytes || counters * (int64_t)sizeof(int) > sacq_workspace_counter_bytes()) {
       rc = set_error(SACQ_ERR_WORKSPACE,
                      "this call (M=%lld, N=%lld) needs %lld bytes of scratch and %lld arrival counters, but the "
                      "built-in scratch holds %lld bytes and %lld counters; use sacq_linear_a8 with a "
                      "caller-provided workspace",
-                     (long long)M, (long long)L->d.out_features, (long long)need, (long long)(row_blocks * chunks),
+                     (long long)M, (long long)L->d.out_features, (long long)need, (long long)counters,
                      (long long)kStaticScratchBytes,
                      (long long)(sacq_workspace_counter_bytes() / (int64_t)sizeof(int)));
       break;

@@ -207,4 +207,8 @@ __device__ __forceinline__ void store_staged_tile(const uint8_t* stg, int pitch,
 int encode_bytes_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t pitch_bytes,
                     uint32_t box_bytes, uint32_t box_rows, CUtensorMapSwizzle swizzle);
 
+// Tile map over a layer's packed index rows: box = one index super-block (two 128-k blocks) x
+// `rows` weight rows (32, 64 or 128).  Built on first use and kept by the layer.
+int large_m_index_map(const sacq_layer* L, int rows, const CUtensorMap** out);
+
 }  // namespace sacq

@@ -22,7 +22,7 @@ import math
 import torch
 
 from . import _lib
-from .packing import index_bits_for, index_window_bytes, pack_indices
+from .packing import check_index_range, index_bits_for, index_window_bytes, pack_indices
 
 _REQUIRED = ("codebook", "scales", "in_features", "out_features", "group_size", "vector_dim")
 
@@ -32,11 +32,12 @@ def _stream_ptr() -> int:
 
 
 class _Workspace:
-    """Per-device scratch shared by the layers of a process: split-K partial sums and the
-    zero-initialised arrival counters of the small-M kernel, plus the FP8 activation
-    staging buffers.  Grown on demand outside captured regions."""
+    """Scratch shared by the layers of a process, one set per (device, stream): split-K partial
+    sums and the zero-initialised arrival counters of the small-M kernel, plus the FP8
+    activation staging buffers.  Calls on one stream are ordered and may share a set; calls on
+    different streams may overlap on the GPU, so each stream gets its own.  Grown on demand."""
 
-    _by_device: dict[int, "_Workspace"] = {}
+    _by_device: dict[tuple[int, int], "_Workspace"] = {}
 
     def __init__(self, device: torch.device):
         self.device = device
@@ -48,10 +49,11 @@ class _Workspace:
     @classmethod
     def get(cls, device: torch.device) -> "_Workspace":
         idx = device.index if device.index is not None else torch.cuda.current_device()
-        w = cls._by_device.get(idx)
+        key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+        w = cls._by_device.get(key)
         if w is None:
             w = cls(torch.device("cuda", idx))
-            cls._by_device[idx] = w
+            cls._by_device[key] = w
         return w
 
     def scratch(self, nbytes: int) -> torch.Tensor:
@@ -104,6 +106,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
             # an unpacked payload (uint8 or int32 indices) is serialised once at load time;
             # the kernels only ever see the bit stream
             source = torch.as_tensor(payload["indices"])
+            check_index_range(source, int(codebook.shape[0]))
             self.index_shape = tuple(int(x) for x in source.shape)
             self.index_bits = index_bits_for(codebook.shape[0])
             packed_source = pack_indices(source, self.index_bits)
@@ -210,12 +213,54 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         from .activation import quantize_rows
         return quantize_rows(x, "fp8_e4m3fn")
 
-    def weight_row_scale(self) -> torch.Tensor:
-        """fp32 [N, 1]: max|W[n,:]| / 448 (the A8 recipe's per-output-row weight scale)."""
+    def weight_row_scale(self, mode: str = "fp8_e4m3fn") -> torch.Tensor:
+        """fp32 [N, 1]: max|W[n,:]| / 448 for ``'fp8_e4m3fn'`` or / 127 for ``'int8_symmetric'`` (the
+        A8 recipe's per-output-row weight scale, ``quantize_rows(W, mode)[1]`` of the reference)."""
+        if mode not in ("fp8_e4m3fn", "int8_symmetric"):
+            raise ValueError(f"unknown weight format {mode!r}")
         sw = torch.empty((self.out_features, 1), dtype=torch.float32, device=self.codebook.device)
+        fn = self._lib.sacq_weight_row_scale if mode == "fp8_e4m3fn" else self._lib.sacq_weight_row_scale_int8
         with torch.cuda.device(sw.device):
-            _lib.check(self._lib.sacq_weight_row_scale(self._handle, sw.data_ptr(), _stream_ptr()))
+            _lib.check(fn(self._handle, sw.data_ptr(), _stream_ptr()))
         return sw
+
+    def decode_weight_int8(self, weight_row_scale: torch.Tensor) -> torch.Tensor:
+        """int8 [N, K] = round_half_even(clamp(W / row_scale, -127, 127)) decoded straight from the
+        packed stream: the weight bytes of the reference's INT8 recipe."""
+        sw = weight_row_scale.to(device=self.codebook.device, dtype=torch.float32).contiguous()
+        if sw.numel() != self.out_features:
+            raise ValueError("weight_row_scale must have out_features entries")
+        wq = torch.empty((self.out_features, self.in_features), dtype=torch.int8, device=self.codebook.device)
+        with torch.cuda.device(wq.device):
+            _lib.check(self._lib.sacq_decode_weight_int8(self._handle, sw.data_ptr(), wq.data_ptr(), _stream_ptr()))
+        return wq
+
+    def linear_w8a8_int8(self, q: torch.Tensor, scale: torch.Tensor, weight_row_scale: torch.Tensor,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
+        """The reference's deployed INT8 recipe: per-token int8 activations (``quantize_rows(x,
+        'int8_symmetric')``) x per-output-row int8 weights (decoded per call), exact int32
+        accumulation, ``bf16(fma(sa, float(acc) * sw, bias))``.  q int8 ``[M, K]``, scale fp32 ``[M]``,
+        weight_row_scale = ``self.weight_row_scale('int8_symmetric')`` -> bf16 ``[M, N]``."""
+        if q.dim() != 2 or q.shape[1] != self.in_features:
+            raise ValueError("q must be [M, in_features]")
+        if not q.is_cuda or q.device != self.codebook.device:
+            raise ValueError("Matching CUDA operands required")
+        if q.dtype != torch.int8:
+            raise TypeError("q must be int8")
+        q = q.contiguous()
+        scale = scale.reshape(-1).to(torch.float32).contiguous()
+        sw = weight_row_scale.reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
+        m = q.shape[0]
+        if scale.numel() != m or sw.numel() != self.out_features:
+            raise ValueError("scale needs one entry per row of q, weight_row_scale one per output feature")
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=q.device)
+        buf = _Workspace.get(q.device).scratch(int(self._lib.sacq_workspace_bytes_w8a8(self._handle, m)))
+        with torch.cuda.device(q.device):
+            _lib.check(self._lib.sacq_linear_w8a8_int8(self._handle, q.data_ptr(), scale.data_ptr(), sw.data_ptr(), m,
+                                                       out.data_ptr(), out.stride(0), buf.data_ptr(), buf.numel(),
+                                                       _stream_ptr()))
+        return out
 
     def decode_weight_fp8(self, weight_row_scale: torch.Tensor) -> torch.Tensor:
         """e4m3 [N, K] = e4m3(clamp(W / row_scale)) decoded straight from the packed stream."""
@@ -377,9 +422,11 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
     # ------------------------------------------------------------------ extras
     def set_kernel(self, which: str | int) -> None:
         """Force a GEMM kernel: 'auto' (0), 'small' (1), 'large' (2), 'small_simt' (3), 'small_mma' (4),
-        'small_mma_direct' (5), 'small_mma_unpacked' (6), 'large_grouped' (7)."""
+        'small_mma_direct' (5), 'small_mma_unpacked' (6), 'large_grouped' (7), 'large_tmem' (8; 9-11 also
+        fix its token sub-tiles per CTA to 1-3)."""
         code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5,
-                "small_mma_unpacked": 6, "large_grouped": 7}.get(which, which)
+                "small_mma_unpacked": 6, "large_grouped": 7, "large_tmem": 8, "large_tmem1": 9,
+                "large_tmem2": 10, "large_tmem3": 11}.get(which, which)
         _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
         self._ws_bytes.clear()
         self._host_bytes.clear()
@@ -388,7 +435,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         k = self._lib.sacq_layer_kernel_for(self._handle, m)
         if k < 0:
             _lib.check(k)
-        return {1: "small", 2: "large", 3: "large_grouped"}[k]
+        return {1: "small", 2: "large", 3: "large_grouped", 4: "large_tmem"}[k]
 
     def device_status(self) -> int:
         st = ctypes.c_int(0)

@@ -23,6 +23,17 @@ def index_window_bytes(index_bits: int) -> int:
     return (index_bits + (8 - math.gcd(index_bits, 8)) + 7) // 8
 
 
+def check_index_range(indices: torch.Tensor, codebook_size: int) -> None:
+    """Raise IndexError if an index does not address a codeword (the reference's CPU gather
+    ``codebook[indices]`` raises the same; a GPU gather would read out of bounds)."""
+    flat = torch.as_tensor(indices).detach().reshape(-1)
+    if flat.numel() == 0:
+        return
+    lo, hi = int(flat.min()), int(flat.max())
+    if lo < 0 or hi >= int(codebook_size):
+        raise IndexError(f"index {lo if lo < 0 else hi} is out of bounds for a codebook of {int(codebook_size)} entries")
+
+
 def pack_indices(indices: torch.Tensor, index_bits: int) -> torch.Tensor:
     """Flat uint8 tensor of ``ceil(count * index_bits / 8)`` bytes."""
     if index_bits < 1 or index_bits > 56:

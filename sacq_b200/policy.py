@@ -76,15 +76,16 @@ class _Block(torch.nn.Module):
         if self.cross:
             self.n3 = torch.nn.LayerNorm(hidden, device=f.device, dtype=torch.bfloat16)
 
-    def _attend(self, q, k, v):
-        # [1, heads, tokens, head_dim] views: the 4-D form lets PyTorch pick a fused attention
-        # kernel, and grouped-query attention needs no materialised key/value repeats
-        t, s = q.shape[0], k.shape[0]
-        q = q.view(1, t, self.heads, self.head_dim).transpose(1, 2)
-        k = k.view(1, s, -1, self.head_dim).transpose(1, 2)
-        v = v.view(1, s, -1, self.head_dim).transpose(1, 2)
+    def _attend(self, q, k, v, batch=1):
+        # [batch, heads, tokens, head_dim] views: the 4-D form lets PyTorch pick a fused attention
+        # kernel, and grouped-query attention needs no materialised key/value repeats; the rows
+        # of q, k, v are request-major, so every request attends to its own tokens only
+        t, s = q.shape[0] // batch, k.shape[0] // batch
+        q = q.view(batch, t, self.heads, self.head_dim).transpose(1, 2)
+        k = k.view(batch, s, -1, self.head_dim).transpose(1, 2)
+        v = v.view(batch, s, -1, self.head_dim).transpose(1, 2)
         out = F.scaled_dot_product_attention(q, k, v, enable_gqa=k.shape[1] != self.heads)
-        return out.transpose(1, 2).reshape(t, self.hidden)
+        return out.transpose(1, 2).reshape(batch * t, self.hidden)
 
     def cross_kv(self, ctx):
         return tuple(forward_shared((self.ck, self.cv), ctx))
@@ -93,17 +94,17 @@ class _Block(torch.nn.Module):
         """LayerNorm (+ AdaLN modulation) inside the quantizer of the projections it feeds."""
         return layernorm_quantize_rows(x, norm.weight, norm.bias, norm.eps, mod_scale=scale, mod_shift=shift)
 
-    def forward(self, x, cond=None, cross_kv=None, modulation=None):
+    def forward(self, x, cond=None, cross_kv=None, modulation=None, batch=1):
         if self.adaln:
             m = (self.mod(cond) if modulation is None else modulation).view(4, self.hidden)
         else:
             m = (None,) * 4
         qa, sa = self._norm_quant(self.n1, x, m[1], m[0])
         q, k, v = linear_a8_multi((self.q, self.k, self.v), qa, sa)        # one launch for q/k/v at small M
-        x = self.o.forward_residual(self._attend(q, k, v), x)            # residual added in the GEMM epilogue
+        x = self.o.forward_residual(self._attend(q, k, v, batch), x)     # residual added in the GEMM epilogue
         if self.cross:
             qc, sc = self._norm_quant(self.n3, x)
-            x = self.co.forward_residual(self._attend(self.cq.linear_a8(qc, sc), cross_kv[0], cross_kv[1]), x)
+            x = self.co.forward_residual(self._attend(self.cq.linear_a8(qc, sc), cross_kv[0], cross_kv[1], batch), x)
         qu, su = self._norm_quant(self.n2, x, m[3], m[2])
         # the activation function runs inside the quantizer of the down projection
         if self.gated:
@@ -119,6 +120,7 @@ class SyntheticGr00tPolicy(torch.nn.Module):
     LLM_LAYERS, LLM_HIDDEN, LLM_MLP, LLM_TOKENS = 12, 2048, 6144, 300
     DIT_LAYERS, DIT_HIDDEN, DIT_MLP, HORIZON, STEPS = 16, 1536, 6144, 16, 4
     ACTION_DIM = 32
+    BENCH_BATCH = 64          # independent requests per forward in the batched-throughput measurement
 
     def __init__(self, device: str = "cuda", seed: int = 0):
         super().__init__()
@@ -149,14 +151,23 @@ class SyntheticGr00tPolicy(torch.nn.Module):
 
     @torch.no_grad()
     def forward(self, image: torch.Tensor, noise: torch.Tensor) -> torch.Tensor:
-        """image: [3, 224, 224] bf16; noise: [HORIZON, ACTION_DIM] bf16 -> actions [HORIZON, ACTION_DIM]."""
-        patches = image.unfold(1, 14, 14).unfold(2, 14, 14).permute(1, 2, 0, 3, 4).reshape(self.PATCHES, -1)
+        """image: [3, 224, 224] bf16 and noise: [HORIZON, ACTION_DIM] bf16 -> actions [HORIZON, ACTION_DIM];
+        or a batch of B independent requests, image [B, 3, 224, 224] and noise [B, HORIZON, ACTION_DIM]
+        -> [B, HORIZON, ACTION_DIM].  The requests of a batch share nothing but the weights: their
+        tokens are stacked along the row dimension of every linear (M = B x tokens) and attention
+        runs per request."""
+        single = image.dim() == 3
+        if single:
+            image, noise = image.unsqueeze(0), noise.unsqueeze(0)
+        b = image.shape[0]
+        patches = image.unfold(2, 14, 14).unfold(3, 14, 14).permute(0, 2, 3, 1, 4, 5).reshape(b * self.PATCHES, -1)
         x = patches @ self.patch_embed
         for blk in self.vit:
-            x = blk(x)
-        tokens = torch.cat([self.vis_proj(x), self.text_embed], dim=0)
+            x = blk(x, batch=b)
+        vis = self.vis_proj(x).view(b, self.PATCHES, self.LLM_HIDDEN)
+        tokens = torch.cat([vis, self.text_embed.unsqueeze(0).expand(b, -1, -1)], dim=1).reshape(-1, self.LLM_HIDDEN)
         for blk in self.llm:
-            tokens = blk(tokens)
+            tokens = blk(tokens, batch=b)
         kv = [blk.cross_kv(tokens) for blk in self.dit]
         # the AdaLN modulation vectors depend on the denoising step only: all blocks' modulation
         # layers read the same one-row input, so they run four to a launch, ahead of the loop
@@ -167,17 +178,21 @@ class SyntheticGr00tPolicy(torch.nn.Module):
             for i in range(0, len(self.dit), 4):
                 per_block += linear_a8_multi([blk.mod for blk in self.dit[i: i + 4]], qc, sc)
             mods.append(per_block)
-        actions = noise
+        actions = noise.reshape(b * self.HORIZON, self.ACTION_DIM)
         dt = 1.0 / self.STEPS
         for step in range(self.STEPS):
             h = actions @ self.action_in
             for blk, ckv, mod in zip(self.dit, kv, mods[step]):
-                h = blk(h, cross_kv=ckv, modulation=mod)
+                h = blk(h, cross_kv=ckv, modulation=mod, batch=b)
             actions = actions + dt * (h @ self.action_out)
-        return actions
+        actions = actions.view(b, self.HORIZON, self.ACTION_DIM)
+        return actions[0] if single else actions
 
-    def example_inputs(self, seed: int = 42):
+    def example_inputs(self, seed: int = 42, batch: int = 1):
+        """Seeded inputs: one request ([3, 224, 224], [HORIZON, ACTION_DIM]) for batch = 1, else
+        a batch of distinct requests with a leading batch dimension."""
         g = torch.Generator().manual_seed(seed)
-        image = torch.rand(3, 224, 224, generator=g).to(device=self.device, dtype=torch.bfloat16)
-        noise = torch.randn(self.HORIZON, self.ACTION_DIM, generator=g).to(device=self.device, dtype=torch.bfloat16)
-        return image, noise
+        image = torch.rand(batch, 3, 224, 224, generator=g).to(device=self.device, dtype=torch.bfloat16)
+        noise = torch.randn(batch, self.HORIZON, self.ACTION_DIM, generator=g).to(device=self.device,
+                                                                                  dtype=torch.bfloat16)
+        return (image[0], noise[0]) if batch == 1 else (image, noise)

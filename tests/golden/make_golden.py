@@ -17,6 +17,7 @@ Reference entry points exercised:
   * cosmos_quant_shim.PrecomputedPackedVectorCodebookLinear (cpu):
     dequantize_weight(), forward()
   * a8_accuracy_recovery_2026_10_20_r1/perrow_a8_candidate_r3.py: quantize_rows
+    (both 'fp8_e4m3fn' and 'int8_symmetric', on activations and on reconstructed weights)
   * a8_rtn_r2.py: Quantizer.quantize (per-tensor twin, zero-scale rule)
 """
 from __future__ import annotations
@@ -123,6 +124,9 @@ def main():
         ("d8_c65536_b16", 16, 64, 64, 8, 65536, 0.0, False, 1),
         ("d8_c4096_shift", 16, 128, 128, 8, 4096, 0.0123, True, 4),
         ("d4_c4096_b12", 32, 128, 128, 4, 4096, 0.0, False, 16),
+        # a shift twelve times the weight magnitude: bf16(w + shift) keeps only 3-4 bits of w, so a
+        # GEMM has to reproduce both roundings of the reconstruction to stay within tolerance
+        ("d8_c4096_bigshift", 32, 256, 256, 8, 4096, -0.25, True, 16),
     ]
     for ci, (name, N, K, G, d, C, shift, with_bias, M) in enumerate(cases):
         torch.manual_seed(100 + ci)
@@ -154,6 +158,11 @@ def main():
             y_ref = y_ref + bias.float()
         y_dense = mod(x)                                                       # stock bf16 forward
         wq, sw = perrow.quantize_rows(w_mod, "fp8_e4m3fn")                     # per-output-row weight producer
+        # the deployed INT8 recipe: per-token int8 activations, per-output-row int8 weights and
+        # the exact integer product the GEMM accumulates (its scaling epilogue is CUDA-only code)
+        q8, s8 = perrow.quantize_rows(x, "int8_symmetric")
+        wq8, sw8 = perrow.quantize_rows(w_mod, "int8_symmetric")
+        acc8 = q8.to(torch.int32) @ wq8.to(torch.int32).t()
 
         out = dict(
             N=N, K=K, G=G, d=d, C=C, index_bits=bits,
@@ -168,6 +177,9 @@ def main():
             y_ref=y_ref.numpy().astype(np.float32),
             y_dense=bf16_bits(y_dense),
             wq=e4m3_bits(wq), w_scale=sw.numpy().astype(np.float32),
+            q_i8=q8.numpy().astype(np.int8), act_scale_i8=s8.numpy().astype(np.float32),
+            wq_i8=wq8.numpy().astype(np.int8), w_scale_i8=sw8.numpy().astype(np.float32),
+            acc_i32=acc8.numpy().astype(np.int32),
         )
         if bias is not None:
             out["bias"] = bf16_bits(bias)

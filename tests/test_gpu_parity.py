@@ -160,8 +160,76 @@ def test_weight_fp8_producer_matches_reference_fixture(name):
 
 # --------------------------------------------------------------------------- quantized linear
 
+def test_shifted_layer_is_reconstructed_exactly():
+    """A shift twelve times the weight magnitude: bf16(bf16(c*s) + shift) keeps 3-4 bits of the
+    weight, so only a kernel that rebuilds both roundings stays within tolerance.  The automatic
+    choice must do that at every M; the kernels that contract bare codewords must refuse."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200._lib import SacqError
+    from sacq_b200.synthetic import make_activations, make_payload
+    g = load_golden("layer_d8_c4096_bigshift")
+    mod = module_from_golden(g)
+    assert np.array_equal(bf16_bits(mod.dequantize_weight()), g["w_ref"])
+    q = torch.from_numpy(g["q"]).cuda().view(torch.float8_e4m3fn)
+    sc = torch.from_numpy(g["act_scale"]).cuda()
+    y = mod.linear_a8(q, sc)
+    assert O.rel_frobenius(y.float().cpu().numpy(), g["y_ref"]) <= GEMM_TOL
+    for k in FAST_KERNELS:
+        mod.set_kernel(k)
+        with pytest.raises(SacqError) as e:
+            mod.linear_a8(q, sc)
+        assert e.value.code == -2, k
+    mod.set_kernel("auto")
+    # a full-width layer with the same shift, at decode and prefill sizes
+    N, K = 512, 2048
+    p = make_payload(N, K, seed=21, device="cuda", iters=1)
+    p["shift"] = torch.tensor(-0.25, dtype=torch.bfloat16)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.05).to(torch.bfloat16)
+    big = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    assert np.array_equal(bf16_bits(big.dequantize_weight()), w_bits)
+    for M in (1, 16, 300):
+        q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 9)))
+        outs = _check_linear(big, q_bits, s, w_bits, bf16_bits(bias), kernels=("auto", "small_simt") + FAST_KERNELS)
+        assert set(outs) == {"auto", "small_simt"}
+        # the INT8-activation entry point takes the same exact path
+        x = make_activations(M, K, seed=M + 9)
+        from sacq_b200 import quantize_rows
+        qi, si = quantize_rows(x.cuda(), "int8_symmetric")
+        yi = big.linear_a8i(qi, si)
+        ref = O.linear_a8i_reference(qi.cpu().numpy(), si.cpu().numpy().reshape(-1), w_bits, bf16_bits(bias))
+        assert O.rel_frobenius(yi.float().cpu().numpy(), ref) <= GEMM_TOL
+
+
+def test_out_of_range_index_is_refused():
+    """An index that does not address a codeword: IndexError for an unpacked payload (as the
+    reference's gather raises), an invalid-argument status from the library for a packed one."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200._lib import SacqError
+    from sacq_b200.packing import pack_payload
+    from sacq_b200.synthetic import make_payload
+    N, K, C = 64, 256, 251
+    p = make_payload(N, K, vector_dim=8, codebook_size=C, seed=4, device="cuda", iters=1, fit=False)
+    PrecomputedPackedVectorCodebookLinear(p, None, "cuda")          # valid as generated
+    bad = dict(p)
+    packed = p["packed_indices"].clone()
+    packed[packed.numel() // 2] = 255                               # 8-bit fields: index 255 >= 251
+    bad["packed_indices"] = packed
+    with pytest.raises(SacqError) as e:
+        PrecomputedPackedVectorCodebookLinear(bad, None, "cuda")
+    assert e.value.code == -1 and "index" in str(e.value)
+    idx = torch.randint(0, C, (N, 1, K // 8), dtype=torch.int32)
+    idx[3, 0, 5] = C
+    unpacked = {k: v for k, v in p.items() if k not in ("packed_indices", "index_bits", "index_shape")}
+    unpacked["indices"] = idx
+    with pytest.raises(IndexError):
+        PrecomputedPackedVectorCodebookLinear(unpacked, None, "cuda")
+
 ALL_SMALL = ("auto", "small_simt", "small_mma", "small_mma_direct", "small_mma_unpacked")
-ALL_KERNELS = ALL_SMALL + ("large",)
+ALL_KERNELS = ALL_SMALL + ("large", "large_tmem")
+FAST_KERNELS = ("small_mma", "small_mma_direct", "small_mma_unpacked", "large", "large_grouped", "large_tmem")
 
 
 def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=ALL_SMALL):
@@ -169,14 +237,16 @@ def _check_linear(mod, q_bits, s, w_bits, bias_bits, kernels=ALL_SMALL):
     q = torch.from_numpy(q_bits).cuda().view(torch.float8_e4m3fn)
     sc = torch.from_numpy(s).cuda()
     outs = {}
+    shifted = float(mod.shift.float().abs().item()) != 0.0
     for k in kernels:
         mod.set_kernel(k)
-        if k in ("large", "large_grouped") and mod._lib.sacq_layer_kernel_for(mod._handle, q.shape[0]) < 0:
+        if k in ("large", "large_grouped", "large_tmem") and mod._lib.sacq_layer_kernel_for(mod._handle, q.shape[0]) < 0:
             continue                                   # geometry outside the tensor-core kernel
         try:
             y = mod.linear_a8(q, sc)
         except Exception as e:                         # the forced variant may not take this geometry
-            if k == "small_mma_unpacked" and getattr(e, "code", 0) == -2:
+            refusable = k == "small_mma_unpacked" or (shifted and k in FAST_KERNELS)
+            if refusable and getattr(e, "code", 0) == -2:
                 continue
             raise
         torch.cuda.synchronize()
@@ -273,20 +343,40 @@ def test_linear_large_m_batched_shapes(K, N, M):
     p = make_payload(N, K, seed=K // 7 + N, device="cuda", iters=1)
     bias = (torch.randn(N, generator=torch.Generator().manual_seed(6)) * 0.05).to(torch.bfloat16)
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
-    assert mod.kernel_for(M) == "large"
+    # from 1024 rows the kernel with the weights in tensor memory takes over, whatever the width
+    assert mod.kernel_for(M) == ("large_tmem" if M >= 1024 else "large")
     w_bits = oracle_weight(p)
     q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 3)))
-    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=("large", "small_mma"))
+    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=("large", "small_mma", "large_tmem", "auto"))
+    assert torch.equal(outs["auto"][0], outs[mod.kernel_for(M)][0])
+    assert O.rel_frobenius(outs["large_tmem"][0].float().cpu().numpy(), outs["large"][0].float().cpu().numpy()) < 1e-3
     # both kernels see the same operands; they may differ only by summation order and the
     # fp16 vs FP8 hi+lo codeword encodings
     a, b = outs["large"][0].float().cpu().numpy(), outs["small_mma"][0].float().cpu().numpy()
     assert O.rel_frobenius(a, b) < 5e-3
 
 
+@pytest.mark.parametrize("K,N", [(2048, 6144), (6144, 2048)])
+@pytest.mark.parametrize("M", [4096, 8192])
+def test_linear_batched_sweep_sizes_against_oracle(K, N, M):
+    """The sizes the batched-throughput figures are quoted on (multi-wave grids, partial last
+    token tile), with a bias, against the float64 reconstruct-then-matmul oracle."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, seed=K // 5 + N, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(8)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M - 37, K, seed=M + 5)))   # ragged last tile
+    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=("auto", "large", "large_tmem"))
+    assert set(outs) == {"auto", "large", "large_tmem"}
+    assert mod.kernel_for(M - 37) in ("large", "large_tmem")
+
+
 def test_linear_large_m_two_subtiles():
     """Enough tiles that a CTA takes two 128-token sub-tiles (two TMEM accumulators); the
-    last CTA's second sub-tile is partial.  Checked against the dense product of the
-    library's own bit-exact reconstruction."""
+    last CTA's second sub-tile is partial.  Checked against the float64 oracle."""
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
     from sacq_b200.synthetic import make_activations, make_payload
@@ -295,10 +385,11 @@ def test_linear_large_m_two_subtiles():
     bias = (torch.randn(N, generator=torch.Generator().manual_seed(4)) * 0.05).to(torch.bfloat16)
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
     q, s = quantize_rows(make_activations(M, K, seed=12).cuda())
-    assert mod.kernel_for(M) == "large"
+    mod.set_kernel("large")
     y = mod.linear_a8(q, s)
-    dense = (q.float() @ mod.dequantize_weight().float().t()) * s + bias.cuda().float()
-    assert O.rel_frobenius(y.float().cpu().numpy(), dense.cpu().numpy()) <= GEMM_TOL
+    dense = O.linear_a8_reference(q.view(torch.uint8).cpu().numpy(), s.cpu().numpy().reshape(-1), oracle_weight(p),
+                                  bf16_bits(bias))
+    assert O.rel_frobenius(y.float().cpu().numpy(), dense) <= GEMM_TOL
     assert torch.equal(y, mod.linear_a8(q, s))
     # rows of the partial sub-tile against the small-M kernel on the same operands
     mod.set_kernel("small_mma")
@@ -359,15 +450,17 @@ def test_linear_large_m_ragged(M, N, K, d, C):
     assert torch.equal(out[:, :N], outs["large"][0]) and float(out[:, N:].float().min()) == 3.0
 
 
+@pytest.mark.parametrize("shift", [0.0, 0.0078125])
 @pytest.mark.parametrize("N,K,d,C,G", [(40, 128, 4, 32, 64), (100, 256, 4, 2048, 64), (33, 512, 8, 4096, 256),
                                        (7, 24, 4, 8, 24), (64, 1536, 4, 128, 64)])
-def test_linear_grouped_and_ragged_geometries(N, K, d, C, G):
-    """Group-64 scales, odd index widths, rows that are not byte aligned, N % 32 != 0."""
+def test_linear_grouped_and_ragged_geometries(N, K, d, C, G, shift):
+    """Group-64 scales, odd index widths, rows that are not byte aligned, N % 32 != 0; without a
+    shift on every small-M variant, with one on the exact-reconstruction path."""
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear
     from sacq_b200.synthetic import make_activations, make_payload
     p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N, device="cuda", iters=1)
-    p["shift"] = torch.tensor(0.0078125, dtype=torch.bfloat16)
+    p["shift"] = torch.tensor(shift, dtype=torch.bfloat16)
     mod = PrecomputedPackedVectorCodebookLinear(p, None, "cuda")
     w_bits = oracle_weight(p)
     assert np.array_equal(bf16_bits(mod.dequantize_weight()), w_bits)
@@ -380,12 +473,13 @@ def test_linear_grouped_and_ragged_geometries(N, K, d, C, G):
                                      (2048, 6144, 32, 64), (1000, 2048, 2048, 128), (520, 1024, 512, 32)])
 def test_linear_deployed_layouts(N, K, C, G):
     """The layouts of the reference's frozen decode selection: dim-4 vectors, 64-wide scale
-    groups, 5- to 11-bit indices; on the index-unpacking warp-MMA variant, with a shift."""
+    groups, 5- to 11-bit indices, zero shift (the reference refuses to accelerate a deployed
+    layer with any other, gr00t_libero/acceleration/install.py:145-155); on the index-unpacking
+    warp-MMA variant."""
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear
     from sacq_b200.synthetic import make_activations, make_payload
     p = make_payload(N, K, vector_dim=4, codebook_size=C, group_size=G, seed=N + C, device="cuda", iters=1)
-    p["shift"] = torch.tensor(-0.00390625, dtype=torch.bfloat16)
     bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.05).to(torch.bfloat16)
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
     w_bits = oracle_weight(p)
@@ -408,12 +502,11 @@ def test_linear_deployed_layouts(N, K, C, G):
 def test_linear_grouped_tensor_core(N, K, d, C, G, M):
     """Grouped scales on the tcgen05 kind::f16 kernel: the deployed dim-4 / group-64 layouts at
     prefill sizes, partial tiles in M and N, one and two token sub-tiles, a token count above
-    one widening slab, a shift and a bias."""
+    one widening slab, a bias."""
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear
     from sacq_b200.synthetic import make_activations, make_payload
     p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N + M, device="cuda", iters=1)
-    p["shift"] = torch.tensor(0.001953125, dtype=torch.bfloat16)
     bias = (torch.randn(N, generator=torch.Generator().manual_seed(7)) * 0.05).to(torch.bfloat16)
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
     w_bits = oracle_weight(p)
@@ -558,9 +651,10 @@ def test_int8_activation_quantizer():
         assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy().view(np.uint32), so.view(np.uint32))
 
 
-@pytest.mark.parametrize("N,K,d,C,G", [(2048, 2048, 8, 4096, None), (1536, 1536, 4, 64, 64), (6144, 2048, 4, 1024, 64),
-                                       (1000, 1024, 4, 256, None), (100, 256, 4, 2048, 64), (264, 512, 8, 65536, None)])
-def test_linear_int8_activations(N, K, d, C, G):
+@pytest.mark.parametrize("N,K,d,C,G,shift", [
+    (2048, 2048, 8, 4096, None, 0.0), (1536, 1536, 4, 64, 64, 0.0), (6144, 2048, 4, 1024, 64, 0.0),
+    (1000, 1024, 4, 256, None, 0.0), (100, 256, 4, 2048, 64, 0.00390625), (264, 512, 8, 65536, None, 0.0)])
+def test_linear_int8_activations(N, K, d, C, G, shift):
     """GEMM on INT8 per-token activations against the oracle (exact weights, reconstruct then
     matmul): fp16 warp-MMA and CUDA-core kernels at small M, tcgen05 kind::f16 from 48 rows."""
     _need_gpu()
@@ -568,7 +662,7 @@ def test_linear_int8_activations(N, K, d, C, G):
     from sacq_b200.synthetic import make_activations, make_payload
     p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N + 3, device="cuda", iters=1,
                      sample_size=max(65536, 2 * C), fit=(C < 65536))
-    p["shift"] = torch.tensor(0.00390625, dtype=torch.bfloat16)
+    p["shift"] = torch.tensor(shift, dtype=torch.bfloat16)
     bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.05).to(torch.bfloat16)
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
     w_bits = oracle_weight(p)
@@ -581,6 +675,69 @@ def test_linear_int8_activations(N, K, d, C, G):
         torch.cuda.synchronize()
         assert O.rel_frobenius(y.float().cpu().numpy(), ref) <= GEMM_TOL, M
         assert torch.equal(y, mod.linear_a8i(q, s)) and torch.equal(y, mod.forward_int8(x.cuda()))
+    assert mod.device_status() == 0
+
+
+@pytest.mark.parametrize("name", golden_layer_names())
+def test_int8_recipe_matches_reference_fixture(name):
+    """The reference's deployed INT8 recipe on its own fixtures: the per-output-row weight scale
+    and the int8 weight bytes of quantize_rows(W, 'int8_symmetric'), and the GEMM's bf16 output
+    bit for bit (integer accumulation is exact)."""
+    _need_gpu()
+    from sacq_b200._lib import SacqError
+    g = load_golden("layer_" + name)
+    mod = module_from_golden(g)
+    sw = mod.weight_row_scale("int8_symmetric")
+    assert np.array_equal(sw.cpu().numpy().view(np.uint32), g["w_scale_i8"].view(np.uint32))
+    wq = mod.decode_weight_int8(sw)
+    assert wq.dtype == torch.int8 and np.array_equal(wq.cpu().numpy(), g["wq_i8"])
+    q = torch.from_numpy(g["q_i8"]).cuda()
+    sa = torch.from_numpy(g["act_scale_i8"]).cuda()
+    if int(g["K"]) % 16:
+        with pytest.raises(SacqError) as e:
+            mod.linear_w8a8_int8(q, sa, sw)
+        assert e.value.code == -2
+        return
+    y = mod.linear_w8a8_int8(q, sa, sw)
+    want = O.linear_w8a8_int8_reference(g["q_i8"], g["act_scale_i8"], g["wq_i8"], g["w_scale_i8"], g.get("bias"))
+    assert np.array_equal(bf16_bits(y), want)
+    assert torch.equal(y, mod.linear_w8a8_int8(q, sa, sw))
+    assert mod.device_status() == 0
+
+
+@pytest.mark.parametrize("N,K,d,C,G,with_bias", [
+    (2048, 2048, 4, 128, 64, True), (6144, 2048, 4, 1024, 64, False), (1536, 1536, 4, 64, 64, True),
+    (2048, 6144, 4, 32, 64, True), (1000, 2048, 4, 2048, 128, False), (2048, 2048, 8, 4096, None, True),
+    (200, 144, 8, 256, None, True)])
+def test_int8_recipe_deployed_layouts(N, K, d, C, G, with_bias):
+    """The deployed layouts (dim-4 vectors, 64-wide scale groups, 5- to 11-bit indices) and the
+    1.5-bit layer at the token counts of the reference's frozen tables: output bytes equal to the
+    CPU restatement of decode -> int8 x int8 -> int32 -> ordered epilogue."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N + C, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.05).to(torch.bfloat16) if with_bias else None
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    wq_ref, sw_ref = O.quantize_weight_rows_int8(w_bits)
+    sw = mod.weight_row_scale("int8_symmetric")
+    assert np.array_equal(sw.cpu().numpy().view(np.uint32), sw_ref.view(np.uint32))
+    assert np.array_equal(mod.decode_weight_int8(sw).cpu().numpy(), wq_ref)
+    for M in (1, 41, 149, 512):
+        x = make_activations(M, K, seed=M + 4)
+        if M > 2:
+            x[1].zero_()
+        q_ref, sa_ref = O.quantize_rows_int8(bf16_bits(x))
+        q, sa = quantize_rows(x.cuda(), "int8_symmetric")
+        assert np.array_equal(q.cpu().numpy(), q_ref)
+        y = mod.linear_w8a8_int8(q, sa, sw)
+        want = O.linear_w8a8_int8_reference(q_ref, sa_ref, wq_ref, sw_ref, None if bias is None else bf16_bits(bias))
+        assert np.array_equal(bf16_bits(y), want), M
+        # a wider output buffer: columns beyond N stay untouched
+        out = torch.full((M, N + 8), 3.0, dtype=torch.bfloat16, device="cuda")
+        mod.linear_w8a8_int8(q, sa, sw, out=out[:, :N])
+        assert torch.equal(out[:, :N], y) and float(out[:, N:].float().min()) == 3.0
     assert mod.device_status() == 0
 
 

@@ -34,6 +34,32 @@ def test_policy_forward_runs_and_is_deterministic():
         assert err <= 1e-2, err
 
 
+def test_policy_batch_matches_single_requests():
+    """A batch of independent requests gives every request the result of its own batch-1
+    forward.  Not bit for bit: with more rows the linears move to other kernels (another
+    summation order, FP8 high/low instead of fp16 codewords) and the attention kernel changes
+    its tiling, and those last-bit differences pass through 52 blocks; the bar is 2e-2 relative
+    Frobenius on the actions (the path's own GEMM tolerance is 1e-2 per layer)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from sacq_b200.policy import SyntheticGr00tPolicy
+    policy = SyntheticGr00tPolicy("cuda", seed=2)
+    image, noise = policy.example_inputs(7, batch=3)
+    batched = policy(image, noise)
+    torch.cuda.synchronize()
+    assert tuple(batched.shape) == (3, 16, 32) and bool(torch.isfinite(batched.float()).all())
+    assert torch.equal(batched, policy(image, noise))
+    for i in range(3):
+        single = policy(image[i], noise[i])
+        err = ((batched[i].float() - single.float()).norm() / single.float().norm()).item()
+        assert err <= 2e-2, (i, err)
+    # requests do not leak into each other: changing request 2 leaves requests 0 and 1 unchanged
+    image2 = image.clone()
+    image2[2] = 1.0 - image2[2]
+    again = policy(image2, noise)
+    assert torch.equal(again[:2], batched[:2]) and not torch.equal(again[2], batched[2])
+
+
 def test_overlay_installs_real_layers():
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")

@@ -168,3 +168,17 @@ def test_c_abi_argument_errors_of_the_new_entry_points_without_gpu():
     assert lib.sacq_peer_buffer_create(0, 0, None, None) == -1
     assert lib.sacq_workspace_bytes_int8(None, 4) == 0
     assert lib.sacq_act_quant_fp8(0, None, 0, None, 0, 0, 8, None, None, None) == 0      # M = 0 is a no-op
+
+
+def test_index_range_check():
+    """An index that does not address a codeword is refused before anything is uploaded (the
+    reference's CPU gather raises IndexError for it; a GPU gather would read out of bounds)."""
+    import pytest
+    import torch
+    from sacq_b200.packing import check_index_range
+    check_index_range(torch.tensor([[0, 250], [3, 7]], dtype=torch.int32), 251)
+    check_index_range(torch.zeros(0, dtype=torch.uint8), 4)
+    with pytest.raises(IndexError):
+        check_index_range(torch.tensor([0, 251], dtype=torch.int32), 251)
+    with pytest.raises(IndexError):
+        check_index_range(torch.tensor([-1, 2], dtype=torch.int32), 251)

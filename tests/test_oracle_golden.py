@@ -133,3 +133,50 @@ def test_layernorm_reference_against_torch_cpu():
     ref = torch.nn.functional.layer_norm(x.float(), (384,), w.float(), b.float(), 1e-5).to(torch.bfloat16).float().numpy()
     assert np.all(np.abs(ours - ref) <= np.maximum(np.abs(ref), 1e-30) * 2.0 ** -7 + 1e-6)
     assert np.mean(ours != ref) < 0.01
+
+
+def test_int8_recipe_operands_match_reference_fixture(golden_layer):
+    """The deployed INT8 recipe's operands: per-token int8 activations, per-output-row int8
+    weights and the integer product, as the reference's quantize_rows produced them."""
+    g = golden_layer
+    q8, s8 = O.quantize_rows_int8(g["x"])
+    assert np.array_equal(q8, g["q_i8"])
+    assert np.array_equal(s8.view(np.uint32), g["act_scale_i8"].view(np.uint32))
+    wq8, sw8 = O.quantize_weight_rows_int8(g["w_ref"])
+    assert np.array_equal(wq8, g["wq_i8"])
+    assert np.array_equal(sw8.view(np.uint32), g["w_scale_i8"].view(np.uint32))
+    acc = q8.astype(np.int64) @ wq8.astype(np.int64).T
+    assert np.array_equal(acc.astype(np.int32), g["acc_i32"])
+
+
+def test_int8_recipe_epilogue_and_fused_multiply_add():
+    """fma_f32 is correctly rounded (checked with exact rational arithmetic, including sums that
+    land on a float64 half-way point), and the GEMM reference applies weight scale, token scale and
+    bias in the reference's order."""
+    from fractions import Fraction
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(4000).astype(np.float32)
+    b = rng.standard_normal(4000).astype(np.float32)
+    for c in ((-(a.astype(np.float64) * b.astype(np.float64))).astype(np.float32),      # heavy cancellation
+              (rng.standard_normal(4000) * 2.0 ** -20).astype(np.float32), rng.standard_normal(4000).astype(np.float32)):
+        r = O.fma_f32(a, b, c)
+        for i in range(0, 4000, 13):
+            exact = Fraction(float(a[i])) * Fraction(float(b[i])) + Fraction(float(c[i]))
+            x = np.float32(float(exact))
+            cands = [np.nextafter(x, np.float32(-np.inf)), x, np.nextafter(x, np.float32(np.inf))]
+            best = min(cands, key=lambda v: (abs(Fraction(float(v)) - exact), int(np.float32(v).view(np.uint32)) & 1))
+            assert np.float32(best) == r[i]
+    # a case where rounding the product first would change the result
+    q = np.array([[3, -7, 127, 0]], dtype=np.int8)
+    wq = np.array([[127, 5, -128 + 1, 9], [1, 1, 1, 1]], dtype=np.int8)
+    sa = np.array([0.0123], dtype=np.float32)
+    sw = np.array([0.00071, 0.25], dtype=np.float32)
+    bias = O.f32_to_bf16_bits(np.array([0.5, -1.0], dtype=np.float32))
+    y = O.linear_w8a8_int8_reference(q, sa, wq, sw, bias)
+    acc = q.astype(np.int64) @ wq.astype(np.int64).T
+    want = [O.fma_f32(sa, (np.float32(acc[0, n]) * sw[n]).astype(np.float32), O.bf16_bits_to_f32(bias[n:n + 1]))
+            for n in range(2)]
+    assert np.array_equal(y[0], O.f32_to_bf16_bits(np.concatenate(want)))
+    # without a bias the product sa * scaled keeps the sign of a negative zero
+    y0 = O.linear_w8a8_int8_reference(np.array([[0, 0, 0, 0]], dtype=np.int8), np.array([-1.0], dtype=np.float32), wq, sw)
+    assert y0[0, 0] == 0x8000
