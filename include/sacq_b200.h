@@ -170,8 +170,9 @@ SACQ_API int sacq_linear_a8i(const sacq_layer_t* layer, const void* q_int8, cons
  * int8_small_m_gemm_20261028_r1.py:7-32 / int8_ordered_epilogue_20261028_r1.py:11-22.  Integer
  * accumulation is exact, so y is bit-identical to any correct evaluation of these formulas.
  * sacq_linear_w8a8_int8 decodes the int8 weight rows per call into `workspace`
- * (sacq_workspace_bytes_w8a8 bytes, 256-byte aligned; nothing expanded is kept between calls, as in
- * the reference) and runs a tcgen05 kind::i8 GEMM on them.  `w_scale` is the vector written by
+ * (sacq_workspace_bytes_w8a8 bytes, 256-byte aligned; its leading sacq_workspace_counter_bytes() are
+ * left untouched, so one buffer can serve every entry point; nothing expanded is kept between calls,
+ * as in the reference) and runs a tcgen05 kind::i8 GEMM on them.  `w_scale` is the vector written by
  * sacq_weight_row_scale_int8 (the reference keeps it as a small per-layer buffer).  in_features must
  * be a multiple of 16. */
 SACQ_API int sacq_weight_row_scale_int8(const sacq_layer_t* layer, float* sw_out, void* stream);

@@ -1,9 +1,9 @@
 """Runs one quantized-linear shape a few times on distinct layer instances -- a small,
 self-terminating workload to put under a profiler (ncu) or to time one kernel:
 
-    python -m sacq_b200.profile_case --K 2048 --N 6144 --M 16 --kernel small_mma --instances 64
-    python -m sacq_b200.profile_case --K 2048 --N 6144 --M 1024 --kernel large --instances 8 --time
-    python -m sacq_b200.profile_case --K 2048 --N 6144 --M 300 --d 4 --C 1024 --G 64 --instances 24
+    python profile_case.py --K 2048 --N 6144 --M 16 --kernel small_mma --instances 64
+    python profile_case.py --K 2048 --N 6144 --M 1024 --kernel large --instances 8 --time
+    python profile_case.py --K 2048 --N 6144 --M 300 --d 4 --C 1024 --G 64 --instances 24
 
 Each instance owns its packed indices, so with enough instances (> 126 MB in total) every
 launch reads its weights from HBM, not from L2.  ``--op`` selects the entry point:
@@ -13,11 +13,17 @@ launch reads its weights from HBM, not from L2.  ``--op`` selects the entry poin
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
-import torch
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
-from . import PrecomputedPackedVectorCodebookLinear
-from .synthetic import algorithmic_bytes, make_activations, make_payload
+import torch  # noqa: E402
+
+from sacq_b200 import PrecomputedPackedVectorCodebookLinear  # noqa: E402
+from sacq_b200.synthetic import algorithmic_bytes, make_activations, make_payload  # noqa: E402
 
 
 def main():

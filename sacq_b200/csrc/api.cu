@@ -447,7 +447,8 @@ SACQ_API int sacq_decode_weight_int8(const sacq_layer_t* L, const float* sw, voi
 
 SACQ_API int64_t sacq_workspace_bytes_w8a8(const sacq_layer_t* L, int64_t M) {
   if (L == nullptr || M < 0) return 0;
-  return ((L->d.out_features * L->d.in_features + 255) & ~(int64_t)255);
+  // the leading counter region of every workspace stays untouched (and zero) for the kernels that use it
+  return kCounterBytes + ((L->d.out_features * L->d.in_features + 255) & ~(int64_t)255);
 }
 
 SACQ_API int sacq_linear_w8a8_int8(const sacq_layer_t* L, const void* q_int8, const float* act_scale, const float* w_scale,
@@ -472,8 +473,9 @@ SACQ_API int sacq_linear_w8a8_int8(const sacq_layer_t* L, const void* q_int8, co
   DeviceGuard guard(L->d.device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // per call, as the reference does: packed stream -> int8 weight rows, then the dense integer GEMM
-  if (int rc = launch_decode_weight_int8(L, w_scale, workspace, s)) return rc;
-  return launch_dense_i8(L, q_int8, act_scale, workspace, w_scale, M, y_out, ldy, s);
+  void* wq = static_cast<uint8_t*>(workspace) + kCounterBytes;
+  if (int rc = launch_decode_weight_int8(L, w_scale, wq, s)) return rc;
+  return launch_dense_i8(L, q_int8, act_scale, wq, w_scale, M, y_out, ldy, s);
 }
 
 SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,

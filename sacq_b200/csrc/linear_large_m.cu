@@ -149,15 +149,14 @@ __host__ __device__ inline SmemLayout make_layout(int bn, int mt, int sb_bytes, 
 // Smaller BN trades tensor-core efficiency for more CTAs when M is only a few tiles.  MT = 2
 // gives the CTA two 128-token sub-tiles (two TMEM accumulators) that share every expanded
 // B tile: the shared-memory gathers, not the MMAs, are what limits this kernel.
-// MERGE: the high and the low B tile are issued as ONE MMA of N = 2*BN (they are adjacent in
-// shared memory, so they form one K-major operand): A x hi lands in accumulator columns
-// [0, BN), A x lo in [BN, 2*BN), and the epilogue adds them.  A small-N MMA is bound by its
+// The high and the low B tile are issued as ONE MMA of N = 2*BN (they are adjacent in shared
+// memory, so they form one K-major operand): A x hi lands in accumulator columns [0, BN),
+// A x lo in [BN, 2*BN), and the epilogue adds them.  A small-N MMA is bound by its
 // shared-memory operand reads, so reading the A tile once instead of twice is what counts at
-// small and medium M; at large M it measures the same as two N = BN MMAs into one accumulator.
-// Every launch uses MERGE = true: the order in which an output element is summed then does not
-// depend on the tile shape, so the shards of a split layer reproduce the whole layer bit for bit
-// (MERGE = false is kept for measurements only).
-template <int D, int BITS, int BN, int MT, bool MERGE, int KBS>
+// small and medium M.  Every tile shape does this, so the order in which an output element is
+// summed does not depend on the tile shape and the shards of a split layer reproduce the whole
+// layer bit for bit.
+template <int D, int BITS, int BN, int MT, int KBS>
 __global__ void __launch_bounds__(kThreads, 1)
 large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ LargeMMulti mp) {
   // blockIdx.z selects the layer: sibling projections that read the same activations run as
@@ -175,7 +174,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr int PARTS = kExpanderThreads / BN;        // expander threads per weight row
   constexpr int CPT = 8 / PARTS;                      // 16-byte chunks each of them writes per K block
   constexpr int IPC = 16 / D;                         // indices per chunk
-  constexpr int ACC_COLS = MERGE ? 2 * BN : BN;       // accumulator columns per token sub-tile
+  constexpr int ACC_COLS = 2 * BN;                    // accumulator columns per token sub-tile (high | low)
   constexpr uint32_t kIdesc = make_idesc(ACC_COLS);
   constexpr int B_TILE = BN * kBK;
   constexpr int kStages = stages_for(BN, MT, KBS);
@@ -268,8 +267,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < KBS; ++kk) {
           const uint32_t a_addr = s_addr + kk * A_BYTES;
-          const uint64_t b_desc = make_smem_desc(s_addr + B_OFF + kk * 2 * B_TILE);            // high half (and, merged, both)
-          const uint64_t bl_desc = make_smem_desc(s_addr + B_OFF + kk * 2 * B_TILE + B_TILE);   // low half
+          const uint64_t b_desc = make_smem_desc(s_addr + B_OFF + kk * 2 * B_TILE);            // high and low halves as one operand
 #pragma unroll
           for (int ks = 0; ks < kBK / 32; ++ks) {
             const uint64_t adv = (uint64_t)((ks * 32) >> 4);
@@ -277,8 +275,6 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int mt = 0; mt < MT; ++mt) {
               const uint64_t a_desc = make_smem_desc(a_addr + mt * kTileBytes);
               umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, b_desc + adv, kIdesc, (it | kk | ks) != 0);
-              if constexpr (!MERGE)
-                umma_f8(tmem_base + (uint32_t)(mt * ACC_COLS), a_desc + adv, bl_desc + adv, kIdesc, 1);
             }
           }
         }
@@ -389,7 +385,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int c0 = cc * 32;
             uint32_t r[32];
             tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0), r);
-            if constexpr (MERGE) {
+            {
               uint32_t rl[32];
               tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * ACC_COLS + BN + c0), rl);
 #pragma unroll
@@ -440,7 +436,7 @@ large_m_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int c0 = cc * 32;
             uint32_t r[32];
             tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0), r);
-            if constexpr (MERGE) {
+            {
               uint32_t rl[32];
               tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * ACC_COLS + BN + c0), rl);
 #pragma unroll
@@ -534,21 +530,21 @@ namespace {
 
 int sb_bytes_for(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
 
-template <int D, int BITS, int BN, int MT, bool MERGE, int KBS = 1>
+template <int D, int BITS, int BN, int MT, int KBS = 1>
 cudaError_t launch_bn(const CUtensorMap& ta, const LargeMMulti& mp, dim3 grid, cudaStream_t s) {
   const size_t smem = make_layout(BN, MT, 2 * (kBK / D) * BITS / 8, mp.layer[0].C * 2 * D, KBS).total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN, MT, MERGE, KBS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(large_m_kernel<D, BITS, BN, MT, KBS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   // (Programmatic dependent launch behind the quantizer was measured and is not used here: the
   // early-resident 200 KB CTAs slowed the kernels around them more than the overlap gained.)
-  large_m_kernel<D, BITS, BN, MT, MERGE, KBS><<<grid, kThreads, smem, s>>>(ta, mp);
+  large_m_kernel<D, BITS, BN, MT, KBS><<<grid, kThreads, smem, s>>>(ta, mp);
   return cudaGetLastError();
 }
 
@@ -557,15 +553,15 @@ cudaError_t launch_one(const CUtensorMap& ta, const LargeMMulti& mp, int bn, int
   // every tile shape issues the high and the low tile as one MMA: an output's summation order
   // is then the same for all shapes (a layer's shards reproduce the whole layer bit for bit)
   if (mt == 2) {
-    if (bn == 32) return launch_bn<D, BITS, 32, 2, true>(ta, mp, grid, s);
-    if (bn == 64) return launch_bn<D, BITS, 64, 2, true>(ta, mp, grid, s);
-    return launch_bn<D, BITS, 128, 2, true>(ta, mp, grid, s);
+    if (bn == 32) return launch_bn<D, BITS, 32, 2>(ta, mp, grid, s);
+    if (bn == 64) return launch_bn<D, BITS, 64, 2>(ta, mp, grid, s);
+    return launch_bn<D, BITS, 128, 2>(ta, mp, grid, s);
   }
   // narrow tiles with one token sub-tile: two K blocks per pipeline stage when that fits
   const bool two = make_layout(bn, 1, 2 * (kBK / D) * BITS / 8, mp.layer[0].C * 2 * D, 2).total + 1024 <= 227 * 1024;
-  if (bn == 32) return two ? launch_bn<D, BITS, 32, 1, true, 2>(ta, mp, grid, s) : launch_bn<D, BITS, 32, 1, true>(ta, mp, grid, s);
-  if (bn == 64) return two ? launch_bn<D, BITS, 64, 1, true, 2>(ta, mp, grid, s) : launch_bn<D, BITS, 64, 1, true>(ta, mp, grid, s);
-  return launch_bn<D, BITS, 128, 1, true>(ta, mp, grid, s);
+  if (bn == 32) return two ? launch_bn<D, BITS, 32, 1, 2>(ta, mp, grid, s) : launch_bn<D, BITS, 32, 1>(ta, mp, grid, s);
+  if (bn == 64) return two ? launch_bn<D, BITS, 64, 1, 2>(ta, mp, grid, s) : launch_bn<D, BITS, 64, 1>(ta, mp, grid, s);
+  return launch_bn<D, BITS, 128, 1>(ta, mp, grid, s);
 }
 
 }  // namespace
@@ -589,17 +585,12 @@ void large_m_release(sacq_layer* L) {
 
 namespace {
 
-// Whether a tile shape issues the high and the low B tile as one MMA (the summation order of an
-// output element depends on this and on nothing else of the tile shape).
-inline bool tile_merges(int, int) { return true; }
-
 // Tile shape: (token sub-tiles per CTA, weight rows per CTA) with the smallest
 // waves x time-per-CTA.  Fitted to measurements (us): a CTA takes about
 // 3.4 + K/2048 * (4.8 + 0.0755 * BN + 3.0 * (MT - 1)): fixed prologue/epilogue, pipeline
 // latency per K block (halved, 2.4, where a stage holds two K blocks: one sub-tile of 32 or
 // 64 rows), expansion per weight row, MMA issue per extra sub-tile.
-// merge_req: -1 free, 0 / 1 only shapes with that tile_merges() value.
-bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers, int merge_req, int& bn, int& mt) {
+bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers, int& bn, int& mt) {
   const sacq_layer_desc& d = L->d;
   const size_t cb_bytes = (size_t)L->cb_entries * d.vector_dim * 2;
   bn = 0;
@@ -608,7 +599,6 @@ bool choose_tile(const sacq_layer* L, int64_t M, const int64_t* ns, int n_layers
   for (int cand_mt = 1; cand_mt <= (M > kBM ? 2 : 1); ++cand_mt) {
     const int64_t m_tiles = (M + kBM * cand_mt - 1) / (kBM * cand_mt);
     for (int cand = 128; cand >= 32; cand >>= 1) {
-      if (merge_req >= 0 && (int)tile_merges(cand, cand_mt) != merge_req) continue;
       if (make_layout(cand, cand_mt, sb_bytes_for(L), (int)cb_bytes).total + 1024 > 227 * 1024) continue;
       int64_t tiles = 0;
       for (int l = 0; l < n_layers; ++l) tiles += ((ns[l] + cand - 1) / cand) * m_tiles;
@@ -716,22 +706,21 @@ int launch_large_m(const sacq_layer* L, const void* q, const float* scale, int64
     return set_error(SACQ_ERR_ALIGNMENT, "large-M kernel: quantized activations must be 16-byte aligned");
   int bn = 0, mt = 1;
   const int64_t n_rows = d.out_features;
-  if (!choose_tile(L, M, &n_rows, 1, -1, bn, mt))
+  if (!choose_tile(L, M, &n_rows, 1, bn, mt))
     return set_error(SACQ_ERR_UNSUPPORTED, "large-M kernel: no tile fits shared memory");
   return launch_layers(&L, 1, q, scale, M, &y, &ldy, bn, mt, s, residual, ldr, bc);
 }
 
 // Several layers of one geometry on the same quantized activations as ONE launch.  Returns
 // SACQ_ERR_UNSUPPORTED (nothing launched) when they cannot share one: the caller falls back
-// to one launch per layer.  The shared tile shape is restricted to the high/low issue mode
-// every layer would use alone, so the results are byte-identical to separate launches.
+// to one launch per layer.  An output's summation order does not depend on the tile shape, so
+// the results are byte-identical to separate launches.
 int launch_large_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
                          void* const* ys, const int64_t* ldys, cudaStream_t s) {
   if (n < 2 || n > kMaxLayersPerLaunch || M <= 0 || M > (1 << 30)) return SACQ_ERR_UNSUPPORTED;
   if (reinterpret_cast<uintptr_t>(q) % 16 != 0) return SACQ_ERR_UNSUPPORTED;
   const sacq_layer_desc& d0 = layers[0]->d;
   int64_t ns[kMaxLayersPerLaunch];
-  int merge = -1;
   for (int l = 0; l < n; ++l) {
     const sacq_layer* L = layers[l];
     const sacq_layer_desc& d = L->d;
@@ -740,14 +729,9 @@ int launch_large_m_multi(const sacq_layer* const* layers, int n, const void* q, 
         d.out_features <= 0)
       return SACQ_ERR_UNSUPPORTED;
     ns[l] = d.out_features;
-    int bn1 = 0, mt1 = 1;
-    if (!choose_tile(L, M, &ns[l], 1, -1, bn1, mt1)) return SACQ_ERR_UNSUPPORTED;
-    const int m1 = (int)tile_merges(bn1, mt1);
-    if (merge >= 0 && m1 != merge) return SACQ_ERR_UNSUPPORTED;
-    merge = m1;
   }
   int bn = 0, mt = 1;
-  if (!choose_tile(layers[0], M, ns, n, merge, bn, mt)) return SACQ_ERR_UNSUPPORTED;
+  if (!choose_tile(layers[0], M, ns, n, bn, mt)) return SACQ_ERR_UNSUPPORTED;
   return launch_layers(layers, n, q, scale, M, ys, ldys, bn, mt, s, nullptr, 0, nullptr);
 }
 

@@ -610,8 +610,9 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   const Plan pl = make_plan(L, M);
   if (L->force_kernel == 6 && !pl.unpacked)
     return set_error(SACQ_ERR_UNSUPPORTED, "index-unpacking warp-MMA variant cannot run this layer");
-  if ((L->force_kernel == 4 || L->force_kernel == 5) && !pl.mma)
-    return set_error(SACQ_ERR_UNSUPPORTED, "warp-MMA variant cannot run this layer");
+  if (has_shift(L) && L->force_kernel >= 4 && L->force_kernel <= 6)
+    return set_error(SACQ_ERR_UNSUPPORTED, "a layer with a non-zero shift needs the exact reconstruction; the "
+                                           "warp-MMA variants contract bare codewords");
   if (pl.smem > kSmemBudget)
     return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel needs %zu bytes of shared memory", pl.smem);
   const int64_t need = small_m_workspace_bytes(L, M);

@@ -80,3 +80,51 @@ def test_overlay_from_env(monkeypatch, tmp_path):
     monkeypatch.setenv("VLM_CODEBOOK_OVERLAY_PATH", str(path))
     assert overlay.apply_overlay_from_env(Toy(), "VLM_CODEBOOK_OVERLAY_PATH", "cpu", packed_only=True,
                                           packed_factory=FakePacked) == 2
+
+
+def test_separate_qkv_entry_installs_three_role_layers():
+    """A fused q/k/v projection whose row blocks keep their own codebooks: three packed layers in
+    the order q, k, v, the bias split by their row counts, counted as one applied entry."""
+    class Fused(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.qkv = torch.nn.Linear(16, 8 + 4 + 4, bias=True)
+
+    roles = {"q": make_payload(8, 16, vector_dim=4, codebook_size=16, seed=1),
+             "k": make_payload(4, 16, vector_dim=4, codebook_size=8, seed=2),
+             "v": make_payload(4, 16, vector_dim=4, codebook_size=32, seed=3)}
+    entry = {"format": "packed_separate_qkv_codebooks_v1", "roles": roles}
+    model = Fused()
+    bias = model.qkv.bias.detach().clone()
+    ov = {"weights": {"qkv": entry}, "expected_applied": 1, "expected_packed_applied": 1}
+    assert overlay.is_packed(entry)
+    assert overlay.apply_overlay(model, ov, "cpu", scope="vlm", packed_only=True, packed_factory=FakePacked) == 1
+    fused = model.qkv
+    assert isinstance(fused, overlay.SeparateQKVCodebookLinear) and fused.runtime_scope == "vlm"
+    assert (fused.in_features, fused.out_features) == (16, 16)
+    assert [m.payload is roles[r] for m, r in zip(fused.roles, "qkv")] == [True] * 3
+    assert torch.equal(torch.cat([m.bias_seen for m in fused.roles]), bias)
+    # the reference's checks: exactly the roles q, k, v, one input width, matching bias length
+    with pytest.raises(ValueError):
+        overlay.split_qkv_roles({"format": "packed_separate_qkv_codebooks_v1", "roles": {"q": roles["q"]}})
+    wide = dict(roles, v=make_payload(4, 32, vector_dim=4, codebook_size=8, seed=4))
+    with pytest.raises(ValueError):
+        overlay.split_qkv_roles({"format": "packed_separate_qkv_codebooks_v1", "roles": wide})
+    with pytest.raises(ValueError):
+        overlay.SeparateQKVCodebookLinear(entry, torch.zeros(15), "cpu", FakePacked)
+
+
+def test_overlay_files_load_without_pickle_execution(tmp_path):
+    """Overlay files are read with weights_only=True; a file that needs the full unpickler is
+    refused unless the caller opts in."""
+    class Evil:
+        def __reduce__(self):
+            return (print, ("executed",))
+
+    path = tmp_path / "evil.pt"
+    torch.save({"weights": {"layers.0.q_proj": torch.zeros(8, 16)}, "meta": Evil()}, path)
+    with pytest.raises(Exception):
+        overlay.load_overlay(str(path))
+    good = tmp_path / "good.pt"
+    torch.save(make_overlay(), good)
+    assert set(overlay.load_overlay(str(good))["weights"]) == set(make_overlay()["weights"])
