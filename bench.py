@@ -355,9 +355,25 @@ def section_large_m(ctx):
             sec, _ = ctx.time_graphs([g], 4, 3, min_seconds=0.1, min_passes=5)
             dense_us = ctx.max_over_ranks([sec])[0] / 4 * 1e6
             del g
+            # the reference's deployed INT8 recipe on the same layer: int8 weight rows decoded per
+            # call + tcgen05 kind::i8 GEMM (another numerical recipe: weights re-quantized per row)
+            q8, s8 = quantize_rows(x, "int8_symmetric")
+            sw8 = mod.weight_row_scale("int8_symmetric")
+
+            def int8_recipe(stream):
+                mod.linear_w8a8_int8(q8, s8, sw8, out=y)
+
+            with torch.cuda.stream(ctx.stream):
+                int8_recipe(ctx.stream)
+            ctx.stream.synchronize()
+            g, _ = ctx.capture(int8_recipe)
+            sec, _ = ctx.time_graphs([g], 4, 3, min_seconds=0.1, min_passes=5)
+            int8_us = ctx.max_over_ranks([sec])[0] / 4 * 1e6
+            del g
             rows.append({"shape_KxN": f"{K}x{N}", "M": M, "us": us, "kernel": kern,
                          "algorithmic_tflops": flops / us / 1e6, "tokens_per_s": M / us * 1e6,
                          "frac_of_bf16_peak": flops / us / 1e6 / peak, "dense_baseline_us": dense_us,
+                         "int8_recipe_us": int8_us, "int8_recipe_tops": flops / int8_us / 1e6,
                          "rotating_sets": n_sets})
     best = max(rows, key=lambda r: r["M"] * 10 + (r["shape_KxN"] == "2048x6144"))
     return {"rows": rows,
@@ -369,7 +385,9 @@ def section_large_m(ctx):
                                       "executes twice the algorithmic flops in FP8 (high + low codeword halves), so "
                                       "the dense-bf16 rate is the equal-work ceiling"},
             "dense_baseline_note": "sacq_dequant_bf16 + torch.matmul (bf16) on the same quantized activations; a "
-                                   "secondary baseline, never on the product path"}
+                                   "secondary baseline, never on the product path",
+            "int8_recipe_note": "sacq_linear_w8a8_int8: the reference's deployed INT8 recipe (per-output-row int8 "
+                                "weights decoded per call, int32 accumulation), one layer instance, GEMM side only"}
 
 
 def section_config0(ctx):

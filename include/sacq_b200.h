@@ -269,10 +269,11 @@ SACQ_API int64_t sacq_host_forward_scratch_bytes(const sacq_layer_t* layer, int6
  * arrival counters live in an array built into the library: sacq_static_scratch_bytes()
  * bytes (8 MiB) of device memory on every GPU that loads it, held until the process
  * exits.  The call allocates and frees nothing.  Limits and rules:
- *   - a call whose partial sums (M * N * 4 bytes per K split) or arrival counters
- *     (ceil(M/16) * ceil(N/32), at most 16384) do not fit the array returns
- *     SACQ_ERR_WORKSPACE and launches nothing; the decode shapes (M <= 64, N <= 6144)
- *     need at most about 2 MiB;
+ *   - a call whose partial sums (M * N * 4 bytes per K split; at least one split's worth
+ *     must fit, whatever the launch plan of the device at hand needs) or arrival counters
+ *     (at most 16384) do not fit the array returns SACQ_ERR_WORKSPACE and launches nothing:
+ *     M * N may not exceed 2,080,768 outputs; the decode shapes (M <= 64, N <= 6144) need
+ *     at most about 2 MiB;
  *   - the first call on a device looks up the array's device address; make that call
  *     before starting any stream capture;
  *   - every call uses the same array: calls that may overlap on the GPU (different

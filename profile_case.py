@@ -5,6 +5,9 @@ self-terminating workload to put under a profiler (ncu) or to time one kernel:
     python profile_case.py --K 2048 --N 6144 --M 1024 --kernel large --instances 8 --time
     python profile_case.py --K 2048 --N 6144 --M 300 --d 4 --C 1024 --G 64 --instances 24
 
+    SACQ_NVCC_EXTRA=-DSACQ_TRACE python -m sacq_b200.build --force    # profiling build with in-kernel timestamps
+    python profile_case.py --K 2048 --N 6144 --M 16 --kernel small_mma --instances 64 --trace
+
 Each instance owns its packed indices, so with enough instances (> 126 MB in total) every
 launch reads its weights from HBM, not from L2.  ``--op`` selects the entry point:
 ``linear`` (GEMM on pre-quantized activations), ``forward`` (quantizer + GEMM),
@@ -39,6 +42,8 @@ def main():
     ap.add_argument("--instances", type=int, default=8)
     ap.add_argument("--passes", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="print the mean time per call (CUDA events)")
+    ap.add_argument("--trace", action="store_true",
+                    help="print the in-kernel phase timestamps of the last launch (needs a library built with -DSACQ_TRACE)")
     a = ap.parse_args()
     payload = make_payload(a.N, a.K, vector_dim=a.d, codebook_size=a.C, group_size=a.G or None, seed=1, device="cuda",
                            iters=1, fit=a.C <= 4096)
@@ -73,6 +78,40 @@ def main():
         ab = algorithmic_bytes(a.N, a.K, a.M, vector_dim=a.d, codebook_size=a.C, group_size=a.G or None)
         msg += f" us_per_call={us:.2f} (eager launches) algorithmic_GBps={ab / us / 1e3:.1f} TFLOPs={2.0 * a.M * a.N * a.K / us / 1e6:.1f}"
     print(msg)
+    if a.trace:
+        print_trace(layers[0], a)
+
+
+def print_trace(layer, a):
+    """Phase breakdown of CTA 0 of the last launch, from %globaltimer stamps (ns) that only a
+    -DSACQ_TRACE build of the library records."""
+    import ctypes
+    lib = ctypes.CDLL(os.path.join(ROOT, "sacq_b200", "libsacq_b200.so"))
+    kern = layer.kernel_for(a.M)
+    if kern == "small" and hasattr(lib, "sacq_debug_small_trace"):
+        buf = (ctypes.c_longlong * 96)()
+        lib.sacq_debug_small_trace(buf)
+        t = list(buf)
+        t0 = t[0]
+        print(f"staged small-M kernel, CTA 0 (ns from kernel entry): barriers+copies issued {t[1]-t0}, "
+              f"predecessor done {t[2]-t0}, codebook landed {t[3]-t0}, activations landed {t[4]-t0}, exit {t[5]-t0}")
+        it = 0
+        while 8 + 6 * it + 5 < 96 and t[8 + 6 * it] >= t0 and t[8 + 6 * it] <= t[5]:
+            b = 8 + 6 * it
+            print(f"  tile {it}: index rows landed {t[b]-t0}, CTA in step {t[b+1]-t0}, gathers+MMAs done {t[b+2]-t0}, "
+                  f"partials exchanged {t[b+3]-t0}, reduced+stored {t[b+4]-t0}, tile closed {t[b+5]-t0}")
+            it += 1
+    elif kern == "large_tmem" and hasattr(lib, "sacq_debug_tmem_trace"):
+        buf = (ctypes.c_longlong * (8 * 72))()
+        lib.sacq_debug_tmem_trace(buf)
+        t = [list(buf)[i * 72:(i + 1) * 72] for i in range(8)]
+        t0, nk = t[0][0], a.K // 128
+        print(f"TMEM-weight kernel, CTA (0,0) (ns from the end of the prologue): accumulator complete {t[0][3]-t0}, exit {t[0][4]-t0}")
+        print("  expander: weight stage free   ", [v - t0 for v in t[2][8:8 + nk]])
+        print("  expander: weight stage written", [v - t0 for v in t[5][8:8 + nk]])
+        print("  issuer: operands ready        ", [v - t0 for v in t[1][8:8 + nk]])
+    else:
+        print("no trace: the library was not built with -DSACQ_TRACE, or this kernel records none")
 
 
 if __name__ == "__main__":

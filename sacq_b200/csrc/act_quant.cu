@@ -37,6 +37,7 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
                      float* __restrict__ scale_out) {
   __shared__ float red[kThreads / 32];
   __shared__ float s_scale;
+  SACQ_TL_BEGIN(1);
   // A GEMM launched with programmatic stream serialization may start its prologue now; it
   // waits for this grid to finish before it reads q or the scales.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -44,6 +45,7 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
   // launch latency overlaps that kernel's tail): wait for it before touching x, q or the scales
   // (the kernel in front may have produced x, or may still be reading q).
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  SACQ_TL(t_dep);
   const int64_t m = blockIdx.x;
   const uint16_t* row = x + m * pitch;
   uint8_t* qrow = q + m * K;
@@ -118,9 +120,14 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
       qrow[k] = (uint8_t)(encode2<I8>(z, 0.f, s) & 0xff);
     }
   }
+  SACQ_TL(t_exit);
 }
 
 }  // namespace
+
+#ifdef SACQ_TRACE
+SACQ_TL_DEFINE_DUMP(sacq_debug_timeline_quant)
+#endif
 
 int launch_quant_act_int8(const void* x, int64_t pitch, int64_t M, int64_t K, void* q, float* scale,
                           cudaStream_t s) {

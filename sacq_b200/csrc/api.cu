@@ -76,6 +76,7 @@ constexpr int64_t kGroupedMinMInt8 = 48;
 
 int pick_kernel(const sacq_layer* L, int64_t M) {
   if (L->force_kernel == 7) return large_m_grouped_supported(L) ? 3 : SACQ_ERR_UNSUPPORTED;
+  if (L->force_kernel >= 12) return large_m_tmem_grouped_supported(L) ? 5 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel >= 8) return large_m_tmem_supported(L) ? 4 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 1 || L->force_kernel >= 3)
     return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
@@ -100,8 +101,10 @@ int pick_kernel(const sacq_layer* L, int64_t M) {
     if (M > 48 && L->d.in_features >= 4096) return 2;
     // ... and on layers of 2048 or more rows (2048 x 2048 at M = 64: 9.8 us against 8.9 us)
     if (M > 48 && L->d.out_features >= 2048) return 2;
+  } else if (large_m_tmem_grouped_supported(L) && M >= large_m_tmem_grouped_min_m(L)) {
+    return 5;                                          // grouped scales, odd index widths: weights in tensor memory
   } else if (M >= grouped_min_m(L) && large_m_grouped_supported(L)) {
-    return 3;                                          // grouped scales, odd index widths, a shift
+    return 3;                                          // ... expanded weight tiles in shared memory
   }
   return small_m_supported(L) ? 1 : SACQ_ERR_UNSUPPORTED;
 }
@@ -300,7 +303,7 @@ SACQ_API int sacq_modulate_quant_fp8(const void* x_bf16, int64_t x_pitch, const 
 
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
-  if (which < 0 || which > 11) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..11", which);
+  if (which < 0 || which > 15) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..15", which);
   L->force_kernel = which;
   return SACQ_OK;
 }
@@ -315,6 +318,7 @@ SACQ_API int sacq_layer_kernel_for(const sacq_layer_t* L, int64_t M) {
 SACQ_API int64_t sacq_workspace_bytes(const sacq_layer_t* L, int64_t M) {
   if (L == nullptr || M < 0) return 0;
   if (pick_kernel(L, M) == 3) return kCounterBytes + large_m_grouped_workspace_bytes(L, M);
+  if (pick_kernel(L, M) == 5) return kCounterBytes + large_m_tmem_grouped_workspace_bytes(L, M);
   const int64_t slab = small_m_slab_rows(L);
   return small_m_workspace_bytes(L, M < slab ? M : slab);
 }
@@ -343,10 +347,14 @@ int linear_a8_impl(const sacq_layer_t* L, const void* q, const float* scale, int
   if (k == 4)
     return launch_large_m_tmem(L, q, scale, M, y_out, ldy, s, residual, ldr, bc,
                                L->force_kernel >= 9 ? L->force_kernel - 8 : 0);
-  if (k == 3) {
+  if (k == 3 || k == 5) {
     if (workspace == nullptr || workspace_bytes < kCounterBytes)
       return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
                        (long long)sacq_workspace_bytes(L, M), (long long)workspace_bytes);
+    if (k == 5)
+      return launch_large_m_tmem_grouped(L, q, scale, M, y_out, ldy, static_cast<uint8_t*>(workspace) + kCounterBytes,
+                                         workspace_bytes - kCounterBytes, s, residual, ldr, 0, bc,
+                                         L->force_kernel >= 13 ? L->force_kernel - 12 : 0);
     return launch_large_m_grouped(L, q, scale, M, y_out, ldy, static_cast<uint8_t*>(workspace) + kCounterBytes,
                                   workspace_bytes - kCounterBytes, s, residual, ldr, 0, bc);
   }
@@ -390,6 +398,8 @@ SACQ_API int sacq_quant_act_int8(const void* x_bf16, int64_t x_pitch, int64_t M,
 
 SACQ_API int64_t sacq_workspace_bytes_int8(const sacq_layer_t* L, int64_t M) {
   if (L == nullptr || M < 0) return 0;
+  if (large_m_tmem_grouped_supported(L) && M >= large_m_tmem_grouped_min_m(L))
+    return kCounterBytes + large_m_tmem_grouped_workspace_bytes(L, M);
   if (M >= kGroupedMinMInt8 && large_m_grouped_supported(L)) return kCounterBytes + large_m_grouped_workspace_bytes(L, M);
   sacq_layer view = *L;
   view.force_kernel = int8_small_selector(L);
@@ -409,6 +419,13 @@ SACQ_API int sacq_linear_a8i(const sacq_layer_t* L, const void* q_int8, const fl
                      (long long)L->d.out_features);
   DeviceGuard guard(L->d.device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (large_m_tmem_grouped_supported(L) && M >= large_m_tmem_grouped_min_m(L)) {
+    if (workspace == nullptr || workspace_bytes < kCounterBytes)
+      return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
+                       (long long)sacq_workspace_bytes_int8(L, M), (long long)workspace_bytes);
+    return launch_large_m_tmem_grouped(L, q_int8, scale, M, y_out, ldy, static_cast<uint8_t*>(workspace) + kCounterBytes,
+                                       workspace_bytes - kCounterBytes, s, nullptr, 0, 1);
+  }
   if (M >= kGroupedMinMInt8 && large_m_grouped_supported(L)) {
     if (workspace == nullptr || workspace_bytes < kCounterBytes)
       return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",
@@ -596,14 +613,34 @@ SACQ_API int sacq_linear_a8_multi(const sacq_layer_t* const* layers, int num_lay
   return SACQ_OK;
 }
 
-SACQ_API int sacq_linear_bf16(const sacq_layer_t* L, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
+namespace {
+// quantizer + GEMM; `x_on_device` = x is ordinary device memory (not a pinned host buffer seen through its
+// device alias, which every CTA of a GEMM should not read over the bus).
+int linear_bf16_impl(const sacq_layer_t* L, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
                      float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
-                     void* stream) {
+                     void* stream, bool x_on_device) {
   if (int rc = check_layer(L)) return rc;
   if (M == 0) return SACQ_OK;
+  // Up to 16 rows on the staged warp-MMA kernel: the GEMM quantizes the rows itself (same bytes and
+  // scales as the stand-alone quantizer), which saves a kernel and two stream hand-overs per call.
+  if (x_on_device && x_bf16 != nullptr && y_out != nullptr && x_pitch >= L->d.in_features && x_pitch % 8 == 0 &&
+      reinterpret_cast<uintptr_t>(x_bf16) % 16 == 0 && ldy >= L->d.out_features && L->d.out_features > 0 &&
+      pick_kernel(L, M) == 1 && small_m_can_fuse_quant(L, M)) {
+    DeviceGuard guard(L->d.device);
+    return launch_small_m(L, nullptr, nullptr, M, y_out, ldy, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream), nullptr, 0, 0, nullptr, x_bf16, x_pitch);
+  }
   int rc = sacq_quant_act_fp8(x_bf16, x_pitch, M, L->d.in_features, q_scratch, scale_scratch, stream);
   if (rc != SACQ_OK) return rc;
   return sacq_linear_a8(L, q_scratch, scale_scratch, M, y_out, ldy, workspace, workspace_bytes, stream);
+}
+}  // namespace
+
+SACQ_API int sacq_linear_bf16(const sacq_layer_t* L, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
+                     float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
+                     void* stream) {
+  return linear_bf16_impl(L, x_bf16, x_pitch, M, q_scratch, scale_scratch, y_out, ldy, workspace, workspace_bytes, stream,
+                          true);
 }
 
 // Layout of the device scratch of sacq_linear_bf16_host: workspace first (its counter
@@ -669,8 +706,8 @@ SACQ_API int sacq_linear_bf16_host(const sacq_layer_t* L, const void* x_host, in
     x_dev = x_alias;                                   // the quantizer reads the pinned buffer itself
   else
     SACQ_CUDA_TRY(cudaMemcpyAsync(base + h.x, x_host, (size_t)(M * K * 2), cudaMemcpyHostToDevice, s));
-  const int rc = sacq_linear_bf16(L, x_dev, K, M, base + h.q, reinterpret_cast<float*>(base + h.scale),
-                                  base + h.y, N, base + h.ws, h.scale, stream);
+  const int rc = linear_bf16_impl(L, x_dev, K, M, base + h.q, reinterpret_cast<float*>(base + h.scale), base + h.y, N,
+                                  base + h.ws, h.scale, stream, x_alias == nullptr);
   if (rc != SACQ_OK) return rc;
   void* y_alias = M * N * 2 <= kDirectHostIoBytes && reinterpret_cast<uintptr_t>(y_host) % 16 == 0
                       ? pinned_alias(y_host) : nullptr;

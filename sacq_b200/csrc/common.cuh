@@ -89,9 +89,12 @@ struct BcastDst {
 };
 
 // `residual` (bf16 [M, ldr], may be null) is added to the rounded output in every GEMM epilogue.
+// `x_bf16` (with row pitch `x_pitch` elements) hands the kernel unquantized activations to quantize
+// itself (small_m_can_fuse_quant() says when that is possible); q and scale are then unused.
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0,
-                   int act_int8 = 0, const BcastDst* bc = nullptr);
+                   int act_int8 = 0, const BcastDst* bc = nullptr, const void* x_bf16 = nullptr, int64_t x_pitch = 0);
+bool small_m_can_fuse_quant(const sacq_layer* L, int64_t M);
 
 int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
                          void* const* ys, const int64_t* ldys, cudaStream_t s);
@@ -121,9 +124,42 @@ int launch_large_m_grouped(const sacq_layer* L, const void* q, const float* scal
                            void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr,
                            int64_t ldr = 0, int act_int8 = 0, const BcastDst* bc = nullptr);
 
+// Grouped-scale tensor-core kernel with the weights in tensor memory (linear_large_m_tmem_grouped.cu).
+bool large_m_tmem_grouped_supported(const sacq_layer* L);
+int64_t large_m_tmem_grouped_workspace_bytes(const sacq_layer* L, int64_t M);
+int64_t large_m_tmem_grouped_min_m(const sacq_layer* L);
+int launch_large_m_tmem_grouped(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
+                                void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr,
+                                int64_t ldr = 0, int act_int8 = 0, const BcastDst* bc = nullptr, int nt_force = 0);
+
 // ----------------------------------------------------------------------------
 // device side
 // ----------------------------------------------------------------------------
+
+#ifdef SACQ_TRACE
+// Profiling builds only (-DSACQ_TRACE): a timeline of kernel phases.  Block 0 of every traced kernel
+// takes a slot (its launch order) and records %globaltimer at entry, after it has waited for its
+// predecessor on the stream, when its staged operands have landed, and at exit.
+struct TimelineEntry { long long kind, t_entry, t_dep, t_ready, t_exit, pad[3]; };
+// (one buffer per translation unit: device symbols are not shared between them without
+// relocatable device code; %globaltimer is, so the dumps merge by time)
+static __device__ TimelineEntry g_timeline[512];
+static __device__ unsigned g_timeline_count = 0;
+#define SACQ_TL_DEFINE_DUMP(name)                                                                              \
+  extern "C" SACQ_API int name(long long* out, int reset) {                                                    \
+    unsigned n = 0;                                                                                            \
+    if (cudaMemcpyFromSymbol(&n, g_timeline_count, sizeof(n)) != cudaSuccess) return -1;                       \
+    if (out != nullptr && cudaMemcpyFromSymbol(out, g_timeline, sizeof(TimelineEntry) * 512) != cudaSuccess) return -1; \
+    if (reset) { unsigned z = 0; cudaMemcpyToSymbol(g_timeline_count, &z, sizeof(z)); }                        \
+    return (int)n;                                                                                             \
+  }
+__device__ __forceinline__ long long tl_now() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define SACQ_TL_BEGIN(kindv) int _tl = -1; if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { _tl = (int)(atomicAdd(&g_timeline_count, 1u) & 511u); g_timeline[_tl].kind = (kindv); g_timeline[_tl].t_entry = tl_now(); }
+#define SACQ_TL(field) do { if (_tl >= 0) g_timeline[_tl].field = tl_now(); } while (0)
+#else
+#define SACQ_TL_BEGIN(kindv) do { } while (0)
+#define SACQ_TL(field) do { } while (0)
+#endif
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
 

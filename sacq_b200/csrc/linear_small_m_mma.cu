@@ -292,7 +292,7 @@ __host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64
   L.red_off = L.act_off + (uint32_t)act_bufs * (uint32_t)((16 * (K + kActPad) + 127) & ~127);
   L.sa_off = L.red_off + (uint32_t)(warps * r8 * 4 * 32 * 4);
   L.bar_off = L.sa_off + 384;             // 16 token scales + 32 row scales + 32 row biases
-  L.total = L.bar_off + 64;
+  L.total = L.bar_off + 64 + 64;          // 5 mbarriers, then 16 row maxima of the in-kernel quantizer
   return L;
 }
 
@@ -303,6 +303,15 @@ __device__ __forceinline__ void mma_m16n8k32_e4m3(float (&c)[4], uint32_t a0, ui
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+
+#ifdef SACQ_TRACE
+// Profiling builds only (-DSACQ_TRACE): CTA 0 records %globaltimer at the phase boundaries of
+// the staged kernel (thread 0; slots 0..7 prologue, then 6 per tile).
+__device__ long long g_small_trace[96];
+#define SACQ_ST(slot) do { if (cta == 0 && threadIdx.x == 0 && (slot) < 96) { long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_small_trace[slot] = _t; } } while (0)
+#else
+#define SACQ_ST(slot) do { } while (0)
+#endif
 
 // HALVES = warps sharing one 32-index span (each takes 8/HALVES of its MMA steps): with
 // two, a CTA runs up to 16 lighter warps, which hides more of the gather -> MMA latency.
@@ -329,7 +338,14 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   const int act_pitch = p.K + kActPad;
   const uint32_t idx_buf_bytes = (L.act_off - L.idx_off) / 2;
   const uint32_t act_buf_bytes = 0;                  // a single activation tile
+  SACQ_ST(0);
+#ifdef SACQ_TRACE
+  int _tl = -1;
+  if (cta == 0 && threadIdx.x == 0) { _tl = (int)(atomicAdd(&g_timeline_count, 1u) & 511u); g_timeline[_tl].kind = 2; g_timeline[_tl].t_entry = tl_now(); }
+#endif
 
+  uint32_t* rowmax_s = reinterpret_cast<uint32_t*>(smem + L.bar_off + 64);   // |x| maxima as float bits (>= 0)
+  const bool fused_quant = p.x_bf16 != nullptr;
   if (threadIdx.x == 0) {
     mbar_init(bar_cb, 1);
     mbar_init(bar_act0, 1);
@@ -338,6 +354,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
     mbar_init(bar_idx0 + 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (threadIdx.x < 16) rowmax_s[threadIdx.x] = 0u;
   __syncthreads();
 
   // Work of this CTA: row tiles rt = blockIdx.x, + gridDim.x, ...; every row tile is
@@ -382,9 +399,65 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   }
   // the next kernel of the stream (a quantizer or another GEMM launched with programmatic
   // serialization) may be scheduled from here on; it waits for this grid before it touches memory
+  SACQ_ST(1);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");                // activations come from that kernel
-  if (threadIdx.x < 16 && first_rt < p.row_blocks) {
+  SACQ_ST(2);
+  SACQ_TL(t_dep);
+  if (fused_quant) {
+    // Per-token quantization of the bf16 activations inside this kernel (at most 16 rows): every CTA
+    // reads the rows from L2, the row maxima meet in shared memory, and the e4m3 bytes go straight
+    // into the activation tile -- the arithmetic of the stand-alone quantizer (act_quant.cu), so the
+    // bytes and scales are the same, without a second kernel and its two stream hand-overs.
+    constexpr int kMaxChunks = 8;                      // 16-byte chunks (8 values) a thread may hold
+    const int cpr = p.K >> 3;                          // chunks per row
+    const int total = toks_here * cpr;
+    uint4 keep[kMaxChunks];
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int idx = (int)threadIdx.x + c * (int)blockDim.x;
+      keep[c] = make_uint4(0, 0, 0, 0);
+      if (idx < total) {
+        const int row = idx / cpr, ch = idx - row * cpr;
+        keep[c] = __ldg(reinterpret_cast<const uint4*>(p.x_bf16 + (int64_t)(m_base + row) * p.x_pitch) + ch);
+        const uint32_t w[4] = {keep[c].x, keep[c].y, keep[c].z, keep[c].w};
+        float mx = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] & 0xffff)));
+          mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] >> 16)));
+        }
+        mx = warp_max(mx);                             // a warp's chunks lie in one row (cpr is a multiple of 32)
+        if (lane == 0) atomicMax(rowmax_s + row, __float_as_uint(mx));
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int idx = (int)threadIdx.x + c * (int)blockDim.x;
+      if (idx < total) {
+        const int row = idx / cpr, ch = idx - row * cpr;
+        const float v = __uint_as_float(rowmax_s[row]);
+        const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
+        const uint32_t w[4] = {keep[c].x, keep[c].y, keep[c].z, keep[c].w};
+        uint32_t o[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint32_t a = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] & 0xffff), s)),
+                                              clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] >> 16), s)));
+          const uint32_t b = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] & 0xffff), s)),
+                                              clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] >> 16), s)));
+          o[j] = a | (b << 16);
+        }
+        *reinterpret_cast<uint2*>(act_base + row * act_pitch + ch * 8) = make_uint2(o[0], o[1]);
+      }
+    }
+    if (threadIdx.x < 16) {
+      const float v = __uint_as_float(rowmax_s[threadIdx.x]);
+      sa_s[threadIdx.x] = (int)threadIdx.x < toks_here ? (v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f) : 0.f;
+    }
+    // (the first tile's __syncthreads_and below publishes the tile and the scales to every warp)
+  } else if (threadIdx.x < 16 && first_rt < p.row_blocks) {
     issue_act(chunk, 0);
     sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
   }
@@ -418,13 +491,18 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
     }
     if (first) {
       ok = mbar_wait_bounded(bar_cb, 0, p.status) && ok;
-      ok = mbar_wait_bounded(bar_act0, 0, p.status) && ok;
+      SACQ_ST(3);
+      if (!fused_quant) ok = mbar_wait_bounded(bar_act0, 0, p.status) && ok;
+      SACQ_ST(4);
+      SACQ_TL(t_ready);
       first = false;
     }
     ok = mbar_wait_bounded(bar_idx0 + 8 * buf, idx_parity[buf], p.status) && ok;
     idx_parity[buf] ^= 1;
+    SACQ_ST(8 + 6 * it);
     ok = __syncthreads_and(ok);
     if (!ok) break;                                    // a bounded wait expired: status word is set
+    SACQ_ST(8 + 6 * it + 1);
 
     // per-row scales of the two output rows this lane holds in each sub-block
     float s0[R8], s1[R8];
@@ -556,6 +634,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
         acc[r][3] = fmaf(s1[r], cs[r][3], acc[r][3]);
       }
     }
+    SACQ_ST(8 + 6 * it + 2);
 #pragma unroll
     for (int r = 0; r < R8; ++r) {
       red[(warp * kFrag + r * 4 + 0) * 32 + lane] = fmaf(acc[r][0], p.out_mul, p.shift * xs_a);
@@ -564,6 +643,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
       red[(warp * kFrag + r * 4 + 3) * 32 + lane] = fmaf(acc[r][3], p.out_mul, p.shift * xs_b);
     }
     __syncthreads();
+    SACQ_ST(8 + 6 * it + 3);
     for (int e = threadIdx.x; e < kFrag * 32; e += blockDim.x) {
       float v = 0.f;
       for (int w = 0; w < nwarps; ++w) v += red[w * kFrag * 32 + e];
@@ -574,7 +654,9 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
         store_out(p, m_base + ml, n, fmaf(sa_s[ml], v, rowb_s[n - n_base]));
       }
     }
+    SACQ_ST(8 + 6 * it + 4);
     __syncthreads();                                   // red and the row constants are reused next
+    SACQ_ST(8 + 6 * it + 5);
     if (threadIdx.x < 8 * R8) {
       rowsc_s[threadIdx.x] = next_sc;
       rowb_s[threadIdx.x] = next_b;
@@ -583,6 +665,8 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   if (first) {                                         // a CTA without a row tile still owns its copies
     mbar_wait_bounded(bar_cb, 0, p.status);
   }
+  SACQ_ST(5);
+  SACQ_TL(t_exit);
 }
 
 template <int D, int BITS, int R8, int HALVES>
@@ -668,6 +752,13 @@ cudaError_t launch_cb(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
 }
 
 }  // namespace
+
+#ifdef SACQ_TRACE
+SACQ_TL_DEFINE_DUMP(sacq_debug_timeline_gemm)
+extern "C" SACQ_API int sacq_debug_small_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_small_trace, sizeof(g_small_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps, int act_bufs) {
   return staged_layout(C, D, K, row_bytes, r8, warps, act_bufs).total;

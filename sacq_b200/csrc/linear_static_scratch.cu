@@ -72,8 +72,12 @@ SACQ_API int sacq_linear_a8_static_scratch(const sacq_layer_t* L, const void* q,
     // the split-K CUDA-core variant is the one that needs scratch; run exactly that one
     sacq_layer view = *L;
     view.force_kernel = 3;
+    // What the launch plan for (layer, M) uses, plus a bound that does not depend on the plan (how
+    // far K is split depends on the device's SM count): one fp32 copy of the output must fit.
     int64_t need = 0, counters = 0;
     small_m_scratch_need(&view, M, &need, &counters);
+    const int64_t one_split = sacq_workspace_counter_bytes() + M * L->d.out_features * (int64_t)sizeof(float);
+    if (one_split > need) need = one_split;
     if (need > (int64_t)kStaticScratchBytes || counters * (int64_t)sizeof(int) > sacq_workspace_counter_bytes()) {
       rc = set_error(SACQ_ERR_WORKSPACE,
                      "this call (M=%lld, N=%lld) needs %lld bytes of scratch and %lld arrival counters, but the "

@@ -423,10 +423,11 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
     def set_kernel(self, which: str | int) -> None:
         """Force a GEMM kernel: 'auto' (0), 'small' (1), 'large' (2), 'small_simt' (3), 'small_mma' (4),
         'small_mma_direct' (5), 'small_mma_unpacked' (6), 'large_grouped' (7), 'large_tmem' (8; 9-11 also
-        fix its token sub-tiles per CTA to 1-3)."""
+        fix its token sub-tiles per CTA to 1-3), 'large_tmem_grouped' (12; 13-15 likewise)."""
         code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5,
                 "small_mma_unpacked": 6, "large_grouped": 7, "large_tmem": 8, "large_tmem1": 9,
-                "large_tmem2": 10, "large_tmem3": 11}.get(which, which)
+                "large_tmem2": 10, "large_tmem3": 11, "large_tmem_grouped": 12, "large_tmem_grouped1": 13,
+                "large_tmem_grouped2": 14, "large_tmem_grouped3": 15}.get(which, which)
         _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
         self._ws_bytes.clear()
         self._host_bytes.clear()
@@ -435,7 +436,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         k = self._lib.sacq_layer_kernel_for(self._handle, m)
         if k < 0:
             _lib.check(k)
-        return {1: "small", 2: "large", 3: "large_grouped", 4: "large_tmem"}[k]
+        return {1: "small", 2: "large", 3: "large_grouped", 4: "large_tmem", 5: "large_tmem_grouped"}[k]
 
     def device_status(self) -> int:
         st = ctypes.c_int(0)

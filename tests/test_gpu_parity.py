@@ -498,7 +498,8 @@ def test_linear_deployed_layouts(N, K, C, G):
 @pytest.mark.parametrize("N,K,d,C,G,M", [
     (2048, 2048, 4, 128, 64, 149), (6144, 2048, 4, 1024, 64, 300), (1536, 1536, 4, 64, 64, 41),
     (2048, 6144, 4, 32, 64, 256), (1000, 2048, 4, 2048, 128, 129), (136, 1024, 8, 512, 64, 77),
-    (520, 1024, 8, 4096, 256, 1), (2048, 2048, 8, 4096, 2048, 1300)])
+    (520, 1024, 8, 4096, 256, 1), (2048, 2048, 8, 4096, 2048, 1300), (6144, 2048, 4, 1024, 64, 1300),
+    (2048, 2048, 4, 128, 64, 4000)])
 def test_linear_grouped_tensor_core(N, K, d, C, G, M):
     """Grouped scales on the tcgen05 kind::f16 kernel: the deployed dim-4 / group-64 layouts at
     prefill sizes, partial tiles in M and N, one and two token sub-tiles, a token count above
@@ -511,12 +512,20 @@ def test_linear_grouped_tensor_core(N, K, d, C, G, M):
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
     w_bits = oracle_weight(p)
     q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 2)))
-    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=("large_grouped", "small"))
-    assert "large_grouped" in outs
-    a, b = outs["large_grouped"][0].float().cpu().numpy(), outs["small"][0].float().cpu().numpy()
-    assert O.rel_frobenius(a, b) < 5e-3
+    small = ("small",) if M <= 1300 else ()               # the warp-MMA kernel walks the weights once per 16 tokens
+    outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias),
+                         kernels=("large_grouped", "large_tmem_grouped", "large_tmem_grouped1", "auto") + small)
+    assert "large_grouped" in outs and "large_tmem_grouped" in outs
+    a = outs["large_grouped"][0].float().cpu().numpy()
+    if small:
+        assert O.rel_frobenius(a, outs["small"][0].float().cpu().numpy()) < 5e-3
+    # the tensor-memory form sums an output in the same order whatever its tile shape
+    assert torch.equal(outs["large_tmem_grouped"][0], outs["large_tmem_grouped1"][0])
+    assert O.rel_frobenius(a, outs["large_tmem_grouped"][0].float().cpu().numpy()) < 1e-3
     if M >= 96 and G < K:
-        assert mod.kernel_for(M) == "large_grouped"
+        assert mod.kernel_for(M) in ("large_grouped", "large_tmem_grouped")
+    if (N, M) == (6144, 1300):
+        assert mod.kernel_for(M) == "large_tmem_grouped"
     # rows of a wider output buffer beyond N stay untouched
     q = torch.from_numpy(q_bits).cuda().view(torch.float8_e4m3fn)
     out = torch.full((M, N + 24), 3.0, dtype=torch.bfloat16, device="cuda")

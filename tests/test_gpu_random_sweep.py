@@ -9,7 +9,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-KERNELS = ("auto", "small", "small_simt", "small_mma_unpacked", "large", "large_grouped", "large_tmem")
+KERNELS = ("auto", "small", "small_simt", "small_mma_unpacked", "large", "large_grouped", "large_tmem", "large_tmem_grouped")
 
 
 @pytest.mark.parametrize("seed", [1, 2, 3])
