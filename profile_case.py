@@ -42,6 +42,10 @@ def main():
     ap.add_argument("--instances", type=int, default=8)
     ap.add_argument("--passes", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="print the mean time per call (CUDA events)")
+    ap.add_argument("--graph", action="store_true", help="run the calls as one CUDA graph replay instead of eager launches")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print entry / dependency / ready / exit times of the kernels of the last pass "
+                         "(needs a library built with -DSACQ_TRACE)")
     ap.add_argument("--trace", action="store_true",
                     help="print the in-kernel phase timestamps of the last launch (needs a library built with -DSACQ_TRACE)")
     a = ap.parse_args()
@@ -66,11 +70,34 @@ def main():
         call(layer)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.passes):
-        for layer in layers:
-            out = call(layer)
-    e1.record()
+    if a.graph:
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            for layer in layers:
+                out = call(layer)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for layer in layers:
+                out = call(layer)
+        with torch.cuda.stream(stream):
+            graph.replay()
+            stream.synchronize()
+            if a.timeline:
+                read_timeline(reset_only=True)
+            e0.record(stream)
+            for _ in range(a.passes):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+    else:
+        if a.timeline:
+            read_timeline(reset_only=True)
+        e0.record()
+        for _ in range(a.passes):
+            for layer in layers:
+                out = call(layer)
+        e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (a.passes * len(layers))
     msg = f"ok op={a.op} kernel={layers[0].kernel_for(a.M)} K={a.K} N={a.N} M={a.M} checksum={float(out.float().abs().mean()):.6f}"
@@ -80,6 +107,31 @@ def main():
     print(msg)
     if a.trace:
         print_trace(layers[0], a)
+    if a.timeline:
+        print(f"per call: {us:.2f} us")
+        for kind, t_entry, t_dep, t_ready, t_exit in read_timeline()[20:32]:
+            print(f"  {kind:5s} entry {t_entry:8d}  predecessor seen finished {t_dep:8d}  operands landed {t_ready:8d}  exit {t_exit:8d}")
+
+
+def read_timeline(reset_only=False):
+    """Merged kernel timeline of a -DSACQ_TRACE build: (kind, entry, dependency, ready, exit) in ns
+    from the first entry, ordered by entry time."""
+    import ctypes
+    lib = ctypes.CDLL(os.path.join(ROOT, "sacq_b200", "libsacq_b200.so"))
+    rows = []
+    for name, kind in (("sacq_debug_timeline_quant", "quant"), ("sacq_debug_timeline_gemm", "gemm")):
+        if not hasattr(lib, name):
+            continue
+        buf = (ctypes.c_longlong * (512 * 8))()
+        n = getattr(lib, name)(None if reset_only else buf, 1)
+        if not reset_only:
+            for i in range(min(n, 512)):
+                rows.append((kind,) + tuple(buf[8 * i + 1: 8 * i + 5]))
+    if not rows:
+        return []
+    rows.sort(key=lambda r: r[1])
+    t0 = rows[0][1]
+    return [(k, e - t0, d - t0, (r - t0) if r else 0, x - t0) for k, e, d, r, x in rows]
 
 
 def print_trace(layer, a):

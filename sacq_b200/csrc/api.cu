@@ -613,34 +613,14 @@ SACQ_API int sacq_linear_a8_multi(const sacq_layer_t* const* layers, int num_lay
   return SACQ_OK;
 }
 
-namespace {
-// quantizer + GEMM; `x_on_device` = x is ordinary device memory (not a pinned host buffer seen through its
-// device alias, which every CTA of a GEMM should not read over the bus).
-int linear_bf16_impl(const sacq_layer_t* L, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
-                     float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
-                     void* stream, bool x_on_device) {
-  if (int rc = check_layer(L)) return rc;
-  if (M == 0) return SACQ_OK;
-  // Up to 16 rows on the staged warp-MMA kernel: the GEMM quantizes the rows itself (same bytes and
-  // scales as the stand-alone quantizer), which saves a kernel and two stream hand-overs per call.
-  if (x_on_device && x_bf16 != nullptr && y_out != nullptr && x_pitch >= L->d.in_features && x_pitch % 8 == 0 &&
-      reinterpret_cast<uintptr_t>(x_bf16) % 16 == 0 && ldy >= L->d.out_features && L->d.out_features > 0 &&
-      pick_kernel(L, M) == 1 && small_m_can_fuse_quant(L, M)) {
-    DeviceGuard guard(L->d.device);
-    return launch_small_m(L, nullptr, nullptr, M, y_out, ldy, workspace, workspace_bytes,
-                          static_cast<cudaStream_t>(stream), nullptr, 0, 0, nullptr, x_bf16, x_pitch);
-  }
-  int rc = sacq_quant_act_fp8(x_bf16, x_pitch, M, L->d.in_features, q_scratch, scale_scratch, stream);
-  if (rc != SACQ_OK) return rc;
-  return sacq_linear_a8(L, q_scratch, scale_scratch, M, y_out, ldy, workspace, workspace_bytes, stream);
-}
-}  // namespace
-
 SACQ_API int sacq_linear_bf16(const sacq_layer_t* L, const void* x_bf16, int64_t x_pitch, int64_t M, void* q_scratch,
                      float* scale_scratch, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
                      void* stream) {
-  return linear_bf16_impl(L, x_bf16, x_pitch, M, q_scratch, scale_scratch, y_out, ldy, workspace, workspace_bytes, stream,
-                          true);
+  if (int rc = check_layer(L)) return rc;
+  if (M == 0) return SACQ_OK;
+  int rc = sacq_quant_act_fp8(x_bf16, x_pitch, M, L->d.in_features, q_scratch, scale_scratch, stream);
+  if (rc != SACQ_OK) return rc;
+  return sacq_linear_a8(L, q_scratch, scale_scratch, M, y_out, ldy, workspace, workspace_bytes, stream);
 }
 
 // Layout of the device scratch of sacq_linear_bf16_host: workspace first (its counter
@@ -706,8 +686,8 @@ SACQ_API int sacq_linear_bf16_host(const sacq_layer_t* L, const void* x_host, in
     x_dev = x_alias;                                   // the quantizer reads the pinned buffer itself
   else
     SACQ_CUDA_TRY(cudaMemcpyAsync(base + h.x, x_host, (size_t)(M * K * 2), cudaMemcpyHostToDevice, s));
-  const int rc = linear_bf16_impl(L, x_dev, K, M, base + h.q, reinterpret_cast<float*>(base + h.scale), base + h.y, N,
-                                  base + h.ws, h.scale, stream, x_alias == nullptr);
+  const int rc = sacq_linear_bf16(L, x_dev, K, M, base + h.q, reinterpret_cast<float*>(base + h.scale),
+                                  base + h.y, N, base + h.ws, h.scale, stream);
   if (rc != SACQ_OK) return rc;
   void* y_alias = M * N * 2 <= kDirectHostIoBytes && reinterpret_cast<uintptr_t>(y_host) % 16 == 0
                       ? pinned_alias(y_host) : nullptr;

@@ -89,12 +89,9 @@ struct BcastDst {
 };
 
 // `residual` (bf16 [M, ldr], may be null) is added to the rounded output in every GEMM epilogue.
-// `x_bf16` (with row pitch `x_pitch` elements) hands the kernel unquantized activations to quantize
-// itself (small_m_can_fuse_quant() says when that is possible); q and scale are then unused.
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual = nullptr, int64_t ldr = 0,
-                   int act_int8 = 0, const BcastDst* bc = nullptr, const void* x_bf16 = nullptr, int64_t x_pitch = 0);
-bool small_m_can_fuse_quant(const sacq_layer* L, int64_t M);
+                   int act_int8 = 0, const BcastDst* bc = nullptr);
 
 int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, const float* scale, int64_t M,
                          void* const* ys, const int64_t* ldys, cudaStream_t s);

@@ -601,19 +601,9 @@ SmallMParams fill_params(const sacq_layer* L, const Plan& pl, const void* q, con
 }
 }  // namespace
 
-// Whether a forward of M bf16 rows can quantize them inside the staged warp-MMA kernel: one token
-// chunk, rows that split into whole warps of 16-byte pieces, and few enough pieces per thread.
-bool small_m_can_fuse_quant(const sacq_layer* L, int64_t M) {
-  if (M < 1 || M > 16 || L->force_kernel != 0) return false;
-  const Plan pl = make_plan(L, M);
-  if (!pl.mma || !pl.staged || pl.unpacked || pl.chunks != 1) return false;
-  const int64_t K = L->d.in_features;
-  return K % 256 == 0 && M * (K / 8) <= 8LL * pl.warps * 32;
-}
-
 int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64_t M, void* y, int64_t ldy,
                    void* ws, int64_t ws_bytes, cudaStream_t s, const void* residual, int64_t ldr, int act_int8,
-                   const BcastDst* bc, const void* x_bf16, int64_t x_pitch) {
+                   const BcastDst* bc) {
   const sacq_layer_desc& d = L->d;
   if (M == 0 || d.out_features == 0) return SACQ_OK;
   if (M > (1 << 20)) return set_error(SACQ_ERR_UNSUPPORTED, "small-M kernel: M=%lld too large", (long long)M);
@@ -639,12 +629,6 @@ int launch_small_m(const sacq_layer* L, const void* q, const float* scale, int64
   p.residual = static_cast<const uint16_t*>(residual);
   p.ldr = ldr;
   p.act_int8 = act_int8;
-  if (x_bf16 != nullptr) {
-    if (!pl.mma || !pl.staged || pl.unpacked || pl.chunks != 1)
-      return set_error(SACQ_ERR_UNSUPPORTED, "in-kernel quantization needs the staged warp-MMA kernel and at most 16 rows");
-    p.x_bf16 = static_cast<const uint16_t*>(x_bf16);
-    p.x_pitch = x_pitch;
-  }
   if (bc != nullptr) {
     p.n_bc = bc->n;
     for (int i = 0; i < bc->n; ++i) p.ybc[i] = static_cast<uint16_t*>(bc->ptr[i]);

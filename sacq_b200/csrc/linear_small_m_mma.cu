@@ -292,7 +292,7 @@ __host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64
   L.red_off = L.act_off + (uint32_t)act_bufs * (uint32_t)((16 * (K + kActPad) + 127) & ~127);
   L.sa_off = L.red_off + (uint32_t)(warps * r8 * 4 * 32 * 4);
   L.bar_off = L.sa_off + 384;             // 16 token scales + 32 row scales + 32 row biases
-  L.total = L.bar_off + 64 + 64;          // 5 mbarriers, then 16 row maxima of the in-kernel quantizer
+  L.total = L.bar_off + 64;
   return L;
 }
 
@@ -344,8 +344,6 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   if (cta == 0 && threadIdx.x == 0) { _tl = (int)(atomicAdd(&g_timeline_count, 1u) & 511u); g_timeline[_tl].kind = 2; g_timeline[_tl].t_entry = tl_now(); }
 #endif
 
-  uint32_t* rowmax_s = reinterpret_cast<uint32_t*>(smem + L.bar_off + 64);   // |x| maxima as float bits (>= 0)
-  const bool fused_quant = p.x_bf16 != nullptr;
   if (threadIdx.x == 0) {
     mbar_init(bar_cb, 1);
     mbar_init(bar_act0, 1);
@@ -354,7 +352,6 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
     mbar_init(bar_idx0 + 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (threadIdx.x < 16) rowmax_s[threadIdx.x] = 0u;
   __syncthreads();
 
   // Work of this CTA: row tiles rt = blockIdx.x, + gridDim.x, ...; every row tile is
@@ -404,60 +401,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   asm volatile("griddepcontrol.wait;" ::: "memory");                // activations come from that kernel
   SACQ_ST(2);
   SACQ_TL(t_dep);
-  if (fused_quant) {
-    // Per-token quantization of the bf16 activations inside this kernel (at most 16 rows): every CTA
-    // reads the rows from L2, the row maxima meet in shared memory, and the e4m3 bytes go straight
-    // into the activation tile -- the arithmetic of the stand-alone quantizer (act_quant.cu), so the
-    // bytes and scales are the same, without a second kernel and its two stream hand-overs.
-    constexpr int kMaxChunks = 8;                      // 16-byte chunks (8 values) a thread may hold
-    const int cpr = p.K >> 3;                          // chunks per row
-    const int total = toks_here * cpr;
-    uint4 keep[kMaxChunks];
-#pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
-      const int idx = (int)threadIdx.x + c * (int)blockDim.x;
-      keep[c] = make_uint4(0, 0, 0, 0);
-      if (idx < total) {
-        const int row = idx / cpr, ch = idx - row * cpr;
-        keep[c] = __ldg(reinterpret_cast<const uint4*>(p.x_bf16 + (int64_t)(m_base + row) * p.x_pitch) + ch);
-        const uint32_t w[4] = {keep[c].x, keep[c].y, keep[c].z, keep[c].w};
-        float mx = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] & 0xffff)));
-          mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] >> 16)));
-        }
-        mx = warp_max(mx);                             // a warp's chunks lie in one row (cpr is a multiple of 32)
-        if (lane == 0) atomicMax(rowmax_s + row, __float_as_uint(mx));
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
-      const int idx = (int)threadIdx.x + c * (int)blockDim.x;
-      if (idx < total) {
-        const int row = idx / cpr, ch = idx - row * cpr;
-        const float v = __uint_as_float(rowmax_s[row]);
-        const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
-        const uint32_t w[4] = {keep[c].x, keep[c].y, keep[c].z, keep[c].w};
-        uint32_t o[2];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const uint32_t a = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] & 0xffff), s)),
-                                              clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] >> 16), s)));
-          const uint32_t b = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] & 0xffff), s)),
-                                              clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] >> 16), s)));
-          o[j] = a | (b << 16);
-        }
-        *reinterpret_cast<uint2*>(act_base + row * act_pitch + ch * 8) = make_uint2(o[0], o[1]);
-      }
-    }
-    if (threadIdx.x < 16) {
-      const float v = __uint_as_float(rowmax_s[threadIdx.x]);
-      sa_s[threadIdx.x] = (int)threadIdx.x < toks_here ? (v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f) : 0.f;
-    }
-    // (the first tile's __syncthreads_and below publishes the tile and the scales to every warp)
-  } else if (threadIdx.x < 16 && first_rt < p.row_blocks) {
+  if (threadIdx.x < 16 && first_rt < p.row_blocks) {
     issue_act(chunk, 0);
     sa_s[threadIdx.x] = threadIdx.x < toks_here ? __ldg(p.act_scale + m_base + threadIdx.x) : 0.f;
   }
@@ -492,7 +436,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
     if (first) {
       ok = mbar_wait_bounded(bar_cb, 0, p.status) && ok;
       SACQ_ST(3);
-      if (!fused_quant) ok = mbar_wait_bounded(bar_act0, 0, p.status) && ok;
+      ok = mbar_wait_bounded(bar_act0, 0, p.status) && ok;
       SACQ_ST(4);
       SACQ_TL(t_ready);
       first = false;

@@ -22,8 +22,6 @@ struct SmallMParams {
   const uint16_t* scales;      // bf16 [N, num_groups]
   const uint16_t* bias;        // bf16 [N] or null
   const uint8_t* q;            // e4m3 [M, K]
-  const uint16_t* x_bf16;      // staged warp-MMA kernel, M <= 16: unquantized bf16 activations [M, x_pitch]; the
-  int64_t x_pitch;             //   kernel quantizes them per token itself (null: q and act_scale are given)
   int* status;                 // layer status word (bounded waits report here)
   const float* act_scale;      // [M]
   uint16_t* y;                 // bf16 [M, ldy]
