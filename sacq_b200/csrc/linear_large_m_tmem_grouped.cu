@@ -7,8 +7,13 @@
 // tcgen05 kind::f16 (linear_large_m_grouped.cu explains the encoding).  This kernel is the
 // tensor-memory form of that one, structured like linear_large_m_tmem.cu:
 //   * a CTA owns 128 weight rows (the 128 TMEM lanes) x 128*NT tokens;
+//   * the packed index tile of a super-block (128 indices = 16*bits bytes per row) is staged as
+//     16-byte column slices, [slice][row][16 B] (one TMA box of 16 bytes x 128 rows per slice): a
+//     thread reads its row's slice with one 16-byte load and the 32 lanes of a warp read 512
+//     contiguous bytes, free of bank conflicts (row-major rows of 16*bits bytes would put the
+//     lanes of a warp 4 to 32 deep on the same banks);
 //   * 16 expander warps: a thread owns one weight row and a quarter of each 64-k block (16
-//     weights): it extracts its index fields (runtime width) from the TMA-staged index tile,
+//     weights): it extracts its index fields (runtime width) from two slices held in registers,
 //     gathers the fp16 codewords from the shared-memory codebook, multiplies by the row's group
 //     scale (HMUL2) and writes 8 registers to the weight stage with tcgen05.st -- no
 //     shared-memory store;
@@ -67,9 +72,11 @@ __host__ __device__ inline GTmemLayout gtmem_layout(int nt, int act_stages, int 
   L.act_stage = (uint32_t)(nt * kTokTile);
   L.idx_off = act_stages * L.act_stage;
   L.idx_slot = (uint32_t)(kRows * 16 * bits);
-  L.cb_off = (L.idx_off + 2 * L.idx_slot + 16 + 127) & ~127u;          // + 16: the extractor reads one word ahead
+  L.cb_off = (L.idx_off + 2 * L.idx_slot + 127) & ~127u;
   L.sc_off = L.cb_off + (uint32_t)((cb_bytes + 127) & ~127);
-  L.bias_off = L.sc_off + (uint32_t)((kRows * num_groups * 2 + 127) & ~127);   // bf16 scales of the tile's rows
+  // bf16 scales of the tile's rows, row pitch num_groups + 1 (odd or even, never a multiple of the 32 banks'
+  // period for the 32 consecutive rows of a warp: an unpadded pitch of 64 bytes made every read a 16-way conflict)
+  L.bias_off = L.sc_off + (uint32_t)((kRows * (num_groups | 1) * 2 + 127) & ~127);
   L.sa_off = L.bias_off + kRows * 4;
   L.bar_off = L.sa_off + (uint32_t)(nt * kBM * 4);
   L.misc_off = L.bar_off + 32 * 8;
@@ -77,12 +84,21 @@ __host__ __device__ inline GTmemLayout gtmem_layout(int nt, int act_stages, int 
   return L;
 }
 
+#ifdef SACQ_TRACE
+// Profiling builds only (-DSACQ_TRACE): CTA (0, 0) records %globaltimer at a few points per role.
+__device__ long long g_gtmem_trace[8][72];
+#define SACQ_GTR(role, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (slot) < 72) { long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_gtmem_trace[role][slot] = _t; } } while (0)
+#else
+#define SACQ_GTR(role, slot) do { } while (0)
+#endif
+
 // D in {4, 8}; NT = 128-token sub-tiles per CTA (1, 2 or 3).  grid = (ceil(N / 128), ceil(M / (128 * NT))).
 template <int D, int NT>
 __global__ void __launch_bounds__(kCtaThreads, 1)
 large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
                             const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ GTmemParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) SACQ_GTR(0, 0);
   constexpr int BT = kBM * NT;
   constexpr int IDX_PER_KB = kBKh / D;                // indices per row per K block
   constexpr int KB_PER_SB = kSbIdx / IDX_PER_KB;      // K blocks per index super-block
@@ -140,6 +156,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) SACQ_GTR(0, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -149,7 +166,9 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
           const int sb = kb / KB_PER_SB, slot = sb & 1;
           if (!mbar_wait(bar(IDX_EMPTY + slot), ((sb >> 1) & 1) ^ 1, abort_flag, p.status)) break;
           mbar_arrive_expect_tx(bar(IDX_FULL + slot), (uint32_t)(kRows * sb_bytes));
-          tma_load_2d(base + L.idx_off + slot * L.idx_slot, &tmap_idx, sb * sb_bytes, n0, bar(IDX_FULL + slot));
+          for (int sl = 0; sl < p.bits; ++sl)          // one 16-byte column slice of the 128 rows per copy
+            tma_load_2d(base + L.idx_off + slot * L.idx_slot + sl * (kRows * 16), &tmap_idx, sb * sb_bytes + sl * 16, n0,
+                        bar(IDX_FULL + slot));
         }
         const int st = kb % act_stages;
         if (!mbar_wait(bar(ACT_EMPTY + st), ((kb / act_stages) & 1) ^ 1, abort_flag, p.status)) break;
@@ -172,6 +191,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
              mbar_wait(bar(W_FULL + ws), (kb / kGWStages) & 1, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
+        SACQ_GTR(1, kb + 8);
         const uint32_t act_addr = base + L.act_off + st * L.act_stage;
         const uint32_t w_col = kWCol0 + (uint32_t)(ws * 32);
 #pragma unroll
@@ -207,10 +227,11 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
       const int n16 = (p.C * D * 2) >> 4;
       for (int i = et; i < n16; i += kXThreads) cp_async_16(dst + i, src + i);
       uint16_t* sc = reinterpret_cast<uint16_t*>(sm + L.sc_off);
+      const int sc_pitch = p.num_groups | 1;
       for (int i = et; i < kRows * p.num_groups; i += kXThreads) {
         const int r = i / p.num_groups, g = i - r * p.num_groups;
         const int n = min(n0 + r, p.out.N - 1);
-        sc[i] = __ldg(p.scales + (int64_t)n * p.num_groups + g);
+        sc[r * sc_pitch + g] = __ldg(p.scales + (int64_t)n * p.num_groups + g);
       }
       if (et < kRows) {
         const int n = min(n0 + et, p.out.N - 1);
@@ -222,9 +243,10 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
       }
       cp_async_wait_all();
       xbarrier();
+      if (et == 0) SACQ_GTR(0, 2);
     }
     const CwVec* cbs = reinterpret_cast<const CwVec*>(sm + L.cb_off);
-    const uint16_t* sc = reinterpret_cast<const uint16_t*>(sm + L.sc_off) + row * p.num_groups;
+    const uint16_t* sc = reinterpret_cast<const uint16_t*>(sm + L.sc_off) + row * (p.num_groups | 1);
     const uint32_t mask = (1u << p.bits) - 1u;
     const int kb_per_group = p.group_size / kBKh;
     bool ok = true;
@@ -236,17 +258,31 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
            mbar_wait(bar(W_EMPTY + ws), ((kb / kGWStages) & 1) ^ 1, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after();                              // the MMAs that read this stage are complete
+      if (warp == 2 && lane == 0) SACQ_GTR(2, kb + 8);
       // scale * 2^sc_exp_shift * 4096 is a bf16 significand with a small exponent: exact in fp16
       const __half sh = __float2half_rn(bf16_bits_to_float(sc[grp]) * p.scale_mul);
       const __half2 s2 = __half2half2(sh);
-      const uint32_t* w32 = reinterpret_cast<const uint32_t*>(sm + L.idx_off + slot * L.idx_slot + row * sb_bytes);
-      const int first = (kb % KB_PER_SB) * IDX_PER_KB + kpart * IPT;     // this thread's first index field
+      // this thread's IPT index fields: a window of at most 64 bits that starts at bit `bit0` of the row's
+      // super-block, i.e. in slice bit0 / 128 and possibly the next one; bit0 is the same for the whole warp
+      const int bit0 = ((kb % KB_PER_SB) * IDX_PER_KB + kpart * IPT) * p.bits;
+      const int sl0 = bit0 >> 7;
+      const uint8_t* slice = sm + L.idx_off + slot * L.idx_slot + row * 16;
+      const uint4 a = *reinterpret_cast<const uint4*>(slice + sl0 * (kRows * 16));
+      uint4 b = a;                                     // the next slice only when the window crosses into it
+      if ((bit0 & 127) + IPT * p.bits > 128) b = *reinterpret_cast<const uint4*>(slice + (sl0 + 1) * (kRows * 16));
+      uint32_t lo, mid, hi;
+      switch ((bit0 >> 5) & 3) {                       // first word of the window inside slice sl0 (warp-uniform)
+        case 0: lo = a.x; mid = a.y; hi = a.z; break;
+        case 1: lo = a.y; mid = a.z; hi = a.w; break;
+        case 2: lo = a.z; mid = a.w; hi = b.x; break;
+        default: lo = a.w; mid = b.x; hi = b.y; break;
+      }
+      const uint32_t wsh = (uint32_t)(bit0 & 31);
+      const uint64_t win = ((uint64_t)__funnelshift_r(mid, hi, wsh) << 32) | __funnelshift_r(lo, mid, wsh);
       uint32_t o[8];
 #pragma unroll
       for (int j = 0; j < IPT; ++j) {
-        const int bit = (first + j) * p.bits;
-        const uint64_t win = (((uint64_t)w32[(bit >> 5) + 1] << 32) | w32[bit >> 5]) >> (bit & 31);
-        const CwVec cw = cbs[(uint32_t)win & mask];
+        const CwVec cw = cbs[(uint32_t)(win >> (j * p.bits)) & mask];
         if constexpr (D == 8) {
           const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
@@ -264,9 +300,11 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         }
       }
       tmem_st_32x8(lane_addr + kWCol0 + (uint32_t)(ws * 32 + kpart * 8), o);
+      if (warp == 2 && lane == 0) SACQ_GTR(4, kb + 8);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
+      if (warp == 2 && lane == 0) SACQ_GTR(5, kb + 8);
       if (lane == 0) {
         mbar_arrive(bar(W_FULL + ws));
         if ((kb + 1) % KB_PER_SB == 0 || kb == num_kb - 1) mbar_arrive(bar(IDX_EMPTY + slot));
@@ -276,6 +314,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
 
     // ---- epilogue
     if (ok) ok = mbar_wait(bar(ACC_FULL), 0, abort_flag, p.status);
+    if (warp == 2 && lane == 0) SACQ_GTR(0, 3);
     ok = xall(ok);                                    // tcgen05.ld and the staging barriers are collective
     if (ok) {
       tc_fence_after();
@@ -288,6 +327,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   // ---- common exit: every thread arrives here, also after an aborted wait
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) SACQ_GTR(0, 4);
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
@@ -366,14 +406,11 @@ bool large_m_tmem_grouped_supported(const sacq_layer* L) {
   return g_act_stages(L, 1) >= 2;
 }
 
-// From how many tokens this kernel beats the shared-memory-tile kernel of linear_large_m_grouped.cu:
-// once its 128-row x 384-token tiles fill about one wave (measured: 2048x6144 from 1024 tokens,
-// 2048x2048 and 6144x2048 from about 3000).
+// From how many tokens this kernel beats the shared-memory-tile kernel of linear_large_m_grouped.cu
+// (measured at d = 4, 10-bit, group 64: 2048x6144 27.6 against 33.1 us at M = 300 and 37 against 66 us
+// at M = 1024; 2048x2048 and 6144x2048 break even at M = 1024 and win 1.5-1.9x from M = 4096).
 int64_t large_m_tmem_grouped_min_m(const sacq_layer* L) {
-  const int64_t row_tiles = (L->d.out_features + kRows - 1) / kRows;
-  const int64_t token_tiles = (L->num_sms * 9 / 10 + row_tiles - 1) / row_tiles;
-  const int64_t m = (token_tiles - 1) * 3 * kBM + 1;
-  return m < 1024 ? 1024 : m;
+  return L->d.out_features >= 5120 ? 288 : 1024;
 }
 
 // Workspace behind the counter region: the fp16 activations of one token slab.
@@ -433,9 +470,11 @@ int launch_large_m_tmem_grouped(const sacq_layer* L, const void* q, const float*
         if (g_act_stages(L, cand) < 2) continue;
         const int64_t tiles = row_tiles * ((rows + kBM * cand - 1) / (kBM * cand));
         const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
-        // measured: a CTA's time barely depends on its token count (about 40 us at K = 2048: the index
-        // extraction of the expanders bounds it), so the fewest waves win and ties go to the larger tile
-        const double cost = (double)waves * (3.5 + (double)K / 2048.0 * 38.0);
+        // measured per wave at K = 2048 (d = 4, 10-bit, group 64), widening pre-pass and launch included:
+        // 27.6 / 33 / 37 us for 1 / 2 / 3 sub-tiles; two sub-tiles lose more than the others once waves queue
+        // (42 us per wave), so they are only chosen where they save a wave outright
+        const double per_wave = cand == 3 ? 32.0 : cand == 2 ? (waves == 1 ? 28.0 : 37.0) : 22.6;
+        const double cost = (double)waves * (5.0 + (double)K / 2048.0 * per_wave);
         if (cost < best - 1e-9) { best = cost; nt = cand; }
       }
     }
@@ -447,8 +486,7 @@ int launch_large_m_tmem_grouped(const sacq_layer* L, const void* q, const float*
                              CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SACQ_OK) return rc;
     const uint64_t row_bytes = (uint64_t)(L->row_bits / 8);
-    rc = encode_bytes_2d(&ti, d.packed, row_bytes, (uint64_t)N, row_bytes, (uint32_t)(16 * d.index_bits), (uint32_t)kRows,
-                         CU_TENSOR_MAP_SWIZZLE_NONE);
+    rc = encode_bytes_2d(&ti, d.packed, row_bytes, (uint64_t)N, row_bytes, 16u, (uint32_t)kRows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != SACQ_OK) return rc;
     uint16_t* y_slab = static_cast<uint16_t*>(y) + m0 * ldy;
     const bool y_tma = residual == nullptr && p.out.n_bc == 0 && reinterpret_cast<uintptr_t>(y_slab) % 16 == 0 &&
@@ -478,3 +516,9 @@ int launch_large_m_tmem_grouped(const sacq_layer* L, const void* q, const float*
 }
 
 }  // namespace sacq
+
+#ifdef SACQ_TRACE
+extern "C" SACQ_API int sacq_debug_gtmem_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, sacq::g_gtmem_trace, sizeof(long long) * 8 * 72) == cudaSuccess ? 0 : -1;
+}
+#endif
