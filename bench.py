@@ -259,25 +259,37 @@ class Ctx:
                     max_passes=2000):
         """Median seconds of one pass (= `replays_per_pass` replays rotating through `graphs`),
         CUDA events on the launching stream, barrier + synchronize on both sides of every pass."""
-        times, total, k = [], 0.0, 0
+        times, k = [], 0
+
+        def one_pass():
+            nonlocal k
+            self.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            for _ in range(replays_per_pass):
+                graphs[k % len(graphs)].replay()
+                k += 1
+            e1.record(self.stream)
+            self.stream.synchronize()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 1e3)
+
         with torch.cuda.stream(self.stream):
             for i in range(warmup):
                 graphs[i % len(graphs)].replay()
             self.stream.synchronize()
-            while len(times) < min_passes or (total < min_seconds and len(times) < max_passes):
-                self.barrier()
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(self.stream)
-                for _ in range(replays_per_pass):
-                    graphs[k % len(graphs)].replay()
-                    k += 1
-                e1.record(self.stream)
-                self.stream.synchronize()
-                torch.cuda.synchronize()
-                dt = e0.elapsed_time(e1) / 1e3
-                times.append(dt)
-                total += dt
+            for _ in range(min_passes):
+                one_pass()
+            # every rank runs the same number of further passes (each pass holds a barrier): the
+            # largest any rank needs to reach min_seconds of timed work
+            total = sum(times)
+            more = 0
+            if total < min_seconds:
+                more = min(max_passes - min_passes, int((min_seconds - total) / max(total / len(times), 1e-7)) + 1)
+            more = int(self.max_over_ranks([more])[0])
+            for _ in range(more):
+                one_pass()
         self.barrier()
         return statistics.median(times), len(times)
 
@@ -587,8 +599,10 @@ def gpu_main(args):
 
     for i in range(max(3, args.warmup)):
         e2e_step(sets[i % n_sets])
-    e2e_times, total, k = [], 0.0, 0
-    while len(e2e_times) < MIN_PASSES or total < MIN_TIMED_SECONDS:
+    e2e_times, k = [], 0
+
+    def e2e_pass():
+        nonlocal k
         torch.cuda.synchronize()
         ctx.barrier()
         t0 = time.perf_counter()
@@ -596,9 +610,14 @@ def gpu_main(args):
             e2e_step(sets[k % n_sets])
             k += 1
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        e2e_times.append(dt)
-        total += dt
+        e2e_times.append(time.perf_counter() - t0)
+
+    for _ in range(MIN_PASSES):
+        e2e_pass()
+    total = sum(e2e_times)
+    more = 0 if total >= MIN_TIMED_SECONDS else int((MIN_TIMED_SECONDS - total) / (total / len(e2e_times))) + 1
+    for _ in range(int(ctx.max_over_ranks([min(more, 2000)])[0])):      # the same count on every rank: each pass holds a barrier
+        e2e_pass()
     sec_e2e = statistics.median(e2e_times)
     sec, sec_gemm, sec_e2e = ctx.max_over_ranks([sec, sec_gemm, sec_e2e])
 

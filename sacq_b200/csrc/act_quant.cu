@@ -35,7 +35,7 @@ template <bool VEC, bool I8 = false>
 __global__ void __launch_bounds__(kThreads)
 quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, uint8_t* __restrict__ q,
                      float* __restrict__ scale_out) {
-  __shared__ float red[kThreads / 32];
+  __shared__ uint32_t red[kThreads / 32];
   __shared__ float s_scale;
   SACQ_TL_BEGIN(1);
   // A GEMM launched with programmatic stream serialization may start its prologue now; it
@@ -51,7 +51,7 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
   uint8_t* qrow = q + m * K;
   const int tid = threadIdx.x;
 
-  float mx = 0.f;
+  uint32_t mx = 0u;                                  // bit pattern of the running |x| maximum (absmax_bits)
   uint4 keep[kMaxChunksPerThread];
   const int64_t chunks = VEC ? (K >> 3) : 0;
   if constexpr (VEC) {
@@ -63,8 +63,8 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
       const uint32_t w[4] = {keep[c].x, keep[c].y, keep[c].z, keep[c].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] & 0xffff)));
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] >> 16)));
+        mx = absmax_bits(mx, bf16_bits_to_float(w[j] & 0xffff));
+        mx = absmax_bits(mx, bf16_bits_to_float(w[j] >> 16));
       }
     }
     for (int64_t ch = tid + (int64_t)kMaxChunksPerThread * kThreads; ch < chunks; ch += kThreads) {
@@ -72,20 +72,21 @@ quant_act_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, int64_t K, u
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] & 0xffff)));
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[j] >> 16)));
+        mx = absmax_bits(mx, bf16_bits_to_float(w[j] & 0xffff));
+        mx = absmax_bits(mx, bf16_bits_to_float(w[j] >> 16));
       }
     }
   } else {
-    for (int64_t k = tid; k < K; k += kThreads) mx = fmaxf(mx, fabsf(bf16_bits_to_float(__ldg(row + k))));
+    for (int64_t k = tid; k < K; k += kThreads) mx = absmax_bits(mx, bf16_bits_to_float(__ldg(row + k)));
   }
-  mx = warp_max(mx);
+  mx = warp_max_bits(mx);
   if ((tid & 31) == 0) red[tid >> 5] = mx;
   __syncthreads();
   if (tid < 32) {
-    float v = tid < kThreads / 32 ? red[tid] : 0.f;
-    v = warp_max(v);
+    const float v = __uint_as_float(warp_max_bits(tid < kThreads / 32 ? red[tid] : 0u));
     if (tid == 0) {
+      // a NaN maximum fails `> 0` like in the reference's torch.where: the row keeps scale 1 and its
+      // NaN elements stay NaN; an infinite maximum gives an infinite scale
       const float s = v > 0.f ? __fdiv_rn(v, I8 ? 127.0f : kE4M3Max) : 1.0f;
       s_scale = s;
       scale_out[m] = s;
@@ -212,14 +213,14 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
                      const uint16_t* __restrict__ c, int64_t K, uint8_t* __restrict__ q,
                      float* __restrict__ scale_out) {
   extern __shared__ __align__(16) uint16_t yrow[];    // the row's bf16 values, kept on chip between the passes
-  __shared__ float red[kThreads / 32];
+  __shared__ uint32_t red[kThreads / 32];
   __shared__ float s_scale;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // launched behind the producer of a / b with programmatic serialization
   const int64_t m = blockIdx.x;
   const uint16_t* arow = a + m * a_pitch;
   const uint16_t* brow = KIND == 1 ? nullptr : b + m * b_pitch;      // pitch 0: one vector for every row
-  float mx = 0.f;
+  uint32_t mx = 0u;                                  // bit pattern of the running maximum (absmax_bits)
   if constexpr (VEC) {
     for (int64_t ch = threadIdx.x; ch < (K >> 3); ch += kThreads) {
       const uint4 a4 = __ldg(reinterpret_cast<const uint4*>(arow) + ch);
@@ -235,7 +236,7 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
                                          bf16_bits_to_float(cw[j] & 0xffff));
         const float y1 = act_value<KIND>(bf16_bits_to_float(aw[j] >> 16), bf16_bits_to_float(bw[j] >> 16),
                                          bf16_bits_to_float(cw[j] >> 16));
-        mx = fmaxf(mx, fmaxf(fabsf(y0), fabsf(y1)));
+        mx = absmax_bits(absmax_bits(mx, y0), y1);
         o[j] = (uint32_t)float_to_bf16_bits(y0) | ((uint32_t)float_to_bf16_bits(y1) << 16);
       }
       reinterpret_cast<uint4*>(yrow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -247,15 +248,14 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
       const float cv = KIND == 2 ? bf16_bits_to_float(__ldg(c + k)) : 0.f;
       const float y = act_value<KIND>(av, bv, cv);
       yrow[k] = float_to_bf16_bits(y);
-      mx = fmaxf(mx, fabsf(y));
+      mx = absmax_bits(mx, y);
     }
   }
-  mx = warp_max(mx);
+  mx = warp_max_bits(mx);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
   __syncthreads();
   if (threadIdx.x < 32) {
-    float v = threadIdx.x < kThreads / 32 ? red[threadIdx.x] : 0.f;
-    v = warp_max(v);
+    const float v = __uint_as_float(warp_max_bits(threadIdx.x < kThreads / 32 ? red[threadIdx.x] : 0u));
     if (threadIdx.x == 0) {
       const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
       s_scale = s;
@@ -397,7 +397,7 @@ layernorm_quant_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, const 
   }
   const float var = block_sum(sq, red) / (float)K;
   const float rstd = 1.0f / sqrtf(var + eps);
-  float mx = 0.f;
+  uint32_t mx = 0u;                                  // bit pattern of the running maximum (absmax_bits)
   for (int64_t k = threadIdx.x; k < K; k += kThreads) {
     float y = (xrow[k] - mean) * rstd;
     if (gamma != nullptr) y = y * bf16_bits_to_float(__ldg(gamma + k));
@@ -408,16 +408,17 @@ layernorm_quant_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, const 
                      bf16_bits_to_float(__ldg(mod_shift + k)));
     xrow[k] = y;
     if (y_out != nullptr) y_out[m * y_pitch + k] = float_to_bf16_bits(y);
-    mx = fmaxf(mx, fabsf(y));
+    mx = absmax_bits(mx, y);
   }
   // absmax over the CTA (max is order-independent)
-  mx = warp_max(mx);
+  mx = warp_max_bits(mx);
   __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = __uint_as_float(mx);
   __syncthreads();
-  float v = 0.f;
+  uint32_t vb = 0u;
 #pragma unroll
-  for (int i = 0; i < kThreads / 32; ++i) v = fmaxf(v, red[i]);
+  for (int i = 0; i < kThreads / 32; ++i) vb = max(vb, __float_as_uint(red[i]));
+  const float v = __uint_as_float(vb);
   const float s = v > 0.f ? __fdiv_rn(v, kE4M3Max) : 1.0f;
   if (threadIdx.x == 0) scale_out[m] = s;
   uint8_t* qrow = q + m * K;

@@ -178,7 +178,17 @@ __device__ __forceinline__ uint32_t float2_to_e4m3x2(float lo, float hi) {
   return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
 }
 
-__device__ __forceinline__ float clamp448(float v) { return fminf(fmaxf(v, -kE4M3Max), kE4M3Max); }
+// clamp(v, -448, 448) that keeps a NaN a NaN, as torch.clamp does (fminf / fmaxf would drop it).
+__device__ __forceinline__ float clamp448(float v) { return v != v ? v : fminf(fmaxf(v, -kE4M3Max), kE4M3Max); }
+
+// Running |v| maximum on bit patterns: among non-negative floats integer order is float order, infinity
+// is above every finite value and every NaN above infinity, so a NaN (or an infinity) in a row survives
+// the reduction the way it does in torch's amax, where fmaxf would drop it.
+__device__ __forceinline__ uint32_t absmax_bits(uint32_t mx, float v) {
+  const uint32_t b = __float_as_uint(v) & 0x7fffffffu;
+  return b > mx ? b : mx;
+}
+__device__ __forceinline__ uint32_t warp_max_bits(uint32_t v) { return __reduce_max_sync(0xffffffffu, v); }
 
 // Index `i` of a little-endian bit stream of `bits`-wide fields, read through
 // aligned 32-bit words (bits <= 24).  `words` must be readable one word past

@@ -48,8 +48,10 @@ using namespace umma;
 using namespace tmemw;
 
 constexpr int kBK = 128;             // e4m3 bytes per K block (one 128-byte swizzle row)
-constexpr int kMaxActStages = 4;
+constexpr int kMaxActStages = 6;
 constexpr int kMaxWStages = 4;
+constexpr int kPairTok = 96;            // tokens of each N = 192 instruction that one CTA of a pair holds
+constexpr bool kPairByDefault = false;   // CTA pairs for the three-sub-tile shape without being asked
 struct TmemParams {
   const uint8_t* cb_hilo;       // [C][2][D] e4m3
   const uint16_t* scales;       // bf16 [N]
@@ -72,10 +74,11 @@ struct TmemLayout {
   uint32_t act_off, act_stage, idx_off, idx_slot, cb_off, sw_off, bias_off, sa_off, bar_off, misc_off, total;
 };
 
-__host__ __device__ inline TmemLayout tmem_layout(int nt, int act_stages, int sb_bytes, int cb_bytes) {
+// pair: the CTA is one of a cta_group::2 pair and holds half of every activation tile
+__host__ __device__ inline TmemLayout tmem_layout(int nt, int act_stages, int sb_bytes, int cb_bytes, bool pair = false) {
   TmemLayout L;
   L.act_off = 0;
-  L.act_stage = (uint32_t)(nt * kTokTile);
+  L.act_stage = (uint32_t)(nt * kTokTile) / (pair ? 2u : 1u);
   L.idx_off = act_stages * L.act_stage;
   L.idx_slot = (uint32_t)(kRows * sb_bytes);
   L.cb_off = (L.idx_off + 2 * L.idx_slot + 127) & ~127u;
@@ -122,8 +125,13 @@ __device__ __forceinline__ void load_fields_w(const uint8_t* base, int first, ui
 // Profiling builds only (-DSACQ_TRACE): CTA (0, 0) records %globaltimer at a few points per role.
 __device__ long long g_tmem_trace[8][72];
 #define SACQ_TR(role, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (slot) < 72) { long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_tmem_trace[role][slot] = _t; } } while (0)
+// Ablation switches of profiling builds (results are wrong with any of them set): 1 = no codeword gathers,
+// 2 = no tcgen05.st of the weights, 4 = activation tiles loaded for the first round of stages only, 8 = no MMAs.
+__device__ int g_tmem_ablate = 0;
+#define SACQ_ABLATE(bit) (g_tmem_ablate & (bit))
 #else
 #define SACQ_TR(role, slot) do { } while (0)
+#define SACQ_ABLATE(bit) false
 #endif
 
 // D in {4, 8}; BITS in {8, 12, 16}; NT = 128-token sub-tiles per CTA (1, 2 or 3); CB_SMEM: the
@@ -131,28 +139,53 @@ __device__ long long g_tmem_trace[8][72];
 // gathered from global memory, where it stays L2-resident.
 // grid = (ceil(N / 128), ceil(M / (128 * NT))).  The last token tile may hold fewer valid
 // sub-tiles: only those are loaded and multiplied.
-template <int D, int BITS, int NT, bool CB_SMEM>
+//
+// PAIR (NT = 3 only; launched as clusters of two CTAs along x, grid.x even): the two CTAs of a
+// cluster form a cta_group::2 pair.  Each keeps its own 128 weight rows in its own TMEM and its
+// own 128 x 384 accumulator, but every activation tile is shared: CTA r loads tokens
+// [96 r, 96 r + 96) of the first 192 and [192 + 96 r, 192 + 96 r + 96) of the last 192, and
+// the pair's MMAs (M = 256: 128 rows in each CTA; two of N = 192), issued by one thread
+// of the leader CTA (rank 0), read both halves.  Per CTA that halves the shared-memory reads of
+// the activation operand and the TMA writes, which is what bounds the single-CTA kernel.  The
+// leader's ACT_FULL barrier counts the bytes of both CTAs' loads, its W_FULL barrier the
+// expander warps of both CTAs (the peer's arrive over the cluster), and the MMA completions
+// are committed to the barriers of both CTAs.
+template <int D, int BITS, int NT, bool CB_SMEM, bool PAIR>
 __global__ void __launch_bounds__(kCtaThreads, 1)
-large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
-                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ TmemParams p) {
+large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_ah,
+                    const __grid_constant__ CUtensorMap tmap_idx, const __grid_constant__ CUtensorMap tmap_y,
+                    const __grid_constant__ TmemParams p) {
+  static_assert(!PAIR || NT == 3, "CTA pairs run the three-sub-tile shape only");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int BT = kBM * NT;                        // tokens per CTA = accumulator columns
   constexpr int IDX_PER_KB = kBK / D;                 // indices per row per K block
   constexpr int KB_BYTES = IDX_PER_KB * BITS / 8;     // index bytes per row per K block
   constexpr int SB_BYTES = 2 * KB_BYTES;              // ... per super block (two K blocks): multiple of 16
   constexpr int CW_BYTES = 2 * D;                     // hi + lo bytes per codeword
-  constexpr int IPT = IDX_PER_KB / 4;                 // indices per expander thread per K block (a quarter row)
+  // A TMEM weight stage holds W_K k of the 128 rows.  Half-block stages (W_K = 64, four of them beside
+  // a 384-column accumulator instead of two whole blocks) were measured SLOWER (2048x6144 at M = 8192:
+  // 217 against 183 us): the per-stage cost of the expanders (barrier waits, tcgen05.wait::st, fences)
+  // does not shrink with the stage.
+  constexpr int W_K = 128;
+  constexpr int WPB = kBK / W_K;                      // weight stages per K block
+  constexpr int W_COLS = W_K / 2;                     // TMEM columns of a stage: W_K / 4 high + W_K / 4 low
+  constexpr int WQ = W_K / 16;                        // 32-bit words a thread writes per half (4 or 8)
+  constexpr int IPT = (W_K / D) / 4;                  // indices per expander thread per weight stage (a quarter row)
   constexpr int kWStages = NT == 3 ? 2 : kMaxWStages; // TMEM weight stages
   constexpr uint32_t kWCol0 = BT;                     // first weight-stage column
   constexpr uint32_t kTmemCols = 512;
-  static_assert(BT + kWStages * 64 <= 512, "TMEM budget");
-  constexpr uint32_t kIdesc256 = make_idesc(256), kIdesc128 = make_idesc(128);
+  static_assert(BT + kWStages * W_COLS <= 512, "TMEM budget");
+  // a pair's MMA spans both CTAs: M = 256 in the descriptor (bit 24 up: M / 16)
+  constexpr uint32_t kPairM = PAIR ? ((uint32_t)(kBM >> 4) << 24) : 0u;
+  constexpr uint32_t kIdesc256 = make_idesc(256) + kPairM, kIdesc128 = make_idesc(128) + kPairM,
+                     kIdesc192 = make_idesc(192) + kPairM;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
-  const TmemLayout L = tmem_layout(NT, p.act_stages, SB_BYTES, CB_SMEM ? p.C * CW_BYTES : 0);
+  const TmemLayout L = tmem_layout(NT, p.act_stages, SB_BYTES, CB_SMEM ? p.C * CW_BYTES : 0, PAIR);
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;      // 0 = the pair's leader
 
   // barrier indices
   constexpr int ACT_FULL = 0, ACT_EMPTY = kMaxActStages, W_FULL = 2 * kMaxActStages,
@@ -169,7 +202,8 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int num_kb = p.K / kBK;
   const int act_stages = p.act_stages;
   const uint32_t cb_bytes = (uint32_t)(p.C * CW_BYTES);
-  const int nt_valid = min(NT, (p.M - m0 + kBM - 1) / kBM);       // sub-tiles of this CTA that hold tokens
+  // sub-tiles of this CTA that hold tokens (a pair always loads and multiplies all three: rows past M read as zero)
+  const int nt_valid = PAIR ? NT : min(NT, (p.M - m0 + kBM - 1) / kBM);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxActStages; ++i) {
@@ -177,7 +211,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(bar(ACT_EMPTY + i), 1);
     }
     for (int i = 0; i < kMaxWStages; ++i) {
-      mbar_init(bar(W_FULL + i), kXWarps);
+      mbar_init(bar(W_FULL + i), PAIR ? 2 * kXWarps : kXWarps);
       mbar_init(bar(W_EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -189,14 +223,20 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&tmap_a);
+    if (PAIR) prefetch_tensormap(&tmap_ah);
     prefetch_tensormap(&tmap_idx);
     if (p.y_tma) prefetch_tensormap(&tmap_y);
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);   // one warp of each CTA, collectively
+    else tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();            // both CTAs' barriers exist before either signals the other
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t leader_bars = PAIR ? map_to_cta(bars, 0) : bars;
   if (threadIdx.x == 0) SACQ_TR(0, 0);
 
   if (warp == 0) {
@@ -215,48 +255,86 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         const int st = kb % act_stages;
         if (!mbar_wait(bar(ACT_EMPTY + st), ((kb / act_stages) & 1) ^ 1, abort_flag, p.status)) break;
-        mbar_arrive_expect_tx(bar(ACT_FULL + st), nt_valid * kTokTile);
+        if (SACQ_ABLATE(4) && kb >= act_stages) {      // no loads: the stage keeps its first tile
+          if (!PAIR || cta_rank == 0) mbar_arrive(bar(ACT_FULL + st));
+          continue;
+        }
+        if constexpr (PAIR) {
+          // this CTA's halves of the pair's two activation tiles; the bytes of both CTAs count on the leader
+          const uint32_t full = leader_bars + 8u * (ACT_FULL + st);
+          if (cta_rank == 0) mbar_arrive_expect_tx(bar(ACT_FULL + st), NT * kTokTile);
+          const uint32_t dst = base + L.act_off + st * L.act_stage;
+          tma_load_2d_pair(dst, &tmap_ah, kb * kBK, m0 + (int)cta_rank * kPairTok, full);
+          tma_load_2d_pair(dst + kTokTile * 3 / 4, &tmap_ah, kb * kBK, m0 + 2 * kPairTok + (int)cta_rank * kPairTok, full);
+        } else {
+          mbar_arrive_expect_tx(bar(ACT_FULL + st), nt_valid * kTokTile);
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
-          if (t < nt_valid)
-            tma_load_2d(base + L.act_off + st * L.act_stage + t * kTokTile, &tmap_a, kb * kBK, m0 + t * kBM,
-                        bar(ACT_FULL + st));
+          for (int t = 0; t < NT; ++t)
+            if (t < nt_valid)
+              tma_load_2d(base + L.act_off + st * L.act_stage + t * kTokTile, &tmap_a, kb * kBK, m0 + t * kBM,
+                          bar(ACT_FULL + st));
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int st = kb % act_stages, ws = kb % kWStages;
-        ok = mbar_wait(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status) &&
-             mbar_wait(bar(W_FULL + ws), (kb / kWStages) & 1, abort_flag, p.status);
+      for (int wb = 0; wb < num_kb * WPB && ok; ++wb) {
+        const int kb = wb / WPB, sub = wb % WPB;       // K block and which part of it this weight stage holds
+        const int st = kb % act_stages, ws = wb % kWStages;
+        if constexpr (PAIR)
+          ok = (sub != 0 || mbar_wait_cluster(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status)) &&
+               mbar_wait_cluster(bar(W_FULL + ws), (wb / kWStages) & 1, abort_flag, p.status);
+        else
+          ok = (sub != 0 || mbar_wait(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status)) &&
+               mbar_wait(bar(W_FULL + ws), (wb / kWStages) & 1, abort_flag, p.status);
         if (!ok) break;
+#ifndef SACQ_EXP_NOFENCE
         tc_fence_after();
-        SACQ_TR(1, kb + 8);
+#endif
+        SACQ_TR(1, wb + 8);
         const uint32_t act_addr = base + L.act_off + st * L.act_stage;
-        const uint32_t w_col = kWCol0 + (uint32_t)(ws * 64);
+        const uint32_t w_col = kWCol0 + (uint32_t)(ws * W_COLS);
 #pragma unroll
-        for (int ks = 0; ks < kBK / 32; ++ks) {
+        for (int ksl = 0; ksl < W_K / 32; ++ksl) {
+          const int ks = sub * (W_K / 32) + ksl;       // 32-byte K step inside the 128-byte activation rows
           const uint64_t adv = (uint64_t)((ks * 32) >> 4);
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            const uint32_t a_tmem = tmem_base + w_col + (uint32_t)(half * 32 + ks * 8);
-            const uint32_t acc = (kb | ks | half) != 0;
-            if (NT >= 2 && nt_valid >= 2) {
+            if (SACQ_ABLATE(8)) continue;
+            const uint32_t a_tmem = tmem_base + w_col + (uint32_t)(half * (W_COLS / 2) + ksl * 8);
+            const uint32_t acc = (wb | ksl | half) != 0;
+            // 384 tokens go as two N = 192 instructions into two accumulators, not as N = 256 + N = 128: an
+            // instruction costs about the same 60 ns for any N from 128 to 256 (microbenchmark: the pair
+            // takes 114 against 126 ns), and consecutive instructions into ONE accumulator wait for each
+            // other (137 ns each), so the two accumulators alternate
+            if constexpr (PAIR) {
+              umma_f8_ts_pair(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc192, acc);
+              umma_f8_ts_pair(tmem_base + 192u, a_tmem, make_smem_desc(act_addr + kTokTile * 3 / 4) + adv, kIdesc192, acc);
+            } else if (NT == 3 && nt_valid == 3) {
+              umma_f8_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc192, acc);
+              umma_f8_ts(tmem_base + 192u, a_tmem, make_smem_desc(act_addr + kTokTile * 3 / 2) + adv, kIdesc192, acc);
+            } else if (NT >= 2 && nt_valid >= 2) {
               umma_f8_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc256, acc);
-              if (NT == 3 && nt_valid == 3)
-                umma_f8_ts(tmem_base + 256u, a_tmem, make_smem_desc(act_addr + 2 * kTokTile) + adv, kIdesc128, acc);
             } else {
               umma_f8_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc128, acc);
             }
           }
         }
-        umma_commit(bar(ACT_EMPTY + st));
-        umma_commit(bar(W_EMPTY + ws));
+        if constexpr (PAIR) {
+          if (sub == WPB - 1) umma_commit_pair(bar(ACT_EMPTY + st));
+          umma_commit_pair(bar(W_EMPTY + ws));
+        } else {
+          if (sub == WPB - 1) umma_commit(bar(ACT_EMPTY + st));
+          umma_commit(bar(W_EMPTY + ws));
+        }
       }
-      if (ok) umma_commit(bar(ACC_FULL));
+      if (ok) {
+        if constexpr (PAIR) umma_commit_pair(bar(ACC_FULL));
+        else umma_commit(bar(ACC_FULL));
+      }
     }
     __syncwarp();
   } else {
@@ -280,21 +358,26 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     const uint8_t* cbs = CB_SMEM ? sm + L.cb_off : p.cb_hilo;
     bool ok = CB_SMEM ? mbar_wait(bar(CB_FULL), 0, abort_flag, p.status) : true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
+    for (int wb = 0; wb < num_kb * WPB && ok; ++wb) {
+      const int kb = wb / WPB, sub = wb % WPB;
       const int sb = kb >> 1, slot = sb & 1;
-      const int ws = kb % kWStages;
-      ok = mbar_wait(bar(IDX_FULL + slot), (sb >> 1) & 1, abort_flag, p.status) &&
-           mbar_wait(bar(W_EMPTY + ws), ((kb / kWStages) & 1) ^ 1, abort_flag, p.status);
+      const int ws = wb % kWStages;
+      ok = (sub != 0 || mbar_wait(bar(IDX_FULL + slot), (sb >> 1) & 1, abort_flag, p.status)) &&
+           mbar_wait(bar(W_EMPTY + ws), ((wb / kWStages) & 1) ^ 1, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after();                              // the MMAs that read this stage are complete
-      if (warp == 2 && lane == 0) SACQ_TR(2, kb + 8);
+      if (warp == 2 && lane == 0) SACQ_TR(2, wb + 8);
       uint32_t idx[IPT];
-      load_fields_w<BITS, IPT>(sm + L.idx_off + slot * L.idx_slot + row * SB_BYTES + (kb & 1) * KB_BYTES,
+      load_fields_w<BITS, IPT>(sm + L.idx_off + slot * L.idx_slot + row * SB_BYTES + (kb & 1) * KB_BYTES +
+                                   sub * (KB_BYTES / WPB),
                                kpart * IPT, idx);
-      uint32_t hi[8], lo[8];
-      if constexpr (D == 8) {
+      uint32_t hi[WQ], lo[WQ];
+      if (SACQ_ABLATE(1)) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < WQ; ++j) { hi[j] = idx[j % IPT]; lo[j] = idx[j % IPT] >> 3; }
+      } else if constexpr (D == 8) {
+#pragma unroll
+        for (int j = 0; j < IPT; ++j) {
           const uint4 c = CB_SMEM ? *reinterpret_cast<const uint4*>(cbs + (size_t)idx[j] * 16)
                                   : __ldg(reinterpret_cast<const uint4*>(cbs + (size_t)idx[j] * 16));
           hi[2 * j] = c.x; hi[2 * j + 1] = c.y;
@@ -302,23 +385,29 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < IPT; ++j) {
           const uint2 c = CB_SMEM ? *reinterpret_cast<const uint2*>(cbs + (size_t)idx[j] * 8)
                                   : __ldg(reinterpret_cast<const uint2*>(cbs + (size_t)idx[j] * 8));
           hi[j] = c.x;
           lo[j] = c.y;
         }
       }
-      const uint32_t w_addr = lane_addr + kWCol0 + (uint32_t)(ws * 64 + kpart * 8);
-      tmem_st_32x8(w_addr, hi);
-      tmem_st_32x8(w_addr + 32u, lo);
+      // the thread's quarter of the stage's k: WQ columns of the high half, WQ of the low half
+      const uint32_t w_addr = lane_addr + kWCol0 + (uint32_t)(ws * W_COLS + kpart * WQ);
+      if (!SACQ_ABLATE(2)) {
+        tmem_st_32xn(w_addr, hi);
+        tmem_st_32xn(w_addr + (uint32_t)(W_COLS / 2), lo);
+      } else if (hi[0] + lo[WQ - 1] == 0x12345678u) {
+        p.status[0] = 99;                              // never true in practice: keeps the gathers alive
+      }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (warp == 2 && lane == 0) SACQ_TR(5, kb + 8);
+      if (warp == 2 && lane == 0) SACQ_TR(5, wb + 8);
       if (lane == 0) {
-        mbar_arrive(bar(W_FULL + ws));
-        if ((kb & 1) == 1 || kb == num_kb - 1) mbar_arrive(bar(IDX_EMPTY + slot));
+        if (PAIR && cta_rank != 0) mbar_arrive_cluster(leader_bars + 8u * (W_FULL + ws));
+        else mbar_arrive(bar(W_FULL + ws));
+        if (sub == WPB - 1 && ((kb & 1) == 1 || kb == num_kb - 1)) mbar_arrive(bar(IDX_EMPTY + slot));
       }
     }
 
@@ -343,7 +432,12 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) SACQ_TR(0, 4);
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if constexpr (PAIR) {
+    cluster_sync_all();                              // neither CTA frees TMEM or leaves while its peer still runs
+    if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+  } else {
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 int sb_bytes_of(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
@@ -358,40 +452,57 @@ size_t smem_request(const TmemLayout& lay) {
 // Codebooks up to 64 KB (high + low halves) are staged in shared memory, larger ones gathered from global memory.
 bool cb_in_smem(const sacq_layer* L) { return (size_t)L->cb_entries * L->d.vector_dim * 2 <= 64 * 1024; }
 
-int pick_act_stages(const sacq_layer* L, int nt) {
+int pick_act_stages(const sacq_layer* L, int nt, bool pair = false) {
   const int cb_bytes = cb_in_smem(L) ? L->cb_entries * L->d.vector_dim * 2 : 0;
-  for (int st = (nt == 3 ? 3 : kMaxActStages); st >= 2; --st)
-    if (tmem_layout(nt, st, sb_bytes_of(L), cb_bytes).total + 1024 <= 227 * 1024) return st;
+  for (int st = (pair ? kMaxActStages : nt == 3 ? 3 : 4); st >= 2; --st)
+    if (tmem_layout(nt, st, sb_bytes_of(L), cb_bytes, pair).total + 1024 <= 227 * 1024) return st;
   return 0;
 }
 
-template <int D, int BITS, int NT, bool CB_SMEM>
-cudaError_t launch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const TmemParams& p,
-                      dim3 grid, size_t smem, cudaStream_t s) {
+template <int D, int BITS, int NT, bool CB_SMEM, bool PAIR>
+cudaError_t launch_nt(const CUtensorMap& ta, const CUtensorMap& tah, const CUtensorMap& ti, const CUtensorMap& ty,
+                      const TmemParams& p, dim3 grid, size_t smem, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(large_m_tmem_kernel<D, BITS, NT, CB_SMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(large_m_tmem_kernel<D, BITS, NT, CB_SMEM, PAIR>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  large_m_tmem_kernel<D, BITS, NT, CB_SMEM><<<grid, kCtaThreads, smem, s>>>(ta, ti, ty, p);
-  return cudaGetLastError();
+  if constexpr (PAIR) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kCtaThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, large_m_tmem_kernel<D, BITS, NT, CB_SMEM, PAIR>, ta, tah, ti, ty, p);
+  } else {
+    large_m_tmem_kernel<D, BITS, NT, CB_SMEM, PAIR><<<grid, kCtaThreads, smem, s>>>(ta, tah, ti, ty, p);
+    return cudaGetLastError();
+  }
 }
 
 template <int D, int BITS>
-cudaError_t launch_db(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const TmemParams& p, int nt,
-                      bool cb_smem, dim3 grid, size_t smem, cudaStream_t s) {
+cudaError_t launch_db(const CUtensorMap& ta, const CUtensorMap& tah, const CUtensorMap& ti, const CUtensorMap& ty,
+                      const TmemParams& p, int nt, bool cb_smem, bool pair, dim3 grid, size_t smem, cudaStream_t s) {
+  if (pair) return launch_nt<D, BITS, 3, true, true>(ta, tah, ti, ty, p, grid, smem, s);
   if (!cb_smem) {
-    if (nt == 3) return launch_nt<D, BITS, 3, false>(ta, ti, ty, p, grid, smem, s);
-    if (nt == 2) return launch_nt<D, BITS, 2, false>(ta, ti, ty, p, grid, smem, s);
-    return launch_nt<D, BITS, 1, false>(ta, ti, ty, p, grid, smem, s);
+    if (nt == 3) return launch_nt<D, BITS, 3, false, false>(ta, tah, ti, ty, p, grid, smem, s);
+    if (nt == 2) return launch_nt<D, BITS, 2, false, false>(ta, tah, ti, ty, p, grid, smem, s);
+    return launch_nt<D, BITS, 1, false, false>(ta, tah, ti, ty, p, grid, smem, s);
   }
-  if (nt == 3) return launch_nt<D, BITS, 3, true>(ta, ti, ty, p, grid, smem, s);
-  if (nt == 2) return launch_nt<D, BITS, 2, true>(ta, ti, ty, p, grid, smem, s);
-  return launch_nt<D, BITS, 1, true>(ta, ti, ty, p, grid, smem, s);
+  if (nt == 3) return launch_nt<D, BITS, 3, true, false>(ta, tah, ti, ty, p, grid, smem, s);
+  if (nt == 2) return launch_nt<D, BITS, 2, true, false>(ta, tah, ti, ty, p, grid, smem, s);
+  return launch_nt<D, BITS, 1, true, false>(ta, tah, ti, ty, p, grid, smem, s);
 }
 
 }  // namespace
@@ -399,6 +510,9 @@ cudaError_t launch_db(const CUtensorMap& ta, const CUtensorMap& ti, const CUtens
 #ifdef SACQ_TRACE
 extern "C" SACQ_API int sacq_debug_tmem_trace(long long* out) {
   return cudaMemcpyFromSymbol(out, g_tmem_trace, sizeof(long long) * 8 * 72) == cudaSuccess ? 0 : -1;
+}
+extern "C" SACQ_API int sacq_debug_tmem_ablate(int flags) {
+  return cudaMemcpyToSymbol(g_tmem_ablate, &flags, sizeof(int)) == cudaSuccess ? 0 : -1;
 }
 #endif
 
@@ -424,10 +538,11 @@ int large_m_tmem_pick_nt(const sacq_layer* L, int64_t M) {
     if (pick_act_stages(L, nt) < 2) continue;
     const int64_t tiles = row_tiles * ((M + kBM * nt - 1) / (kBM * nt));
     const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
-    // per-CTA time model (us at K = 2048): fixed 3.5 + mainloop: the MMA time of nt sub-tiles, or
-    // the gather time of the expanders, whichever is longer
-    const double mma = 4.2 * nt, gather = 6.5;
-    const double cost = (double)waves * (3.5 + (double)L->d.in_features / 2048.0 * (mma > gather ? mma : gather));
+    // whole waves x time of one CTA, fitted to measurements of 2048x6144, 2048x2048 and 6144x2048 at
+    // 1,024 - 8,192 tokens (us; k = K / 2048): 3.5 + 6.5 k, 5.6 + 13.5 k and 5.4 + 17.2 k for 1, 2, 3 sub-tiles
+    const double k = (double)L->d.in_features / 2048.0;
+    const double per_cta = nt == 3 ? 5.4 + 17.2 * k : nt == 2 ? 5.6 + 13.5 * k : 3.5 + 6.5 * k;
+    const double cost = (double)waves * per_cta;
     if (cost < best_cost - 1e-9) { best_cost = cost; best = nt; }
   }
   return best;
@@ -441,13 +556,25 @@ int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, 
   if (M > (1 << 30)) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld too large", (long long)M);
   if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
     return set_error(SACQ_ERR_ALIGNMENT, "quantized activations must be 16-byte aligned");
-  int nt = nt_force > 0 ? nt_force : large_m_tmem_pick_nt(L, M);
+  // nt_force: 1..3 fix the sub-tiles of the single-CTA kernel, 4 asks for CTA pairs, 0 chooses
+  const bool want_pair = nt_force == 4;
+  int nt = want_pair ? 3 : nt_force > 0 ? nt_force : large_m_tmem_pick_nt(L, M);
   if (nt < 1 || nt > 3) return set_error(SACQ_ERR_UNSUPPORTED, "TMEM-weight kernel: no tile shape fits");
-  const int act_stages = pick_act_stages(L, nt);
+  const bool cb_smem = cb_in_smem(L);
+  const bool pair = (want_pair || (nt_force == 0 && nt == 3 && kPairByDefault)) && cb_smem &&
+                    pick_act_stages(L, 3, true) >= 2;
+  if (want_pair && !pair) return set_error(SACQ_ERR_UNSUPPORTED, "TMEM-weight kernel: CTA pairs cannot run this layer");
+  const int act_stages = pick_act_stages(L, nt, pair);
   if (act_stages < 2) return set_error(SACQ_ERR_UNSUPPORTED, "TMEM-weight kernel: shared memory too small for %d sub-tiles", nt);
   CUtensorMap ta;
   {
     const int rc = encode_bytes_2d(&ta, q, (uint64_t)d.in_features, (uint64_t)M, (uint64_t)d.in_features, kBK, kBM,
+                                   CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SACQ_OK) return rc;
+  }
+  CUtensorMap tah = ta;                              // the 96-token tile a CTA of a pair loads
+  if (pair) {
+    const int rc = encode_bytes_2d(&tah, q, (uint64_t)d.in_features, (uint64_t)M, (uint64_t)d.in_features, kBK, kPairTok,
                                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SACQ_OK) return rc;
   }
@@ -483,19 +610,20 @@ int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, 
   p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features; p.C = L->cb_entries;
   p.act_stages = act_stages;
   p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
-  const bool cb_smem = cb_in_smem(L);
-  const TmemLayout lay = tmem_layout(nt, act_stages, sb_bytes_of(L), cb_smem ? L->cb_entries * d.vector_dim * 2 : 0);
+  const TmemLayout lay = tmem_layout(nt, act_stages, sb_bytes_of(L), cb_smem ? L->cb_entries * d.vector_dim * 2 : 0, pair);
   const size_t smem = smem_request(lay);
-  const dim3 grid((unsigned)((d.out_features + kRows - 1) / kRows), (unsigned)((M + kBM * nt - 1) / (kBM * nt)), 1);
+  unsigned row_tiles = (unsigned)((d.out_features + kRows - 1) / kRows);
+  if (pair) row_tiles = (row_tiles + 1u) & ~1u;       // whole pairs: a CTA past the last row loads zeros and stores nothing
+  const dim3 grid(row_tiles, (unsigned)((M + kBM * nt - 1) / (kBM * nt)), 1);
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   cudaError_t e;
   const int D = d.vector_dim, B = d.index_bits;
-  if (D == 8 && B == 12) e = launch_db<8, 12>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 8 && B == 8) e = launch_db<8, 8>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 8 && B == 16) e = launch_db<8, 16>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 4 && B == 12) e = launch_db<4, 12>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 4 && B == 8) e = launch_db<4, 8>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else e = launch_db<4, 16>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
+  if (D == 8 && B == 12) e = launch_db<8, 12>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
+  else if (D == 8 && B == 8) e = launch_db<8, 8>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
+  else if (D == 8 && B == 16) e = launch_db<8, 16>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
+  else if (D == 4 && B == 12) e = launch_db<4, 12>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
+  else if (D == 4 && B == 8) e = launch_db<4, 8>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
+  else e = launch_db<4, 16>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
   count_launch();
   if (e != cudaSuccess) return cuda_fail(e, "TMEM-weight large-M launch");
   return SACQ_OK;

@@ -106,7 +106,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   constexpr uint32_t kWCol0 = BT;
   constexpr uint32_t kTmemCols = 512;
   static_assert(BT + kGWStages * 32 <= 512, "TMEM budget");
-  constexpr uint32_t kIdesc256 = make_idesc(256), kIdesc128 = make_idesc(128);
+  constexpr uint32_t kIdesc256 = make_idesc(256), kIdesc128 = make_idesc(128), kIdesc192 = make_idesc(192);
   using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;
 
   extern __shared__ uint8_t smem_raw[];
@@ -199,10 +199,12 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
           const uint64_t adv = (uint64_t)((ks * 32) >> 4);              // 16 fp16 = 32 bytes per K step
           const uint32_t a_tmem = tmem_base + w_col + (uint32_t)(ks * 8);
           const uint32_t acc = (kb | ks) != 0;
-          if (NT >= 2 && nt_valid >= 2) {
+          if (NT == 3 && nt_valid == 3) {
+            // two N = 192 instructions into two accumulators (an instruction costs about 60 ns whatever its N)
+            umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc192, acc);
+            umma_f16_ts(tmem_base + 192u, a_tmem, make_smem_desc(act_addr + kTokTile * 3 / 2) + adv, kIdesc192, acc);
+          } else if (NT >= 2 && nt_valid >= 2) {
             umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc256, acc);
-            if (NT == 3 && nt_valid == 3)
-              umma_f16_ts(tmem_base + 256u, a_tmem, make_smem_desc(act_addr + 2 * kTokTile) + adv, kIdesc128, acc);
           } else {
             umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc128, acc);
           }

@@ -70,6 +70,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the SACQ reference tree")
     ap.add_argument("--only-int8", action="store_true", help="regenerate act_int8.npz only")
+    ap.add_argument("--only-nonfinite", action="store_true", help="regenerate act_nonfinite.npz only")
     args = ap.parse_args()
     ref = args.reference
     sys.path.insert(0, ref)
@@ -87,6 +88,23 @@ def main():
     perrow = load_by_path("ref_perrow", os.path.join(ref, SRC, "a8_accuracy_recovery_2026_10_20_r1",
                                                      "perrow_a8_candidate_r3.py"))
     rtn = load_by_path("ref_rtn", os.path.join(ref, SRC, "a8_rtn_r2.py"))
+
+    # ---- 0a. non-finite activations through the FP8 per-token quantizer: a row with a NaN keeps
+    # scale 1 (NaN > 0 is false in the reference's torch.where) and its NaN stays NaN; a row with an
+    # infinity gets an infinite scale, zeros for its finite elements and NaN for the infinite ones
+    xn = make_activations(6, 256, seed=902)
+    xn[1, 17] = float("nan")
+    xn[2, 40] = float("inf")
+    xn[3, 41] = float("-inf")
+    xn[4, 5] = float("nan")
+    xn[4, 77] = float("inf")
+    xn[4, 100] = 1000.0                                  # above the e4m3 range on a scale-1 row: clamps to 448
+    qn, sn = perrow.quantize_rows(xn, "fp8_e4m3fn")
+    np.savez_compressed(os.path.join(HERE, "act_nonfinite.npz"), x=bf16_bits(xn), q=e4m3_bits(qn),
+                        s=sn.numpy().astype(np.float32).view(np.uint32))
+    if args.only_nonfinite:
+        print("act_nonfinite.npz written")
+        return
 
     # ---- 0. INT8 per-token quantizer (the deployed recipe's activation format) ----
     # rows spanning magnitudes, an all-zero row, and rows built so that x/scale lands on

@@ -642,6 +642,26 @@ def test_activation_fused_into_quantizer(M, K):
         act_quantize_rows("silu_mul", a)
 
 
+def test_nonfinite_activations_are_not_hidden():
+    """NaN and infinite activations through the FP8 quantizer: bytes and scale bits of the fixture
+    generated by the reference's quantize_rows (a NaN keeps scale 1 and stays NaN, an infinity gives an
+    infinite scale).  NaN bytes are compared without their sign: inf / inf is a negative NaN on the CPU
+    that wrote the fixture and a positive one on the GPU."""
+    _need_gpu()
+    from sacq_b200 import quantize_rows
+    f = load_golden("act_nonfinite")
+    q, s = quantize_rows(from_bf16_bits(f["x"]).cuda())
+    got = q.view(torch.uint8).cpu().numpy()
+    canon = lambda b: np.where((b & 0x7F) == 0x7F, 0x7F, b)
+    assert np.array_equal(canon(got), canon(f["q"]))
+    assert np.array_equal(s.cpu().numpy().view(np.uint32).ravel(), f["s"].ravel())
+    # the fused producers use the same reduction: a NaN gate makes the row's scale 1, not a finite maximum
+    from sacq_b200 import act_quantize_rows
+    a = from_bf16_bits(f["x"]).cuda()
+    qa, sa = act_quantize_rows("gelu", a)
+    assert float(sa.reshape(-1)[1]) == 1.0 and int(qa.view(torch.uint8)[1, 17]) & 0x7F == 0x7F
+
+
 def test_int8_activation_quantizer():
     """quantize_rows(x, 'int8_symmetric'): bytes and scale bits of the reference fixture and of
     the oracle on larger and ragged inputs."""
@@ -896,7 +916,7 @@ def test_c_abi_error_codes_on_device():
     need = lib.sacq_workspace_bytes(mod._handle, 4)
     if need > lib.sacq_workspace_counter_bytes():
         assert lib.sacq_linear_a8(mod._handle, q.data_ptr(), s.data_ptr(), 4, y.data_ptr(), 64, None, 0, None) == -4
-    assert lib.sacq_layer_set_kernel(mod._handle, 16) == -1
+    assert lib.sacq_layer_set_kernel(mod._handle, 17) == -1
     assert lib.sacq_layer_set_kernel(mod._handle, 0) == 0
     assert lib.sacq_launch_count() > 0
     # misaligned packed pointer is refused at creation

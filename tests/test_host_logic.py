@@ -167,6 +167,8 @@ def test_c_abi_argument_errors_of_the_new_entry_points_without_gpu():
     assert lib.sacq_linear_a8_residual(None, None, None, 1, None, 0, None, 0, None, 0, None) == -1
     assert lib.sacq_peer_buffer_create(0, 0, None, None) == -1
     assert lib.sacq_workspace_bytes_int8(None, 4) == 0
+    assert lib.sacq_linear_a8_static_scratch(None, None, None, 0, None, 0, None) == -1      # null layer, whatever M is
+    assert "layer handle" in _lib.last_error()
     assert lib.sacq_act_quant_fp8(0, None, 0, None, 0, 0, 8, None, None, None) == 0      # M = 0 is a no-op
 
 

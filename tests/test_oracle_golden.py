@@ -121,6 +121,18 @@ def test_int8_activation_quantizer_matches_reference_fixture():
     assert list(q[5, 1:5]) == [0, 2, 2, 4] and float(s[1, 0]) == 1.0
 
 
+def test_nonfinite_activations_match_reference_fixture():
+    """A NaN in a row: scale 1 (the reference's `maximum > 0` is false for NaN) and the NaN stays a
+    NaN; an infinity: infinite scale, zeros for the finite elements, NaN for the infinite ones."""
+    f = load_golden("act_nonfinite")
+    with np.errstate(invalid="ignore"):
+        q, s = O.quantize_rows_e4m3(f["x"])
+    assert np.array_equal(s.view(np.uint32).ravel(), f["s"].ravel())
+    assert np.array_equal(q, f["q"])
+    assert f["q"][1, 17] & 0x7F == 0x7F and f["q"][2, 0] == 0 and f["q"][4, 100] == 0x7E
+    assert float(s[1, 0]) == 1.0 and np.isinf(s[2, 0]) and np.isinf(s[3, 0])
+
+
 def test_layernorm_reference_against_torch_cpu():
     """The float64 LayerNorm reference agrees with PyTorch's CPU LayerNorm to one bf16 ulp."""
     import torch

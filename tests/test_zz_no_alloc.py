@@ -60,3 +60,16 @@ def test_static_scratch_matches_workspace_entry_point_twice():
     rc = lib.sacq_linear_a8_static_scratch(layer._handle, q.data_ptr(), s.data_ptr(), big, out.data_ptr(), N, stream)
     assert rc == -4 and "built-in scratch" in _lib.last_error()
     assert layer.device_status() == 0
+
+    # argument checks: an empty batch is a no-op that touches nothing, a negative one, a null
+    # buffer, a short pitch and a null layer are refused before anything is launched
+    sentinel = out[:4].clone()
+    assert lib.sacq_linear_a8_static_scratch(layer._handle, None, None, 0, None, N, stream) == 0
+    assert lib.sacq_linear_a8_static_scratch(layer._handle, q.data_ptr(), s.data_ptr(), -1, out.data_ptr(), N, stream) == -1
+    assert lib.sacq_linear_a8_static_scratch(layer._handle, None, s.data_ptr(), 4, out.data_ptr(), N, stream) == -1
+    assert lib.sacq_linear_a8_static_scratch(layer._handle, q.data_ptr(), None, 4, out.data_ptr(), N, stream) == -1
+    assert lib.sacq_linear_a8_static_scratch(layer._handle, q.data_ptr(), s.data_ptr(), 4, None, N, stream) == -1
+    assert lib.sacq_linear_a8_static_scratch(layer._handle, q.data_ptr(), s.data_ptr(), 4, out.data_ptr(), N - 1, stream) == -1
+    assert lib.sacq_linear_a8_static_scratch(None, q.data_ptr(), s.data_ptr(), 4, out.data_ptr(), N, stream) == -1
+    torch.cuda.synchronize()
+    assert torch.equal(out[:4], sentinel) and layer.device_status() == 0
