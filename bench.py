@@ -486,7 +486,14 @@ def section_column_split(ctx):
     rows, all_equal = [], True
     ms = (1024, 8192)
     for K, N in ((2048, 6144), (6144, 2048)):
-        payload = make_payload(N, K, seed=1, iters=1, device=ctx.dev)
+        # ONE payload for all ranks: the k-means fit runs on the GPU with atomics, so two ranks fitting
+        # "the same" layer can differ in an index or a scale; rank 0 fits, everyone receives its bytes
+        box = [None]
+        if ctx.rank == 0:
+            made = make_payload(N, K, seed=1, iters=1, device=ctx.dev)
+            box[0] = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in made.items()}
+        dist.broadcast_object_list(box, src=0)
+        payload = box[0]
         bias = (torch.randn(N, generator=torch.Generator().manual_seed(6)) * 0.05).to(torch.bfloat16)
         whole = PrecomputedPackedVectorCodebookLinear(payload, bias, str(ctx.dev))
         gathered = ColumnParallelCodebookLinear(payload, bias, str(ctx.dev))

@@ -289,8 +289,8 @@ SACQ_API int64_t sacq_static_scratch_bytes(void);
  * without shared-memory staging, 6 = warp-MMA variant that unpacks the indices in shared memory
  * (any index width, any group size that is a multiple of 32), 7 = tensor-core kernel for grouped
  * scales, 8 = tensor-core kernel with the expanded weights in tensor memory (9, 10, 11: the same
- * with 1, 2, 3 token sub-tiles of 128 per CTA; 16: three sub-tiles on pairs of CTAs that share
- * every activation tile), 12 = that design for grouped scales (13, 14, 15: 1, 2, 3 sub-tiles).
+ * with 1, 2, 3 token sub-tiles of 128 per CTA), 12 = that design for grouped scales (13, 14, 15:
+ * 1, 2, 3 sub-tiles).
  * Returns SACQ_ERR_UNSUPPORTED from the next forward if the forced kernel cannot run the layer. */
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* layer, int which);
 /* Which kernel a forward with M rows would use (1 = small-M, 2 = tensor-core kernel with

@@ -76,7 +76,6 @@ constexpr int64_t kGroupedMinMInt8 = 48;
 
 int pick_kernel(const sacq_layer* L, int64_t M) {
   if (L->force_kernel == 7) return large_m_grouped_supported(L) ? 3 : SACQ_ERR_UNSUPPORTED;
-  if (L->force_kernel == 16) return large_m_tmem_supported(L) ? 4 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel >= 12) return large_m_tmem_grouped_supported(L) ? 5 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel >= 8) return large_m_tmem_supported(L) ? 4 : SACQ_ERR_UNSUPPORTED;
   if (L->force_kernel == 1 || L->force_kernel >= 3)
@@ -304,7 +303,7 @@ SACQ_API int sacq_modulate_quant_fp8(const void* x_bf16, int64_t x_pitch, const 
 
 SACQ_API int sacq_layer_set_kernel(sacq_layer_t* L, int which) {
   if (int rc = check_layer(L)) return rc;
-  if (which < 0 || which > 16) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..16", which);
+  if (which < 0 || which > 15) return set_error(SACQ_ERR_INVALID_ARGUMENT, "kernel selector %d not in 0..15", which);
   L->force_kernel = which;
   return SACQ_OK;
 }
@@ -347,7 +346,7 @@ int linear_a8_impl(const sacq_layer_t* L, const void* q, const float* scale, int
   if (k == 2) return launch_large_m(L, q, scale, M, y_out, ldy, s, residual, ldr, bc);
   if (k == 4)
     return launch_large_m_tmem(L, q, scale, M, y_out, ldy, s, residual, ldr, bc,
-                               L->force_kernel == 16 ? 4 : L->force_kernel >= 9 ? L->force_kernel - 8 : 0);
+                               L->force_kernel >= 9 ? L->force_kernel - 8 : 0);
   if (k == 3 || k == 5) {
     if (workspace == nullptr || workspace_bytes < kCounterBytes)
       return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given",

@@ -48,10 +48,8 @@ using namespace umma;
 using namespace tmemw;
 
 constexpr int kBK = 128;             // e4m3 bytes per K block (one 128-byte swizzle row)
-constexpr int kMaxActStages = 6;
+constexpr int kMaxActStages = 4;
 constexpr int kMaxWStages = 4;
-constexpr int kPairTok = 96;            // tokens of each N = 192 instruction that one CTA of a pair holds
-constexpr bool kPairByDefault = false;   // CTA pairs for the three-sub-tile shape without being asked
 struct TmemParams {
   const uint8_t* cb_hilo;       // [C][2][D] e4m3
   const uint16_t* scales;       // bf16 [N]
@@ -74,11 +72,10 @@ struct TmemLayout {
   uint32_t act_off, act_stage, idx_off, idx_slot, cb_off, sw_off, bias_off, sa_off, bar_off, misc_off, total;
 };
 
-// pair: the CTA is one of a cta_group::2 pair and holds half of every activation tile
-__host__ __device__ inline TmemLayout tmem_layout(int nt, int act_stages, int sb_bytes, int cb_bytes, bool pair = false) {
+__host__ __device__ inline TmemLayout tmem_layout(int nt, int act_stages, int sb_bytes, int cb_bytes) {
   TmemLayout L;
   L.act_off = 0;
-  L.act_stage = (uint32_t)(nt * kTokTile) / (pair ? 2u : 1u);
+  L.act_stage = (uint32_t)(nt * kTokTile);
   L.idx_off = act_stages * L.act_stage;
   L.idx_slot = (uint32_t)(kRows * sb_bytes);
   L.cb_off = (L.idx_off + 2 * L.idx_slot + 127) & ~127u;
@@ -139,23 +136,10 @@ __device__ int g_tmem_ablate = 0;
 // gathered from global memory, where it stays L2-resident.
 // grid = (ceil(N / 128), ceil(M / (128 * NT))).  The last token tile may hold fewer valid
 // sub-tiles: only those are loaded and multiplied.
-//
-// PAIR (NT = 3 only; launched as clusters of two CTAs along x, grid.x even): the two CTAs of a
-// cluster form a cta_group::2 pair.  Each keeps its own 128 weight rows in its own TMEM and its
-// own 128 x 384 accumulator, but every activation tile is shared: CTA r loads tokens
-// [96 r, 96 r + 96) of the first 192 and [192 + 96 r, 192 + 96 r + 96) of the last 192, and
-// the pair's MMAs (M = 256: 128 rows in each CTA; two of N = 192), issued by one thread
-// of the leader CTA (rank 0), read both halves.  Per CTA that halves the shared-memory reads of
-// the activation operand and the TMA writes, which is what bounds the single-CTA kernel.  The
-// leader's ACT_FULL barrier counts the bytes of both CTAs' loads, its W_FULL barrier the
-// expander warps of both CTAs (the peer's arrive over the cluster), and the MMA completions
-// are committed to the barriers of both CTAs.
-template <int D, int BITS, int NT, bool CB_SMEM, bool PAIR>
+template <int D, int BITS, int NT, bool CB_SMEM>
 __global__ void __launch_bounds__(kCtaThreads, 1)
-large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_ah,
-                    const __grid_constant__ CUtensorMap tmap_idx, const __grid_constant__ CUtensorMap tmap_y,
-                    const __grid_constant__ TmemParams p) {
-  static_assert(!PAIR || NT == 3, "CTA pairs run the three-sub-tile shape only");
+large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
+                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ TmemParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int BT = kBM * NT;                        // tokens per CTA = accumulator columns
   constexpr int IDX_PER_KB = kBK / D;                 // indices per row per K block
@@ -175,17 +159,13 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr uint32_t kWCol0 = BT;                     // first weight-stage column
   constexpr uint32_t kTmemCols = 512;
   static_assert(BT + kWStages * W_COLS <= 512, "TMEM budget");
-  // a pair's MMA spans both CTAs: M = 256 in the descriptor (bit 24 up: M / 16)
-  constexpr uint32_t kPairM = PAIR ? ((uint32_t)(kBM >> 4) << 24) : 0u;
-  constexpr uint32_t kIdesc256 = make_idesc(256) + kPairM, kIdesc128 = make_idesc(128) + kPairM,
-                     kIdesc192 = make_idesc(192) + kPairM;
+  constexpr uint32_t kIdesc256 = make_idesc(256), kIdesc128 = make_idesc(128), kIdesc192 = make_idesc(192);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
-  const TmemLayout L = tmem_layout(NT, p.act_stages, SB_BYTES, CB_SMEM ? p.C * CW_BYTES : 0, PAIR);
-  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;      // 0 = the pair's leader
+  const TmemLayout L = tmem_layout(NT, p.act_stages, SB_BYTES, CB_SMEM ? p.C * CW_BYTES : 0);
 
   // barrier indices
   constexpr int ACT_FULL = 0, ACT_EMPTY = kMaxActStages, W_FULL = 2 * kMaxActStages,
@@ -202,8 +182,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int num_kb = p.K / kBK;
   const int act_stages = p.act_stages;
   const uint32_t cb_bytes = (uint32_t)(p.C * CW_BYTES);
-  // sub-tiles of this CTA that hold tokens (a pair always loads and multiplies all three: rows past M read as zero)
-  const int nt_valid = PAIR ? NT : min(NT, (p.M - m0 + kBM - 1) / kBM);
+  const int nt_valid = min(NT, (p.M - m0 + kBM - 1) / kBM);       // sub-tiles of this CTA that hold tokens
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxActStages; ++i) {
@@ -211,7 +190,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(bar(ACT_EMPTY + i), 1);
     }
     for (int i = 0; i < kMaxWStages; ++i) {
-      mbar_init(bar(W_FULL + i), PAIR ? 2 * kXWarps : kXWarps);
+      mbar_init(bar(W_FULL + i), kXWarps);
       mbar_init(bar(W_EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -223,20 +202,14 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tensormap(&tmap_a);
-    if (PAIR) prefetch_tensormap(&tmap_ah);
     prefetch_tensormap(&tmap_idx);
     if (p.y_tma) prefetch_tensormap(&tmap_y);
   }
-  if (warp == 1) {
-    if constexpr (PAIR) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);   // one warp of each CTA, collectively
-    else tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
   __syncthreads();
-  if constexpr (PAIR) cluster_sync_all();            // both CTAs' barriers exist before either signals the other
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t leader_bars = PAIR ? map_to_cta(bars, 0) : bars;
   if (threadIdx.x == 0) SACQ_TR(0, 0);
 
   if (warp == 0) {
@@ -256,40 +229,27 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int st = kb % act_stages;
         if (!mbar_wait(bar(ACT_EMPTY + st), ((kb / act_stages) & 1) ^ 1, abort_flag, p.status)) break;
         if (SACQ_ABLATE(4) && kb >= act_stages) {      // no loads: the stage keeps its first tile
-          if (!PAIR || cta_rank == 0) mbar_arrive(bar(ACT_FULL + st));
+          mbar_arrive(bar(ACT_FULL + st));
           continue;
         }
-        if constexpr (PAIR) {
-          // this CTA's halves of the pair's two activation tiles; the bytes of both CTAs count on the leader
-          const uint32_t full = leader_bars + 8u * (ACT_FULL + st);
-          if (cta_rank == 0) mbar_arrive_expect_tx(bar(ACT_FULL + st), NT * kTokTile);
-          const uint32_t dst = base + L.act_off + st * L.act_stage;
-          tma_load_2d_pair(dst, &tmap_ah, kb * kBK, m0 + (int)cta_rank * kPairTok, full);
-          tma_load_2d_pair(dst + kTokTile * 3 / 4, &tmap_ah, kb * kBK, m0 + 2 * kPairTok + (int)cta_rank * kPairTok, full);
-        } else {
-          mbar_arrive_expect_tx(bar(ACT_FULL + st), nt_valid * kTokTile);
+        mbar_arrive_expect_tx(bar(ACT_FULL + st), nt_valid * kTokTile);
 #pragma unroll
-          for (int t = 0; t < NT; ++t)
-            if (t < nt_valid)
-              tma_load_2d(base + L.act_off + st * L.act_stage + t * kTokTile, &tmap_a, kb * kBK, m0 + t * kBM,
-                          bar(ACT_FULL + st));
-        }
+        for (int t = 0; t < NT; ++t)
+          if (t < nt_valid)
+            tma_load_2d(base + L.act_off + st * L.act_stage + t * kTokTile, &tmap_a, kb * kBK, m0 + t * kBM,
+                        bar(ACT_FULL + st));
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && cta_rank == 0) {
+    if (lane == 0) {
       bool ok = true;
       for (int wb = 0; wb < num_kb * WPB && ok; ++wb) {
         const int kb = wb / WPB, sub = wb % WPB;       // K block and which part of it this weight stage holds
         const int st = kb % act_stages, ws = wb % kWStages;
-        if constexpr (PAIR)
-          ok = (sub != 0 || mbar_wait_cluster(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status)) &&
-               mbar_wait_cluster(bar(W_FULL + ws), (wb / kWStages) & 1, abort_flag, p.status);
-        else
-          ok = (sub != 0 || mbar_wait(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status)) &&
-               mbar_wait(bar(W_FULL + ws), (wb / kWStages) & 1, abort_flag, p.status);
+        ok = (sub != 0 || mbar_wait(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status)) &&
+             mbar_wait(bar(W_FULL + ws), (wb / kWStages) & 1, abort_flag, p.status);
         if (!ok) break;
 #ifndef SACQ_EXP_NOFENCE
         tc_fence_after();
@@ -310,10 +270,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // instruction costs about the same 60 ns for any N from 128 to 256 (microbenchmark: the pair
             // takes 114 against 126 ns), and consecutive instructions into ONE accumulator wait for each
             // other (137 ns each), so the two accumulators alternate
-            if constexpr (PAIR) {
-              umma_f8_ts_pair(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc192, acc);
-              umma_f8_ts_pair(tmem_base + 192u, a_tmem, make_smem_desc(act_addr + kTokTile * 3 / 4) + adv, kIdesc192, acc);
-            } else if (NT == 3 && nt_valid == 3) {
+            if (NT == 3 && nt_valid == 3) {
               umma_f8_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc192, acc);
               umma_f8_ts(tmem_base + 192u, a_tmem, make_smem_desc(act_addr + kTokTile * 3 / 2) + adv, kIdesc192, acc);
             } else if (NT >= 2 && nt_valid >= 2) {
@@ -323,18 +280,10 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
         }
-        if constexpr (PAIR) {
-          if (sub == WPB - 1) umma_commit_pair(bar(ACT_EMPTY + st));
-          umma_commit_pair(bar(W_EMPTY + ws));
-        } else {
-          if (sub == WPB - 1) umma_commit(bar(ACT_EMPTY + st));
-          umma_commit(bar(W_EMPTY + ws));
-        }
+        if (sub == WPB - 1) umma_commit(bar(ACT_EMPTY + st));
+        umma_commit(bar(W_EMPTY + ws));
       }
-      if (ok) {
-        if constexpr (PAIR) umma_commit_pair(bar(ACC_FULL));
-        else umma_commit(bar(ACC_FULL));
-      }
+      if (ok) umma_commit(bar(ACC_FULL));
     }
     __syncwarp();
   } else {
@@ -405,8 +354,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (warp == 2 && lane == 0) SACQ_TR(5, wb + 8);
       if (lane == 0) {
-        if (PAIR && cta_rank != 0) mbar_arrive_cluster(leader_bars + 8u * (W_FULL + ws));
-        else mbar_arrive(bar(W_FULL + ws));
+        mbar_arrive(bar(W_FULL + ws));
         if (sub == WPB - 1 && ((kb & 1) == 1 || kb == num_kb - 1)) mbar_arrive(bar(IDX_EMPTY + slot));
       }
     }
@@ -424,7 +372,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const float sw = reinterpret_cast<const float*>(sm + L.sw_off)[row];
       const float bs = reinterpret_cast<const float*>(sm + L.bias_off)[row];
       tmem_epilogue<NT>(o, &tmap_y, lane_addr, row, kpart, et, reinterpret_cast<const float*>(sm + L.sa_off), sw, bs,
-                        sm + L.act_off, (act_stages * NT * kTokTile >= 2 * kStageTile) ? 2 : 1, m0, n0);
+                        sm + L.act_off, (act_stages * L.act_stage >= 2u * kStageTile) ? 2 : 1, m0, n0);
     }
   }
 
@@ -432,12 +380,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) SACQ_TR(0, 4);
-  if constexpr (PAIR) {
-    cluster_sync_all();                              // neither CTA frees TMEM or leaves while its peer still runs
-    if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
-  } else {
-    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
-  }
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 int sb_bytes_of(const sacq_layer* L) { return 2 * (kBK / L->d.vector_dim) * L->d.index_bits / 8; }
@@ -452,57 +395,40 @@ size_t smem_request(const TmemLayout& lay) {
 // Codebooks up to 64 KB (high + low halves) are staged in shared memory, larger ones gathered from global memory.
 bool cb_in_smem(const sacq_layer* L) { return (size_t)L->cb_entries * L->d.vector_dim * 2 <= 64 * 1024; }
 
-int pick_act_stages(const sacq_layer* L, int nt, bool pair = false) {
+int pick_act_stages(const sacq_layer* L, int nt) {
   const int cb_bytes = cb_in_smem(L) ? L->cb_entries * L->d.vector_dim * 2 : 0;
-  for (int st = (pair ? kMaxActStages : nt == 3 ? 3 : 4); st >= 2; --st)
-    if (tmem_layout(nt, st, sb_bytes_of(L), cb_bytes, pair).total + 1024 <= 227 * 1024) return st;
+  for (int st = (nt == 3 ? 3 : kMaxActStages); st >= 2; --st)
+    if (tmem_layout(nt, st, sb_bytes_of(L), cb_bytes).total + 1024 <= 227 * 1024) return st;
   return 0;
 }
 
-template <int D, int BITS, int NT, bool CB_SMEM, bool PAIR>
-cudaError_t launch_nt(const CUtensorMap& ta, const CUtensorMap& tah, const CUtensorMap& ti, const CUtensorMap& ty,
-                      const TmemParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+template <int D, int BITS, int NT, bool CB_SMEM>
+cudaError_t launch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const TmemParams& p,
+                      dim3 grid, size_t smem, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(large_m_tmem_kernel<D, BITS, NT, CB_SMEM, PAIR>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(large_m_tmem_kernel<D, BITS, NT, CB_SMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         227 * 1024);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  if constexpr (PAIR) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kCtaThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, large_m_tmem_kernel<D, BITS, NT, CB_SMEM, PAIR>, ta, tah, ti, ty, p);
-  } else {
-    large_m_tmem_kernel<D, BITS, NT, CB_SMEM, PAIR><<<grid, kCtaThreads, smem, s>>>(ta, tah, ti, ty, p);
-    return cudaGetLastError();
-  }
+  large_m_tmem_kernel<D, BITS, NT, CB_SMEM><<<grid, kCtaThreads, smem, s>>>(ta, ti, ty, p);
+  return cudaGetLastError();
 }
 
 template <int D, int BITS>
-cudaError_t launch_db(const CUtensorMap& ta, const CUtensorMap& tah, const CUtensorMap& ti, const CUtensorMap& ty,
-                      const TmemParams& p, int nt, bool cb_smem, bool pair, dim3 grid, size_t smem, cudaStream_t s) {
-  if (pair) return launch_nt<D, BITS, 3, true, true>(ta, tah, ti, ty, p, grid, smem, s);
+cudaError_t launch_db(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const TmemParams& p, int nt,
+                      bool cb_smem, dim3 grid, size_t smem, cudaStream_t s) {
   if (!cb_smem) {
-    if (nt == 3) return launch_nt<D, BITS, 3, false, false>(ta, tah, ti, ty, p, grid, smem, s);
-    if (nt == 2) return launch_nt<D, BITS, 2, false, false>(ta, tah, ti, ty, p, grid, smem, s);
-    return launch_nt<D, BITS, 1, false, false>(ta, tah, ti, ty, p, grid, smem, s);
+    if (nt == 3) return launch_nt<D, BITS, 3, false>(ta, ti, ty, p, grid, smem, s);
+    if (nt == 2) return launch_nt<D, BITS, 2, false>(ta, ti, ty, p, grid, smem, s);
+    return launch_nt<D, BITS, 1, false>(ta, ti, ty, p, grid, smem, s);
   }
-  if (nt == 3) return launch_nt<D, BITS, 3, true, false>(ta, tah, ti, ty, p, grid, smem, s);
-  if (nt == 2) return launch_nt<D, BITS, 2, true, false>(ta, tah, ti, ty, p, grid, smem, s);
-  return launch_nt<D, BITS, 1, true, false>(ta, tah, ti, ty, p, grid, smem, s);
+  if (nt == 3) return launch_nt<D, BITS, 3, true>(ta, ti, ty, p, grid, smem, s);
+  if (nt == 2) return launch_nt<D, BITS, 2, true>(ta, ti, ty, p, grid, smem, s);
+  return launch_nt<D, BITS, 1, true>(ta, ti, ty, p, grid, smem, s);
 }
 
 }  // namespace
@@ -539,9 +465,9 @@ int large_m_tmem_pick_nt(const sacq_layer* L, int64_t M) {
     const int64_t tiles = row_tiles * ((M + kBM * nt - 1) / (kBM * nt));
     const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
     // whole waves x time of one CTA, fitted to measurements of 2048x6144, 2048x2048 and 6144x2048 at
-    // 1,024 - 8,192 tokens (us; k = K / 2048): 3.5 + 6.5 k, 5.6 + 13.5 k and 5.4 + 17.2 k for 1, 2, 3 sub-tiles
+    // 1,024 - 8,192 tokens (us; k = K / 2048): 4.5 + 10 k, 5.6 + 13.5 k and 5.4 + 17.2 k for 1, 2, 3 sub-tiles
     const double k = (double)L->d.in_features / 2048.0;
-    const double per_cta = nt == 3 ? 5.4 + 17.2 * k : nt == 2 ? 5.6 + 13.5 * k : 3.5 + 6.5 * k;
+    const double per_cta = nt == 3 ? 5.4 + 17.2 * k : nt == 2 ? 5.6 + 13.5 * k : 4.5 + 10.0 * k;
     const double cost = (double)waves * per_cta;
     if (cost < best_cost - 1e-9) { best_cost = cost; best = nt; }
   }
@@ -556,25 +482,14 @@ int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, 
   if (M > (1 << 30)) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld too large", (long long)M);
   if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
     return set_error(SACQ_ERR_ALIGNMENT, "quantized activations must be 16-byte aligned");
-  // nt_force: 1..3 fix the sub-tiles of the single-CTA kernel, 4 asks for CTA pairs, 0 chooses
-  const bool want_pair = nt_force == 4;
-  int nt = want_pair ? 3 : nt_force > 0 ? nt_force : large_m_tmem_pick_nt(L, M);
+  int nt = nt_force > 0 ? nt_force : large_m_tmem_pick_nt(L, M);
   if (nt < 1 || nt > 3) return set_error(SACQ_ERR_UNSUPPORTED, "TMEM-weight kernel: no tile shape fits");
   const bool cb_smem = cb_in_smem(L);
-  const bool pair = (want_pair || (nt_force == 0 && nt == 3 && kPairByDefault)) && cb_smem &&
-                    pick_act_stages(L, 3, true) >= 2;
-  if (want_pair && !pair) return set_error(SACQ_ERR_UNSUPPORTED, "TMEM-weight kernel: CTA pairs cannot run this layer");
-  const int act_stages = pick_act_stages(L, nt, pair);
+  const int act_stages = pick_act_stages(L, nt);
   if (act_stages < 2) return set_error(SACQ_ERR_UNSUPPORTED, "TMEM-weight kernel: shared memory too small for %d sub-tiles", nt);
   CUtensorMap ta;
   {
     const int rc = encode_bytes_2d(&ta, q, (uint64_t)d.in_features, (uint64_t)M, (uint64_t)d.in_features, kBK, kBM,
-                                   CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != SACQ_OK) return rc;
-  }
-  CUtensorMap tah = ta;                              // the 96-token tile a CTA of a pair loads
-  if (pair) {
-    const int rc = encode_bytes_2d(&tah, q, (uint64_t)d.in_features, (uint64_t)M, (uint64_t)d.in_features, kBK, kPairTok,
                                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SACQ_OK) return rc;
   }
@@ -610,20 +525,18 @@ int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, 
   p.M = (int)M; p.N = (int)d.out_features; p.K = (int)d.in_features; p.C = L->cb_entries;
   p.act_stages = act_stages;
   p.out_mul = ldexpf(1.f, -L->cb8_exp_shift);
-  const TmemLayout lay = tmem_layout(nt, act_stages, sb_bytes_of(L), cb_smem ? L->cb_entries * d.vector_dim * 2 : 0, pair);
+  const TmemLayout lay = tmem_layout(nt, act_stages, sb_bytes_of(L), cb_smem ? L->cb_entries * d.vector_dim * 2 : 0);
   const size_t smem = smem_request(lay);
-  unsigned row_tiles = (unsigned)((d.out_features + kRows - 1) / kRows);
-  if (pair) row_tiles = (row_tiles + 1u) & ~1u;       // whole pairs: a CTA past the last row loads zeros and stores nothing
-  const dim3 grid(row_tiles, (unsigned)((M + kBM * nt - 1) / (kBM * nt)), 1);
+  const dim3 grid((unsigned)((d.out_features + kRows - 1) / kRows), (unsigned)((M + kBM * nt - 1) / (kBM * nt)), 1);
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   cudaError_t e;
   const int D = d.vector_dim, B = d.index_bits;
-  if (D == 8 && B == 12) e = launch_db<8, 12>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
-  else if (D == 8 && B == 8) e = launch_db<8, 8>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
-  else if (D == 8 && B == 16) e = launch_db<8, 16>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
-  else if (D == 4 && B == 12) e = launch_db<4, 12>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
-  else if (D == 4 && B == 8) e = launch_db<4, 8>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
-  else e = launch_db<4, 16>(ta, tah, *ti, ty, p, nt, cb_smem, pair, grid, smem, s);
+  if (D == 8 && B == 12) e = launch_db<8, 12>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
+  else if (D == 8 && B == 8) e = launch_db<8, 8>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
+  else if (D == 8 && B == 16) e = launch_db<8, 16>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
+  else if (D == 4 && B == 12) e = launch_db<4, 12>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
+  else if (D == 4 && B == 8) e = launch_db<4, 8>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
+  else e = launch_db<4, 16>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
   count_launch();
   if (e != cudaSuccess) return cuda_fail(e, "TMEM-weight large-M launch");
   return SACQ_OK;

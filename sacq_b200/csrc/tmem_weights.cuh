@@ -59,90 +59,6 @@ __device__ __forceinline__ void umma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       : "memory");
 }
 
-// ---- CTA pairs (cta_group::2): two CTAs of a cluster, 128 weight rows each in their own TMEM,
-// share every activation tile: each loads half of its tokens and the pair's MMA reads both halves.
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Address of `local` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// One arrival on an mbarrier of another CTA of the cluster (shared::cluster address).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait on a barrier that threads of the peer CTA arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (uint32_t it = 0;; ++it) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((it & 63) == 63) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > 2000000000ull) {
-        *abort_flag = 1;
-        atomicExch(status, kErrTimeout);
-        return false;
-      }
-    }
-  }
-}
-// Tile load into this CTA's shared memory whose bytes are counted on an mbarrier of the pair's
-// leader CTA (`bar_cluster`: a shared::cluster address).  No multicast: one destination.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-// Pair MMA issued by one thread of the leader CTA: D (128 lanes in each CTA) (+)= A (each CTA's
-// own TMEM) * B (N tokens, half of them in each CTA's shared memory at the same offset).
-__device__ __forceinline__ void umma_f8_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// One arrival on the mbarrier at this offset in BOTH CTAs of the pair once every MMA issued so far is done.
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-  const uint16_t mask = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"(mask)
-               : "memory");
-}
-
 // 8 consecutive 32-bit columns of the warp's TMEM lane quarter, one lane per thread.
 __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile(

@@ -427,7 +427,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         code = {"auto": 0, "small": 1, "large": 2, "small_simt": 3, "small_mma": 4, "small_mma_direct": 5,
                 "small_mma_unpacked": 6, "large_grouped": 7, "large_tmem": 8, "large_tmem1": 9,
                 "large_tmem2": 10, "large_tmem3": 11, "large_tmem_grouped": 12, "large_tmem_grouped1": 13,
-                "large_tmem_grouped2": 14, "large_tmem_grouped3": 15, "large_tmem_pair": 16}.get(which, which)
+                "large_tmem_grouped2": 14, "large_tmem_grouped3": 15}.get(which, which)
         _lib.check(self._lib.sacq_layer_set_kernel(self._handle, int(code)))
         self._ws_bytes.clear()
         self._host_bytes.clear()

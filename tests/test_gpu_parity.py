@@ -916,7 +916,7 @@ def test_c_abi_error_codes_on_device():
     need = lib.sacq_workspace_bytes(mod._handle, 4)
     if need > lib.sacq_workspace_counter_bytes():
         assert lib.sacq_linear_a8(mod._handle, q.data_ptr(), s.data_ptr(), 4, y.data_ptr(), 64, None, 0, None) == -4
-    assert lib.sacq_layer_set_kernel(mod._handle, 17) == -1
+    assert lib.sacq_layer_set_kernel(mod._handle, 16) == -1
     assert lib.sacq_layer_set_kernel(mod._handle, 0) == 0
     assert lib.sacq_launch_count() > 0
     # misaligned packed pointer is refused at creation
