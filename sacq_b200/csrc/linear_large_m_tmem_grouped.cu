@@ -19,9 +19,11 @@
 //     shared-memory store;
 //   * the fp16 activation tiles (e4m3 or int8 widened exactly by a pre-pass into the caller's
 //     workspace) are the MMA's B operand, TMA-loaded K-major / SWIZZLE_128B;
-//   * warp 1 issues tcgen05.mma.kind::f16 with A from TMEM: four K = 16 steps per 64-k block;
+//   * warp 1 issues tcgen05.mma.kind::f16 with A from TMEM: four K = 16 steps per 64-k block
+//     (384 tokens as two N = 192 instructions into two accumulators);
 //   * epilogue: the shared transposing epilogue (tiled bulk stores of [token][row] bf16 tiles).
-// TMEM: 128*NT accumulator columns + 4 weight stages of 32 columns.
+// TMEM: 128*NT accumulator columns + weight stages of 64 columns (two K blocks each): two
+// stages with three sub-tiles, four otherwise.
 //
 // Replaces, for batched sizes, the reference's per-forward decode kernel plus 8-bit GEMM on
 // these layouts (perrow_int8_fused_decode_r1.py:12-88, perrow_a8_candidate_r3.py:56-69).
@@ -45,7 +47,7 @@ using namespace tmemw;
 constexpr int kBKh = 64;                      // fp16 elements per K block: one 128-byte swizzle row
 constexpr int kSbIdx = 128;                   // indices per row per index super-block (16 * bits bytes)
 constexpr int kGMaxActStages = 4;
-constexpr int kGWStages = 4;                  // TMEM weight stages of 32 columns
+constexpr int kGMaxWStages = 4;               // TMEM weight stages of 64 columns (two K blocks): 4, or 2 beside a 384-column accumulator
 constexpr float kPreScale = 4096.f;           // keeps fp16(codeword x scale) far from the subnormals
 
 struct GTmemParams {
@@ -103,9 +105,13 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   constexpr int IDX_PER_KB = kBKh / D;                // indices per row per K block
   constexpr int KB_PER_SB = kSbIdx / IDX_PER_KB;      // K blocks per index super-block
   constexpr int IPT = IDX_PER_KB / 4;                 // indices per expander thread per K block (16 weights)
+  // A weight stage holds TWO K blocks (128 k, 64 columns): the per-stage cost of the expanders and of the
+  // issuer (barrier waits, tcgen05.wait::st, fences, commits) is paid half as often as with one block per
+  // stage.  Two stages fit beside three sub-tiles of accumulators, four otherwise.
+  constexpr int kGWStages = NT == 3 ? 2 : kGMaxWStages;
   constexpr uint32_t kWCol0 = BT;
   constexpr uint32_t kTmemCols = 512;
-  static_assert(BT + kGWStages * 32 <= 512, "TMEM budget");
+  static_assert(BT + kGWStages * 64 <= 512, "TMEM budget");
   constexpr uint32_t kIdesc256 = make_idesc(256), kIdesc128 = make_idesc(128), kIdesc192 = make_idesc(192);
   using CwVec = typename std::conditional<D == 8, uint4, uint2>::type;
 
@@ -116,7 +122,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   const GTmemLayout L = gtmem_layout(NT, p.act_stages, p.bits, p.C * D * 2, p.num_groups);
 
   constexpr int ACT_FULL = 0, ACT_EMPTY = kGMaxActStages, W_FULL = 2 * kGMaxActStages,
-                W_EMPTY = 2 * kGMaxActStages + kGWStages, IDX_FULL = 2 * kGMaxActStages + 2 * kGWStages,
+                W_EMPTY = 2 * kGMaxActStages + kGMaxWStages, IDX_FULL = 2 * kGMaxActStages + 2 * kGMaxWStages,
                 IDX_EMPTY = IDX_FULL + 2, ACC_FULL = IDX_FULL + 4;
   const uint32_t bars = base + L.bar_off;
   auto bar = [&](int i) { return bars + 8u * i; };
@@ -136,7 +142,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
       mbar_init(bar(ACT_FULL + i), 1);
       mbar_init(bar(ACT_EMPTY + i), 1);
     }
-    for (int i = 0; i < kGWStages; ++i) {
+    for (int i = 0; i < kGMaxWStages; ++i) {
       mbar_init(bar(W_FULL + i), kXWarps);
       mbar_init(bar(W_EMPTY + i), 1);
     }
@@ -185,32 +191,36 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int st = kb % act_stages, ws = kb % kGWStages;
-        ok = mbar_wait(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status) &&
-             mbar_wait(bar(W_FULL + ws), (kb / kGWStages) & 1, abort_flag, p.status);
-        if (!ok) break;
-        tc_fence_after();
-        SACQ_GTR(1, kb + 8);
-        const uint32_t act_addr = base + L.act_off + st * L.act_stage;
-        const uint32_t w_col = kWCol0 + (uint32_t)(ws * 32);
+      for (int wi = 0; wi < num_kb / 2 && ok; ++wi) {         // weight stage by weight stage: two K blocks each
+        const int ws = wi % kGWStages;
+        ok = mbar_wait(bar(W_FULL + ws), (wi / kGWStages) & 1, abort_flag, p.status);
 #pragma unroll
-        for (int ks = 0; ks < kBKh / 16; ++ks) {
-          const uint64_t adv = (uint64_t)((ks * 32) >> 4);              // 16 fp16 = 32 bytes per K step
-          const uint32_t a_tmem = tmem_base + w_col + (uint32_t)(ks * 8);
-          const uint32_t acc = (kb | ks) != 0;
-          if (NT == 3 && nt_valid == 3) {
-            // two N = 192 instructions into two accumulators (an instruction costs about 60 ns whatever its N)
-            umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc192, acc);
-            umma_f16_ts(tmem_base + 192u, a_tmem, make_smem_desc(act_addr + kTokTile * 3 / 2) + adv, kIdesc192, acc);
-          } else if (NT >= 2 && nt_valid >= 2) {
-            umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc256, acc);
-          } else {
-            umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc128, acc);
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          const int kb = 2 * wi + sub, st = kb % act_stages;
+          ok = mbar_wait(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status);
+          if (!ok) break;
+          if (sub == 0) tc_fence_after();
+          SACQ_GTR(1, kb + 8);
+          const uint32_t act_addr = base + L.act_off + st * L.act_stage;
+          const uint32_t w_col = kWCol0 + (uint32_t)(ws * 64 + sub * 32);
+#pragma unroll
+          for (int ks = 0; ks < kBKh / 16; ++ks) {
+            const uint64_t adv = (uint64_t)((ks * 32) >> 4);              // 16 fp16 = 32 bytes per K step
+            const uint32_t a_tmem = tmem_base + w_col + (uint32_t)(ks * 8);
+            const uint32_t acc = (kb | ks) != 0;
+            if (NT == 3 && nt_valid == 3) {
+              // two N = 192 instructions into two accumulators (an instruction costs about 60 ns whatever its N)
+              umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc192, acc);
+              umma_f16_ts(tmem_base + 192u, a_tmem, make_smem_desc(act_addr + kTokTile * 3 / 2) + adv, kIdesc192, acc);
+            } else if (NT >= 2 && nt_valid >= 2) {
+              umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc256, acc);
+            } else {
+              umma_f16_ts(tmem_base, a_tmem, make_smem_desc(act_addr) + adv, kIdesc128, acc);
+            }
           }
+          umma_commit(bar(ACT_EMPTY + st));
         }
-        umma_commit(bar(ACT_EMPTY + st));
-        umma_commit(bar(W_EMPTY + ws));
+        if (ok) umma_commit(bar(W_EMPTY + ws));
       }
       if (ok) umma_commit(bar(ACC_FULL));
     }
@@ -253,65 +263,73 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     const int kb_per_group = p.group_size / kBKh;
     bool ok = true;
     int grp = 0, left_in_group = kb_per_group;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int sb = kb / KB_PER_SB, slot = sb & 1;
-      const int ws = kb % kGWStages;
-      ok = mbar_wait(bar(IDX_FULL + slot), (sb >> 1) & 1, abort_flag, p.status) &&
-           mbar_wait(bar(W_EMPTY + ws), ((kb / kGWStages) & 1) ^ 1, abort_flag, p.status);
+    for (int wi = 0; wi < num_kb / 2 && ok; ++wi) {
+      const int ws = wi % kGWStages;
+      ok = mbar_wait(bar(W_EMPTY + ws), ((wi / kGWStages) & 1) ^ 1, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after();                              // the MMAs that read this stage are complete
-      if (warp == 2 && lane == 0) SACQ_GTR(2, kb + 8);
-      // scale * 2^sc_exp_shift * 4096 is a bf16 significand with a small exponent: exact in fp16
-      const __half sh = __float2half_rn(bf16_bits_to_float(sc[grp]) * p.scale_mul);
-      const __half2 s2 = __half2half2(sh);
-      // this thread's IPT index fields: a window of at most 64 bits that starts at bit `bit0` of the row's
-      // super-block, i.e. in slice bit0 / 128 and possibly the next one; bit0 is the same for the whole warp
-      const int bit0 = ((kb % KB_PER_SB) * IDX_PER_KB + kpart * IPT) * p.bits;
-      const int sl0 = bit0 >> 7;
-      const uint8_t* slice = sm + L.idx_off + slot * L.idx_slot + row * 16;
-      const uint4 a = *reinterpret_cast<const uint4*>(slice + sl0 * (kRows * 16));
-      uint4 b = a;                                     // the next slice only when the window crosses into it
-      if ((bit0 & 127) + IPT * p.bits > 128) b = *reinterpret_cast<const uint4*>(slice + (sl0 + 1) * (kRows * 16));
-      uint32_t lo, mid, hi;
-      switch ((bit0 >> 5) & 3) {                       // first word of the window inside slice sl0 (warp-uniform)
-        case 0: lo = a.x; mid = a.y; hi = a.z; break;
-        case 1: lo = a.y; mid = a.z; hi = a.w; break;
-        case 2: lo = a.z; mid = a.w; hi = b.x; break;
-        default: lo = a.w; mid = b.x; hi = b.y; break;
-      }
-      const uint32_t wsh = (uint32_t)(bit0 & 31);
-      const uint64_t win = ((uint64_t)__funnelshift_r(mid, hi, wsh) << 32) | __funnelshift_r(lo, mid, wsh);
-      uint32_t o[8];
+      if (warp == 2 && lane == 0) SACQ_GTR(2, wi + 8);
 #pragma unroll
-      for (int j = 0; j < IPT; ++j) {
-        const CwVec cw = cbs[(uint32_t)(win >> (j * p.bits)) & mask];
-        if constexpr (D == 8) {
-          const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
+      for (int sub = 0; sub < 2; ++sub) {
+        const int kb = 2 * wi + sub;
+        const int sb = kb / KB_PER_SB, slot = sb & 1;
+        if (kb % KB_PER_SB == 0) ok = mbar_wait(bar(IDX_FULL + slot), (sb >> 1) & 1, abort_flag, p.status);
+        if (!ok) break;
+        // scale * 2^sc_exp_shift * 4096 is a bf16 significand with a small exponent: exact in fp16
+        const __half sh = __float2half_rn(bf16_bits_to_float(sc[grp]) * p.scale_mul);
+        const __half2 s2 = __half2half2(sh);
+        // this thread's IPT index fields: a window of at most 64 bits that starts at bit `bit0` of the row's
+        // super-block, i.e. in slice bit0 / 128 and possibly the next one; bit0 is the same for the whole warp
+        const int bit0 = ((kb % KB_PER_SB) * IDX_PER_KB + kpart * IPT) * p.bits;
+        const int sl0 = bit0 >> 7;
+        const uint8_t* slice = sm + L.idx_off + slot * L.idx_slot + row * 16;
+        const uint4 a = *reinterpret_cast<const uint4*>(slice + sl0 * (kRows * 16));
+        uint4 b = a;                                     // the next slice only when the window crosses into it
+        if ((bit0 & 127) + IPT * p.bits > 128) b = *reinterpret_cast<const uint4*>(slice + (sl0 + 1) * (kRows * 16));
+        uint32_t lo, mid, hi;
+        switch ((bit0 >> 5) & 3) {                       // first word of the window inside slice sl0 (warp-uniform)
+          case 0: lo = a.x; mid = a.y; hi = a.z; break;
+          case 1: lo = a.y; mid = a.z; hi = a.w; break;
+          case 2: lo = a.z; mid = a.w; hi = b.x; break;
+          default: lo = a.w; mid = b.x; hi = b.y; break;
+        }
+        const uint32_t wsh = (uint32_t)(bit0 & 31);
+        const uint64_t win = ((uint64_t)__funnelshift_r(mid, hi, wsh) << 32) | __funnelshift_r(lo, mid, wsh);
+        uint32_t o[8];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&w4[e]), s2);
-            o[4 * j + e] = *reinterpret_cast<const uint32_t*>(&h);
-          }
-        } else {
-          const uint32_t w2[2] = {cw.x, cw.y};
+        for (int j = 0; j < IPT; ++j) {
+          const CwVec cw = cbs[(uint32_t)(win >> (j * p.bits)) & mask];
+          if constexpr (D == 8) {
+            const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&w2[e]), s2);
-            o[2 * j + e] = *reinterpret_cast<const uint32_t*>(&h);
+            for (int e = 0; e < 4; ++e) {
+              const __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&w4[e]), s2);
+              o[4 * j + e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          } else {
+            const uint32_t w2[2] = {cw.x, cw.y};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&w2[e]), s2);
+              o[2 * j + e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
           }
         }
+        tmem_st_32x8(lane_addr + kWCol0 + (uint32_t)(ws * 64 + sub * 32 + kpart * 8), o);
+        if (--left_in_group == 0) { ++grp; left_in_group = kb_per_group; }
       }
-      tmem_st_32x8(lane_addr + kWCol0 + (uint32_t)(ws * 32 + kpart * 8), o);
-      if (warp == 2 && lane == 0) SACQ_GTR(4, kb + 8);
+      if (!ok) break;
+      if (warp == 2 && lane == 0) SACQ_GTR(4, wi + 8);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (warp == 2 && lane == 0) SACQ_GTR(5, kb + 8);
+      if (warp == 2 && lane == 0) SACQ_GTR(5, wi + 8);
       if (lane == 0) {
         mbar_arrive(bar(W_FULL + ws));
-        if ((kb + 1) % KB_PER_SB == 0 || kb == num_kb - 1) mbar_arrive(bar(IDX_EMPTY + slot));
+        // the index slot is free once its last K block has been read (KB_PER_SB is even: that is an odd block)
+        const int kb_last = 2 * wi + 1;
+        if ((kb_last + 1) % KB_PER_SB == 0 || kb_last == num_kb - 1) mbar_arrive(bar(IDX_EMPTY + (kb_last / KB_PER_SB & 1)));
       }
-      if (--left_in_group == 0) { ++grp; left_in_group = kb_per_group; }
     }
 
     // ---- epilogue
@@ -402,7 +420,7 @@ bool large_m_tmem_grouped_supported(const sacq_layer* L) {
   if (d.vector_dim != 8 && d.vector_dim != 4) return false;
   if (d.index_bits < 1 || d.index_bits > 16) return false;
   if (!L->rows_16b_aligned) return false;
-  if (d.in_features % kBKh != 0 || d.group_size % kBKh != 0) return false;
+  if (d.in_features % (2 * kBKh) != 0 || d.group_size % kBKh != 0) return false;   // whole weight stages of two K blocks
   if (((size_t)L->cb_entries * d.vector_dim * 2) % 16 != 0) return false;
   if (has_shift(L)) return false;
   return g_act_stages(L, 1) >= 2;
