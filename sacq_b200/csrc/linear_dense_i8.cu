@@ -9,11 +9,16 @@
 //
 // Like the reference (perrow_a8_candidate_r3.py:52-63: "no persistent decoded weight cache")
 // the int8 weight matrix is produced per call from the packed stream into the caller's
-// workspace (decode_weight_int8_kernel, dequant.cu) and consumed by a plain dense GEMM:
-//   warp 0 (one lane) : TMA producer, 128 x 128-byte tiles of activations and weights,
-//                       SWIZZLE_128B, no multicast;
-//   warp 1 (one lane) : tcgen05.mma kind::i8 (M128 x N128 x K32), int32 accumulator in TMEM;
-//   warps 2..5        : epilogue, one TMEM lane quarter each.
+// workspace (decode_weight_int8_kernel, dequant.cu) and consumed by a plain dense GEMM.  A CTA
+// computes 256 tokens x 256 weight rows:
+//   warp 0 (one lane) : TMA producer: per 128-byte K block two 128-token activation tiles and one
+//                       256-row weight tile, SWIZZLE_128B, no multicast; 3 stages of 64 KB;
+//   warp 1 (one lane) : tcgen05.mma kind::i8, M128 x N256 x K32, into TWO int32 accumulators (one
+//                       per token sub-tile, 2 x 256 = all 512 TMEM columns) that alternate
+//                       instruction by instruction: consecutive MMAs into one accumulator wait
+//                       for each other (about 100 ns per instruction against 65 ns of tensor work);
+//   warps 2..17       : epilogue: TMEM lane quarter x token sub-tile x column half each.
+// A last token tile of at most 128 tokens loads and multiplies one sub-tile only.
 // Every mbarrier wait is bounded (status word + CTA-wide abort flag), as in the other
 // tensor-core kernels.
 #include <cuda.h>
@@ -28,11 +33,14 @@ namespace {
 
 using namespace umma;
 
-constexpr int kDBN = 128;                 // weight rows per tile = accumulator columns
+constexpr int kDBN = 256;                 // weight rows per tile = columns of one accumulator
 constexpr int kDBK = 128;                 // bytes per K block
-constexpr int kDStages = 6;
-constexpr int kDTile = kBM * kDBK;        // 16 KB
-constexpr int kDThreads = 6 * 32;
+constexpr int kDSub = 2;                  // 128-token sub-tiles per CTA, one accumulator each
+constexpr int kDStages = 3;
+constexpr int kDTileA = kBM * kDBK;       // 16 KB: one sub-tile of activations
+constexpr int kDTileB = kDBN * kDBK;      // 32 KB: the weight tile
+constexpr int kDEpiWarps = 16;
+constexpr int kDThreads = 64 + kDEpiWarps * 32;
 
 struct DenseParams {
   const float* act_scale;       // [M]
@@ -67,18 +75,20 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
-  constexpr uint32_t kStageBytes = 2 * kDTile;
+  constexpr uint32_t kStageBytes = kDSub * kDTileA + kDTileB;       // 64 KB
   constexpr uint32_t kSwOff = kDStages * kStageBytes, kBiasOff = kSwOff + kDBN * 4, kBarOff = kBiasOff + kDBN * 4,
                      kMiscOff = kBarOff + 16 * 8;
   constexpr int FULL = 0, EMPTY = kDStages, ACC_FULL = 2 * kDStages;
+  constexpr uint32_t kTmemCols = kDSub * kDBN;                      // 512
   const uint32_t bars = base + kBarOff;
   auto bar = [&](int i) { return bars + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kMiscOff + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kDBN, m0 = blockIdx.y * kBM;
+  const int n0 = blockIdx.x * kDBN, m0 = blockIdx.y * (kDSub * kBM);
   const int num_kb = (p.K + kDBK - 1) / kDBK;
+  const int subs = (p.M - m0 > kBM) ? 2 : 1;        // token sub-tiles of this CTA that hold tokens
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kDStages; ++i) {
@@ -91,7 +101,7 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kDBN);
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -102,9 +112,10 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       for (int kb = 0; kb < num_kb; ++kb) {
         const int st = kb % kDStages;
         if (!mbar_wait(bar(EMPTY + st), ((kb / kDStages) & 1) ^ 1, abort_flag, p.status)) break;
-        mbar_arrive_expect_tx(bar(FULL + st), kStageBytes);
-        tma_load_2d(base + st * kStageBytes, &tmap_a, kb * kDBK, m0, bar(FULL + st));
-        tma_load_2d(base + st * kStageBytes + kDTile, &tmap_b, kb * kDBK, n0, bar(FULL + st));
+        mbar_arrive_expect_tx(bar(FULL + st), (uint32_t)(subs * kDTileA + kDTileB));
+        const uint32_t dst = base + st * kStageBytes;
+        for (int t = 0; t < subs; ++t) tma_load_2d(dst + t * kDTileA, &tmap_a, kb * kDBK, m0 + t * kBM, bar(FULL + st));
+        tma_load_2d(dst + kDSub * kDTileA, &tmap_b, kb * kDBK, n0, bar(FULL + st));
       }
     }
     __syncwarp();
@@ -117,12 +128,14 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         ok = mbar_wait(bar(FULL + st), (kb / kDStages) & 1, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t a_desc = make_smem_desc(base + st * kStageBytes);
-        const uint64_t b_desc = make_smem_desc(base + st * kStageBytes + kDTile);
+        const uint64_t a0_desc = make_smem_desc(base + st * kStageBytes);
+        const uint64_t a1_desc = make_smem_desc(base + st * kStageBytes + kDTileA);
+        const uint64_t b_desc = make_smem_desc(base + st * kStageBytes + kDSub * kDTileA);
 #pragma unroll
         for (int ks = 0; ks < kDBK / 32; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32) >> 4);
-          umma_i8(tmem_base, a_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+          umma_i8(tmem_base, a0_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+          if (subs == 2) umma_i8(tmem_base + kDBN, a1_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
         }
         umma_commit(bar(EMPTY + st));
       }
@@ -130,28 +143,32 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     __syncwarp();
   } else {
-    const int et = threadIdx.x - 64;                  // 0..127
+    const int et = threadIdx.x - 64;                  // 0..511
     {
-      const int n = min(n0 + et, p.N - 1);
-      reinterpret_cast<float*>(sm + kSwOff)[et] = __ldg(p.w_scale + n);
-      reinterpret_cast<float*>(sm + kBiasOff)[et] = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et < kDBN) {
+        const int n = min(n0 + et, p.N - 1);
+        reinterpret_cast<float*>(sm + kSwOff)[et] = __ldg(p.w_scale + n);
+        reinterpret_cast<float*>(sm + kBiasOff)[et] = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kDEpiWarps * 32) : "memory");
     }
-    const int quarter = warp & 3;
-    const int m = m0 + quarter * 32 + lane;
+    const int ew = warp - 2;                          // 0..15
+    const int quarter = warp & 3;                     // the TMEM lane quarter a warp may read is warp % 4
+    const int sub = (ew >> 2) & 1, chalf = ew >> 3;   // every four consecutive warps cover the four quarters
+    const int m = m0 + sub * kBM + quarter * 32 + lane;
     const float sa = m < p.M ? __ldg(p.act_scale + m) : 0.f;
     const bool ok = mbar_wait(bar(ACC_FULL), 0, abort_flag, p.status);   // tcgen05.ld below is per warp: no CTA-wide collective
-    if (__all_sync(0xffffffffu, ok)) {
+    if (__all_sync(0xffffffffu, ok) && sub < subs) {
       tc_fence_after();
       const float* swp = reinterpret_cast<const float*>(sm + kSwOff);
       const float* bp = reinterpret_cast<const float*>(sm + kBiasOff);
       const bool has_bias = p.bias != nullptr;
 #pragma unroll 1
-      for (int cc = 0; cc < kDBN / 32; ++cc) {
-        const int c0 = cc * 32;
+      for (int cc = 0; cc < kDBN / 64; ++cc) {
+        const int c0 = chalf * (kDBN / 2) + cc * 32;
         if (n0 + c0 >= p.N) break;
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(sub * kDBN + c0), r);
         if (m < p.M) {
           uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
           // weight scale first, then the token scale; the bias rides in the same fused multiply-add
@@ -181,10 +198,10 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kDBN);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-constexpr size_t kDenseSmem = kDStages * 2 * kDTile + 2 * kDBN * 4 + 16 * 8 + 64 + 1024;
+constexpr size_t kDenseSmem = kDStages * (kDSub * kDTileA + kDTileB) + 2 * kDBN * 4 + 16 * 8 + 64 + 1024;
 
 }  // namespace
 
@@ -224,7 +241,7 @@ int launch_dense_i8(const sacq_layer* L, const void* q, const float* act_scale, 
     SACQ_CUDA_TRY(cudaFuncSetAttribute(dense_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const dim3 grid((unsigned)((d.out_features + kDBN - 1) / kDBN), (unsigned)((M + kBM - 1) / kBM), 1);
+  const dim3 grid((unsigned)((d.out_features + kDBN - 1) / kDBN), (unsigned)((M + kDSub * kBM - 1) / (kDSub * kBM)), 1);
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   dense_i8_kernel<<<grid, kDThreads, kDenseSmem, s>>>(ta, tb, p);
   count_launch();
