@@ -38,7 +38,7 @@ def main():
     ap.add_argument("--C", type=int, default=4096)
     ap.add_argument("--G", type=int, default=0, help="scale group size (0 = one scale per output row)")
     ap.add_argument("--kernel", default="auto")
-    ap.add_argument("--op", default="linear", choices=["linear", "forward", "dequant", "quant"])
+    ap.add_argument("--op", default="linear", choices=["linear", "forward", "dequant", "quant", "w8a8"])
     ap.add_argument("--instances", type=int, default=8)
     ap.add_argument("--passes", type=int, default=1)
     ap.add_argument("--time", action="store_true", help="print the mean time per call (CUDA events)")
@@ -57,7 +57,14 @@ def main():
     x = make_activations(a.M, a.K).cuda()
     q, s = layers[0].quantize_activations(x)
 
+    if a.op == "w8a8":                                 # the INT8 recipe: weight decode + integer GEMM per call
+        from sacq_b200 import quantize_rows
+        q8, s8 = quantize_rows(x, "int8_symmetric")
+        sw8 = layers[0].weight_row_scale("int8_symmetric")
+
     def call(layer):
+        if a.op == "w8a8":
+            return layer.linear_w8a8_int8(q8, s8, sw8)
         if a.op == "linear":
             return layer.linear_a8(q, s)
         if a.op == "forward":
