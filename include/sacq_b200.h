@@ -93,7 +93,10 @@ SACQ_API int sacq_dequant_bf16(const sacq_layer_t* layer, void* w_out, void* str
  *   s[m] = max_k |x[m,k]| / 448 (1 when the row is all zero)
  *   q[m,k] = e4m3_rne( clamp(x[m,k] / s[m], -448, 448) )
  * x: bf16 [M, K] row-major with row pitch `x_pitch` elements; q: uint8 [M, K];
- * scale: float [M].  Bit-exact with the reference for finite input. */
+ * scale: float [M].  Bit-exact with the reference, non-finite input included: a NaN in a row
+ * fails the reference's `maximum > 0` test, so the row keeps scale 1 and the NaN stays a NaN
+ * byte (0x7f / 0xff); an infinity gives an infinite scale, zeros for the row's finite elements
+ * and NaN for the infinite ones (the sign of that NaN is the platform's). */
 SACQ_API int sacq_quant_act_fp8(const void* x_bf16, int64_t x_pitch, int64_t M, int64_t K, void* q_out, float* scale_out,
                        void* stream);
 
