@@ -138,16 +138,28 @@ decode_weight_int8_kernel(const uint32_t* __restrict__ words, const uint16_t* __
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vectors; i += stride) {
     const uint32_t idx = extract_index(words, i, bits);
-    const int64_t n = i / vpr;
+    // 32-bit arithmetic where it fits: a 64-bit division costs several times the rest of the index math
+    const int64_t n = total_vectors <= 0x7fffffffLL ? (int64_t)((uint32_t)i / (uint32_t)vpr) : i / vpr;
     const int v = (int)(i - n * vpr);
     const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
     const float row = __ldg(sw + n);
-    auto enc = [&](int j) -> uint32_t {
-      const float a = bf16_bits_to_float(reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j), s, shift));
+    auto enc_bits = [&](uint32_t c_bits) -> uint32_t {
+      const float a = bf16_bits_to_float(reconstruct_bf16(c_bits, s, shift));
       const float q = fminf(fmaxf(__fdiv_rn(a, row), -127.f), 127.f);
       return (uint32_t)(__float2int_rn(q) & 0xff);
     };
-    if ((d & 3) == 0 && ((reinterpret_cast<uintptr_t>(wq) & 3) == 0)) {
+    auto enc = [&](int j) -> uint32_t { return enc_bits(__ldg(cb + (int64_t)idx * d + j)); };
+    auto enc4 = [&](uint32_t w0, uint32_t w1) -> uint32_t {     // four codeword elements (two bf16 pairs) -> four bytes
+      return enc_bits(w0 & 0xffffu) | (enc_bits(w0 >> 16) << 8) | (enc_bits(w1 & 0xffffu) << 16) | (enc_bits(w1 >> 16) << 24);
+    };
+    if (d == 8 && ((reinterpret_cast<uintptr_t>(cb) & 15) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 7) == 0)) {
+      // one 16-byte codeword load, one 8-byte store
+      const uint4 c = __ldg(reinterpret_cast<const uint4*>(cb) + idx);
+      *reinterpret_cast<uint2*>(wq + i * 8) = make_uint2(enc4(c.x, c.y), enc4(c.z, c.w));
+    } else if (d == 4 && ((reinterpret_cast<uintptr_t>(cb) & 7) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 3) == 0)) {
+      const uint2 c = __ldg(reinterpret_cast<const uint2*>(cb) + idx);
+      *reinterpret_cast<uint32_t*>(wq + i * 4) = enc4(c.x, c.y);
+    } else if ((d & 3) == 0 && ((reinterpret_cast<uintptr_t>(wq) & 3) == 0)) {
       for (int j = 0; j < d; j += 4)
         *reinterpret_cast<uint32_t*>(wq + i * d + j) = enc(j) | (enc(j + 1) << 8) | (enc(j + 2) << 16) | (enc(j + 3) << 24);
     } else {

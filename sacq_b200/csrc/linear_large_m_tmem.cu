@@ -139,7 +139,8 @@ __device__ int g_tmem_ablate = 0;
 template <int D, int BITS, int NT, bool CB_SMEM>
 __global__ void __launch_bounds__(kCtaThreads, 1)
 large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
-                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ TmemParams p) {
+                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ BcastMaps tmap_bc,
+                    const __grid_constant__ TmemParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int BT = kBM * NT;                        // tokens per CTA = accumulator columns
   constexpr int IDX_PER_KB = kBK / D;                 // indices per row per K block
@@ -371,7 +372,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       o.M = p.M; o.N = p.N; o.y_tma = p.y_tma;
       const float sw = reinterpret_cast<const float*>(sm + L.sw_off)[row];
       const float bs = reinterpret_cast<const float*>(sm + L.bias_off)[row];
-      tmem_epilogue<NT>(o, &tmap_y, lane_addr, row, kpart, et, reinterpret_cast<const float*>(sm + L.sa_off), sw, bs,
+      tmem_epilogue<NT>(o, &tmap_y, tmap_bc.m, lane_addr, row, kpart, et, reinterpret_cast<const float*>(sm + L.sa_off), sw, bs,
                         sm + L.act_off, (act_stages * L.act_stage >= 2u * kStageTile) ? 2 : 1, m0, n0);
     }
   }
@@ -403,8 +404,8 @@ int pick_act_stages(const sacq_layer* L, int nt) {
 }
 
 template <int D, int BITS, int NT, bool CB_SMEM>
-cudaError_t launch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const TmemParams& p,
-                      dim3 grid, size_t smem, cudaStream_t s) {
+cudaError_t launch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const BcastMaps& tb,
+                      const TmemParams& p, dim3 grid, size_t smem, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -414,21 +415,21 @@ cudaError_t launch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUtens
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  large_m_tmem_kernel<D, BITS, NT, CB_SMEM><<<grid, kCtaThreads, smem, s>>>(ta, ti, ty, p);
+  large_m_tmem_kernel<D, BITS, NT, CB_SMEM><<<grid, kCtaThreads, smem, s>>>(ta, ti, ty, tb, p);
   return cudaGetLastError();
 }
 
 template <int D, int BITS>
-cudaError_t launch_db(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const TmemParams& p, int nt,
-                      bool cb_smem, dim3 grid, size_t smem, cudaStream_t s) {
+cudaError_t launch_db(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const BcastMaps& tb,
+                      const TmemParams& p, int nt, bool cb_smem, dim3 grid, size_t smem, cudaStream_t s) {
   if (!cb_smem) {
-    if (nt == 3) return launch_nt<D, BITS, 3, false>(ta, ti, ty, p, grid, smem, s);
-    if (nt == 2) return launch_nt<D, BITS, 2, false>(ta, ti, ty, p, grid, smem, s);
-    return launch_nt<D, BITS, 1, false>(ta, ti, ty, p, grid, smem, s);
+    if (nt == 3) return launch_nt<D, BITS, 3, false>(ta, ti, ty, tb, p, grid, smem, s);
+    if (nt == 2) return launch_nt<D, BITS, 2, false>(ta, ti, ty, tb, p, grid, smem, s);
+    return launch_nt<D, BITS, 1, false>(ta, ti, ty, tb, p, grid, smem, s);
   }
-  if (nt == 3) return launch_nt<D, BITS, 3, true>(ta, ti, ty, p, grid, smem, s);
-  if (nt == 2) return launch_nt<D, BITS, 2, true>(ta, ti, ty, p, grid, smem, s);
-  return launch_nt<D, BITS, 1, true>(ta, ti, ty, p, grid, smem, s);
+  if (nt == 3) return launch_nt<D, BITS, 3, true>(ta, ti, ty, tb, p, grid, smem, s);
+  if (nt == 2) return launch_nt<D, BITS, 2, true>(ta, ti, ty, tb, p, grid, smem, s);
+  return launch_nt<D, BITS, 1, true>(ta, ti, ty, tb, p, grid, smem, s);
 }
 
 }  // namespace
@@ -498,14 +499,28 @@ int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, 
     const int rc = large_m_index_map(L, kRows, &ti);
     if (rc != SACQ_OK) return rc;
   }
-  // the output leaves by tiled bulk stores when y allows it: 16-byte aligned base and row pitch
-  const bool y_tma = residual == nullptr && (bc == nullptr || bc->n == 0) &&
-                     reinterpret_cast<uintptr_t>(y) % 16 == 0 && (ldy * 2) % 16 == 0 && d.out_features >= kRows;
+  // the output leaves by tiled bulk stores when y (and every peer copy of a column split) allows it:
+  // 16-byte aligned base and row pitch
+  bool y_tma = residual == nullptr && reinterpret_cast<uintptr_t>(y) % 16 == 0 && (ldy * 2) % 16 == 0 &&
+               d.out_features >= kRows;
+  for (int i = 0; bc != nullptr && i < bc->n; ++i) y_tma = y_tma && reinterpret_cast<uintptr_t>(bc->ptr[i]) % 16 == 0;
   CUtensorMap ty = ta;                                // a valid map is passed either way
+  static const BcastMaps kNoMaps = {};
+  BcastMaps tb_local;
+  const BcastMaps* tb = &kNoMaps;
   if (y_tma) {
-    const int rc = encode_bytes_2d(&ty, y, (uint64_t)d.out_features * 2, (uint64_t)M, (uint64_t)ldy * 2, kRows * 2, kBM,
-                                   CU_TENSOR_MAP_SWIZZLE_NONE);
+    int rc = encode_bytes_2d(&ty, y, (uint64_t)d.out_features * 2, (uint64_t)M, (uint64_t)ldy * 2, kRows * 2, kBM,
+                             CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != SACQ_OK) return rc;
+    if (bc != nullptr && bc->n > 0) {
+      tb_local = kNoMaps;
+      for (int i = 0; i < bc->n; ++i) {
+        rc = encode_bytes_2d(&tb_local.m[i], bc->ptr[i], (uint64_t)d.out_features * 2, (uint64_t)M, (uint64_t)ldy * 2,
+                             kRows * 2, kBM, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != SACQ_OK) return rc;
+      }
+      tb = &tb_local;
+    }
   }
   TmemParams p{};
   p.y_tma = y_tma ? 1 : 0;
@@ -531,12 +546,12 @@ int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, 
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
   cudaError_t e;
   const int D = d.vector_dim, B = d.index_bits;
-  if (D == 8 && B == 12) e = launch_db<8, 12>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 8 && B == 8) e = launch_db<8, 8>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 8 && B == 16) e = launch_db<8, 16>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 4 && B == 12) e = launch_db<4, 12>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else if (D == 4 && B == 8) e = launch_db<4, 8>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
-  else e = launch_db<4, 16>(ta, *ti, ty, p, nt, cb_smem, grid, smem, s);
+  if (D == 8 && B == 12) e = launch_db<8, 12>(ta, *ti, ty, *tb, p, nt, cb_smem, grid, smem, s);
+  else if (D == 8 && B == 8) e = launch_db<8, 8>(ta, *ti, ty, *tb, p, nt, cb_smem, grid, smem, s);
+  else if (D == 8 && B == 16) e = launch_db<8, 16>(ta, *ti, ty, *tb, p, nt, cb_smem, grid, smem, s);
+  else if (D == 4 && B == 12) e = launch_db<4, 12>(ta, *ti, ty, *tb, p, nt, cb_smem, grid, smem, s);
+  else if (D == 4 && B == 8) e = launch_db<4, 8>(ta, *ti, ty, *tb, p, nt, cb_smem, grid, smem, s);
+  else e = launch_db<4, 16>(ta, *ti, ty, *tb, p, nt, cb_smem, grid, smem, s);
   count_launch();
   if (e != cudaSuccess) return cuda_fail(e, "TMEM-weight large-M launch");
   return SACQ_OK;

@@ -98,7 +98,8 @@ __device__ long long g_gtmem_trace[8][72];
 template <int D, int NT>
 __global__ void __launch_bounds__(kCtaThreads, 1)
 large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_idx,
-                            const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ GTmemParams p) {
+                            const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ BcastMaps tmap_bc,
+                            const __grid_constant__ GTmemParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) SACQ_GTR(0, 0);
   constexpr int BT = kBM * NT;
@@ -339,7 +340,7 @@ large_m_tmem_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     if (ok) {
       tc_fence_after();
       const float bs = reinterpret_cast<const float*>(sm + L.bias_off)[row];
-      tmem_epilogue<NT>(p.out, &tmap_y, lane_addr, row, kpart, et, reinterpret_cast<const float*>(sm + L.sa_off),
+      tmem_epilogue<NT>(p.out, &tmap_y, tmap_bc.m, lane_addr, row, kpart, et, reinterpret_cast<const float*>(sm + L.sa_off),
                         p.out_mul, bs, sm + L.act_off, (act_stages * NT * kTokTile >= 2 * kStageTile) ? 2 : 1, m0, n0);
     }
   }
@@ -390,8 +391,8 @@ int g_act_stages(const sacq_layer* L, int nt) {
 }
 
 template <int D, int NT>
-cudaError_t glaunch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const GTmemParams& p,
-                       dim3 grid, size_t smem, cudaStream_t s) {
+cudaError_t glaunch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const BcastMaps& tb,
+                       const GTmemParams& p, dim3 grid, size_t smem, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -401,16 +402,16 @@ cudaError_t glaunch_nt(const CUtensorMap& ta, const CUtensorMap& ti, const CUten
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  large_m_tmem_grouped_kernel<D, NT><<<grid, kCtaThreads, smem, s>>>(ta, ti, ty, p);
+  large_m_tmem_grouped_kernel<D, NT><<<grid, kCtaThreads, smem, s>>>(ta, ti, ty, tb, p);
   return cudaGetLastError();
 }
 
 template <int D>
-cudaError_t glaunch_d(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const GTmemParams& p, int nt,
-                      dim3 grid, size_t smem, cudaStream_t s) {
-  if (nt == 3) return glaunch_nt<D, 3>(ta, ti, ty, p, grid, smem, s);
-  if (nt == 2) return glaunch_nt<D, 2>(ta, ti, ty, p, grid, smem, s);
-  return glaunch_nt<D, 1>(ta, ti, ty, p, grid, smem, s);
+cudaError_t glaunch_d(const CUtensorMap& ta, const CUtensorMap& ti, const CUtensorMap& ty, const BcastMaps& tb,
+                      const GTmemParams& p, int nt, dim3 grid, size_t smem, cudaStream_t s) {
+  if (nt == 3) return glaunch_nt<D, 3>(ta, ti, ty, tb, p, grid, smem, s);
+  if (nt == 2) return glaunch_nt<D, 2>(ta, ti, ty, tb, p, grid, smem, s);
+  return glaunch_nt<D, 1>(ta, ti, ty, tb, p, grid, smem, s);
 }
 
 }  // namespace
@@ -509,13 +510,20 @@ int launch_large_m_tmem_grouped(const sacq_layer* L, const void* q, const float*
     rc = encode_bytes_2d(&ti, d.packed, row_bytes, (uint64_t)N, row_bytes, 16u, (uint32_t)kRows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != SACQ_OK) return rc;
     uint16_t* y_slab = static_cast<uint16_t*>(y) + m0 * ldy;
-    const bool y_tma = residual == nullptr && p.out.n_bc == 0 && reinterpret_cast<uintptr_t>(y_slab) % 16 == 0 &&
-                       (ldy * 2) % 16 == 0 && N >= kRows;
+    bool y_tma = residual == nullptr && reinterpret_cast<uintptr_t>(y_slab) % 16 == 0 && (ldy * 2) % 16 == 0 && N >= kRows;
+    for (int i = 0; i < p.out.n_bc; ++i)
+      y_tma = y_tma && reinterpret_cast<uintptr_t>(static_cast<uint16_t*>(bc->ptr[i]) + m0 * ldy) % 16 == 0;
     ty = ta;
+    BcastMaps tb = {};
     if (y_tma) {
       rc = encode_bytes_2d(&ty, y_slab, (uint64_t)N * 2, (uint64_t)rows, (uint64_t)ldy * 2, kRows * 2, kBM,
                            CU_TENSOR_MAP_SWIZZLE_NONE);
       if (rc != SACQ_OK) return rc;
+      for (int i = 0; i < p.out.n_bc; ++i) {         // the peers' copies of a column split take the same tiled stores
+        rc = encode_bytes_2d(&tb.m[i], static_cast<uint16_t*>(bc->ptr[i]) + m0 * ldy, (uint64_t)N * 2, (uint64_t)rows,
+                             (uint64_t)ldy * 2, kRows * 2, kBM, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != SACQ_OK) return rc;
+      }
     }
     p.act_scale = scale + m0;
     p.out.y = y_slab;
@@ -527,8 +535,8 @@ int launch_large_m_tmem_grouped(const sacq_layer* L, const void* q, const float*
     const GTmemLayout lay = gtmem_layout(nt, p.act_stages, d.index_bits, L->cb_entries * d.vector_dim * 2, (int)L->num_groups);
     size_t smem = lay.total + 1024;
     if (smem < 120 * 1024) smem = 120 * 1024;      // two CTAs (each takes all 512 TMEM columns) never share an SM
-    const cudaError_t e = d.vector_dim == 8 ? glaunch_d<8>(ta, ti, ty, p, nt, grid, smem, s)
-                                            : glaunch_d<4>(ta, ti, ty, p, nt, grid, smem, s);
+    const cudaError_t e = d.vector_dim == 8 ? glaunch_d<8>(ta, ti, ty, tb, p, nt, grid, smem, s)
+                                            : glaunch_d<4>(ta, ti, ty, tb, p, nt, grid, smem, s);
     count_launch();
     if (e != cudaSuccess) return cuda_fail(e, "grouped TMEM-weight launch");
   }

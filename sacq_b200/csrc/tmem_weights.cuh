@@ -36,12 +36,12 @@ __device__ __forceinline__ bool xall(bool v) {
   return r != 0;
 }
 // Tiled bulk store shared -> global (the tile is clipped at the tensor's edges).
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+__device__ __forceinline__ void tma_store_2d_issue(const CUtensorMap* map, int x, int y, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                ::"l"(map), "r"(x), "r"(y), "r"(src)
                : "memory");
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
@@ -97,7 +97,13 @@ struct TmemOut {
   int n_bc;                     // further copies of the output (peer GPUs' buffers), same pitch as y
   uint16_t* ybc[kMaxBcast];
   int M, N;
-  int y_tma;                    // y takes tiled bulk stores (aligned, no residual, no peer copies)
+  int y_tma;                    // y (and every peer copy) takes tiled bulk stores (aligned, no residual)
+};
+
+// Tensor maps over the peer GPUs' copies of the output (the column split's exchange): the same
+// [M][N] view as y's map, one per peer.  Plain tiled stores into peer memory, no multicast.
+struct BcastMaps {
+  CUtensorMap m[kMaxBcast];
 };
 
 // Epilogue of one CTA, run by all expander threads after the accumulator is complete:
@@ -107,7 +113,8 @@ struct TmemOut {
 // warp converts, `sap` = the NT*128 token scales in shared memory, `stage_base` = n_stage idle
 // buffers of kStageTile bytes.
 template <int NT>
-__device__ __forceinline__ void tmem_epilogue(const TmemOut& o, const CUtensorMap* tmap_y, uint32_t lane_addr, int row,
+__device__ __forceinline__ void tmem_epilogue(const TmemOut& o, const CUtensorMap* tmap_y, const CUtensorMap* tmap_bc,
+                                              uint32_t lane_addr, int row,
                                               int kpart, int et, const float* sap, float sw, float bs,
                                               uint8_t* stage_base, int n_stage, int m0, int n0) {
   // The accumulator holds y transposed (lane = weight row, column = token).  Each 128-token
@@ -147,7 +154,10 @@ __device__ __forceinline__ void tmem_epilogue(const TmemOut& o, const CUtensorMa
       fence_proxy_async();                        // generic-proxy writes -> visible to the bulk store
       xbarrier();                                 // the sub-tile is staged
       if (et == 0) {
-        tma_store_2d(tmap_y, n0 * 2, m_first, smem_u32(stg));
+        // one bulk-store group per sub-tile: the local copy and, in a column split, every peer's copy
+        tma_store_2d_issue(tmap_y, n0 * 2, m_first, smem_u32(stg));
+        for (int c = 0; c < o.n_bc; ++c) tma_store_2d_issue(tmap_bc + c, n0 * 2, m_first, smem_u32(stg));
+        tma_store_commit();
         // the other buffer's store (the previous sub-tile) must have read its tile before that
         // buffer is written again; with a single buffer, this store itself
         if (n_stage == 2) tma_store_wait_read<1>(); else tma_store_wait_read<0>();
@@ -192,7 +202,9 @@ __device__ __forceinline__ void tmem_epilogue(const TmemOut& o, const CUtensorMa
       if (n_stage == 1) xbarrier();               // before the next sub-tile reuses the staging rows
     }
   }
-  if (o.y_tma && et == 0) tma_store_wait_read<0>();   // shared memory stays valid until every store has read it
+  // shared memory stays valid until every store has read it; the writes themselves (local and peer)
+  // are in the memory system then, like plain stores, and the grid's end orders them
+  if (o.y_tma && et == 0) tma_store_wait_read<0>();
 }
 
 }  // namespace tmemw
