@@ -252,9 +252,7 @@ large_m_tmem_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         ok = (sub != 0 || mbar_wait(bar(ACT_FULL + st), (kb / act_stages) & 1, abort_flag, p.status)) &&
              mbar_wait(bar(W_FULL + ws), (wb / kWStages) & 1, abort_flag, p.status);
         if (!ok) break;
-#ifndef SACQ_EXP_NOFENCE
         tc_fence_after();
-#endif
         SACQ_TR(1, wb + 8);
         const uint32_t act_addr = base + L.act_off + st * L.act_stage;
         const uint32_t w_col = kWCol0 + (uint32_t)(ws * W_COLS);
