@@ -382,10 +382,25 @@ def section_large_m(ctx):
             sec, _ = ctx.time_graphs([g], 4, 3, min_seconds=0.1, min_passes=5)
             int8_us = ctx.max_over_ranks([sec])[0] / 4 * 1e6
             del g
+            # ... and its FP8 recipe (per-row e4m3 weights decoded per call + tcgen05 kind::f8f6f4 GEMM)
+            qf, sf = quantize_rows(x)
+            swf = mod.weight_row_scale("fp8_e4m3fn")
+
+            def fp8_recipe(stream):
+                mod.linear_w8a8_fp8(qf, sf, swf, out=y)
+
+            with torch.cuda.stream(ctx.stream):
+                fp8_recipe(ctx.stream)
+            ctx.stream.synchronize()
+            g, _ = ctx.capture(fp8_recipe)
+            sec, _ = ctx.time_graphs([g], 4, 3, min_seconds=0.1, min_passes=5)
+            fp8_us = ctx.max_over_ranks([sec])[0] / 4 * 1e6
+            del g
             rows.append({"shape_KxN": f"{K}x{N}", "M": M, "us": us, "kernel": kern,
                          "algorithmic_tflops": flops / us / 1e6, "tokens_per_s": M / us * 1e6,
                          "frac_of_bf16_peak": flops / us / 1e6 / peak, "dense_baseline_us": dense_us,
                          "int8_recipe_us": int8_us, "int8_recipe_tops": flops / int8_us / 1e6,
+                         "fp8_recipe_us": fp8_us,
                          "rotating_sets": n_sets})
     best = max(rows, key=lambda r: r["M"] * 10 + (r["shape_KxN"] == "2048x6144"))
     return {"rows": rows,

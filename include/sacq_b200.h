@@ -185,6 +185,18 @@ SACQ_API int sacq_linear_w8a8_int8(const sacq_layer_t* layer, const void* q_int8
                                    const float* w_scale, int64_t M, void* y_out, int64_t ldy, void* workspace,
                                    int64_t workspace_bytes, void* stream);
 
+/* The reference's FP8 recipe (`projection_format: fp8_e4m3fn`): per-token e4m3 activations
+ * (sacq_quant_act_fp8) x per-output-row e4m3 weights (sacq_weight_row_scale + sacq_decode_weight_fp8,
+ * decoded per call into `workspace` exactly as above), fp32 accumulation on the tensor cores and
+ *   y[m,n] = bf16(fma(sa[m], acc * sw[n], bias[n]))  or  bf16(sa[m] * (acc * sw[n])) without bias
+ * -- what torch._scaled_mm(aq, wq.t(), sa, sw, bias) and cutlass_scaled_mm compute in
+ * a8_joint_pair_r1.py:374 / perrow_a8_candidate_r3.py:56-69.  The weights are RE-QUANTIZED to 8 bits
+ * here, as in the reference; sacq_linear_a8 is the path that multiplies the exact codebook weights.
+ * The operands are bit-exact with the reference; the sum is fp32 in the tensor core's order. */
+SACQ_API int sacq_linear_w8a8_fp8(const sacq_layer_t* layer, const void* q_e4m3, const float* act_scale,
+                                  const float* w_scale, int64_t M, void* y_out, int64_t ldy, void* workspace,
+                                  int64_t workspace_bytes, void* stream);
+
 /* Activation function fused into the per-token quantizer (the producer of the MLP's down
  * projection; the reference fuses this stage for its INT8 path,
  * int8_swiglu_lookup_fusion_20261028_r1.py:9-21).  One launch, the [M, K] intermediate is

@@ -71,6 +71,7 @@ SIGNATURES = {
     "sacq_decode_weight_int8": (_int, [_vp, _fp, _vp, _vp]),
     "sacq_workspace_bytes_w8a8": (_i64, [_vp, _i64]),
     "sacq_linear_w8a8_int8": (_int, [_vp, _vp, _fp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "sacq_linear_w8a8_fp8": (_int, [_vp, _vp, _fp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "sacq_workspace_bytes": (_i64, [_vp, _i64]),
     "sacq_workspace_counter_bytes": (_i64, []),
     "sacq_linear_a8": (_int, [_vp, _vp, _fp, _i64, _vp, _i64, _vp, _i64, _vp]),

@@ -495,6 +495,33 @@ SACQ_API int sacq_linear_w8a8_int8(const sacq_layer_t* L, const void* q_int8, co
   return launch_dense_i8(L, q_int8, act_scale, wq, w_scale, M, y_out, ldy, s);
 }
 
+SACQ_API int sacq_linear_w8a8_fp8(const sacq_layer_t* L, const void* q_e4m3, const float* act_scale, const float* w_scale,
+                                  int64_t M, void* y_out, int64_t ldy, void* workspace, int64_t workspace_bytes,
+                                  void* stream) {
+  if (int rc = check_layer(L)) return rc;
+  if (M < 0) return set_error(SACQ_ERR_INVALID_ARGUMENT, "M=%lld is negative", (long long)M);
+  if (M == 0 || L->d.out_features == 0) return SACQ_OK;
+  if (q_e4m3 == nullptr || act_scale == nullptr || w_scale == nullptr || y_out == nullptr)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "null argument");
+  if (ldy < L->d.out_features)
+    return set_error(SACQ_ERR_INVALID_ARGUMENT, "ldy=%lld smaller than out_features=%lld", (long long)ldy,
+                     (long long)L->d.out_features);
+  if (!dense_i8_supported(L))
+    return set_error(SACQ_ERR_UNSUPPORTED, "FP8 recipe needs in_features to be a multiple of 16");
+  const int64_t need = sacq_workspace_bytes_w8a8(L, M);
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(SACQ_ERR_WORKSPACE, "workspace of %lld bytes needed, %lld given", (long long)need,
+                     (long long)workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return set_error(SACQ_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+  DeviceGuard guard(L->d.device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // per call, as the reference does: packed stream -> e4m3 weight rows, then the dense FP8 GEMM
+  void* wq = static_cast<uint8_t*>(workspace) + kCounterBytes;
+  if (int rc = launch_decode_weight_fp8(L, w_scale, wq, s)) return rc;
+  return launch_dense_i8(L, q_e4m3, act_scale, wq, w_scale, M, y_out, ldy, s, true);
+}
+
 SACQ_API int sacq_linear_a8(const sacq_layer_t* L, const void* q, const float* scale, int64_t M, void* y_out, int64_t ldy,
                    void* workspace, int64_t workspace_bytes, void* stream) {
   return linear_a8_impl(L, q, scale, M, nullptr, 0, y_out, ldy, workspace, workspace_bytes, stream);

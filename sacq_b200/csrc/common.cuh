@@ -113,7 +113,7 @@ int launch_large_m_tmem(const sacq_layer* L, const void* q, const float* scale, 
 // Dense int8 x int8 -> int32 GEMM of the reference's deployed INT8 recipe (linear_dense_i8.cu).
 bool dense_i8_supported(const sacq_layer* L);
 int launch_dense_i8(const sacq_layer* L, const void* q, const float* act_scale, const void* wq, const float* w_scale,
-                    int64_t M, void* y, int64_t ldy, cudaStream_t s);
+                    int64_t M, void* y, int64_t ldy, cudaStream_t s, bool fp8 = false);
 
 bool large_m_grouped_supported(const sacq_layer* L);
 int64_t large_m_grouped_workspace_bytes(const sacq_layer* L, int64_t M);

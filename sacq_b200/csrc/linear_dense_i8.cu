@@ -1,3 +1,5 @@
+// The reference's 8-bit weight recipes as dense 8-bit work on the 5th-generation tensor cores.
+// INT8 (the deployed one; FP8 below):
 // The reference's deployed INT8 recipe as integer work on the 5th-generation tensor cores
 // (sm_100a): per-token int8 activations x per-output-row int8 weights -> int32, then
 //   y[m,n] = bf16( fma(sa[m], float(acc[m,n]) * sw[n], bias[n]) )        (bias given)
@@ -21,6 +23,11 @@
 // A last token tile of at most 128 tokens loads and multiplies one sub-tile only.
 // Every mbarrier wait is bounded (status word + CTA-wide abort flag), as in the other
 // tensor-core kernels.
+//
+// The FP8 recipe (`projection_format: fp8_e4m3fn`; a8_joint_pair_r1.py:374,
+// perrow_a8_candidate_r3.py:56-69: per-token e4m3 activations x per-output-row e4m3 weights,
+// torch._scaled_mm / cutlass_scaled_mm with fp32 accumulation and the same epilogue order) is the
+// same kernel with kind::f8f6f4 instructions and fp32 accumulators (FP8 = true).
 #include <cuda.h>
 #include <math.h>
 
@@ -67,6 +74,8 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
       : "memory");
 }
 
+// FP8: e4m3 operands, fp32 accumulators (kind::f8f6f4); else int8 operands, int32 accumulators.
+template <bool FP8>
 __global__ void __launch_bounds__(kDThreads, 1)
 dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ DenseParams p) {
@@ -121,7 +130,7 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t kIdesc = make_idesc_i8(kDBN);
+      constexpr uint32_t kIdesc = FP8 ? make_idesc(kDBN) : make_idesc_i8(kDBN);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int st = kb % kDStages;
@@ -134,8 +143,13 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
         for (int ks = 0; ks < kDBK / 32; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32) >> 4);
-          umma_i8(tmem_base, a0_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
-          if (subs == 2) umma_i8(tmem_base + kDBN, a1_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+          if constexpr (FP8) {
+            umma_f8(tmem_base, a0_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+            if (subs == 2) umma_f8(tmem_base + kDBN, a1_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+          } else {
+            umma_i8(tmem_base, a0_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+            if (subs == 2) umma_i8(tmem_base + kDBN, a1_desc + adv, b_desc + adv, kIdesc, (kb | ks) != 0);
+          }
         }
         umma_commit(bar(EMPTY + st));
       }
@@ -173,7 +187,7 @@ dense_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           uint16_t* yrow = p.y + (int64_t)m * p.ldy + n0 + c0;
           // weight scale first, then the token scale; the bias rides in the same fused multiply-add
           auto fin = [&](int c) -> uint32_t {
-            const float scaled = __fmul_rn(__int2float_rn((int)r[c]), swp[c0 + c]);
+            const float scaled = __fmul_rn(FP8 ? __uint_as_float(r[c]) : __int2float_rn((int)r[c]), swp[c0 + c]);
             const float v = has_bias ? fmaf(sa, scaled, bp[c0 + c]) : __fmul_rn(sa, scaled);
             return (uint32_t)float_to_bf16_bits(v);
           };
@@ -209,15 +223,15 @@ bool dense_i8_supported(const sacq_layer* L) { return L->d.in_features % 16 == 0
 
 // y = epilogue(q [M,K] int8 x wq [N,K] int8): the dense part of the INT8 recipe.
 int launch_dense_i8(const sacq_layer* L, const void* q, const float* act_scale, const void* wq, const float* w_scale,
-                    int64_t M, void* y, int64_t ldy, cudaStream_t s) {
+                    int64_t M, void* y, int64_t ldy, cudaStream_t s, bool fp8) {
   const sacq_layer_desc& d = L->d;
   if (M <= 0 || d.out_features == 0) return SACQ_OK;
   if (!dense_i8_supported(L))
-    return set_error(SACQ_ERR_UNSUPPORTED, "INT8 GEMM needs in_features to be a multiple of 16, got %lld",
+    return set_error(SACQ_ERR_UNSUPPORTED, "the 8-bit GEMM needs in_features to be a multiple of 16, got %lld",
                      (long long)d.in_features);
   if (reinterpret_cast<uintptr_t>(q) % 16 != 0 || reinterpret_cast<uintptr_t>(wq) % 16 != 0)
-    return set_error(SACQ_ERR_ALIGNMENT, "INT8 GEMM operands must be 16-byte aligned");
-  if ((int64_t)d.in_features * 127 * 127 > 2147483647LL)
+    return set_error(SACQ_ERR_ALIGNMENT, "8-bit GEMM operands must be 16-byte aligned");
+  if (!fp8 && (int64_t)d.in_features * 127 * 127 > 2147483647LL)
     return set_error(SACQ_ERR_UNSUPPORTED, "in_features=%lld could overflow the int32 accumulator", (long long)d.in_features);
   CUtensorMap ta, tb;
   int rc = encode_bytes_2d(&ta, q, (uint64_t)d.in_features, (uint64_t)M, (uint64_t)d.in_features, kDBK, kBM,
@@ -238,12 +252,14 @@ int launch_dense_i8(const sacq_layer* L, const void* q, const float* act_scale, 
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    SACQ_CUDA_TRY(cudaFuncSetAttribute(dense_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem));
+    SACQ_CUDA_TRY(cudaFuncSetAttribute(dense_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem));
+    SACQ_CUDA_TRY(cudaFuncSetAttribute(dense_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const dim3 grid((unsigned)((d.out_features + kDBN - 1) / kDBN), (unsigned)((M + kDSub * kBM - 1) / (kDSub * kBM)), 1);
   if (grid.y > 65535) return set_error(SACQ_ERR_UNSUPPORTED, "M=%lld exceeds the grid limit", (long long)M);
-  dense_i8_kernel<<<grid, kDThreads, kDenseSmem, s>>>(ta, tb, p);
+  if (fp8) dense_i8_kernel<true><<<grid, kDThreads, kDenseSmem, s>>>(ta, tb, p);
+  else dense_i8_kernel<false><<<grid, kDThreads, kDenseSmem, s>>>(ta, tb, p);
   count_launch();
   SACQ_CUDA_TRY(cudaGetLastError());
   return SACQ_OK;

@@ -262,6 +262,33 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
                                                        _stream_ptr()))
         return out
 
+    def linear_w8a8_fp8(self, q: torch.Tensor, scale: torch.Tensor, weight_row_scale: torch.Tensor,
+                        out: torch.Tensor | None = None) -> torch.Tensor:
+        """The reference's FP8 recipe: per-token e4m3 activations (``quantize_rows(x)``) x per-output-row
+        e4m3 weights (re-quantized from the codebook weights, decoded per call), fp32 accumulation,
+        ``bf16(fma(sa, acc * sw, bias))`` -- ``torch._scaled_mm(aq, wq.t(), sa, sw, bias)``.  q e4m3 (or its
+        bytes) ``[M, K]``, scale fp32 ``[M]``, weight_row_scale = ``self.weight_row_scale('fp8_e4m3fn')``."""
+        if q.dim() != 2 or q.shape[1] != self.in_features:
+            raise ValueError("q must be [M, in_features]")
+        if not q.is_cuda or q.device != self.codebook.device:
+            raise ValueError("Matching CUDA operands required")
+        if q.dtype not in (torch.float8_e4m3fn, torch.uint8):
+            raise TypeError("q must be float8_e4m3fn (or its bytes as uint8)")
+        q = q.contiguous()
+        scale = scale.reshape(-1).to(torch.float32).contiguous()
+        sw = weight_row_scale.reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
+        m = q.shape[0]
+        if scale.numel() != m or sw.numel() != self.out_features:
+            raise ValueError("scale needs one entry per row of q, weight_row_scale one per output feature")
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=torch.bfloat16, device=q.device)
+        buf = _Workspace.get(q.device).scratch(int(self._lib.sacq_workspace_bytes_w8a8(self._handle, m)))
+        with torch.cuda.device(q.device):
+            _lib.check(self._lib.sacq_linear_w8a8_fp8(self._handle, q.data_ptr(), scale.data_ptr(), sw.data_ptr(), m,
+                                                      out.data_ptr(), out.stride(0), buf.data_ptr(), buf.numel(),
+                                                      _stream_ptr()))
+        return out
+
     def decode_weight_fp8(self, weight_row_scale: torch.Tensor) -> torch.Tensor:
         """e4m3 [N, K] = e4m3(clamp(W / row_scale)) decoded straight from the packed stream."""
         sw = weight_row_scale.to(device=self.codebook.device, dtype=torch.float32).contiguous()

@@ -770,6 +770,42 @@ def test_int8_recipe_deployed_layouts(N, K, d, C, G, with_bias):
     assert mod.device_status() == 0
 
 
+@pytest.mark.parametrize("N,K,d,C,G,with_bias", [
+    (2048, 2048, 4, 128, 64, True), (6144, 2048, 4, 1024, 64, False), (2048, 6144, 4, 32, 64, True),
+    (2048, 2048, 8, 4096, None, True), (200, 144, 8, 256, None, False)])
+def test_fp8_recipe_against_oracle(N, K, d, C, G, with_bias):
+    """The reference's FP8 recipe (per-row e4m3 weights x per-token e4m3 activations, fp32 accumulation,
+    scale order weight then token, bias in the same fma): the operands are the reference's bytes
+    (weight bytes and row scales against the CPU restatement), the product is compared with the
+    float64 evaluation of the same operands (fp32 summation order is the tensor core's)."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear, quantize_rows
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N + C, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.05).to(torch.bfloat16) if with_bias else None
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    wq_ref, sw_ref = O.quantize_weight_rows_e4m3(w_bits)
+    sw = mod.weight_row_scale("fp8_e4m3fn")
+    assert np.array_equal(sw.cpu().numpy().view(np.uint32).ravel(), sw_ref.view(np.uint32).ravel())
+    assert np.array_equal(mod.decode_weight_fp8(sw).view(torch.uint8).cpu().numpy(), wq_ref)
+    for M in (1, 41, 300, 600):
+        x = make_activations(M, K, seed=M + 4)
+        q_ref, sa_ref = O.quantize_rows_e4m3(bf16_bits(x))
+        q, sa = quantize_rows(x.cuda())
+        y = mod.linear_w8a8_fp8(q, sa, sw)
+        want = O.linear_w8a8_fp8_reference(q_ref, sa_ref, wq_ref, sw_ref, None if bias is None else bf16_bits(bias))
+        assert O.rel_frobenius(y.float().cpu().numpy(), want) <= 3e-3, M      # bf16 rounding of the output: 2.3e-3
+        assert torch.equal(y, mod.linear_w8a8_fp8(q, sa, sw))
+        # the recipe re-quantizes the weights: it stays near, not at, the exact-weight product
+        exact = mod.linear_a8(q, sa)
+        assert O.rel_frobenius(y.float().cpu().numpy(), exact.float().cpu().numpy()) <= 6e-2, M
+        out = torch.full((M, N + 8), 3.0, dtype=torch.bfloat16, device="cuda")
+        mod.linear_w8a8_fp8(q, sa, sw, out=out[:, :N])
+        assert torch.equal(out[:, :N], y) and float(out[:, N:].float().min()) == 3.0
+    assert mod.device_status() == 0
+
+
 @pytest.mark.parametrize("M,K", [(16, 1536), (1, 2048), (300, 1024), (5, 100)])
 def test_modulation_fused_into_quantizer(M, K):
     """x * (1 + scale) + shift fused into the quantizer: bytes and scales of quantizing the

@@ -121,6 +121,26 @@ def test_int8_activation_quantizer_matches_reference_fixture():
     assert list(q[5, 1:5]) == [0, 2, 2, 4] and float(s[1, 0]) == 1.0
 
 
+def test_fp8_recipe_reference_on_fixture_operands():
+    """The FP8 recipe's CPU evaluation on the reference-generated operands of a fixture (e4m3
+    activation bytes, per-row e4m3 weight bytes, both scale vectors): equal to a plain float64
+    evaluation written out element by element, and within the weight re-quantization error of the
+    exact-weight product the same fixture holds."""
+    f = load_golden("layer_d8_c4096_b12")
+    bias = f["bias"] if "bias" in f else None
+    y = O.linear_w8a8_fp8_reference(f["q"], f["act_scale"], f["wq"], f["w_scale"], bias)
+    a = O.e4m3_bits_to_f32(f["q"]).astype(np.float64)
+    w = O.e4m3_bits_to_f32(f["wq"]).astype(np.float64)
+    m, n = 1, 3
+    acc = sum(a[m, k] * w[n, k] for k in range(a.shape[1]))
+    val = float(f["act_scale"].reshape(-1)[m]) * (acc * float(f["w_scale"].reshape(-1)[n]))
+    if bias is not None:
+        val += float(O.bf16_bits_to_f32(bias)[n])
+    assert abs(float(y[m, n]) - val) <= 2.0 ** -8 * abs(val) + 1e-30
+    exact = O.bf16_bits_to_f32(f["y_ref"]) if f["y_ref"].dtype == np.uint16 else f["y_ref"]
+    assert O.rel_frobenius(y, exact) < 6e-2
+
+
 def test_nonfinite_activations_match_reference_fixture():
     """A NaN in a row: scale 1 (the reference's `maximum > 0` is false for NaN) and the NaN stays a
     NaN; an infinity: infinite scale, zeros for the finite elements, NaN for the infinite ones."""
