@@ -172,6 +172,18 @@ __device__ __forceinline__ uint16_t reconstruct_bf16(uint32_t c_bits, float s, f
   return float_to_bf16_bits(__fadd_rn(p, shift));
 }
 
+// Two weights at once, packed (low half = first): the conversions are the paired instruction
+// (cvt.rn.bf16x2.f32), which halves the load on the conversion pipe that bounds the reconstruction
+// kernels.  Same bits as two reconstruct_bf16 calls.
+__device__ __forceinline__ uint32_t reconstruct_bf16x2(uint32_t c0_bits, uint32_t c1_bits, float s, float shift) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(__fmul_rn(bf16_bits_to_float(c0_bits), s),
+                                                 __fmul_rn(bf16_bits_to_float(c1_bits), s));
+  const uint32_t pb = *reinterpret_cast<const uint32_t*>(&p);
+  const __nv_bfloat162 w = __floats2bfloat162_rn(__fadd_rn(__uint_as_float(pb << 16), shift),
+                                                 __fadd_rn(__uint_as_float(pb & 0xffff0000u), shift));
+  return *reinterpret_cast<const uint32_t*>(&w);
+}
+
 // One e4m3 byte from a float with RNE and saturation; callers clamp first so
 // saturation never changes a value.
 __device__ __forceinline__ uint32_t float2_to_e4m3x2(float lo, float hi) {

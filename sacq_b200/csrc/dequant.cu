@@ -52,7 +52,8 @@ dequant_bf16_kernel(const uint32_t* __restrict__ words, const uint16_t* __restri
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vectors; i += stride) {
     const uint32_t idx = extract_index(words, i, bits);
-    const int64_t n = i / vpr;
+    // 32-bit arithmetic where it fits: a 64-bit division costs several times the rest of the index math
+    const int64_t n = total_vectors <= 0x7fffffffLL ? (int64_t)((uint32_t)i / (uint32_t)vpr) : i / vpr;
     const int v = (int)(i - n * vpr);
     const int g = (v * d) / group_size;
     const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + g));
@@ -62,8 +63,7 @@ dequant_bf16_kernel(const uint32_t* __restrict__ words, const uint16_t* __restri
       uint32_t o[D / 2];
 #pragma unroll
       for (int j = 0; j < D / 2; ++j) {
-        o[j] = (uint32_t)reconstruct_bf16(c[2 * j], s, shift) |
-               ((uint32_t)reconstruct_bf16(c[2 * j + 1], s, shift) << 16);
+        o[j] = reconstruct_bf16x2(c[2 * j], c[2 * j + 1], s, shift);
       }
       typename VecStore<D>::T* dst = reinterpret_cast<typename VecStore<D>::T*>(w_out) + i;
       if constexpr (D == 8) *dst = make_uint4(o[0], o[1], o[2], o[3]);
