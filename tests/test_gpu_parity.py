@@ -104,7 +104,8 @@ def test_act_quant_matches_reference_fixture(name):
     assert np.array_equal(s.cpu().numpy().view(np.uint32), g["act_scale"].view(np.uint32))
 
 
-@pytest.mark.parametrize("M,K", [(1, 2048), (4, 2048), (16, 2048), (64, 6144), (3, 100), (5, 8200), (2, 7), (300, 1536)])
+@pytest.mark.parametrize("M,K", [(1, 2048), (4, 2048), (16, 2048), (64, 6144), (3, 100), (5, 8200), (2, 7), (300, 1536),
+                                 (1000, 2048), (257, 8), (256, 2056), (300, 6144)])
 def test_act_quant_against_oracle(M, K):
     _need_gpu()
     from sacq_b200 import quantize_rows
@@ -655,6 +656,11 @@ def test_nonfinite_activations_are_not_hidden():
     canon = lambda b: np.where((b & 0x7F) == 0x7F, 0x7F, b)
     assert np.array_equal(canon(got), canon(f["q"]))
     assert np.array_equal(s.cpu().numpy().view(np.uint32).ravel(), f["s"].ravel())
+    # the batched (one warp per row) quantizer takes over from 256 rows: same bytes for the same rows
+    many = from_bf16_bits(f["x"]).repeat(50, 1).cuda()
+    qm, sm = quantize_rows(many)
+    assert np.array_equal(canon(qm.view(torch.uint8).cpu().numpy()), canon(np.tile(f["q"], (50, 1))))
+    assert np.array_equal(sm.cpu().numpy().view(np.uint32).ravel(), np.tile(f["s"].ravel(), 50))
     # the fused producers use the same reduction: a NaN gate makes the row's scale 1, not a finite maximum
     from sacq_b200 import act_quantize_rows
     a = from_bf16_bits(f["x"]).cuda()
@@ -673,8 +679,10 @@ def test_int8_activation_quantizer():
     assert q.dtype == torch.int8
     assert np.array_equal(q.cpu().numpy(), f["q"])
     assert np.array_equal(s.cpu().numpy().view(np.uint32), f["s"].view(np.uint32))
-    for M, K in ((1, 2048), (64, 6144), (3, 100), (5, 8200), (2, 7)):
+    for M, K in ((1, 2048), (64, 6144), (3, 100), (5, 8200), (2, 7), (300, 1536), (1000, 2048), (256, 2056)):
         x = make_activations(M, K, seed=M + K)
+        if M > 2:
+            x[1].zero_()
         qo, so = O.quantize_rows_int8(bf16_bits(x))
         q, s = quantize_rows(x.cuda(), "int8_symmetric")
         assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy().view(np.uint32), so.view(np.uint32))
