@@ -106,11 +106,24 @@ decode_weight_fp8_kernel(const uint32_t* __restrict__ words, const uint16_t* __r
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vectors; i += stride) {
     const uint32_t idx = extract_index(words, i, bits);
-    const int64_t n = i / vpr;
+    // 32-bit arithmetic where it fits: a 64-bit division costs several times the rest of the index math
+    const int64_t n = total_vectors <= 0x7fffffffLL ? (int64_t)((uint32_t)i / (uint32_t)vpr) : i / vpr;
     const int v = (int)(i - n * vpr);
     const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
     const float row = __ldg(sw + n);
-    if ((d & 1) == 0) {
+    auto enc2 = [&](uint32_t pair_bits) -> uint32_t {           // two codeword elements (one bf16 pair) -> two bytes
+      const float a = bf16_bits_to_float(reconstruct_bf16(pair_bits & 0xffffu, s, shift));
+      const float b = bf16_bits_to_float(reconstruct_bf16(pair_bits >> 16, s, shift));
+      return float2_to_e4m3x2(clamp448(__fdiv_rn(a, row)), clamp448(__fdiv_rn(b, row)));
+    };
+    if (d == 8 && ((reinterpret_cast<uintptr_t>(cb) & 15) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 7) == 0)) {
+      // one 16-byte codeword load, one 8-byte store
+      const uint4 c = __ldg(reinterpret_cast<const uint4*>(cb) + idx);
+      *reinterpret_cast<uint2*>(wq + i * 8) = make_uint2(enc2(c.x) | (enc2(c.y) << 16), enc2(c.z) | (enc2(c.w) << 16));
+    } else if (d == 4 && ((reinterpret_cast<uintptr_t>(cb) & 7) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 3) == 0)) {
+      const uint2 c = __ldg(reinterpret_cast<const uint2*>(cb) + idx);
+      *reinterpret_cast<uint32_t*>(wq + i * 4) = enc2(c.x) | (enc2(c.y) << 16);
+    } else if ((d & 1) == 0) {
       for (int j = 0; j < d; j += 2) {
         const float a = bf16_bits_to_float(reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j), s, shift));
         const float b = bf16_bits_to_float(reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j + 1), s, shift));
