@@ -112,9 +112,9 @@ decode_weight_fp8_kernel(const uint32_t* __restrict__ words, const uint16_t* __r
     const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
     const float row = __ldg(sw + n);
     auto enc2 = [&](uint32_t pair_bits) -> uint32_t {           // two codeword elements (one bf16 pair) -> two bytes
-      const float a = bf16_bits_to_float(reconstruct_bf16(pair_bits & 0xffffu, s, shift));
-      const float b = bf16_bits_to_float(reconstruct_bf16(pair_bits >> 16, s, shift));
-      return float2_to_e4m3x2(clamp448(__fdiv_rn(a, row)), clamp448(__fdiv_rn(b, row)));
+      const uint32_t w = reconstruct_bf16x2(pair_bits & 0xffffu, pair_bits >> 16, s, shift);
+      return float2_to_e4m3x2(clamp448(__fdiv_rn(__uint_as_float(w << 16), row)),
+                              clamp448(__fdiv_rn(__uint_as_float(w & 0xffff0000u), row)));
     };
     if (d == 8 && ((reinterpret_cast<uintptr_t>(cb) & 15) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 7) == 0)) {
       // one 16-byte codeword load, one 8-byte store
@@ -156,15 +156,20 @@ decode_weight_int8_kernel(const uint32_t* __restrict__ words, const uint16_t* __
     const int v = (int)(i - n * vpr);
     const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
     const float row = __ldg(sw + n);
-    auto enc_bits = [&](uint32_t c_bits) -> uint32_t {
-      const float a = bf16_bits_to_float(reconstruct_bf16(c_bits, s, shift));
+    // round_half_even(clamp(a / row, +-127)) as a byte.  The rounding is the add of 1.5 * 2^23 (exact RNE for
+    // |q| < 2^22; q is clamped to 127), which keeps the float -> int conversion off the conversion pipe that
+    // bounds this kernel (ncu: 72 % busy with the reciprocal, two bf16 roundings and one F2I per weight).
+    auto q_byte = [&](float a) -> uint32_t {
       const float q = fminf(fmaxf(__fdiv_rn(a, row), -127.f), 127.f);
-      return (uint32_t)(__float2int_rn(q) & 0xff);
+      return (uint32_t)(__float_as_int(__fadd_rn(q, 12582912.0f)) - 0x4B400000) & 0xffu;
     };
+    auto enc_bits = [&](uint32_t c_bits) -> uint32_t { return q_byte(bf16_bits_to_float(reconstruct_bf16(c_bits, s, shift))); };
     auto enc = [&](int j) -> uint32_t { return enc_bits(__ldg(cb + (int64_t)idx * d + j)); };
-    auto enc4 = [&](uint32_t w0, uint32_t w1) -> uint32_t {     // four codeword elements (two bf16 pairs) -> four bytes
-      return enc_bits(w0 & 0xffffu) | (enc_bits(w0 >> 16) << 8) | (enc_bits(w1 & 0xffffu) << 16) | (enc_bits(w1 >> 16) << 24);
+    auto enc2 = [&](uint32_t pair) -> uint32_t {                // one bf16 pair of the codeword -> two bytes
+      const uint32_t w = reconstruct_bf16x2(pair & 0xffffu, pair >> 16, s, shift);
+      return q_byte(__uint_as_float(w << 16)) | (q_byte(__uint_as_float(w & 0xffff0000u)) << 8);
     };
+    auto enc4 = [&](uint32_t w0, uint32_t w1) -> uint32_t { return enc2(w0) | (enc2(w1) << 16); };
     if (d == 8 && ((reinterpret_cast<uintptr_t>(cb) & 15) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 7) == 0)) {
       // one 16-byte codeword load, one 8-byte store
       const uint4 c = __ldg(reinterpret_cast<const uint4*>(cb) + idx);
