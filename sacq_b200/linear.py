@@ -27,8 +27,16 @@ from .packing import check_index_range, index_bits_for, index_window_bytes, pack
 _REQUIRED = ("codebook", "scales", "in_features", "out_features", "group_size", "vector_dim")
 
 
-def _stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream_ptr(index: int | None = None) -> int:
+    """The current CUDA stream of device ``index`` (default: the current device) as an integer handle.
+    The raw getter skips building a ``torch.cuda.Stream`` object, which costs more than a microsecond per
+    call -- a visible share of a decode-sized layer call, whose whole host side is a few microseconds."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device() if index is None else index)
+    return (torch.cuda.current_stream() if index is None else torch.cuda.current_stream(index)).cuda_stream
 
 
 class _Workspace:
@@ -49,7 +57,7 @@ class _Workspace:
     @classmethod
     def get(cls, device: torch.device) -> "_Workspace":
         idx = device.index if device.index is not None else torch.cuda.current_device()
-        key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+        key = (idx, _stream_ptr(idx))
         w = cls._by_device.get(key)
         if w is None:
             w = cls(torch.device("cuda", idx))
@@ -154,6 +162,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         self.runtime_kernel_eligible = True
         self._ws_bytes = {}
         self._host_bytes = {}
+        self._dev = device_obj                        # plain attribute: a buffer lookup per call costs a microsecond
         self._handle = None
         self._create_handle()
 
@@ -385,7 +394,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape[-1] != self.in_features:
             raise ValueError("Linear shape mismatch")
-        dev = self.codebook.device
+        dev = self._dev
         if not x.is_cuda or x.device != dev:
             raise ValueError("Matching CUDA operands required")
         a = x if x.dim() == 2 else x.reshape(-1, self.in_features)
@@ -405,12 +414,12 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
             if torch.cuda.current_device() == dev.index:
                 rc = self._lib.sacq_linear_bf16(
                     self._handle, a.data_ptr(), a.stride(0), m, q.data_ptr(), s.data_ptr(), y.data_ptr(),
-                    y.stride(0), buf.data_ptr(), buf.numel(), torch.cuda.current_stream().cuda_stream)
+                    y.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr(dev.index))
             else:
                 with torch.cuda.device(dev):
                     rc = self._lib.sacq_linear_bf16(
                         self._handle, a.data_ptr(), a.stride(0), m, q.data_ptr(), s.data_ptr(), y.data_ptr(),
-                        y.stride(0), buf.data_ptr(), buf.numel(), torch.cuda.current_stream().cuda_stream)
+                        y.stride(0), buf.data_ptr(), buf.numel(), _stream_ptr(dev.index))
             if rc != 0:
                 _lib.check(rc)
         if x.dim() != 2:
@@ -429,7 +438,7 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
         m = x_host.shape[0]
         if out_host is None:
             out_host = torch.empty((m, self.out_features), dtype=torch.bfloat16, pin_memory=x_host.is_pinned())
-        dev = self.codebook.device
+        dev = self._dev
         need = self._host_bytes.get(m)
         if need is None:
             need = self._host_bytes[m] = int(self._lib.sacq_host_forward_scratch_bytes(self._handle, m))
@@ -438,10 +447,9 @@ class PrecomputedPackedVectorCodebookLinear(torch.nn.Module):
             ws.host_scratch = torch.zeros(max(need, 1 << 22), dtype=torch.uint8, device=dev)
         buf = ws.host_scratch
         if m > 0 and self.out_features > 0:
-            with torch.cuda.device(dev):
-                rc = self._lib.sacq_linear_bf16_host(self._handle, x_host.data_ptr(), m, out_host.data_ptr(),
-                                                     buf.data_ptr(), buf.numel(),
-                                                     torch.cuda.current_stream().cuda_stream)
+            # the library switches to the layer's device itself; the stream is that device's current one
+            rc = self._lib.sacq_linear_bf16_host(self._handle, x_host.data_ptr(), m, out_host.data_ptr(),
+                                                 buf.data_ptr(), buf.numel(), _stream_ptr(dev.index))
             if rc != 0:
                 _lib.check(rc)
         return out_host
