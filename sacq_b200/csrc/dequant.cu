@@ -55,7 +55,7 @@ dequant_bf16_kernel(const uint32_t* __restrict__ words, const uint16_t* __restri
     // 32-bit arithmetic where it fits: a 64-bit division costs several times the rest of the index math
     const int64_t n = total_vectors <= 0x7fffffffLL ? (int64_t)((uint32_t)i / (uint32_t)vpr) : i / vpr;
     const int v = (int)(i - n * vpr);
-    const int g = (v * d) / group_size;
+    const int g = num_groups == 1 ? 0 : (v * d) / group_size;     // one scale per row: no division
     const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + g));
     if constexpr (D != 0) {
       uint32_t c[D];
@@ -87,7 +87,7 @@ weight_row_scale_kernel(const uint32_t* __restrict__ words, const uint16_t* __re
   float m = 0.f;
   for (int v = lane; v < vpr; v += 32) {
     const uint32_t idx = extract_index(words, n * vpr + v, bits);
-    const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
+    const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (num_groups == 1 ? 0 : (v * d) / group_size)));
     for (int j = 0; j < d; ++j) {
       const uint16_t w = reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j), s, shift);
       m = fmaxf(m, fabsf(bf16_bits_to_float(w)));
@@ -109,7 +109,7 @@ decode_weight_fp8_kernel(const uint32_t* __restrict__ words, const uint16_t* __r
     // 32-bit arithmetic where it fits: a 64-bit division costs several times the rest of the index math
     const int64_t n = total_vectors <= 0x7fffffffLL ? (int64_t)((uint32_t)i / (uint32_t)vpr) : i / vpr;
     const int v = (int)(i - n * vpr);
-    const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
+    const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (num_groups == 1 ? 0 : (v * d) / group_size)));
     const float row = __ldg(sw + n);
     auto enc2 = [&](uint32_t pair_bits) -> uint32_t {           // two codeword elements (one bf16 pair) -> two bytes
       const uint32_t w = reconstruct_bf16x2(pair_bits & 0xffffu, pair_bits >> 16, s, shift);
@@ -154,7 +154,7 @@ decode_weight_int8_kernel(const uint32_t* __restrict__ words, const uint16_t* __
     // 32-bit arithmetic where it fits: a 64-bit division costs several times the rest of the index math
     const int64_t n = total_vectors <= 0x7fffffffLL ? (int64_t)((uint32_t)i / (uint32_t)vpr) : i / vpr;
     const int v = (int)(i - n * vpr);
-    const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (v * d) / group_size));
+    const float s = bf16_bits_to_float(__ldg(scales + n * num_groups + (num_groups == 1 ? 0 : (v * d) / group_size)));
     const float row = __ldg(sw + n);
     // round_half_even(clamp(a / row, +-127)) as a byte.  The rounding is the add of 1.5 * 2^23 (exact RNE for
     // |q| < 2^22; q is clamped to 127), which keeps the float -> int conversion off the conversion pipe that
