@@ -18,7 +18,8 @@ GEMM kernels); `e2e` through the module's forward with host buffers (pinned H2D 
 activations and D2H of the result inside the timed region); `roofline` for the dominant kernel
 (small-M GEMM; algorithmic bytes / its mean launch time measured with CUDA events on a graph
 that holds only that kernel); `cpu_baseline` = the reference's CPU path (PyTorch ops, all host
-threads) on the same sweep.  Further objects carry the rest of the metric, each timed with CUDA
+threads) on the same sweep, with the C restatement of the same arithmetic (all threads and one
+thread) beside it as `cpu_baseline.c_restatement`.  Further objects carry the rest of the metric, each timed with CUDA
 events over graph replays that rotate through more than two L2 sizes of distinct operands:
 
   `large_m`      batched sweep: 2048x6144 and 6144x2048 at M in {256, 1024, 4096, 8192}; us,
@@ -172,6 +173,43 @@ def run_cpu_reference(steps: int, warmup: int):
         step()
     dt = time.perf_counter() - t0
     return dt, threads
+
+
+def run_c_restatement(passes: int):
+    """The same sweep through the C restatement (oracle/sacq_oracle.c: unpack, two-rounding bf16
+    reconstruction, per-row e4m3 quantizer, fp32 dot products; OpenMP over output rows): seconds
+    per pass with all threads and with one, so that there is a CPU figure that does not depend
+    on PyTorch's kernels."""
+    import numpy as np
+    from oracle import build_oracle as C
+
+    def bits(t):
+        return t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    layers = {}
+    for name, p in cpu_sweep_payloads().items():
+        N, K = int(p["out_features"]), int(p["in_features"])
+        layers[name] = (p["packed_indices"].numpy(), int(p["index_bits"]), bits(p["codebook"]),
+                        bits(p["scales"]).reshape(N, -1), int(bits(p["shift"].reshape(1))[0]), None, N, K,
+                        int(p["group_size"]))
+    xs = {(name, M): bits(make_activations(M, K, seed=M)) for (name, K, N, M) in sweep_calls()}
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for name, K, N, M in sweep_calls():
+            q, s = C.quant_rows(xs[(name, M)])
+            C.linear(*layers[name], q, s)
+        return time.perf_counter() - t0
+
+    all_threads = C.threads()
+    one_pass()
+    t_all = min(one_pass() for _ in range(passes))
+    C.set_threads(1)
+    try:
+        t_one = one_pass()
+    finally:
+        C.set_threads(all_threads)
+    return t_all, all_threads, t_one
 
 
 def reference_main(args):
@@ -700,6 +738,12 @@ def gpu_main(args):
                 "value": dt / (cpu_steps * n_calls) * 1e6, "unit": UNIT, "cores": threads, "kind": "port",
                 "sample": f"the same 35-call sweep, {cpu_steps} passes after 1 warm-up, PyTorch CPU ops as the "
                           "reference runs them (random-index layers of the same shapes)"}
+            t_all, c_threads, t_one = run_c_restatement(2)
+            line["cpu_baseline"]["c_restatement"] = {
+                "value": t_all / n_calls * 1e6, "unit": UNIT, "cores": c_threads,
+                "value_one_thread": t_one / n_calls * 1e6,
+                "sample": "the same sweep through oracle/sacq_oracle.c (gcc -O3, OpenMP over output rows): best of 2 "
+                          "passes with all threads, one pass with a single thread"}
         print(json.dumps(line), flush=True)
     if ctx.dist is not None:
         ctx.dist.destroy_process_group()

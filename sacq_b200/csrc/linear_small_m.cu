@@ -441,13 +441,18 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
     int best = 1;
     bool best_staged = false;
     double best_cost = -1.0;
-    for (int r8 = 1; r8 <= 4; r8 *= 2) {
-      if ((halves_req == 2 && r8 > 2) || (halves_req == 1 && r8 <= 2)) continue;
+    // 48-row tiles (r8 = 6, staged kernel only): a 6144-row layer is then ONE tile on each of 128 SMs
+    // instead of three 16-row tiles on each of 148, which saves two of the three per-tile round trips
+    // (index wait, CTA barrier, cross-warp reduction, epilogue: about 1 us each)
+    const int r8_choices[4] = {1, 2, 4, 6};
+    for (int ci = 0; ci < 4; ++ci) {
+      const int r8 = r8_choices[ci];
+      if (halves_req != 0 && staged_halves(r8) != halves_req) continue;
       const int64_t row_tiles = (sub + r8 - 1) / r8;
       // staged kernel: a CTA walks row tiles and, inside each, all token chunks; the fixed
       // start-up (launch, codebook copy) is paid once.  Unit = one sub-block of one span set.
       // tiles of at most 16 rows run two warps per span (up to 16 warps per CTA)
-      const int halves = r8 <= 2 ? 2 : 1;
+      const int halves = staged_halves(r8);
       const int st_warps = pl.spans_per_row * halves < kMaxWarps * halves ? pl.spans_per_row * halves
                                                                           : kMaxWarps * halves;
       const size_t need = small_m_mma_staged_smem(L->cb_entries, d.vector_dim, (int)d.in_features,
@@ -459,7 +464,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
         const int64_t waves = (row_tiles + stride - 1) / stride;
         const double cost = 3.0 + (double)waves * (0.2 + 0.6 * r8);
         if (best_cost < 0 || cost < best_cost - 1e-9 || !best_staged) { best_cost = cost; best = r8; best_staged = true; }
-      } else if (!best_staged) {
+      } else if (!best_staged && r8 <= 4) {
         const int64_t tiles = row_tiles * pl.chunks;
         const int64_t waves = (tiles + L->num_sms - 1) / L->num_sms;
         const double cost = (double)waves * (3 + r8);
@@ -484,7 +489,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
     if (pl.grid < 1) pl.grid = 1;
     pl.act_bufs = 1;
     if (pl.staged) {
-      const int halves = pl.r8 <= 2 ? 2 : 1;
+      const int halves = staged_halves(pl.r8);
       pl.warps = pl.spans_per_row * halves < kMaxWarps * halves ? pl.spans_per_row * halves : kMaxWarps * halves;
     }
     pl.smem = pl.staged ? small_m_mma_staged_smem(L->cb_entries, d.vector_dim, (int)d.in_features, L->row_bits / 8,
@@ -690,7 +695,7 @@ int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, 
   for (int l = 0; l < n; ++l) {
     const Plan one = make_plan(layers[l], M);
     if (!one.mma || !one.staged || one.unpacked) return SACQ_ERR_UNSUPPORTED;
-    const int h = one.r8 <= 2 ? 2 : 1;
+    const int h = staged_halves(one.r8);
     if (halves != 0 && h != halves) return SACQ_ERR_UNSUPPORTED;
     halves = h;
   }
@@ -698,7 +703,7 @@ int launch_small_m_multi(const sacq_layer* const* layers, int n, const void* q, 
   sacq_layer virt = *L0;
   virt.d.out_features = n_total;
   Plan pl = make_plan(&virt, M, halves);
-  if (!pl.mma || !pl.staged || pl.unpacked || pl.smem > kSmemBudget || (pl.r8 <= 2 ? 2 : 1) != halves)
+  if (!pl.mma || !pl.staged || pl.unpacked || pl.smem > kSmemBudget || staged_halves(pl.r8) != halves)
     return SACQ_ERR_UNSUPPORTED;
   const int rows_per_tile = 8 * pl.r8;
   int rb[kMaxMulti], stride[kMaxMulti];

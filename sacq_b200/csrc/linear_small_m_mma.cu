@@ -32,7 +32,7 @@ __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// D in {4, 8}; BITS in {8, 12, 16}; R8 = 8-row sub-blocks per tile.
+// D in {4, 8}; BITS in {8, 12, 16}; R8 = 8-row sub-blocks per tile (1, 2, 4; the staged variant also 6).
 //
 // Work decomposition: a CTA owns a tile of 16 tokens x (8*R8) output rows and loops over
 // tiles; its warps split the row's 32-index spans among themselves (warp w takes spans w,
@@ -291,7 +291,7 @@ __host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64
   L.act_off = L.idx_off + 2 * (uint32_t)((8 * r8 * row_bytes + 127) & ~127);
   L.red_off = L.act_off + (uint32_t)act_bufs * (uint32_t)((16 * (K + kActPad) + 127) & ~127);
   L.sa_off = L.red_off + (uint32_t)(warps * r8 * 4 * 32 * 4);
-  L.bar_off = L.sa_off + 384;             // 16 token scales + 32 row scales + 32 row biases
+  L.bar_off = L.sa_off + 512;             // 16 token scales + 48 row scales + 48 row biases
   L.total = L.bar_off + 64;
   return L;
 }
@@ -333,7 +333,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   float* red = reinterpret_cast<float*>(smem + L.red_off);
   float* sa_s = reinterpret_cast<float*>(smem + L.sa_off);          // [16] token scales of the current chunk
   float* rowsc_s = sa_s + 16;                                         // [8*R8] scale of the tile's rows (group 0)
-  float* rowb_s = rowsc_s + 32;                                       // [8*R8] bias of the tile's rows
+  float* rowb_s = rowsc_s + 48;                                       // [8*R8] bias of the tile's rows
   const uint32_t bar_cb = sm_addr(smem + L.bar_off), bar_act0 = bar_cb + 8, bar_idx0 = bar_cb + 24;
   const int act_pitch = p.K + kActPad;
   const uint32_t idx_buf_bytes = (L.act_off - L.idx_off) / 2;
@@ -508,74 +508,80 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
         xs_a += ta;
         xs_b += tb;
       }
-      uint32_t wcur[R8][WPG];
+      // Sub-blocks are processed RG at a time: their step accumulators interleave (independent MMA
+      // chains), while the 48-row tile keeps only half of them live at once (register budget).
+      constexpr int RG = R8 == 6 ? 3 : R8;
 #pragma unroll
-      for (int r = 0; r < R8; ++r) {
-        const int rr = min(r * 8 + g, rows_here - 1);
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(idx_s + (int64_t)rr * p.row_bytes + sp * (4 * BITS) + t * BITS);
+      for (int r0 = 0; r0 < R8; r0 += RG) {
+        uint32_t wcur[RG][WPG];
 #pragma unroll
-        for (int j = 0; j < WPG; ++j) wcur[r][j] = src[j];
-      }
-      // two accumulators per sub-block (even / odd steps) halve the dependent MMA chain
-      float cs[R8][4], ct[R8][4];
+        for (int r = 0; r < RG; ++r) {
+          const int rr = min((r0 + r) * 8 + g, rows_here - 1);
+          const uint32_t* src = reinterpret_cast<const uint32_t*>(idx_s + (int64_t)rr * p.row_bytes + sp * (4 * BITS) + t * BITS);
 #pragma unroll
-      for (int r = 0; r < R8; ++r)
+          for (int j = 0; j < WPG; ++j) wcur[r][j] = src[j];
+        }
+        // two accumulators per sub-block (even / odd steps) halve the dependent MMA chain
+        float cs[RG][4], ct[RG][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { cs[r][j] = 0.f; ct[r][j] = 0.f; }
-      // the half index selects compile-time field positions, so dispatch on it once
-      auto mma_steps = [&](auto HF) {
-        constexpr int kFirst = decltype(HF)::value * NS;
-        if constexpr (D == 8) {
-          // one codeword per step: 16 bytes = e4m3 high half | low half
+        for (int r = 0; r < RG; ++r)
 #pragma unroll
-          for (int s8 = 0; s8 < NS; ++s8) {
+          for (int j = 0; j < 4; ++j) { cs[r][j] = 0.f; ct[r][j] = 0.f; }
+        // the half index selects compile-time field positions, so dispatch on it once
+        auto mma_steps = [&](auto HF) {
+          constexpr int kFirst = decltype(HF)::value * NS;
+          if constexpr (D == 8) {
+            // one codeword per step: 16 bytes = e4m3 high half | low half
 #pragma unroll
-            for (int r = 0; r < R8; ++r) {
-              const uint4 c = cbs[field8<BITS>(wcur[r], kFirst + s8)];
-              float (&acc2)[4] = (s8 & 1) ? ct[r] : cs[r];
-              mma_m16n8k32_e4m3(acc2, fa[2 * s8], fb[2 * s8], fa[2 * s8 + 1], fb[2 * s8 + 1], c.x, c.y);
-              mma_m16n8k32_e4m3(acc2, fa[2 * s8], fb[2 * s8], fa[2 * s8 + 1], fb[2 * s8 + 1], c.z, c.w);
+            for (int s8 = 0; s8 < NS; ++s8) {
+#pragma unroll
+              for (int r = 0; r < RG; ++r) {
+                const uint4 c = cbs[field8<BITS>(wcur[r], kFirst + s8)];
+                float (&acc2)[4] = (s8 & 1) ? ct[r] : cs[r];
+                mma_m16n8k32_e4m3(acc2, fa[2 * s8], fb[2 * s8], fa[2 * s8 + 1], fb[2 * s8 + 1], c.x, c.y);
+                mma_m16n8k32_e4m3(acc2, fa[2 * s8], fb[2 * s8], fa[2 * s8 + 1], fb[2 * s8 + 1], c.z, c.w);
+              }
+            }
+          } else {
+            // two 4-byte codewords per step (8 bytes each = high | low)
+#pragma unroll
+            for (int s2 = 0; s2 < NS / 2; ++s2) {
+#pragma unroll
+              for (int r = 0; r < RG; ++r) {
+                const uint2 ca = cbs[field8<BITS>(wcur[r], kFirst + 2 * s2)];
+                const uint2 cb2 = cbs[field8<BITS>(wcur[r], kFirst + 2 * s2 + 1)];
+                float (&acc2)[4] = (s2 & 1) ? ct[r] : cs[r];
+                mma_m16n8k32_e4m3(acc2, fa[2 * s2], fb[2 * s2], fa[2 * s2 + 1], fb[2 * s2 + 1], ca.x, cb2.x);
+                mma_m16n8k32_e4m3(acc2, fa[2 * s2], fb[2 * s2], fa[2 * s2 + 1], fb[2 * s2 + 1], ca.y, cb2.y);
+              }
             }
           }
+        };
+        if constexpr (HALVES == 1) {
+          mma_steps(std::integral_constant<int, 0>{});
         } else {
-          // two 4-byte codewords per step (8 bytes each = high | low)
+          if (hf == 0) mma_steps(std::integral_constant<int, 0>{});
+          else mma_steps(std::integral_constant<int, 1>{});
+        }
 #pragma unroll
-          for (int s2 = 0; s2 < NS / 2; ++s2) {
+        for (int r = 0; r < RG; ++r)
 #pragma unroll
-            for (int r = 0; r < R8; ++r) {
-              const uint2 ca = cbs[field8<BITS>(wcur[r], kFirst + 2 * s2)];
-              const uint2 cb2 = cbs[field8<BITS>(wcur[r], kFirst + 2 * s2 + 1)];
-              float (&acc2)[4] = (s2 & 1) ? ct[r] : cs[r];
-              mma_m16n8k32_e4m3(acc2, fa[2 * s2], fb[2 * s2], fa[2 * s2 + 1], fb[2 * s2 + 1], ca.x, cb2.x);
-              mma_m16n8k32_e4m3(acc2, fa[2 * s2], fb[2 * s2], fa[2 * s2 + 1], fb[2 * s2 + 1], ca.y, cb2.y);
-            }
+          for (int j = 0; j < 4; ++j) cs[r][j] += ct[r][j];
+        if (p.num_groups > 1) {
+          const int grp = (sp * kSpanIdx * D) / p.group_size;
+#pragma unroll
+          for (int r = 0; r < RG; ++r) {
+            s0[r0 + r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn0[r0 + r] * p.num_groups + grp));
+            s1[r0 + r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn1[r0 + r] * p.num_groups + grp));
           }
         }
-      };
-      if constexpr (HALVES == 1) {
-        mma_steps(std::integral_constant<int, 0>{});
-      } else {
-        if (hf == 0) mma_steps(std::integral_constant<int, 0>{});
-        else mma_steps(std::integral_constant<int, 1>{});
-      }
 #pragma unroll
-      for (int r = 0; r < R8; ++r)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) cs[r][j] += ct[r][j];
-      if (p.num_groups > 1) {
-        const int grp = (sp * kSpanIdx * D) / p.group_size;
-#pragma unroll
-        for (int r = 0; r < R8; ++r) {
-          s0[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn0[r] * p.num_groups + grp));
-          s1[r] = bf16_bits_to_float(__ldg(p.scales + (int64_t)sn1[r] * p.num_groups + grp));
+        for (int r = 0; r < RG; ++r) {
+          acc[r0 + r][0] = fmaf(s0[r0 + r], cs[r][0], acc[r0 + r][0]);
+          acc[r0 + r][1] = fmaf(s1[r0 + r], cs[r][1], acc[r0 + r][1]);
+          acc[r0 + r][2] = fmaf(s0[r0 + r], cs[r][2], acc[r0 + r][2]);
+          acc[r0 + r][3] = fmaf(s1[r0 + r], cs[r][3], acc[r0 + r][3]);
         }
-      }
-#pragma unroll
-      for (int r = 0; r < R8; ++r) {
-        acc[r][0] = fmaf(s0[r], cs[r][0], acc[r][0]);
-        acc[r][1] = fmaf(s1[r], cs[r][1], acc[r][1]);
-        acc[r][2] = fmaf(s0[r], cs[r][2], acc[r][2]);
-        acc[r][3] = fmaf(s1[r], cs[r][3], acc[r][3]);
       }
     }
     SACQ_ST(8 + 6 * it + 2);
@@ -645,6 +651,7 @@ cudaError_t launch_staged(const Plan& pl, const SmallMParams& p, cudaStream_t s)
   switch (pl.r8) {
     case 1: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 1, 2>>(pl, p, s);
     case 2: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 2, 2>>(pl, p, s);
+    case 6: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 6, 2>>(pl, p, s);
     default: return launch_kernel_pdl<small_m_mma_staged_kernel<D, BITS, 4, 1>>(pl, p, s);
   }
 }
@@ -677,6 +684,7 @@ cudaError_t launch_staged_multi(const Plan& pl, const MultiParams& g, cudaStream
   switch (pl.r8) {
     case 1: return launch_multi_kernel<small_m_mma_staged_multi_kernel<D, BITS, 1, 2>>(pl, g, s);
     case 2: return launch_multi_kernel<small_m_mma_staged_multi_kernel<D, BITS, 2, 2>>(pl, g, s);
+    case 6: return launch_multi_kernel<small_m_mma_staged_multi_kernel<D, BITS, 6, 2>>(pl, g, s);
     default: return launch_multi_kernel<small_m_mma_staged_multi_kernel<D, BITS, 4, 1>>(pl, g, s);
   }
 }

@@ -131,7 +131,7 @@ struct Plan {
   int span_idx, spans_per_row, spans_per_item, num_sg, row_blocks, chunks;
   int64_t num_items;
   int warps, grid;
-  int r8;                    // warp-MMA variant: 8-row sub-blocks per tile (1, 2 or 4)
+  int r8;                    // warp-MMA variant: 8-row sub-blocks per tile (1, 2, 4; staged kernel also 6)
   bool staged;               // warp-MMA variant with bulk-copied tiles in shared memory
   int act_bufs;              // ... and how many activation tile buffers fit (1 or 2)
   bool unpacked;             // warp-MMA variant that unpacks indices to 16 bits in shared memory
@@ -186,6 +186,11 @@ cudaError_t launch_kernel_pdl(const Plan& pl, const SmallMParams& p, cudaStream_
 // linear_small_m_mma.cu
 cudaError_t launch_small_m_mma(const Plan& pl, const SmallMParams& p, cudaStream_t s);
 cudaError_t launch_small_m_mma_multi(const Plan& pl, const MultiParams& g, cudaStream_t s);
+// Warps that share one 32-index span in the staged warp-MMA kernel, by tile height: tiles of 8, 16 and
+// 48 rows run two lighter warps per span, the 32-row tile one.  The order in which an output's partial
+// sums are added depends on this number and on nothing else of the tile.
+inline int staged_halves(int r8) { return (r8 <= 2 || r8 == 6) ? 2 : 1; }
+
 // Shared memory the staged warp-MMA kernel needs for (layer, r8); 0 if it cannot run it.
 size_t small_m_mma_staged_smem(int C, int D, int K, int64_t row_bytes, int r8, int warps, int act_bufs);
 
