@@ -355,6 +355,14 @@ bool unpacked_eligible(const sacq_layer* L) {
   return true;
 }
 
+// Tallest tile (in 8-row sub-blocks) the planners may pick; compile-time switches for A/B measurements.
+#ifndef SACQ_STAGED_MAX_R8
+#define SACQ_STAGED_MAX_R8 6
+#endif
+#ifndef SACQ_UNPACKED_MAX_R8
+#define SACQ_UNPACKED_MAX_R8 6
+#endif
+
 // Fills the plan for that variant; false if no tile height fits shared memory.
 bool plan_unpacked(const sacq_layer* L, Plan& pl) {
   const sacq_layer_desc& d = L->d;
@@ -365,7 +373,10 @@ bool plan_unpacked(const sacq_layer* L, Plan& pl) {
   if (stride < 1) stride = 1;
   double best_cost = -1.0;
   int best = 0;
-  for (int r8 = 1; r8 <= 4; r8 *= 2) {
+  const int r8_choices[4] = {1, 2, 4, 6};                 // 48-row tiles: one tile per SM on 6144-row layers
+  for (int ci = 0; ci < 4; ++ci) {
+    const int r8 = r8_choices[ci];
+    if (r8 > SACQ_UNPACKED_MAX_R8) continue;
     const size_t need = small_m_mma_unpacked_smem(L->cb_entries, d.vector_dim, (int)d.in_features, L->row_bits / 8,
                                                   (int)L->num_groups, r8, warps);
     if (need > kSmemBudget) continue;
@@ -448,6 +459,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
     for (int ci = 0; ci < 4; ++ci) {
       const int r8 = r8_choices[ci];
       if (halves_req != 0 && staged_halves(r8) != halves_req) continue;
+      if (r8 > SACQ_STAGED_MAX_R8) continue;
       const int64_t row_tiles = (sub + r8 - 1) / r8;
       // staged kernel: a CTA walks row tiles and, inside each, all token chunks; the fixed
       // start-up (launch, codebook copy) is paid once.  Unit = one sub-block of one span set.

@@ -91,7 +91,7 @@ __host__ __device__ inline UnpLayout unp_layout(int C, int D, int K, int64_t row
   L.sc_off = L.act_off + (uint32_t)((16 * L.act_pitch + 127) & ~127);
   L.red_off = L.sc_off + (uint32_t)((rows * num_groups * 4 + 127) & ~127);
   L.sa_off = L.red_off + (uint32_t)(warps * r8 * 4 * 32 * 4);
-  L.bar_off = L.sa_off + 256;                                          // 16 token scales + 32 row biases
+  L.bar_off = L.sa_off + 256;                                          // 16 token scales + up to 48 row biases
   L.total = L.bar_off + 64;
   return L;
 }
@@ -311,6 +311,7 @@ cudaError_t launch_d(const Plan& pl, const SmallMParams& p, cudaStream_t s) {
   switch (pl.r8) {
     case 1: return launch_kernel_pdl<small_m_mma_unpacked_kernel<D, 1>>(pl, p, s);
     case 2: return launch_kernel_pdl<small_m_mma_unpacked_kernel<D, 2>>(pl, p, s);
+    case 6: return launch_kernel_pdl<small_m_mma_unpacked_kernel<D, 6>>(pl, p, s);
     default: return launch_kernel_pdl<small_m_mma_unpacked_kernel<D, 4>>(pl, p, s);
   }
 }

@@ -318,6 +318,28 @@ def test_linear_decode_shapes(K, N):
         assert torch.equal(mod(wide[:, :K]), outs["auto"][0])
 
 
+@pytest.mark.parametrize("N,K,d,C,G", [(5992, 2048, 8, 4096, None), (6144, 1536, 8, 4096, None), (5000, 2048, 4, 512, 64),
+                                       (6144, 2048, 4, 4096, None)])
+def test_linear_small_m_48_row_tiles(N, K, d, C, G):
+    """Layers wide enough that the warp-MMA kernels walk them in 48-row tiles (one tile per SM), with a
+    last tile of 40 or 8 rows: packed-index and index-unpacking variants against the oracle, and the
+    bytes of the CUDA-core kernel's neighbours where the variants must agree."""
+    _need_gpu()
+    from sacq_b200 import PrecomputedPackedVectorCodebookLinear
+    from sacq_b200.synthetic import make_activations, make_payload
+    p = make_payload(N, K, vector_dim=d, codebook_size=C, group_size=G, seed=N + C, device="cuda", iters=1)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(11)) * 0.05).to(torch.bfloat16)
+    mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
+    w_bits = oracle_weight(p)
+    for M in (1, 3, 16):
+        q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 7)))
+        outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias),
+                             kernels=("auto", "small_simt", "small_mma", "small_mma_unpacked"))
+        assert "small_mma_unpacked" in outs and ("small_mma" in outs or G is not None)
+        assert mod.kernel_for(M) == "small"
+        assert torch.equal(outs["auto"][0], outs["small_mma_unpacked" if G is not None else "small_mma"][0])
+
+
 @pytest.mark.parametrize("d,C", [(8, 256), (8, 4096), (8, 65536), (4, 4096)])
 @pytest.mark.parametrize("M", [1, 16, 256])
 def test_linear_mixed_bits(d, C, M):
