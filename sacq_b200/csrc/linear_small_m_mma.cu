@@ -237,6 +237,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) small_m_mma_kernel(const Sm
 // is paid once per tile instead of once per span.
 
 constexpr int kActPad = 16;                       // bytes of padding per staged activation row
+// ... and per staged index row, where it pays: when a row is a multiple of 128 bytes the eight rows a
+// warp reads in one instruction start in the same bank (8-way conflict); padded rows start four banks
+// apart but need one bulk copy per row instead of one per tile.  Measured at M = 16: long rows gain
+// (6144 x 2048: 7.70 -> 7.21 us; dim-4 vectors on 2048 x 6144: 8.73 -> 7.91 us), rows of 256-384 bytes
+// lose 1-3 % to the extra copies, so those keep the single copy.
+__host__ __device__ inline uint32_t staged_idx_pad(int64_t row_bytes) {
+  return (row_bytes % 128 == 0 && row_bytes >= 768) ? 16u : 0u;
+}
 
 __device__ __forceinline__ uint32_t sm_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -288,7 +296,7 @@ __host__ __device__ inline StagedLayout staged_layout(int C, int D, int K, int64
   StagedLayout L;
   L.cb_off = 0;
   L.idx_off = (uint32_t)((C * D * 2 + 127) & ~127);
-  L.act_off = L.idx_off + 2 * (uint32_t)((8 * r8 * row_bytes + 127) & ~127);
+  L.act_off = L.idx_off + 2 * (uint32_t)((8 * r8 * (row_bytes + staged_idx_pad(row_bytes)) + 127) & ~127);
   L.red_off = L.act_off + (uint32_t)act_bufs * (uint32_t)((16 * (K + kActPad) + 127) & ~127);
   L.sa_off = L.red_off + (uint32_t)(warps * r8 * 4 * 32 * 4);
   L.bar_off = L.sa_off + 512;             // 16 token scales + 48 row scales + 48 row biases
@@ -359,12 +367,24 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
   // from HBM once.  Index tiles are double buffered (the next tile's copy flies during this
   // tile's compute); the 16-token activation tile is copied once when there is a single
   // chunk and once per (row tile, chunk) otherwise.
+  // Called by threads 0 .. 8*R8-1.  Unpadded rows: thread 0 copies the tile's rows (one contiguous block
+  // of the stream) at once.  Padded rows: every thread copies one row into its slot.  Either way thread 0
+  // posts the expected byte count (its arrival is the one the barrier waits for).
+  const uint32_t idx_pad = staged_idx_pad(p.row_bytes);
+  const uint32_t idx_pitch = (uint32_t)p.row_bytes + idx_pad;
   auto issue_idx = [&](int rt, int buf) {
     const int n_base = rt * 8 * R8;
-    const uint32_t bytes = (uint32_t)(min(8 * R8, p.N - n_base) * p.row_bytes);
-    mbar_expect_tx(bar_idx0 + 8 * buf, bytes);
-    bulk_copy_g2s(smem + L.idx_off + buf * idx_buf_bytes, p.packed + (int64_t)n_base * p.row_bytes, bytes,
-                  bar_idx0 + 8 * buf);
+    const int rows = min(8 * R8, p.N - n_base);
+    const int r = threadIdx.x;
+    uint8_t* dst = smem + L.idx_off + buf * idx_buf_bytes;
+    if (r == 0) mbar_expect_tx(bar_idx0 + 8 * buf, (uint32_t)(rows * p.row_bytes));
+    if (idx_pad == 0) {
+      if (r == 0)
+        bulk_copy_g2s(dst, p.packed + (int64_t)n_base * p.row_bytes, (uint32_t)(rows * p.row_bytes), bar_idx0 + 8 * buf);
+    } else if (r < rows) {
+      bulk_copy_g2s(dst + r * idx_pitch, p.packed + (int64_t)(n_base + r) * p.row_bytes, (uint32_t)p.row_bytes,
+                    bar_idx0 + 8 * buf);
+    }
   };
   // Called by threads 0..15: thread 0 posts the expected byte count (its arrival is the one
   // the barrier waits for), every thread copies one token row.
@@ -392,8 +412,8 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
     const uint32_t cb_bytes = (uint32_t)(p.C * D * 2);
     mbar_expect_tx(bar_cb, cb_bytes);
     bulk_copy_g2s(smem + L.cb_off, p.cb_hilo, cb_bytes, bar_cb);    // layer constants: may overlap
-    if (first_rt < p.row_blocks) issue_idx(first_rt, 0);            // the previous kernel of the stream
-  }
+  }                                                                  // the previous kernel of the stream
+  if (threadIdx.x < 8 * R8 && first_rt < p.row_blocks) issue_idx(first_rt, 0);
   // the next kernel of the stream (a quantizer or another GEMM launched with programmatic
   // serialization) may be scheduled from here on; it waits for this grid before it touches memory
   SACQ_ST(1);
@@ -429,7 +449,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
       next_sc = bf16_bits_to_float(__ldg(p.scales + (int64_t)n * p.num_groups));
       next_b = p.bias ? bf16_bits_to_float(__ldg(p.bias + n)) : 0.f;
     }
-    if (threadIdx.x == 0 && rt + rt_stride < p.row_blocks) {
+    if (threadIdx.x < 8 * R8 && rt + rt_stride < p.row_blocks) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the other buffer's readers are done
       issue_idx(rt + rt_stride, buf ^ 1);
     }
@@ -517,7 +537,7 @@ __device__ __forceinline__ void staged_body(const SmallMParams& p, const int cta
 #pragma unroll
         for (int r = 0; r < RG; ++r) {
           const int rr = min((r0 + r) * 8 + g, rows_here - 1);
-          const uint32_t* src = reinterpret_cast<const uint32_t*>(idx_s + (int64_t)rr * p.row_bytes + sp * (4 * BITS) + t * BITS);
+          const uint32_t* src = reinterpret_cast<const uint32_t*>(idx_s + rr * idx_pitch + sp * (4 * BITS) + t * BITS);
 #pragma unroll
           for (int j = 0; j < WPG; ++j) wcur[r][j] = src[j];
         }
