@@ -22,11 +22,15 @@ constexpr int kMaxChunksPerThread = 4;  // 16-byte chunks a thread keeps in regi
 template <bool I8>
 __device__ __forceinline__ uint32_t encode2(float z0, float z1, float s) {
   if constexpr (I8) {
-    const int a = __float2int_rn(fminf(fmaxf(__fdiv_rn(z0, s), -127.f), 127.f));
-    const int b = __float2int_rn(fminf(fmaxf(__fdiv_rn(z1, s), -127.f), 127.f));
-    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8);
+    // round-half-even of the clamped quotient through the add of 1.5 * 2^23 (exact for |q| <= 127):
+    // keeps the float -> int conversion off the special-function pipe the division already loads
+    const float qa = fminf(fmaxf(__fdiv_rn(z0, s), -127.f), 127.f);
+    const float qb = fminf(fmaxf(__fdiv_rn(z1, s), -127.f), 127.f);
+    const uint32_t a = (uint32_t)(__float_as_int(__fadd_rn(qa, 12582912.0f)) - 0x4B400000) & 0xffu;
+    const uint32_t b = (uint32_t)(__float_as_int(__fadd_rn(qb, 12582912.0f)) - 0x4B400000) & 0xffu;
+    return a | (b << 8);
   } else {
-    return float2_to_e4m3x2(clamp448(__fdiv_rn(z0, s)), clamp448(__fdiv_rn(z1, s)));
+    return float2_to_e4m3x2(sat448(__fdiv_rn(z0, s)), sat448(__fdiv_rn(z1, s)));
   }
 }
 
@@ -354,10 +358,10 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
       uint32_t o[2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const uint32_t lo = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] & 0xffff), s)),
-                                             clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j] >> 16), s)));
-        const uint32_t hi = float2_to_e4m3x2(clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] & 0xffff), s)),
-                                             clamp448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] >> 16), s)));
+        const uint32_t lo = float2_to_e4m3x2(sat448(__fdiv_rn(bf16_bits_to_float(w[2 * j] & 0xffff), s)),
+                                             sat448(__fdiv_rn(bf16_bits_to_float(w[2 * j] >> 16), s)));
+        const uint32_t hi = float2_to_e4m3x2(sat448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] & 0xffff), s)),
+                                             sat448(__fdiv_rn(bf16_bits_to_float(w[2 * j + 1] >> 16), s)));
         o[j] = lo | (hi << 16);
       }
       *(reinterpret_cast<uint2*>(qrow) + ch) = make_uint2(o[0], o[1]);
@@ -366,7 +370,7 @@ act_quant_fp8_kernel(const uint16_t* __restrict__ a, int64_t a_pitch, const uint
     for (int64_t k2 = 2 * (int64_t)threadIdx.x; k2 < K; k2 += 2 * kThreads) {
       const float y0 = bf16_bits_to_float(yrow[k2]);
       const float y1 = k2 + 1 < K ? bf16_bits_to_float(yrow[k2 + 1]) : 0.f;
-      const uint32_t pair = float2_to_e4m3x2(clamp448(__fdiv_rn(y0, s)), clamp448(__fdiv_rn(y1, s)));
+      const uint32_t pair = float2_to_e4m3x2(sat448(__fdiv_rn(y0, s)), sat448(__fdiv_rn(y1, s)));
       if (k2 + 1 < K && (reinterpret_cast<uintptr_t>(qrow + k2) & 1) == 0)
         *reinterpret_cast<uint16_t*>(qrow + k2) = (uint16_t)pair;
       else {
@@ -505,7 +509,7 @@ layernorm_quant_fp8_kernel(const uint16_t* __restrict__ x, int64_t pitch, const 
   if (threadIdx.x == 0) scale_out[m] = s;
   uint8_t* qrow = q + m * K;
   for (int64_t k = threadIdx.x; k < K; k += kThreads)
-    qrow[k] = (uint8_t)(float2_to_e4m3x2(clamp448(__fdiv_rn(xrow[k], s)), 0.f) & 0xff);
+    qrow[k] = (uint8_t)(float2_to_e4m3x2(sat448(__fdiv_rn(xrow[k], s)), 0.f) & 0xff);
 }
 
 }  // namespace

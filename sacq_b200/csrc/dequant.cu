@@ -113,8 +113,8 @@ decode_weight_fp8_kernel(const uint32_t* __restrict__ words, const uint16_t* __r
     const float row = __ldg(sw + n);
     auto enc2 = [&](uint32_t pair_bits) -> uint32_t {           // two codeword elements (one bf16 pair) -> two bytes
       const uint32_t w = reconstruct_bf16x2(pair_bits & 0xffffu, pair_bits >> 16, s, shift);
-      return float2_to_e4m3x2(clamp448(__fdiv_rn(__uint_as_float(w << 16), row)),
-                              clamp448(__fdiv_rn(__uint_as_float(w & 0xffff0000u), row)));
+      return float2_to_e4m3x2(sat448(__fdiv_rn(__uint_as_float(w << 16), row)),
+                              sat448(__fdiv_rn(__uint_as_float(w & 0xffff0000u), row)));
     };
     if (d == 8 && ((reinterpret_cast<uintptr_t>(cb) & 15) == 0) && ((reinterpret_cast<uintptr_t>(wq) & 7) == 0)) {
       // one 16-byte codeword load, one 8-byte store
@@ -127,14 +127,14 @@ decode_weight_fp8_kernel(const uint32_t* __restrict__ words, const uint16_t* __r
       for (int j = 0; j < d; j += 2) {
         const float a = bf16_bits_to_float(reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j), s, shift));
         const float b = bf16_bits_to_float(reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j + 1), s, shift));
-        const uint32_t pr = float2_to_e4m3x2(clamp448(__fdiv_rn(a, row)), clamp448(__fdiv_rn(b, row)));
+        const uint32_t pr = float2_to_e4m3x2(sat448(__fdiv_rn(a, row)), sat448(__fdiv_rn(b, row)));
         wq[i * d + j] = (uint8_t)(pr & 0xff);
         wq[i * d + j + 1] = (uint8_t)(pr >> 8);
       }
     } else {
       for (int j = 0; j < d; ++j) {
         const float a = bf16_bits_to_float(reconstruct_bf16(__ldg(cb + (int64_t)idx * d + j), s, shift));
-        wq[i * d + j] = (uint8_t)(float2_to_e4m3x2(clamp448(__fdiv_rn(a, row)), 0.f) & 0xff);
+        wq[i * d + j] = (uint8_t)(float2_to_e4m3x2(sat448(__fdiv_rn(a, row)), 0.f) & 0xff);
       }
     }
   }
@@ -217,9 +217,9 @@ __global__ void build_tables_kernel(const uint16_t* __restrict__ cb, int64_t C, 
     const float c = bf16_bits_to_float(__ldg(cb + i));
     cb_f16[i] = __float2half_rn(c * mul16);
     const float c8 = c * mul8;
-    const uint32_t hi_b = float2_to_e4m3x2(clamp448(c8), 0.f) & 0xff;
+    const uint32_t hi_b = float2_to_e4m3x2(sat448(c8), 0.f) & 0xff;
     const float hi = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)hi_b, __NV_E4M3)));
-    const uint32_t lo_b = float2_to_e4m3x2(clamp448(c8 - hi), 0.f) & 0xff;
+    const uint32_t lo_b = float2_to_e4m3x2(sat448(c8 - hi), 0.f) & 0xff;
     const int64_t cw = i / d;
     const int j = (int)(i - cw * d);
     cb_hilo[(cw * 2 + 0) * d + j] = (uint8_t)hi_b;
