@@ -474,7 +474,9 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
         int64_t stride = L->num_sms / pl.chunks;
         if (stride < 1) stride = 1;
         const int64_t waves = (row_tiles + stride - 1) / stride;
-        const double cost = 3.0 + (double)waves * (0.2 + 0.6 * r8);
+        // measured (us): 2.5 of launch and codebook copy, then per tile round about 1.0 of fixed cost (index
+        // wait, barriers, cross-warp reduction, epilogue) plus 0.7 per 8-row sub-block and 2048 of K
+        const double cost = 2.5 + (double)waves * (1.0 + 0.7 * r8 * (double)d.in_features / 2048.0);
         if (best_cost < 0 || cost < best_cost - 1e-9 || !best_staged) { best_cost = cost; best = r8; best_staged = true; }
       } else if (!best_staged && r8 <= 4) {
         const int64_t tiles = row_tiles * pl.chunks;
