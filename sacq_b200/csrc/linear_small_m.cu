@@ -383,7 +383,7 @@ bool plan_unpacked(const sacq_layer* L, Plan& pl) {
     const int64_t row_tiles = (sub + r8 - 1) / r8;
     const int64_t waves = (row_tiles + stride - 1) / stride;
     // measured (us, dim-4 vectors with 64-wide groups on 2048 x 6144: 13.9 with three 16-row rounds, 11.95
-    // with one 48-row tile): 2.5 of launch and codebook copy, then per tile round 1.0 of fixed cost plus
+    // with one 48-row tile): 2.5 of launch and codebook copy, then per pass over the tiles 1.0 of fixed cost plus
     // 1.4 per 8-row sub-block and 2048 of K (dim-8 vectors gather half as often)
     const double cost = 2.5 + (double)waves * (1.0 + (d.vector_dim == 4 ? 1.4 : 0.8) * r8 * (double)d.in_features / 2048.0);
     if (best_cost < 0 || cost < best_cost - 1e-9) { best_cost = cost; best = r8; }
@@ -477,7 +477,7 @@ Plan make_plan(const sacq_layer* L, int64_t M, int halves_req = 0) {
         int64_t stride = L->num_sms / pl.chunks;
         if (stride < 1) stride = 1;
         const int64_t waves = (row_tiles + stride - 1) / stride;
-        // measured (us): 2.5 of launch and codebook copy, then per tile round about 1.0 of fixed cost (index
+        // measured (us): 2.5 of launch and codebook copy, then per pass over the tiles about 1.0 of fixed cost (index
         // wait, barriers, cross-warp reduction, epilogue) plus 0.7 per 8-row sub-block and 2048 of K
         const double cost = 2.5 + (double)waves * (1.0 + 0.7 * r8 * (double)d.in_features / 2048.0);
         if (best_cost < 0 || cost < best_cost - 1e-9 || !best_staged) { best_cost = cost; best = r8; best_staged = true; }
