@@ -318,12 +318,15 @@ def test_linear_decode_shapes(K, N):
         assert torch.equal(mod(wide[:, :K]), outs["auto"][0])
 
 
-@pytest.mark.parametrize("N,K,d,C,G", [(5992, 2048, 8, 4096, None), (6144, 1536, 8, 4096, None), (5000, 2048, 4, 512, 64),
-                                       (6144, 2048, 4, 4096, None)])
-def test_linear_small_m_48_row_tiles(N, K, d, C, G):
+@pytest.mark.parametrize("N,K,d,C,G,same_as", [
+    (5992, 2048, 8, 4096, None, "small_mma"), (6144, 1536, 8, 4096, None, "small_mma"),
+    (5000, 2048, 4, 512, 64, "small_mma_unpacked"), (6144, 2048, 4, 4096, None, "small_mma"),
+    # grouped scales on the packed-index kernel (a scale per 256 or 512 weights), one with a last tile of 40 rows
+    (6144, 2048, 8, 4096, 256, "small_mma"), (5992, 2048, 8, 256, 512, "small_mma")])
+def test_linear_small_m_48_row_tiles(N, K, d, C, G, same_as):
     """Layers wide enough that the warp-MMA kernels walk them in 48-row tiles (one tile per SM), with a
     last tile of 40 or 8 rows: packed-index and index-unpacking variants against the oracle, and the
-    bytes of the CUDA-core kernel's neighbours where the variants must agree."""
+    automatic choice gives the bytes of the variant it is expected to pick."""
     _need_gpu()
     from sacq_b200 import PrecomputedPackedVectorCodebookLinear
     from sacq_b200.synthetic import make_activations, make_payload
@@ -331,13 +334,13 @@ def test_linear_small_m_48_row_tiles(N, K, d, C, G):
     bias = (torch.randn(N, generator=torch.Generator().manual_seed(11)) * 0.05).to(torch.bfloat16)
     mod = PrecomputedPackedVectorCodebookLinear(p, bias, "cuda")
     w_bits = oracle_weight(p)
+    kernels = ("auto", "small_simt", "small_mma") + (("small_mma_unpacked",) if G is None or G == 64 else ())
     for M in (1, 3, 16):
         q_bits, s = O.quantize_rows_e4m3(bf16_bits(make_activations(M, K, seed=M + 7)))
-        outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias),
-                             kernels=("auto", "small_simt", "small_mma", "small_mma_unpacked"))
-        assert "small_mma_unpacked" in outs and ("small_mma" in outs or G is not None)
+        outs = _check_linear(mod, q_bits, s, w_bits, bf16_bits(bias), kernels=kernels)
+        assert same_as in outs
         assert mod.kernel_for(M) == "small"
-        assert torch.equal(outs["auto"][0], outs["small_mma_unpacked" if G is not None else "small_mma"][0])
+        assert torch.equal(outs["auto"][0], outs[same_as][0])
 
 
 @pytest.mark.parametrize("d,C", [(8, 256), (8, 4096), (8, 65536), (4, 4096)])
